@@ -1,0 +1,223 @@
+/*
+ * rmn_b200 — C ABI of the B200 (sm_100a) sparse-convolution hot path:
+ * coordinate hashing, kernel-map generation and gather-GEMM-scatter
+ * convolution (forward / backward, plain, strided-down and transposed).
+ *
+ * This is the boundary a host binding (C++/LibTorch, Python ctypes, ...) links
+ * against. The reference project has no C ABI; every entry point below names
+ * the reference C++ interface it stands in for (paths relative to the
+ * reference project root).
+ *
+ * Conventions
+ *  - Every function returns an int status (RMN_OK == 0). No exceptions cross
+ *    the boundary.
+ *  - All `d_*` pointers are DEVICE pointers on the current CUDA device; all
+ *    buffers are allocated by the caller. `*_bytes` queries say how large.
+ *    The library never allocates device memory.
+ *  - `stream` is a cudaStream_t passed as void*. Calls only enqueue work;
+ *    they do not synchronise unless the comment says so.
+ *  - Coordinates are int32 rows [N, W], W = 1 + D, batch index first,
+ *    contiguous (reference: engine/grid/space_impl.hpp:268-276).
+ *  - Row counts are < 2^31.
+ *  - There is no CPU fallback: without a CUDA device every compute entry
+ *    point returns RMN_ERR_CUDA.
+ */
+#ifndef RMN_B200_H
+#define RMN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+#define RMN_OK 0
+#define RMN_ERR_BAD_ARG 1      /* null pointer, bad size, unsupported W/K/channels */
+#define RMN_ERR_ALLOC 2        /* a caller-provided buffer is too small */
+#define RMN_ERR_PROBE_LIMIT 3  /* a hash probe sequence hit its bound (table full) */
+#define RMN_ERR_TIMEOUT 4      /* a bounded device-side wait ran out */
+#define RMN_ERR_CUDA 5         /* a CUDA runtime call failed */
+#define RMN_ERR_RANGE 6        /* coordinate bounding box does not pack into 63 bits */
+#define RMN_ERR_UNSUPPORTED 7  /* shape / dtype combination has no kernel */
+
+/* ---- feature element types -------------------------------------------- */
+#define RMN_F32 0
+#define RMN_BF16 1
+
+/* ---- region types (reference: engine/foundation/types.hpp RegionType) -- */
+#define RMN_HYPER_CUBE 0
+#define RMN_HYPER_CROSS 1
+#define RMN_CUSTOM 2
+
+#define RMN_MAX_W 8 /* batch column + up to 7 spatial/temporal axes */
+
+/* Library version (major*10000 + minor*100 + patch) and status text. */
+int rmn_version(void);
+const char *rmn_status_string(int status);
+
+/* =======================================================================
+ * Coordinate hash table
+ * Replaces: CoordinateMapCPU / CoordinateMapGPU storage
+ *   (engine/grid/lattice_cpu.hpp:356-398, engine/grid/lattice_gpu.cuh:519-678)
+ *   and the vendored concurrent_unordered_map
+ *   (vendor/concurrent_unordered_map.cuh:305-391).
+ * An open-addressing table of 16-byte slots {packed key, first row, unique
+ * row} at <= 50 % load, preceded by a 256-byte header.
+ * ===================================================================== */
+
+/* Bytes of device memory a table for `n_rows` input rows needs. */
+size_t rmn_table_bytes(uint32_t n_rows);
+/* Bytes of scratch rmn_table_build needs for `n_rows` rows. */
+size_t rmn_table_build_workspace_bytes(uint32_t n_rows);
+
+/*
+ * Dedup-insert `n_rows` coordinate rows and number the unique rows in
+ * first-occurrence order.
+ * Replaces: CoordinateMapCPU::insert_and_map<true>
+ *   (engine/grid/lattice_cpu.hpp:419-444), CoordinateMapGPU::insert<true>
+ *   (engine/grid/lattice_gpu.cu:160-230) and the uint32->int64 widening of
+ *   engine/grid/space.cu:60-80.
+ *  d_mapping  [n_rows] int64: first n_unique entries = first-occurrence rows
+ *  d_inverse  [n_rows] int64: unique row of every input row
+ *  d_unique_coords [n_rows, W] int32 or NULL: unique rows in map order
+ *    (what CoordinateMapManager::get_coordinates returns,
+ *     engine/grid/space_impl.hpp:947-975)
+ * n_unique and the device-side status are read back with rmn_table_info.
+ */
+int rmn_table_build(const int32_t *d_coords, uint32_t n_rows, int W, void *d_table,
+                    size_t table_bytes, int64_t *d_mapping, int64_t *d_inverse,
+                    int32_t *d_unique_coords, void *d_workspace, size_t workspace_bytes,
+                    void *stream);
+
+/*
+ * Synchronising read-back: info[0] = n_unique, info[1] = device status
+ * (RMN_OK / RMN_ERR_PROBE_LIMIT / RMN_ERR_RANGE), info[2] = slot count,
+ * info[3] = n_rows. Returns info[1] when it is non-zero.
+ */
+int rmn_table_info(const void *d_table, uint32_t info[4], void *stream);
+
+/*
+ * Look rows up: d_rows[i] = unique row of d_query[i] or -1.
+ * Replaces: CoordinateMapCPU::find (engine/grid/lattice_cpu.hpp:449-470),
+ *   remap_inverse_map (engine/grid/lattice_gpu.cu:58-71).
+ */
+int rmn_table_find(const void *d_table, const int32_t *d_query, uint32_t n_query, int W,
+                   int32_t *d_rows, void *stream);
+
+/*
+ * Floor-align the spatial columns of `d_coords` to `out_tensor_stride[D]`
+ * (host array; batch column copied). Integer floor; equal to the reference's
+ * float floor for |c| < 2^24.
+ * Replaces: detail::stride_coordinate (engine/grid/stencil.hpp:35-53),
+ *   stride_copy (engine/grid/lattice_gpu.cu:309-336).
+ * Feeding the result to rmn_table_build gives the strided-down map of
+ * CoordinateMapCPU::stride (engine/grid/lattice_cpu.hpp:475-493); its
+ * d_inverse is the stride map of lattice_cpu.hpp:679-710.
+ */
+int rmn_coords_stride(const int32_t *d_coords, uint32_t n_rows, int W,
+                      const int32_t *out_tensor_stride, int32_t *d_out, void *stream);
+
+/* =======================================================================
+ * Kernel regions and kernel maps
+ * ===================================================================== */
+
+/* Number of offsets of a region. Replaces kernel_region::set_volume
+ * (engine/grid/stencil.hpp:283-303). */
+int rmn_region_volume(int region_type, int D, const int32_t *kernel_size, int n_custom);
+
+/*
+ * HOST helper: offsets[K, D] with neighbour = centre + offsets[k], in the
+ * reference's enumeration order (axis 0 fastest; odd sizes centred, even
+ * sizes 0..k-1; cross = centre then per-axis; custom scaled by stride*dil).
+ * Replaces: kernel_region::coordinate_at (engine/grid/stencil.hpp:223-278).
+ * Returns K, or a negative status.
+ */
+int rmn_region_offsets(int region_type, int D, const int32_t *kernel_size,
+                       const int32_t *dilation, const int32_t *tensor_stride,
+                       const int32_t *custom_offsets, int n_custom, int32_t *offsets);
+
+/* Scratch bytes of rmn_kmap_build / rmn_kmap_pairs for n_query rows, K offsets. */
+size_t rmn_kmap_workspace_bytes(uint32_t n_query, int K);
+
+/*
+ * For every query row q and offset k: d_nbr[k * n_query + q] = unique row a
+ * of the table with coords_a == d_query[q] + d_offsets[k], else -1.
+ * d_offset_ptr [K+1] int64 (device) receives the CSR row pointer of the pair
+ * lists (pairs of offset k occupy [ptr[k], ptr[k+1])).
+ * Replaces: CoordinateMapCPU::kernel_map (engine/grid/lattice_cpu.hpp:606-673),
+ *   CoordinateMapGPU::kernel_map + direct_kernel_map / count_kernel
+ *   (engine/grid/lattice_gpu.cu:1145-1549).
+ * Forward convolution: table = input map, query = output coordinates,
+ * offsets on the input tensor stride -> d_nbr is [K, N_out] of input rows.
+ * Transposed convolution: table = output (fine) map, query = input (coarse)
+ * coordinates, offsets on the output tensor stride
+ * (engine/grid/space_impl.hpp:649-697) -> d_nbr is [K, N_in] of output rows.
+ * d_offsets: DEVICE [K, D] int32.
+ */
+int rmn_kmap_build(const void *d_table, const int32_t *d_query, uint32_t n_query, int W,
+                   const int32_t *d_offsets, int K, int32_t *d_nbr, int64_t *d_offset_ptr,
+                   void *d_workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Materialise the pair lists of the last rmn_kmap_build (same d_nbr,
+ * d_offset_ptr and d_workspace): d_a_idx[p], d_q_idx[p] for p < ptr[K],
+ * pairs of one offset sorted by query row. `capacity` = entries available in
+ * each index array (K * n_query always suffices; ptr[K] is exact).
+ * Replaces: the per-offset in/out vectors of cpu_kernel_map
+ *   (engine/grid/maps.hpp:19-79) and gpu_kernel_map::decompose
+ *   (engine/grid/lattice_gpu.cuh:440-488). Passing the arrays in the other
+ *   order is the in/out swap of swap_in_out_map_functor
+ *   (engine/grid/space.cpp:104-107).
+ */
+int rmn_kmap_pairs(const int32_t *d_nbr, uint32_t n_query, int K, const int64_t *d_offset_ptr,
+                   const void *d_workspace, int32_t *d_a_idx, int32_t *d_q_idx,
+                   uint64_t capacity, void *stream);
+
+/*
+ * Invert a neighbour table: d_nbr_t[k * n_a + a] = q where
+ * d_nbr[k * n_query + q] == a, else -1. Used for the input-gradient pass and
+ * for running a transposed convolution output-stationary.
+ */
+int rmn_kmap_transpose(const int32_t *d_nbr, uint32_t n_query, int K, uint32_t n_a,
+                       int32_t *d_nbr_t, void *stream);
+
+/* =======================================================================
+ * Convolution over a neighbour table
+ * Replaces: evaluate_sparse_convolution (engine/nn/conv.cpp:9-66), its torch
+ *   autograd (index_select / matmul / index_add_ chain) and the scalar
+ *   kernels of engine/ops/convolution_cpu.hpp:27-88.
+ * Weights are [K, c_in, c_out] row-major, of the feature dtype
+ * (engine/nn/conv.cpp:83-84). Accumulation is fp32.
+ * ===================================================================== */
+
+/* out[j, :] = sum_k feats[nbr[k, j], :] @ weights[k]      (rows with -1 skipped)
+ * d_nbr: [K, n_dst]; d_feats: [n_src, c_in]; d_out: [n_dst, c_out] (overwritten). */
+int rmn_conv_forward(const void *d_feats, uint32_t n_src, int c_in, const void *d_weights, int K,
+                     int c_out, const int32_t *d_nbr, uint32_t n_dst, void *d_out, int dtype,
+                     void *stream);
+
+/* grad_feats[i, :] = sum_k grad_out[nbr_t[k, i], :] @ weights[k]^T
+ * d_nbr_t: [K, n_src] of destination rows (rmn_kmap_transpose of the forward table). */
+int rmn_conv_backward_input(const void *d_grad_out, uint32_t n_dst, int c_out,
+                            const void *d_weights, int K, int c_in, const int32_t *d_nbr_t,
+                            uint32_t n_src, void *d_grad_feats, int dtype, void *stream);
+
+/* Scratch bytes of rmn_conv_backward_weight. */
+size_t rmn_conv_backward_weight_workspace_bytes(uint32_t n_dst, int K, int c_in, int c_out,
+                                                int dtype);
+
+/* grad_weights[k] = sum_j feats[nbr[k, j], :]^T @ grad_out[j, :]   -> fp32 [K, c_in, c_out]
+ * (fp32 for either feature dtype, so that gradients can be all-reduced
+ * across GPUs without a cast). Deterministic: partial sums are reduced in a
+ * fixed order through the workspace. */
+int rmn_conv_backward_weight(const void *d_feats, uint32_t n_src, int c_in,
+                             const void *d_grad_out, uint32_t n_dst, int c_out,
+                             const int32_t *d_nbr, int K, float *d_grad_weights, int dtype,
+                             void *d_workspace, size_t workspace_bytes, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RMN_B200_H */

@@ -1,0 +1,72 @@
+"""Generate the golden fixtures in this directory from the reference itself.
+
+Runs the unmodified reference CPU path (``oracle/_ref/ref_driver``, built by
+``make -C oracle ref`` from the reference checkout) on small seeded inputs and
+stores inputs + reference outputs as ``<case>.npz``. The parity tests load the
+fixtures only; they never need the reference at run time.
+
+    python tests/golden/make_golden.py
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from oracle import refrun  # noqa: E402
+
+# name: (seed, D, n_rows, batches, lo, hi, c_in, c_out, kernel, stride, dilation, chain c2)
+CASES = {
+    "d3_k3_s1": (11, 3, 400, 2, -6, 6, 5, 7, 3, 1, 1, None),
+    "d3_k2_s2_chain": (12, 3, 500, 2, -7, 7, 4, 6, 2, 2, 1, 3),
+    "d3_k3_s2_chain": (13, 3, 500, 3, -7, 8, 3, 5, 3, 2, 1, 4),
+    "d4_k3_s1": (14, 4, 300, 2, -3, 3, 3, 4, 3, 1, 1, None),
+    "d2_k3_s1_dil2": (15, 2, 300, 2, -10, 10, 2, 3, 3, 1, 2, None),
+    "d3_k1_s1": (16, 3, 200, 1, -4, 4, 6, 2, 1, 1, 1, None),
+    "d3_k5_s1": (17, 3, 350, 1, 0, 7, 2, 2, 5, 1, 1, None),
+}
+
+
+def make_inputs(seed, D, n, batches, lo, hi, c_in, c_out, kernel, stride, dilation, c2):
+    rng = np.random.default_rng(seed)
+    spatial = rng.integers(lo, hi + 1, size=(n, D), dtype=np.int32)
+    batch = rng.integers(0, batches, size=(n, 1), dtype=np.int32)
+    coords = np.concatenate([batch, spatial], axis=1)
+    # force some exact duplicate rows (dedup path)
+    dup = rng.integers(0, n, size=n // 10)
+    coords[rng.integers(0, n, size=n // 10)] = coords[dup]
+    feats = rng.standard_normal((n, c_in)).astype(np.float32)
+    K = kernel ** D
+    bound = 1.0 / np.sqrt(c_in * K)
+    weights = rng.uniform(-bound, bound, size=(K, c_in, c_out)).astype(np.float32)
+    weights2 = None
+    if c2 is not None:
+        bound2 = 1.0 / np.sqrt(c2 * K)
+        weights2 = rng.uniform(-bound2, bound2, size=(K, c_out, c2)).astype(np.float32)
+    return coords, feats, weights, weights2
+
+
+def main() -> None:
+    for name, spec in CASES.items():
+        coords, feats, weights, weights2 = make_inputs(*spec)
+        _, D, _, _, _, _, _, _, kernel, stride, dilation, _ = spec
+        ref = refrun.run(coords, feats, weights, kernel, stride, dilation, weights2=weights2, threads=1)
+        ref.pop("times_ms", None)
+        ref.pop("info", None)
+        arrays = {"in_coords_raw": coords, "in_feats_raw": feats, "weights": weights,
+                  "spec": np.array([D, kernel, stride, dilation], np.int32)}
+        if weights2 is not None:
+            arrays["weights2"] = weights2
+        for k, v in ref.items():
+            arrays["ref_" + k] = v
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **arrays)
+        print(name, {k: v.shape for k, v in ref.items()}, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()
