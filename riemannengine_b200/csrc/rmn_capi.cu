@@ -1,0 +1,96 @@
+// C-ABI entry points of the convolution passes: argument checks and dispatch
+// between the tensor-core (tcgen05, bf16) and SIMT (fp32 / odd shapes) kernels.
+#include "rmn_common.cuh"
+
+namespace rmn {
+int simt_conv_forward(const void* feats, int c_in, const void* w, int K, int c_out,
+                      const int32_t* nbr, uint32_t n_dst, void* out, int dtype, cudaStream_t stream);
+int simt_conv_backward_input(const void* grad_out, int c_out, const void* w, int K, int c_in,
+                             const int32_t* nbr_t, uint32_t n_src, void* grad_feats, int dtype,
+                             cudaStream_t stream);
+size_t simt_wgrad_workspace_bytes(uint32_t n_dst, int K, int c_in, int c_out);
+int simt_conv_backward_weight(const void* feats, int c_in, const void* grad_out, uint32_t n_dst,
+                              int c_out, const int32_t* nbr, int K, float* dw, int dtype,
+                              void* workspace, cudaStream_t stream);
+}  // namespace rmn
+
+using namespace rmn;
+
+extern "C" int rmn_version(void) { return 100; }
+
+extern "C" const char* rmn_status_string(int status) {
+  switch (status) {
+    case RMN_OK: return "ok";
+    case RMN_ERR_BAD_ARG: return "bad argument";
+    case RMN_ERR_ALLOC: return "caller-provided buffer too small";
+    case RMN_ERR_PROBE_LIMIT: return "hash probe limit reached (table full)";
+    case RMN_ERR_TIMEOUT: return "bounded device wait ran out";
+    case RMN_ERR_CUDA: return "CUDA runtime error";
+    case RMN_ERR_RANGE: return "coordinate bounding box does not pack into 63 bits";
+    case RMN_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+    default: return "unknown status";
+  }
+}
+
+static bool conv_args_ok(const void* a, const void* w, const int32_t* nbr, const void* out, int K,
+                         int c_in, int c_out, int dtype) {
+  return a && w && nbr && out && K >= 1 && K <= 65535 && c_in >= 1 && c_out >= 1 &&
+         c_in <= 65536 && c_out <= 65536 && (dtype == RMN_F32 || dtype == RMN_BF16);
+}
+
+extern "C" int rmn_conv_forward(const void* d_feats, uint32_t n_src, int c_in,
+                                const void* d_weights, int K, int c_out, const int32_t* d_nbr,
+                                uint32_t n_dst, void* d_out, int dtype, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (n_dst == 0) return RMN_OK;
+  if (n_src == 0) {
+    if (!d_out || (dtype != RMN_F32 && dtype != RMN_BF16)) return RMN_ERR_BAD_ARG;
+    RMN_CUDA_TRY(cudaMemsetAsync(d_out, 0, (size_t)n_dst * c_out * (dtype == RMN_F32 ? 4 : 2), stream));
+    return RMN_OK;
+  }
+  if (!conv_args_ok(d_feats, d_weights, d_nbr, d_out, K, c_in, c_out, dtype)) return RMN_ERR_BAD_ARG;
+  return simt_conv_forward(d_feats, c_in, d_weights, K, c_out, d_nbr, n_dst, d_out, dtype, stream);
+}
+
+extern "C" int rmn_conv_backward_input(const void* d_grad_out, uint32_t n_dst, int c_out,
+                                       const void* d_weights, int K, int c_in,
+                                       const int32_t* d_nbr_t, uint32_t n_src, void* d_grad_feats,
+                                       int dtype, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (n_src == 0) return RMN_OK;
+  if (n_dst == 0) {
+    if (!d_grad_feats || (dtype != RMN_F32 && dtype != RMN_BF16)) return RMN_ERR_BAD_ARG;
+    RMN_CUDA_TRY(cudaMemsetAsync(d_grad_feats, 0, (size_t)n_src * c_in * (dtype == RMN_F32 ? 4 : 2), stream));
+    return RMN_OK;
+  }
+  if (!conv_args_ok(d_grad_out, d_weights, d_nbr_t, d_grad_feats, K, c_in, c_out, dtype))
+    return RMN_ERR_BAD_ARG;
+  return simt_conv_backward_input(d_grad_out, c_out, d_weights, K, c_in, d_nbr_t, n_src,
+                                  d_grad_feats, dtype, stream);
+}
+
+extern "C" size_t rmn_conv_backward_weight_workspace_bytes(uint32_t n_dst, int K, int c_in,
+                                                           int c_out, int dtype) {
+  (void)dtype;
+  if (K < 1 || c_in < 1 || c_out < 1) return 0;
+  return simt_wgrad_workspace_bytes(n_dst, K, c_in, c_out);
+}
+
+extern "C" int rmn_conv_backward_weight(const void* d_feats, uint32_t n_src, int c_in,
+                                        const void* d_grad_out, uint32_t n_dst, int c_out,
+                                        const int32_t* d_nbr, int K, float* d_grad_weights,
+                                        int dtype, void* d_workspace, size_t workspace_bytes,
+                                        void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!d_grad_weights || K < 1 || c_in < 1 || c_out < 1) return RMN_ERR_BAD_ARG;
+  if (n_dst == 0 || n_src == 0) {
+    RMN_CUDA_TRY(cudaMemsetAsync(d_grad_weights, 0, (size_t)K * c_in * c_out * sizeof(float), stream));
+    return RMN_OK;
+  }
+  if (!conv_args_ok(d_feats, d_grad_out, d_nbr, d_grad_weights, K, c_in, c_out, dtype) || !d_workspace)
+    return RMN_ERR_BAD_ARG;
+  if (workspace_bytes < rmn_conv_backward_weight_workspace_bytes(n_dst, K, c_in, c_out, dtype))
+    return RMN_ERR_ALLOC;
+  return simt_conv_backward_weight(d_feats, c_in, d_grad_out, n_dst, c_out, d_nbr, K,
+                                   d_grad_weights, dtype, d_workspace, stream);
+}

@@ -1,0 +1,152 @@
+// Shared device/host definitions of the rmn_b200 library (sm_100a).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "rmn_b200.h"
+
+namespace rmn {
+
+// ---------------------------------------------------------------------------
+// Hash-table layout in device memory:
+//   [ TableHeader (256 B) | Slot[capacity] ]
+// A coordinate row is packed into one 63-bit key: column c contributes
+// (value - mn[c]) << shift[c] using bits[c] bits, where mn/mx are the column
+// extrema of the rows the table was built from. A query row outside the
+// bounding box cannot be in the table and is rejected before probing.
+// ---------------------------------------------------------------------------
+struct __align__(16) Slot {
+  unsigned long long key;  // kEmptyKey when free
+  uint32_t first_row;      // smallest input row holding this key
+  uint32_t uid;            // row in the unique (first-occurrence) numbering
+};
+static_assert(sizeof(Slot) == 16, "slot must be 16 bytes");
+
+constexpr unsigned long long kEmptyKey = ~0ull;
+constexpr uint32_t kTableMagic = 0x524d4e54u;  // "RMNT"
+
+struct __align__(16) TableHeader {
+  uint32_t magic;
+  uint32_t W;
+  uint32_t n_rows;
+  uint32_t n_unique;
+  uint32_t status;
+  uint32_t cap_log2;
+  uint32_t total_bits;
+  uint32_t reserved;
+  int32_t mn[RMN_MAX_W];
+  int32_t mx[RMN_MAX_W];
+  uint32_t bits[RMN_MAX_W];
+  uint32_t shift[RMN_MAX_W];
+  uint32_t pad[24];
+};
+static_assert(sizeof(TableHeader) == 256, "header must be 256 bytes");
+
+// Packing parameters held in registers by the kernels.
+template <int W>
+struct Packer {
+  int32_t mn[W];
+  uint32_t span[W];  // mx - mn
+  uint32_t shift[W];
+
+  __device__ __forceinline__ void load(const TableHeader* h) {
+#pragma unroll
+    for (int c = 0; c < W; ++c) {
+      mn[c] = h->mn[c];
+      span[c] = (uint32_t)(h->mx[c] - h->mn[c]);
+      shift[c] = h->shift[c];
+    }
+  }
+  // false when the row lies outside the bounding box of the table's rows
+  __device__ __forceinline__ bool pack(const int32_t (&c)[W], unsigned long long& key) const {
+    unsigned long long k = 0;
+    bool ok = true;
+#pragma unroll
+    for (int i = 0; i < W; ++i) {
+      uint32_t d = (uint32_t)c[i] - (uint32_t)mn[i];
+      ok = ok && (d <= span[i]);
+      k |= (unsigned long long)d << shift[i];
+    }
+    key = k;
+    return ok;
+  }
+};
+
+__device__ __forceinline__ uint32_t hash_key(unsigned long long k, uint32_t mask) {
+  k ^= k >> 33;
+  k *= 0xff51afd7ed558ccdull;
+  k ^= k >> 33;
+  k *= 0xc4ceb9fe1a85ec53ull;
+  k ^= k >> 33;
+  return (uint32_t)k & mask;
+}
+
+__device__ __forceinline__ ulonglong2 load_slot(const Slot* s) {
+  return __ldg(reinterpret_cast<const ulonglong2*>(s));
+}
+
+// Lookup; returns uid or 0xFFFFFFFF. Probing is bounded by the slot count.
+__device__ __forceinline__ uint32_t table_find(const Slot* slots, uint32_t mask,
+                                               unsigned long long key) {
+  uint32_t s = hash_key(key, mask);
+  for (uint32_t probe = 0; probe <= mask; ++probe) {
+    ulonglong2 v = load_slot(slots + s);
+    if (v.x == key) return (uint32_t)(v.y >> 32);
+    if (v.x == kEmptyKey) return 0xFFFFFFFFu;
+    s = (s + 1) & mask;
+  }
+  return 0xFFFFFFFFu;
+}
+
+template <int W>
+__device__ __forceinline__ void load_row(const int32_t* __restrict__ coords, uint32_t row,
+                                         int32_t (&c)[W]) {
+  if constexpr (W == 4) {
+    int4 v = __ldg(reinterpret_cast<const int4*>(coords) + row);
+    c[0] = v.x; c[1] = v.y; c[2] = v.z; c[3] = v.w;
+  } else if constexpr (W == 2) {
+    int2 v = __ldg(reinterpret_cast<const int2*>(coords) + row);
+    c[0] = v.x; c[1] = v.y;
+  } else {
+#pragma unroll
+    for (int i = 0; i < W; ++i) c[i] = __ldg(coords + (size_t)row * W + i);
+  }
+}
+
+inline uint32_t table_cap_log2(uint32_t n_rows) {
+  uint32_t lg = 4;
+  while ((1ull << lg) < 2ull * n_rows + 2ull) ++lg;
+  return lg;
+}
+
+// load_row uses 16-byte (W == 4) / 8-byte (W == 2) vector loads
+inline bool coords_aligned(const void* p, int W) {
+  const uintptr_t a = (uintptr_t)p;
+  return W == 4 ? (a & 15) == 0 : W == 2 ? (a & 7) == 0 : (a & 3) == 0;
+}
+
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? RMN_OK : RMN_ERR_CUDA; }
+
+#define RMN_CUDA_TRY(expr)                        \
+  do {                                            \
+    cudaError_t _e = (expr);                      \
+    if (_e != cudaSuccess) return RMN_ERR_CUDA;   \
+  } while (0)
+
+#define RMN_LAUNCH_CHECK() RMN_CUDA_TRY(cudaGetLastError())
+
+// Dispatch a functor templated on the coordinate width.
+#define RMN_DISPATCH_W(W_, ...)                   \
+  switch (W_) {                                   \
+    case 2: { constexpr int kW = 2; __VA_ARGS__; } break; \
+    case 3: { constexpr int kW = 3; __VA_ARGS__; } break; \
+    case 4: { constexpr int kW = 4; __VA_ARGS__; } break; \
+    case 5: { constexpr int kW = 5; __VA_ARGS__; } break; \
+    case 6: { constexpr int kW = 6; __VA_ARGS__; } break; \
+    case 7: { constexpr int kW = 7; __VA_ARGS__; } break; \
+    case 8: { constexpr int kW = 8; __VA_ARGS__; } break; \
+    default: return RMN_ERR_BAD_ARG;              \
+  }
+
+}  // namespace rmn

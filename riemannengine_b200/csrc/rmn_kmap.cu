@@ -1,0 +1,289 @@
+// Kernel-map generation: for every query row and kernel offset, probe the
+// coordinate table; results land in an offset-major neighbour table
+// nbr[K][n_query] (what the convolution kernels consume) and, on request, in
+// CSR-over-offsets pair lists (the reference's per-offset in/out vectors,
+// engine/grid/maps.hpp:19-79).
+//
+// Pass 1 (k_kmap_probe): one thread per query row keeps the row in registers
+// (one vectorised 16-byte load for W = 4), loops over the K offsets held in
+// shared memory, probes, writes nbr[k][q] (coalesced: consecutive lanes are
+// consecutive rows) and counts hits per offset with warp ballots.
+// Pass 2 (k_kmap_scan): exclusive scan of the per-(offset, block) hit counts
+// and of the per-offset totals -> offset_ptr[K+1].
+// Pass 3 (k_kmap_pairs, optional): ballot compaction of nbr into (a, q) pair
+// lists at deterministic positions (pairs of one offset sorted by query row),
+// with no sort and no atomics. The reference instead sorts all triplets by
+// offset (engine/grid/lattice_gpu.cuh:440-488).
+#include "rmn_common.cuh"
+
+namespace rmn {
+
+constexpr int kKmapBlock = 256;
+
+template <int W>
+__global__ void __launch_bounds__(kKmapBlock) k_kmap_probe(
+    const TableHeader* __restrict__ h, const Slot* __restrict__ slots,
+    const int32_t* __restrict__ query, uint32_t n_query, const int32_t* __restrict__ offsets,
+    int K, int32_t* __restrict__ nbr, uint32_t* __restrict__ block_counts, uint32_t n_blocks) {
+  extern __shared__ int32_t smem[];
+  int32_t* s_off = smem;                                       // [K][W-1]
+  uint32_t* s_cnt = reinterpret_cast<uint32_t*>(smem + K * (W - 1));  // [K]
+  constexpr int D = W - 1;
+  for (int i = threadIdx.x; i < K * D; i += kKmapBlock) s_off[i] = offsets[i];
+  for (int i = threadIdx.x; i < K; i += kKmapBlock) s_cnt[i] = 0;
+  __syncthreads();
+
+  Packer<W> pk;
+  pk.load(h);
+  const uint32_t mask = (1u << h->cap_log2) - 1u;
+  const uint32_t q = blockIdx.x * kKmapBlock + threadIdx.x;
+  const bool active = q < n_query;
+  int32_t c[W];
+  if (active) {
+    load_row<W>(query, q, c);
+  } else {
+#pragma unroll
+    for (int i = 0; i < W; ++i) c[i] = 0;
+  }
+  const int lane = threadIdx.x & 31;
+  for (int k = 0; k < K; ++k) {
+    int32_t nb[W];
+    nb[0] = c[0];
+#pragma unroll
+    for (int a = 0; a < D; ++a) nb[a + 1] = c[a + 1] + s_off[k * D + a];
+    unsigned long long key;
+    uint32_t uid = 0xFFFFFFFFu;
+    if (active && pk.pack(nb, key)) uid = table_find(slots, mask, key);
+    if (active) nbr[(size_t)k * n_query + q] = (int32_t)uid;
+    const uint32_t hits = __ballot_sync(0xFFFFFFFFu, uid != 0xFFFFFFFFu);
+    if (lane == 0 && hits) atomicAdd(&s_cnt[k], (uint32_t)__popc(hits));
+  }
+  __syncthreads();
+  for (int k = threadIdx.x; k < K; k += kKmapBlock)
+    block_counts[(size_t)k * n_blocks + blockIdx.x] = s_cnt[k];
+}
+
+// grid = K blocks of 1024 threads: exclusive scan of block_counts[k][0..n_blocks) in place,
+// totals[k] = number of pairs of offset k.
+__global__ void __launch_bounds__(1024) k_kmap_scan_blocks(uint32_t* __restrict__ block_counts,
+                                                           uint32_t n_blocks,
+                                                           uint32_t* __restrict__ totals) {
+  __shared__ uint32_t warp_sums[32];
+  uint32_t* counts = block_counts + (size_t)blockIdx.x * n_blocks;
+  const uint32_t per = (n_blocks + 1023u) / 1024u;
+  const uint32_t begin = min(n_blocks, threadIdx.x * per), end = min(n_blocks, begin + per);
+  uint32_t sum = 0;
+  for (uint32_t i = begin; i < end; ++i) sum += counts[i];
+  uint32_t incl = sum;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+    if (lane >= d) incl += t;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t w = warp_sums[lane], wi = w;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      uint32_t t = __shfl_up_sync(0xFFFFFFFFu, wi, d);
+      if (lane >= d) wi += t;
+    }
+    warp_sums[lane] = wi - w;
+    if (lane == 31) totals[blockIdx.x] = wi;
+  }
+  __syncthreads();
+  uint32_t run = warp_sums[warp] + incl - sum;
+  for (uint32_t i = begin; i < end; ++i) {
+    uint32_t v = counts[i];
+    counts[i] = run;
+    run += v;
+  }
+}
+
+// one thread: offset_ptr[0..K] = exclusive scan of totals (K is small)
+__global__ void k_kmap_offset_ptr(const uint32_t* __restrict__ totals, int K,
+                                  int64_t* __restrict__ offset_ptr) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int64_t run = 0;
+  for (int k = 0; k < K; ++k) {
+    offset_ptr[k] = run;
+    run += totals[k];
+  }
+  offset_ptr[K] = run;
+}
+
+// Block b covers query rows [b*256, b*256+256). Warp w handles offsets
+// k = w, w+8, ...; for each it walks the 8 row groups of the block keeping a
+// running prefix, so no block-level synchronisation is needed.
+__global__ void __launch_bounds__(kKmapBlock) k_kmap_pairs(
+    const int32_t* __restrict__ nbr, uint32_t n_query, int K,
+    const int64_t* __restrict__ offset_ptr, const uint32_t* __restrict__ block_prefix,
+    uint32_t n_blocks, int32_t* __restrict__ a_idx, int32_t* __restrict__ q_idx,
+    unsigned long long capacity, uint32_t* __restrict__ overflow) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t row0 = blockIdx.x * kKmapBlock;
+  for (int k = warp; k < K; k += kKmapBlock / 32) {
+    unsigned long long pos =
+        (unsigned long long)offset_ptr[k] + block_prefix[(size_t)k * n_blocks + blockIdx.x];
+#pragma unroll
+    for (int g = 0; g < kKmapBlock / 32; ++g) {
+      const uint32_t q = row0 + g * 32 + lane;
+      int32_t a = -1;
+      if (q < n_query) a = __ldg(nbr + (size_t)k * n_query + q);
+      const uint32_t hits = __ballot_sync(0xFFFFFFFFu, a >= 0);
+      if (a >= 0) {
+        const unsigned long long p = pos + __popc(hits & ((1u << lane) - 1u));
+        if (p < capacity) {
+          a_idx[p] = a;
+          q_idx[p] = (int32_t)q;
+        } else {
+          *overflow = 1;
+        }
+      }
+      pos += __popc(hits);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) k_kmap_transpose(const int32_t* __restrict__ nbr,
+                                                        uint32_t n_query, int K, uint32_t n_a,
+                                                        int32_t* __restrict__ nbr_t) {
+  const uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= (uint64_t)K * n_query) return;
+  const int32_t a = __ldg(nbr + i);
+  if (a < 0 || (uint32_t)a >= n_a) return;
+  const uint64_t k = i / n_query;
+  const uint32_t q = (uint32_t)(i - k * n_query);
+  nbr_t[k * n_a + (uint32_t)a] = (int32_t)q;
+}
+
+inline uint32_t kmap_blocks(uint32_t n_query) { return (n_query + kKmapBlock - 1) / kKmapBlock; }
+
+}  // namespace rmn
+
+using namespace rmn;
+
+extern "C" int rmn_region_volume(int region_type, int D, const int32_t* kernel_size, int n_custom) {
+  if (D < 1 || D >= RMN_MAX_W) return -RMN_ERR_BAD_ARG;
+  if (region_type == RMN_CUSTOM) return n_custom;
+  if (!kernel_size) return -RMN_ERR_BAD_ARG;
+  long long v = 1;
+  if (region_type == RMN_HYPER_CUBE) {
+    for (int a = 0; a < D; ++a) v *= kernel_size[a];
+  } else if (region_type == RMN_HYPER_CROSS) {
+    for (int a = 0; a < D; ++a) v += kernel_size[a] - 1;
+  } else {
+    return -RMN_ERR_BAD_ARG;
+  }
+  return v > 0 && v < (1 << 20) ? (int)v : -RMN_ERR_BAD_ARG;
+}
+
+extern "C" int rmn_region_offsets(int region_type, int D, const int32_t* kernel_size,
+                                  const int32_t* dilation, const int32_t* tensor_stride,
+                                  const int32_t* custom_offsets, int n_custom, int32_t* offsets) {
+  const int K = rmn_region_volume(region_type, D, kernel_size, n_custom);
+  if (K < 0) return K;
+  if (!dilation || !tensor_stride || !offsets) return -RMN_ERR_BAD_ARG;
+  if (region_type == RMN_CUSTOM && n_custom > 0 && !custom_offsets) return -RMN_ERR_BAD_ARG;
+  for (int k = 0; k < K; ++k) {
+    int32_t* o = offsets + (size_t)k * D;
+    for (int a = 0; a < D; ++a) o[a] = 0;
+    if (region_type == RMN_HYPER_CUBE) {
+      int idx = k;
+      for (int a = 0; a < D; ++a) {
+        const int ks = kernel_size[a];
+        const int cur = idx % ks;
+        const int step = dilation[a] * tensor_stride[a];
+        o[a] = (ks % 2 == 0) ? cur * step : (cur - ks / 2) * step;
+        idx /= ks;
+      }
+    } else if (region_type == RMN_HYPER_CROSS) {
+      if (k == 0) continue;
+      int ind = k - 1, axis = 0;
+      while (axis < D && ind >= kernel_size[axis] - 1) {
+        ind -= kernel_size[axis] - 1;
+        ++axis;
+      }
+      const int r = (kernel_size[axis] - 1) / 2;
+      const int co = ind < r ? ind + 1 : ind - 2 * r;
+      o[axis] = co * dilation[axis] * tensor_stride[axis];
+    } else {
+      for (int a = 0; a < D; ++a)
+        o[a] = (int32_t)((long long)custom_offsets[(size_t)k * D + a] * tensor_stride[a] *
+                         dilation[a]);
+    }
+  }
+  return K;
+}
+
+extern "C" size_t rmn_kmap_workspace_bytes(uint32_t n_query, int K) {
+  if (K < 1) K = 1;
+  return ((size_t)K * kmap_blocks(n_query) + (size_t)K + 64) * sizeof(uint32_t);
+}
+
+extern "C" int rmn_kmap_build(const void* d_table, const int32_t* d_query, uint32_t n_query, int W,
+                              const int32_t* d_offsets, int K, int32_t* d_nbr,
+                              int64_t* d_offset_ptr, void* d_workspace, size_t workspace_bytes,
+                              void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!d_table || W < 2 || W > RMN_MAX_W || K < 1 || K > 4096 || !d_offsets || !d_offset_ptr ||
+      !d_workspace)
+    return RMN_ERR_BAD_ARG;
+  if (workspace_bytes < rmn_kmap_workspace_bytes(n_query, K)) return RMN_ERR_ALLOC;
+  const uint32_t nb = kmap_blocks(n_query);
+  uint32_t* block_counts = reinterpret_cast<uint32_t*>(d_workspace);
+  uint32_t* totals = block_counts + (size_t)K * nb;
+  if (n_query == 0) {
+    RMN_CUDA_TRY(cudaMemsetAsync(d_offset_ptr, 0, sizeof(int64_t) * (K + 1), stream));
+    return RMN_OK;
+  }
+  if (!d_query || !d_nbr || !coords_aligned(d_query, W)) return RMN_ERR_BAD_ARG;
+  auto* h = reinterpret_cast<const TableHeader*>(d_table);
+  auto* slots =
+      reinterpret_cast<const Slot*>(reinterpret_cast<const char*>(d_table) + sizeof(TableHeader));
+  const size_t smem = (size_t)K * (W - 1) * 4 + (size_t)K * 4;
+  RMN_DISPATCH_W(W, k_kmap_probe<kW><<<nb, kKmapBlock, smem, stream>>>(
+                        h, slots, d_query, n_query, d_offsets, K, d_nbr, block_counts, nb));
+  RMN_LAUNCH_CHECK();
+  k_kmap_scan_blocks<<<K, 1024, 0, stream>>>(block_counts, nb, totals);
+  RMN_LAUNCH_CHECK();
+  k_kmap_offset_ptr<<<1, 32, 0, stream>>>(totals, K, d_offset_ptr);
+  RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}
+
+extern "C" int rmn_kmap_pairs(const int32_t* d_nbr, uint32_t n_query, int K,
+                              const int64_t* d_offset_ptr, const void* d_workspace,
+                              int32_t* d_a_idx, int32_t* d_q_idx, uint64_t capacity,
+                              void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (K < 1 || !d_offset_ptr || !d_workspace) return RMN_ERR_BAD_ARG;
+  if (n_query == 0 || capacity == 0) return RMN_OK;
+  if (!d_nbr || !d_a_idx || !d_q_idx) return RMN_ERR_BAD_ARG;
+  const uint32_t nb = kmap_blocks(n_query);
+  const uint32_t* block_prefix = reinterpret_cast<const uint32_t*>(d_workspace);
+  // the word after the totals flags a capacity overflow (kept for debugging reads)
+  uint32_t* overflow = const_cast<uint32_t*>(block_prefix) + (size_t)K * nb + K;
+  k_kmap_pairs<<<nb, kKmapBlock, 0, stream>>>(d_nbr, n_query, K, d_offset_ptr, block_prefix, nb,
+                                              d_a_idx, d_q_idx, capacity, overflow);
+  RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}
+
+extern "C" int rmn_kmap_transpose(const int32_t* d_nbr, uint32_t n_query, int K, uint32_t n_a,
+                                  int32_t* d_nbr_t, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (K < 1) return RMN_ERR_BAD_ARG;
+  if (n_a == 0) return RMN_OK;
+  if (!d_nbr_t) return RMN_ERR_BAD_ARG;
+  RMN_CUDA_TRY(cudaMemsetAsync(d_nbr_t, 0xFF, (size_t)K * n_a * sizeof(int32_t), stream));
+  if (n_query == 0) return RMN_OK;
+  if (!d_nbr) return RMN_ERR_BAD_ARG;
+  const uint64_t total = (uint64_t)K * n_query;
+  k_kmap_transpose<<<(uint32_t)((total + 255) / 256), 256, 0, stream>>>(d_nbr, n_query, K, n_a,
+                                                                       d_nbr_t);
+  RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}

@@ -1,0 +1,345 @@
+// Coordinate hash table: dedup insert with first-occurrence numbering, lookup,
+// stride alignment. Integer work bound by HBM/L2 bandwidth.
+//
+// Build pipeline (all on the caller's stream, no host synchronisation):
+//   header_init -> range (column min/max) -> plan (bit packing) -> memset slots
+//   -> insert (CAS on the packed key, atomicMin on the first row)
+//   -> count (rows that are the first occurrence, per 256-row block)
+//   -> scan (one block, exclusive scan of the block counts)
+//   -> finalize (unique ids, mapping, unique coordinates)
+//   -> inverse
+// Numbering unique rows by first occurrence reproduces the reference CPU map
+// (engine/grid/lattice_cpu.hpp:419-444) deterministically; the reference GPU
+// map lets a CAS race pick the surviving duplicate
+// (engine/grid/lattice_gpu.cu:30-51).
+#include "rmn_common.cuh"
+
+#include <limits.h>
+
+namespace rmn {
+
+constexpr int kRowsPerBlock = 256;
+
+__global__ void k_header_init(TableHeader* h, uint32_t W, uint32_t n_rows, uint32_t cap_log2) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  h->magic = kTableMagic;
+  h->W = W;
+  h->n_rows = n_rows;
+  h->n_unique = 0;
+  h->status = RMN_OK;
+  h->cap_log2 = cap_log2;
+  h->total_bits = 0;
+  h->reserved = 0;
+  for (int c = 0; c < RMN_MAX_W; ++c) {
+    h->mn[c] = INT_MAX;
+    h->mx[c] = INT_MIN;
+    h->bits[c] = 0;
+    h->shift[c] = 0;
+  }
+}
+
+template <int W>
+__global__ void __launch_bounds__(256) k_range(const int32_t* __restrict__ coords, uint32_t n,
+                                               TableHeader* h) {
+  int32_t mn[W], mx[W];
+#pragma unroll
+  for (int c = 0; c < W; ++c) { mn[c] = INT_MAX; mx[c] = INT_MIN; }
+  for (uint32_t r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
+    int32_t v[W];
+    load_row<W>(coords, r, v);
+#pragma unroll
+    for (int c = 0; c < W; ++c) { mn[c] = min(mn[c], v[c]); mx[c] = max(mx[c], v[c]); }
+  }
+#pragma unroll
+  for (int c = 0; c < W; ++c) {
+    int32_t a = __reduce_min_sync(0xFFFFFFFFu, mn[c]);
+    int32_t b = __reduce_max_sync(0xFFFFFFFFu, mx[c]);
+    if ((threadIdx.x & 31) == 0) {
+      atomicMin(&h->mn[c], a);
+      atomicMax(&h->mx[c], b);
+    }
+  }
+}
+
+__global__ void k_plan(TableHeader* h) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  uint32_t total = 0;
+  for (uint32_t c = 0; c < h->W; ++c) {
+    uint32_t b = 0;
+    if (h->n_rows > 0) {
+      uint32_t span = (uint32_t)h->mx[c] - (uint32_t)h->mn[c];
+      b = span == 0 ? 0 : 32 - __clz(span);
+    } else {
+      h->mn[c] = 0;
+      h->mx[c] = 0;  // empty table: every probe ends on a free slot
+    }
+    h->bits[c] = b;
+    h->shift[c] = total > 63 ? 63 : total;
+    total += b;
+  }
+  h->total_bits = total;
+  if (total > 63) h->status = RMN_ERR_RANGE;
+}
+
+template <int W>
+__global__ void __launch_bounds__(256) k_insert(const int32_t* __restrict__ coords, uint32_t n,
+                                                TableHeader* h, Slot* slots,
+                                                uint32_t* __restrict__ slot_of_row) {
+  if (h->status != RMN_OK) return;
+  const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= n) return;
+  Packer<W> pk;
+  pk.load(h);
+  const uint32_t mask = (1u << h->cap_log2) - 1u;
+  int32_t c[W];
+  load_row<W>(coords, row, c);
+  unsigned long long key;
+  pk.pack(c, key);
+  uint32_t s = hash_key(key, mask);
+  bool placed = false;
+  for (uint32_t probe = 0; probe <= mask; ++probe) {
+    unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(&slots[s].key);
+    if (cur == kEmptyKey) cur = atomicCAS(&slots[s].key, kEmptyKey, key);
+    if (cur == kEmptyKey || cur == key) {
+      atomicMin(&slots[s].first_row, row);
+      slot_of_row[row] = s;
+      placed = true;
+      break;
+    }
+    s = (s + 1) & mask;
+  }
+  if (!placed) atomicExch(&h->status, (uint32_t)RMN_ERR_PROBE_LIMIT);
+}
+
+__global__ void __launch_bounds__(kRowsPerBlock) k_count_first(const Slot* __restrict__ slots,
+                                                              const uint32_t* __restrict__ slot_of_row,
+                                                              uint32_t n, const TableHeader* h,
+                                                              uint32_t* __restrict__ block_counts) {
+  const uint32_t row = blockIdx.x * kRowsPerBlock + threadIdx.x;
+  int flag = 0;
+  if (row < n && h->status == RMN_OK) flag = slots[slot_of_row[row]].first_row == row;
+  int total = __syncthreads_count(flag);
+  if (threadIdx.x == 0) block_counts[blockIdx.x] = (uint32_t)total;
+}
+
+// One block: in-place exclusive scan of counts[n]; the total goes to *total_out.
+__global__ void __launch_bounds__(1024) k_scan_u32(uint32_t* __restrict__ counts, uint32_t n,
+                                                   uint32_t* total_out) {
+  __shared__ uint32_t warp_sums[32];
+  const uint32_t per = (n + 1023u) / 1024u;
+  const uint32_t begin = min(n, threadIdx.x * per), end = min(n, begin + per);
+  uint32_t sum = 0;
+  for (uint32_t i = begin; i < end; ++i) sum += counts[i];
+  // block exclusive scan of `sum`
+  uint32_t incl = sum;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+    if (lane >= d) incl += t;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t w = warp_sums[lane], wi = w;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      uint32_t t = __shfl_up_sync(0xFFFFFFFFu, wi, d);
+      if (lane >= d) wi += t;
+    }
+    warp_sums[lane] = wi - w;  // exclusive
+    if (lane == 31 && total_out) *total_out = wi;
+  }
+  __syncthreads();
+  uint32_t run = warp_sums[warp] + incl - sum;
+  for (uint32_t i = begin; i < end; ++i) {
+    uint32_t v = counts[i];
+    counts[i] = run;
+    run += v;
+  }
+}
+
+template <int W>
+__global__ void __launch_bounds__(kRowsPerBlock) k_finalize(
+    const int32_t* __restrict__ coords, uint32_t n, const TableHeader* h, Slot* slots,
+    const uint32_t* __restrict__ slot_of_row, const uint32_t* __restrict__ block_offsets,
+    int64_t* __restrict__ mapping, int32_t* __restrict__ unique_coords) {
+  __shared__ uint32_t warp_counts[kRowsPerBlock / 32];
+  if (h->status != RMN_OK) return;
+  const uint32_t row = blockIdx.x * kRowsPerBlock + threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t s = 0;
+  int flag = 0;
+  if (row < n) {
+    s = slot_of_row[row];
+    flag = slots[s].first_row == row;
+  }
+  const uint32_t ballot = __ballot_sync(0xFFFFFFFFu, flag);
+  if (lane == 0) warp_counts[warp] = __popc(ballot);
+  __syncthreads();
+  uint32_t base = block_offsets[blockIdx.x];
+  for (int w = 0; w < warp; ++w) base += warp_counts[w];
+  if (flag) {
+    const uint32_t uid = base + __popc(ballot & ((1u << lane) - 1u));
+    slots[s].uid = uid;
+    mapping[uid] = (int64_t)row;
+    if (unique_coords) {
+      int32_t c[W];
+      load_row<W>(coords, row, c);
+#pragma unroll
+      for (int i = 0; i < W; ++i) unique_coords[(size_t)uid * W + i] = c[i];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) k_inverse(const Slot* __restrict__ slots,
+                                                 const uint32_t* __restrict__ slot_of_row,
+                                                 uint32_t n, const TableHeader* h,
+                                                 int64_t* __restrict__ inverse) {
+  const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= n || h->status != RMN_OK) return;
+  inverse[row] = (int64_t)slots[slot_of_row[row]].uid;
+}
+
+template <int W>
+__global__ void __launch_bounds__(256) k_find(const TableHeader* __restrict__ h,
+                                              const Slot* __restrict__ slots,
+                                              const int32_t* __restrict__ query, uint32_t n,
+                                              int32_t* __restrict__ rows) {
+  const uint32_t q = blockIdx.x * blockDim.x + threadIdx.x;
+  if (q >= n) return;
+  Packer<W> pk;
+  pk.load(h);
+  const uint32_t mask = (1u << h->cap_log2) - 1u;
+  int32_t c[W];
+  load_row<W>(query, q, c);
+  unsigned long long key;
+  uint32_t uid = 0xFFFFFFFFu;
+  if (pk.pack(c, key)) uid = table_find(slots, mask, key);
+  rows[q] = (int32_t)uid;
+}
+
+struct StrideArg {
+  int32_t s[RMN_MAX_W];
+};
+
+__global__ void __launch_bounds__(256) k_stride(const int32_t* __restrict__ coords, uint64_t total,
+                                                int W, StrideArg st, int32_t* __restrict__ out) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int col = (int)(i % (uint64_t)W);
+  int32_t c = coords[i];
+  if (col > 0) {
+    const int32_t s = st.s[col - 1];
+    int32_t q = c / s;
+    if ((c % s != 0) && (c < 0)) --q;  // floor for negative coordinates
+    c = q * s;
+  }
+  out[i] = c;
+}
+
+}  // namespace rmn
+
+using namespace rmn;
+
+extern "C" size_t rmn_table_bytes(uint32_t n_rows) {
+  return sizeof(TableHeader) + (sizeof(Slot) << table_cap_log2(n_rows));
+}
+
+extern "C" size_t rmn_table_build_workspace_bytes(uint32_t n_rows) {
+  const size_t nb = (n_rows + kRowsPerBlock - 1) / kRowsPerBlock;
+  return (size_t)n_rows * 4 + (nb + 1) * 4 + 256;
+}
+
+extern "C" int rmn_table_build(const int32_t* d_coords, uint32_t n_rows, int W, void* d_table,
+                               size_t table_bytes, int64_t* d_mapping, int64_t* d_inverse,
+                               int32_t* d_unique_coords, void* d_workspace,
+                               size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!d_table || W < 2 || W > RMN_MAX_W || n_rows >= 0x7FFFFFFFu) return RMN_ERR_BAD_ARG;
+  if (n_rows > 0 && (!d_coords || !d_mapping || !d_inverse || !d_workspace)) return RMN_ERR_BAD_ARG;
+  if (((uintptr_t)d_table & 15) || !coords_aligned(d_coords, W)) return RMN_ERR_BAD_ARG;
+  if (table_bytes < rmn_table_bytes(n_rows) ||
+      (n_rows > 0 && workspace_bytes < rmn_table_build_workspace_bytes(n_rows)))
+    return RMN_ERR_ALLOC;
+  auto* h = reinterpret_cast<TableHeader*>(d_table);
+  auto* slots = reinterpret_cast<Slot*>(reinterpret_cast<char*>(d_table) + sizeof(TableHeader));
+  const uint32_t cap_log2 = table_cap_log2(n_rows);
+  k_header_init<<<1, 32, 0, stream>>>(h, (uint32_t)W, n_rows, cap_log2);
+  RMN_LAUNCH_CHECK();
+  RMN_CUDA_TRY(cudaMemsetAsync(slots, 0xFF, sizeof(Slot) << cap_log2, stream));
+  if (n_rows == 0) {
+    k_plan<<<1, 32, 0, stream>>>(h);
+    RMN_LAUNCH_CHECK();
+    return RMN_OK;
+  }
+  uint32_t* slot_of_row = reinterpret_cast<uint32_t*>(d_workspace);
+  uint32_t* block_counts = slot_of_row + n_rows;
+  const uint32_t nb = (n_rows + kRowsPerBlock - 1) / kRowsPerBlock;
+  const uint32_t range_blocks = nb < 148u * 8u ? nb : 148u * 8u;
+  RMN_DISPATCH_W(W, k_range<kW><<<range_blocks, 256, 0, stream>>>(d_coords, n_rows, h));
+  RMN_LAUNCH_CHECK();
+  k_plan<<<1, 32, 0, stream>>>(h);
+  RMN_LAUNCH_CHECK();
+  RMN_DISPATCH_W(W, k_insert<kW><<<nb, 256, 0, stream>>>(d_coords, n_rows, h, slots, slot_of_row));
+  RMN_LAUNCH_CHECK();
+  k_count_first<<<nb, kRowsPerBlock, 0, stream>>>(slots, slot_of_row, n_rows, h, block_counts);
+  RMN_LAUNCH_CHECK();
+  k_scan_u32<<<1, 1024, 0, stream>>>(block_counts, nb, &h->n_unique);
+  RMN_LAUNCH_CHECK();
+  RMN_DISPATCH_W(W, k_finalize<kW><<<nb, kRowsPerBlock, 0, stream>>>(
+                        d_coords, n_rows, h, slots, slot_of_row, block_counts, d_mapping,
+                        d_unique_coords));
+  RMN_LAUNCH_CHECK();
+  k_inverse<<<nb, 256, 0, stream>>>(slots, slot_of_row, n_rows, h, d_inverse);
+  RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}
+
+extern "C" int rmn_table_info(const void* d_table, uint32_t info[4], void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!d_table || !info) return RMN_ERR_BAD_ARG;
+  TableHeader h;
+  RMN_CUDA_TRY(cudaMemcpyAsync(&h, d_table, sizeof(TableHeader), cudaMemcpyDeviceToHost, stream));
+  RMN_CUDA_TRY(cudaStreamSynchronize(stream));
+  if (h.magic != kTableMagic) return RMN_ERR_BAD_ARG;
+  info[0] = h.n_unique;
+  info[1] = h.status;
+  info[2] = 1u << h.cap_log2;
+  info[3] = h.n_rows;
+  return (int)h.status;
+}
+
+extern "C" int rmn_table_find(const void* d_table, const int32_t* d_query, uint32_t n_query, int W,
+                              int32_t* d_rows, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!d_table || W < 2 || W > RMN_MAX_W) return RMN_ERR_BAD_ARG;
+  if (n_query == 0) return RMN_OK;
+  if (!d_query || !d_rows || !coords_aligned(d_query, W)) return RMN_ERR_BAD_ARG;
+  auto* h = reinterpret_cast<const TableHeader*>(d_table);
+  auto* slots =
+      reinterpret_cast<const Slot*>(reinterpret_cast<const char*>(d_table) + sizeof(TableHeader));
+  const uint32_t nb = (n_query + 255) / 256;
+  RMN_DISPATCH_W(W, k_find<kW><<<nb, 256, 0, stream>>>(h, slots, d_query, n_query, d_rows));
+  RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}
+
+extern "C" int rmn_coords_stride(const int32_t* d_coords, uint32_t n_rows, int W,
+                                 const int32_t* out_tensor_stride, int32_t* d_out, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (W < 2 || W > RMN_MAX_W || !out_tensor_stride) return RMN_ERR_BAD_ARG;
+  if (n_rows == 0) return RMN_OK;
+  if (!d_coords || !d_out) return RMN_ERR_BAD_ARG;
+  StrideArg st;
+  for (int a = 0; a < RMN_MAX_W; ++a) st.s[a] = 1;
+  for (int a = 0; a < W - 1; ++a) {
+    if (out_tensor_stride[a] <= 0) return RMN_ERR_BAD_ARG;
+    st.s[a] = out_tensor_stride[a];
+  }
+  const uint64_t total = (uint64_t)n_rows * W;
+  const uint32_t nb = (uint32_t)((total + 255) / 256);
+  k_stride<<<nb, 256, 0, stream>>>(d_coords, total, W, st, d_out);
+  RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}

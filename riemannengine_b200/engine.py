@@ -1,0 +1,637 @@
+"""Host-side mirror of the reference's sparse-convolution interface.
+
+Same names, argument order, defaults and error behaviour as the reference's
+Python module (python/src/sparse_bindings.cpp:79-199, nn_bindings.cpp:91-117),
+which re-exports the C++ classes of engine/grid/key.hpp,
+engine/grid/space.hpp, engine/tensor/sparse_tensor.hpp and engine/nn/conv.hpp.
+Every coordinate and convolution operation runs in the CUDA library through
+:mod:`riemannengine_b200.ops`; CPU tensors are rejected.
+"""
+from __future__ import annotations
+
+import math
+import random
+import string
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import ops
+
+
+# --- enums (engine/foundation/types.hpp:87-151) ------------------------------------------
+class SparseTensorQuantizationMode:
+    RANDOM_SUBSAMPLE, UNWEIGHTED_AVERAGE, UNWEIGHTED_SUM, MAX_POOL, NO_QUANTIZATION = range(5)
+
+
+class GPUMemoryAllocatorBackend:
+    PYTORCH, CUDA = 0, 1
+
+
+class RiemannAlgorithm:
+    DEFAULT, MEMORY_EFFICIENT, SPEED_OPTIMIZED = 0, 1, 2
+
+
+class CoordinateMapBackend:
+    CPU, CUDA = 0, 1
+
+
+class RegionType:
+    HYPER_CUBE, HYPER_CROSS, CUSTOM = 0, 1, 2
+
+
+class ConvolutionMode:
+    DEFAULT, DIRECT_GEMM, COPY_GEMM = 0, 1, 2
+
+
+ERROR_MAP_NOT_FOUND = "CoordinateMap not found"
+
+
+def _stride_list(v, dimension: int) -> List[int]:
+    if isinstance(v, int):
+        return [int(v)] * dimension
+    v = [int(x) for x in v]
+    if len(v) == 1 and dimension > 1:
+        v = v * dimension
+    return v
+
+
+class CoordinateMapKey:
+    """(tensor stride, string id) handle of one coordinate map (engine/grid/key.hpp:18-99)."""
+
+    def __init__(self, tensor_stride: Sequence[int], string_id: str = ""):
+        self._stride = tuple(int(s) for s in tensor_stride)
+        self._id = str(string_id)
+
+    @property
+    def tensor_stride(self) -> List[int]:
+        return list(self._stride)
+
+    def get_tensor_stride(self) -> List[int]:
+        return list(self._stride)
+
+    @property
+    def coordinate_size(self) -> int:
+        return len(self._stride) + 1
+
+    def get_coordinate_size(self) -> int:
+        return len(self._stride) + 1
+
+    def get_key(self) -> Tuple[Tuple[int, ...], str]:
+        return (self._stride, self._id)
+
+    def is_key_set(self) -> bool:
+        return True
+
+    def __eq__(self, other) -> bool:
+        return isinstance(other, CoordinateMapKey) and self.get_key() == other.get_key()
+
+    def __hash__(self) -> int:
+        return hash(self.get_key())
+
+    def __repr__(self) -> str:
+        s = "coordinate map key:" + str(list(self._stride))
+        return s + (":" + self._id if self._id else "")
+
+
+class KernelMap:
+    """One cached kernel map.
+
+    ``nbr_out`` [K, N_out] holds, for every output row and offset, the input row
+    (or -1): the output-stationary form the convolution kernels consume.
+    ``nbr_in`` [K, N_in] is its inverse (built on first use; the input-gradient
+    pass and the in/out swap of a transposed map use it). ``pairs()`` gives the
+    reference's representation: per-offset (in, out) lists.
+    """
+
+    def __init__(self, nbr_out: torch.Tensor, n_in: int, n_out: int, table_result=None,
+                 nbr_in: Optional[torch.Tensor] = None, parent: Optional["KernelMap"] = None):
+        self.nbr_out = nbr_out
+        self.n_in = n_in
+        self.n_out = n_out
+        self.K = int(nbr_out.size(0))
+        self._table_result = table_result   # ops.NeighbourTable (table = input map, query = output map)
+        self._nbr_in = nbr_in
+        self._parent = parent               # set on a swapped view
+        self._pairs = None
+
+    @property
+    def nbr_in(self) -> torch.Tensor:
+        if self._nbr_in is None:
+            self._nbr_in = ops.kmap_transpose(self.nbr_out, self.n_in)
+        return self._nbr_in
+
+    def swapped(self) -> "KernelMap":
+        """in <-> out (engine/grid/space.cpp:104-107)."""
+        return KernelMap(self.nbr_in, self.n_out, self.n_in, None, self.nbr_out, parent=self)
+
+    def pairs(self):
+        """(offset_ptr int64 [K+1] (host), in_idx int32 [P], out_idx int32 [P]) on the device."""
+        if self._pairs is None:
+            if self._parent is not None:
+                ptr, i, o = self._parent.pairs()
+                self._pairs = (ptr, o, i)
+            else:
+                self._pairs = self._table_result.pairs()
+        return self._pairs
+
+    def total_pairs(self) -> int:
+        return int(self.pairs()[0][-1])
+
+
+class _CoordinateMap:
+    def __init__(self, table: "ops.CoordinateTable", tensor_stride: Tuple[int, ...]):
+        self.table = table
+        self.tensor_stride = tensor_stride
+
+    @property
+    def coords(self) -> torch.Tensor:
+        return self.table.coords
+
+    @property
+    def size(self) -> int:
+        return self.table.n_unique
+
+
+class CoordinateManager:
+    """Owns coordinate maps and cached kernel maps (engine/grid/space.hpp:817-906).
+
+    Only the CUDA backend exists here. ``GPUMemoryAllocatorBackend`` and
+    ``RiemannAlgorithm`` are accepted and ignored: device memory always comes
+    from torch's caching allocator and there is a single kernel-map algorithm.
+    """
+
+    def __init__(self, dimension: int, backend: int = CoordinateMapBackend.CUDA,
+                 allocator: int = GPUMemoryAllocatorBackend.PYTORCH, algorithm: int = RiemannAlgorithm.DEFAULT):
+        if backend != CoordinateMapBackend.CUDA:
+            raise RuntimeError("riemannengine_b200 has no CPU coordinate-map backend")
+        self._D = int(dimension)
+        self._backend = backend
+        self._maps: Dict[Tuple[Tuple[int, ...], str], _CoordinateMap] = {}
+        self._kernel_maps: Dict[tuple, KernelMap] = {}
+
+    # -- introspection -------------------------------------------------------------------
+    @property
+    def dimension(self) -> int:
+        return self._D
+
+    def D(self) -> int:
+        return self._D
+
+    def backend(self) -> int:
+        return self._backend
+
+    def exists(self, key: CoordinateMapKey) -> bool:
+        return key.get_key() in self._maps
+
+    def _map(self, key: CoordinateMapKey, what: str = "") -> _CoordinateMap:
+        m = self._maps.get(key.get_key())
+        if m is None:
+            raise RuntimeError((what + " " if what else "") + ERROR_MAP_NOT_FOUND)
+        return m
+
+    def size(self, coordinate_map_key: CoordinateMapKey) -> int:
+        return self._map(coordinate_map_key).size
+
+    def get_coordinates(self, coordinate_map_key: CoordinateMapKey) -> torch.Tensor:
+        """[N, 1 + D] int32 coordinates in row order (engine/grid/space_impl.hpp:947-975)."""
+        return self._map(coordinate_map_key).coords
+
+    # -- insertion -------------------------------------------------------------------------
+    def _fresh_id(self, stride: Tuple[int, ...], string_id: str) -> str:
+        # key collision -> random string id (engine/grid/space_impl.hpp:284-289)
+        while True:
+            cand = string_id + "-" + "".join(random.choice(string.ascii_lowercase) for _ in range(8))
+            if (stride, cand) not in self._maps:
+                return cand
+
+    def insert_and_map(self, coordinates: torch.Tensor, tensor_stride: Sequence[int], string_id: str = ""):
+        """Returns (key, (mapping, inverse_mapping)), int64 tensors
+        (engine/grid/space_impl.hpp:262-302, engine/grid/lattice_cpu.hpp:419-444)."""
+        ops._check_coords(coordinates)
+        stride = tuple(int(s) for s in tensor_stride)
+        if coordinates.size(1) - 1 != len(stride):
+            raise RuntimeError(f"The coordinate dimension (coordinate_size - 1): {coordinates.size(1) - 1} "
+                               f"must match the size of tensor stride: {list(stride)}")
+        if (stride, string_id) in self._maps:
+            string_id = self._fresh_id(stride, string_id)
+        table = ops.table_build(coordinates)
+        self._maps[(stride, string_id)] = _CoordinateMap(table, stride)
+        return CoordinateMapKey(stride, string_id), (table.mapping, table.inverse)
+
+    def stride(self, in_key: CoordinateMapKey, kernel_stride: Sequence[int], string_id: str = "") -> CoordinateMapKey:
+        """Strided-down map, created if absent (engine/grid/space_impl.hpp:331-350). Coarse rows
+        are numbered by first occurrence over the input rows."""
+        in_map = self._map(in_key)
+        ks = _stride_list(kernel_stride, self._D)
+        if len(ks) != len(in_map.tensor_stride):
+            raise RuntimeError("stride size mismatch.")
+        out_stride = tuple(a * b for a, b in zip(in_map.tensor_stride, ks))
+        out_key = (out_stride, string_id if string_id else in_key.get_key()[1])
+        if out_key not in self._maps:
+            aligned = ops.coords_stride(in_map.coords, out_stride)
+            self._maps[out_key] = _CoordinateMap(ops.table_build(aligned), out_stride)
+        return CoordinateMapKey(*out_key)
+
+    def stride_map(self, in_key: CoordinateMapKey, out_key: CoordinateMapKey) -> torch.Tensor:
+        """Row of ``out_key`` that every row of ``in_key`` floor-aligns to
+        (engine/grid/lattice_cpu.hpp:679-710)."""
+        in_map, out_map = self._map(in_key), self._map(out_key)
+        aligned = ops.coords_stride(in_map.coords, out_map.tensor_stride)
+        return ops.table_find(out_map.table, aligned)
+
+    # -- kernel maps -----------------------------------------------------------------------
+    def kernel_map(self, in_key: CoordinateMapKey, out_key: CoordinateMapKey, kernel_size: Sequence[int],
+                   kernel_stride: Sequence[int], kernel_dilation: Sequence[int],
+                   region_type: int = RegionType.HYPER_CUBE, offsets: Optional[torch.Tensor] = None,
+                   is_transpose: bool = False, is_pool: bool = False) -> KernelMap:
+        """Cached kernel map between two coordinate maps (engine/grid/space_impl.hpp:499-706)."""
+        ks, kst, kd = list(kernel_size), list(kernel_stride), list(kernel_dilation)
+        if not (len(ks) == len(kst) == len(kd)):
+            raise RuntimeError("kernel size mismatch")
+        custom = None
+        if region_type == RegionType.CUSTOM:
+            if offsets is None:
+                raise RuntimeError("CUSTOM region needs offsets")
+            custom = np.ascontiguousarray(offsets.detach().cpu().numpy(), np.int32).reshape(-1, len(ks))
+            if min(ks + kst + kd) <= 0:
+                raise RuntimeError("CUSTOM kernel size, stride and dilation must be positive")
+        cache_key = (in_key.get_key(), out_key.get_key(), tuple(ks), tuple(kst), tuple(kd), region_type,
+                     bool(is_transpose), bool(is_pool), None if custom is None else custom.tobytes())
+        hit = self._kernel_maps.get(cache_key)
+        if hit is not None:
+            return hit
+        in_map, out_map = self._map(in_key, "in_map"), self._map(out_key, "out_map")
+        if len(ks) + 1 != in_map.table.width or len(ks) + 1 != out_map.table.width:
+            raise RuntimeError("kernel size mismatch")
+        if not is_transpose:
+            # region on the INPUT tensor stride; probe the input map around every output row
+            off = ops.region_offsets(region_type, ks, kd, in_map.tensor_stride, custom)
+            res = ops.kmap_build(in_map.table, out_map.coords, off)
+            kmap = KernelMap(res.nbr, in_map.size, out_map.size, res)
+        else:
+            swapped_key = (out_key.get_key(), in_key.get_key(), tuple(ks), tuple(kst), tuple(kd), region_type,
+                           False, bool(is_pool), None if custom is None else custom.tobytes())
+            fwd = self._kernel_maps.get(swapped_key)
+            if fwd is not None:
+                kmap = fwd.swapped()
+            else:
+                # region on the OUTPUT (fine) tensor stride: out = in + off_k. Probing the input
+                # map at out - off_k yields the output-stationary table directly.
+                off = ops.region_offsets(region_type, ks, kd, out_map.tensor_stride, custom)
+                res = ops.kmap_build(in_map.table, out_map.coords, -off)
+                kmap = KernelMap(res.nbr, in_map.size, out_map.size, res)
+        self._kernel_maps[cache_key] = kmap
+        return kmap
+
+    def kernel_map_th(self, *args, **kwargs) -> Dict[int, torch.Tensor]:
+        """{offset index -> int32 [2, P_k]} with rows (in, out); empty offsets omitted
+        (engine/grid/space.cpp:202-228)."""
+        ptr, a, q = self.kernel_map(*args, **kwargs).pairs()
+        out = {}
+        for k in range(len(ptr) - 1):
+            lo, hi = int(ptr[k]), int(ptr[k + 1])
+            if hi > lo:
+                out[k] = torch.stack([a[lo:hi], q[lo:hi]])
+        return out
+
+
+class SparseTensor:
+    """Features [N, C] + coordinate map key + manager (engine/tensor/sparse_tensor.hpp:16-80)."""
+
+    def __init__(self, features: torch.Tensor, coordinates: Optional[torch.Tensor] = None,
+                 coordinate_manager: Optional[CoordinateManager] = None,
+                 quantization_mode: int = SparseTensorQuantizationMode.RANDOM_SUBSAMPLE,
+                 algorithm: int = RiemannAlgorithm.DEFAULT, *, coordinate_map_key: Optional[CoordinateMapKey] = None):
+        if isinstance(coordinates, CoordinateMapKey):  # (features, key, manager) form
+            coordinate_map_key, coordinates = coordinates, None
+        if features.dim() != 2:
+            raise RuntimeError("Features must be a 2D tensor")
+        self._coords_cache = None
+        if coordinate_map_key is not None:
+            if coordinate_manager is None:
+                raise RuntimeError("Manager must not be null")
+            self._manager = coordinate_manager
+            self._key = coordinate_map_key
+            self._dimension = coordinate_map_key.get_coordinate_size() - 1
+            if coordinate_manager.D() != self._dimension:
+                raise RuntimeError("Coordinate manager dimension does not match coordinate key")
+            if features.size(0) != coordinate_manager.size(coordinate_map_key):
+                raise RuntimeError("Feature row count must match coordinate map size")
+            self._features = features
+            return
+        if coordinates is None or coordinates.dim() != 2:
+            raise RuntimeError("Coordinates must be a 2D tensor")
+        if features.size(0) != coordinates.size(0):
+            raise RuntimeError("Features and coordinates must have same number of rows")
+        if coordinates.size(1) < 2:
+            raise RuntimeError("Coordinates must contain a batch column and spatial columns")
+        self._dimension = int(coordinates.size(1)) - 1
+        if coordinate_manager is None:
+            coordinate_manager = CoordinateManager(self._dimension, CoordinateMapBackend.CUDA)
+        if coordinate_manager.D() != self._dimension:
+            raise RuntimeError("Coordinate manager dimension does not match coordinates")
+        self._manager = coordinate_manager
+        key, (first_rows, row_to_unique) = coordinate_manager.insert_and_map(
+            coordinates.contiguous(), [1] * self._dimension)
+        self._key = key
+        self._features = self._quantize(features, first_rows, row_to_unique,
+                                        coordinate_manager.size(key), quantization_mode)
+
+    # engine/tensor/sparse_tensor.cpp:447-481
+    @staticmethod
+    def _quantize(features, first_rows, row_to_unique, unique_count, mode):
+        M = SparseTensorQuantizationMode
+        if mode == M.RANDOM_SUBSAMPLE:
+            if features.size(0) == unique_count:  # all rows unique => first rows are 0..N-1
+                return features
+            return features.index_select(0, first_rows)
+        if mode == M.NO_QUANTIZATION:
+            return features
+        if mode in (M.UNWEIGHTED_SUM, M.UNWEIGHTED_AVERAGE):
+            result = torch.zeros((unique_count, features.size(1)), dtype=features.dtype, device=features.device)
+            result.index_add_(0, row_to_unique, features)
+            if mode == M.UNWEIGHTED_SUM:
+                return result
+            counts = torch.zeros(unique_count, dtype=features.dtype, device=features.device)
+            counts.index_add_(0, row_to_unique, torch.ones(features.size(0), dtype=features.dtype,
+                                                           device=features.device))
+            return result / counts.clamp_min(1).unsqueeze(1)
+        if mode == M.MAX_POOL:
+            result = torch.zeros((unique_count, features.size(1)), dtype=features.dtype, device=features.device)
+            return result.scatter_reduce(0, row_to_unique.unsqueeze(1).expand_as(features), features, "amax",
+                                         include_self=False)
+        raise RuntimeError("Unknown quantization mode")
+
+    @property
+    def F(self) -> torch.Tensor:
+        return self._features
+
+    features = F
+
+    @property
+    def C(self) -> torch.Tensor:
+        if self._coords_cache is None:
+            self._coords_cache = self._manager.get_coordinates(self._key)
+        return self._coords_cache
+
+    coordinates = C
+
+    @property
+    def coordinate_map_key(self) -> CoordinateMapKey:
+        return self._key
+
+    @property
+    def coordinate_manager(self) -> CoordinateManager:
+        return self._manager
+
+    @property
+    def tensor_stride(self) -> List[int]:
+        return self._key.get_tensor_stride()
+
+    @property
+    def dimension(self) -> int:
+        return self._dimension
+
+    @property
+    def device(self):
+        return self._features.device
+
+    @property
+    def dtype(self):
+        return self._features.dtype
+
+    @property
+    def requires_grad(self) -> bool:
+        return self._features.requires_grad
+
+    @property
+    def shape(self):
+        return (self._features.size(0), self._features.size(1))
+
+    def __len__(self) -> int:
+        return int(self._features.size(0))
+
+    def to(self, arg) -> "SparseTensor":
+        if isinstance(arg, torch.dtype):
+            return SparseTensor(self._features.to(arg), self._key, self._manager)
+        dev = torch.device(arg)
+        if dev.type != "cuda":
+            raise RuntimeError("riemannengine_b200 tensors live on CUDA devices only")
+        return SparseTensor(self._features.to(dev), self._key, self._manager)
+
+    def float(self) -> "SparseTensor":
+        return self.to(torch.float32)
+
+    def detach(self) -> "SparseTensor":
+        return SparseTensor(self._features.detach(), self._key, self._manager)
+
+    def __repr__(self) -> str:
+        return (f"SparseTensor(N={self._features.size(0)}, C={self._features.size(1)}, D={self._dimension}, "
+                f"device={self._features.device})")
+
+
+class KernelGenerator:
+    """Normalised kernel hyper-parameters (engine/grid/stencil.hpp:533-598, stencil.cpp:81-193)."""
+
+    class KernelParams:
+        def __init__(self, kernel_size, kernel_stride, kernel_dilation, region_type, region_offsets,
+                     expand_coordinates, D):
+            self.kernel_size, self.kernel_stride, self.kernel_dilation = kernel_size, kernel_stride, kernel_dilation
+            self.region_type, self.region_offsets = region_type, region_offsets
+            self.expand_coordinates, self.D = expand_coordinates, D
+
+    def __init__(self, kernel_size, stride=1, dilation=1, is_transpose: bool = False,
+                 region_type: int = RegionType.HYPER_CUBE, region_offsets: Optional[torch.Tensor] = None,
+                 expand_coordinates: bool = False, axis_types=None, dimension: int = -1):
+        ks = [kernel_size] if isinstance(kernel_size, int) else list(kernel_size)
+        D = dimension if dimension > 0 else len(ks)
+        self._D = D
+        self._ks, self._st, self._dl = _stride_list(ks, D), _stride_list(stride, D), _stride_list(dilation, D)
+        for name, v in (("kernel_size", self._ks), ("kernel_stride", self._st), ("kernel_dilation", self._dl)):
+            if len(v) != D:
+                raise RuntimeError(f"{name} dimension mismatch")
+        if axis_types:
+            raise RuntimeError("axis_types must be empty")
+        self._is_transpose = is_transpose
+        self._region_type = region_type
+        self._offsets = region_offsets
+        if region_type == RegionType.CUSTOM:
+            if region_offsets is None:
+                raise RuntimeError("CUSTOM region needs region_offsets")
+            self._offsets = region_offsets.to(torch.int32).reshape(-1, D).cpu()
+        elif region_offsets is not None and region_offsets.numel() != 0:
+            raise RuntimeError("region_offsets must be empty for HYPER_CUBE/HYPER_CROSS")
+        self._expand = expand_coordinates
+        if region_type == RegionType.HYPER_CUBE:
+            self._volume = int(np.prod(self._ks))
+        elif region_type == RegionType.HYPER_CROSS:
+            self._volume = 1 + sum(k - 1 for k in self._ks)
+        else:
+            self._volume = int(self._offsets.size(0))
+
+    def kernel_volume(self) -> int:
+        return self._volume
+
+    def kernel_size(self):
+        return list(self._ks)
+
+    def kernel_stride(self):
+        return list(self._st)
+
+    def kernel_dilation(self):
+        return list(self._dl)
+
+    def region_type(self):
+        return self._region_type
+
+    def expand_coordinates(self):
+        return self._expand
+
+    def dimension(self):
+        return self._D
+
+    def get_kernel(self, tensor_stride: Sequence[int], is_transpose: bool) -> "KernelGenerator.KernelParams":
+        ts = list(tensor_stride)
+        if len(ts) != self._D:
+            raise RuntimeError("tensor_stride dimension mismatch")
+        if any(s <= 0 for s in ts):
+            raise RuntimeError("tensor_stride must be positive")
+        return KernelGenerator.KernelParams(list(self._ks), list(self._st), list(self._dl), self._region_type,
+                                            self._offsets, self._expand, self._D)
+
+
+class _SparseConvolutionFunction(torch.autograd.Function):
+    """out = sum_k F[in_k] @ W[k] scattered to out_k, with hand-written backward
+    (the reference relies on torch autograd of index_select/matmul/index_add_,
+    engine/nn/conv.cpp:47-64)."""
+
+    @staticmethod
+    def forward(ctx, features, kernel, kmap: KernelMap):
+        ctx.kmap = kmap
+        ctx.save_for_backward(features, kernel)
+        return ops.conv_forward(features, kernel, kmap.nbr_out)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        features, kernel = ctx.saved_tensors
+        kmap: KernelMap = ctx.kmap
+        grad_out = grad_out.contiguous()
+        g_feat = g_kernel = None
+        if ctx.needs_input_grad[0]:
+            g_feat = ops.conv_backward_input(grad_out, kernel, kmap.nbr_in)
+        if ctx.needs_input_grad[1]:
+            g_kernel = ops.conv_backward_weight(features, grad_out, kmap.nbr_out).to(kernel.dtype)
+        return g_feat, g_kernel, None
+
+
+def sparse_convolution(features: torch.Tensor, kernel: torch.Tensor, kmap: KernelMap) -> torch.Tensor:
+    return _SparseConvolutionFunction.apply(features, kernel, kmap)
+
+
+class RiemannConvolutionBase(torch.nn.Module):
+    """engine/nn/conv.hpp:13-37, conv.cpp:70-138."""
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size=3, stride=1, dilation=1, bias: bool = False,
+                 is_transpose: bool = False, expand_coordinates: bool = False,
+                 convolution_mode: int = ConvolutionMode.DEFAULT, dimension: int = 3,
+                 region_type: int = RegionType.HYPER_CUBE):
+        super().__init__()
+        if in_channels <= 0 or out_channels <= 0:
+            raise RuntimeError("Convolution channel counts must be positive")
+        self.in_channels, self.out_channels = in_channels, out_channels
+        self.is_transpose = is_transpose
+        self.dimension = dimension
+        self.convolution_mode = convolution_mode
+        self.kernel_generator = KernelGenerator(kernel_size, stride, dilation, is_transpose, region_type, None,
+                                                expand_coordinates, None, dimension)
+        volume = self.kernel_generator.kernel_volume()
+        self.kernel = torch.nn.Parameter(torch.empty(volume, in_channels, out_channels))
+        if bias:
+            self.bias = torch.nn.Parameter(torch.empty(1, out_channels))
+        else:
+            self.register_parameter("bias", None)
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        # U(-1/sqrt(fan), 1/sqrt(fan)), fan = (C_out if transpose else C_in) * K  (conv.cpp:94-102)
+        fan = (self.out_channels if self.is_transpose else self.in_channels) * self.kernel_generator.kernel_volume()
+        bound = 1.0 / math.sqrt(fan)
+        with torch.no_grad():
+            self.kernel.uniform_(-bound, bound)
+            if self.bias is not None:
+                self.bias.uniform_(-bound, bound)
+
+    def forward(self, input: SparseTensor) -> SparseTensor:
+        if input.dimension != self.dimension:
+            raise RuntimeError("Input dimension mismatch")
+        if input.F.size(1) != self.in_channels:
+            raise RuntimeError("Input channel count does not match convolution")
+        params = self.kernel_generator.get_kernel(input.tensor_stride, self.is_transpose)
+        in_stride, string_id = input.coordinate_map_key.get_key()
+        out_stride = list(in_stride)
+        for axis, step in enumerate(params.kernel_stride):
+            if self.is_transpose:
+                if step == 0 or out_stride[axis] % step != 0:
+                    raise RuntimeError("Transpose convolution stride must divide tensor stride")
+                out_stride[axis] //= step
+            else:
+                out_stride[axis] *= step
+        out_key = CoordinateMapKey(out_stride, string_id)
+        manager = input.coordinate_manager
+        if not self.is_transpose and any(s != 1 for s in params.kernel_stride):
+            out_key = manager.stride(input.coordinate_map_key, params.kernel_stride)
+        kmap = manager.kernel_map(input.coordinate_map_key, out_key, params.kernel_size, params.kernel_stride,
+                                  params.kernel_dilation, params.region_type, params.region_offsets,
+                                  self.is_transpose, False)
+        result = sparse_convolution(input.F, self.kernel, kmap)
+        if self.bias is not None:
+            result = result + self.bias
+        return SparseTensor(result, out_key, manager)
+
+
+class _ConvWrapper(torch.nn.Module):
+    _transpose = False
+    _expand_default = False
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size: int = 3, stride: int = 1, dilation: int = 1,
+                 bias: bool = False, expand_coordinates: bool = False,
+                 convolution_mode: int = ConvolutionMode.DEFAULT, dimension: int = 3):
+        super().__init__()
+        self.base = RiemannConvolutionBase(in_channels, out_channels, kernel_size, stride, dilation, bias,
+                                           self._transpose, expand_coordinates or self._expand_default,
+                                           convolution_mode, dimension)
+
+    @property
+    def kernel(self) -> torch.nn.Parameter:
+        return self.base.kernel
+
+    @property
+    def bias(self):
+        return self.base.bias
+
+    def forward(self, input: SparseTensor) -> SparseTensor:
+        return self.base(input)
+
+
+class RiemannConvolution(_ConvWrapper):
+    """engine/nn/conv.hpp:39-55."""
+
+
+class RiemannConvolutionTranspose(_ConvWrapper):
+    """engine/nn/conv.hpp:57-72; the output map must already exist in the manager."""
+    _transpose = True
+
+
+class RiemannGenerativeConvolutionTranspose(_ConvWrapper):
+    """engine/nn/conv.hpp:74-88. As in the reference the layer never expands coordinates
+    (conv.cpp:104-138 does not call stride_region), so it behaves like the plain transposed
+    convolution."""
+    _transpose = True
+    _expand_default = True
+
+    def __init__(self, in_channels: int, out_channels: int, kernel_size: int = 3, stride: int = 1, dilation: int = 1,
+                 bias: bool = False, convolution_mode: int = ConvolutionMode.DEFAULT, dimension: int = 3):
+        super().__init__(in_channels, out_channels, kernel_size, stride, dilation, bias, True, convolution_mode,
+                         dimension)

@@ -1,0 +1,64 @@
+"""The C-ABI library loads without a GPU and exports every symbol the header declares."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "rmn_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(rmn_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_entry_points():
+    syms = declared_symbols()
+    for must in ("rmn_table_build", "rmn_kmap_build", "rmn_kmap_pairs", "rmn_conv_forward",
+                 "rmn_conv_backward_input", "rmn_conv_backward_weight", "rmn_coords_stride"):
+        assert must in syms
+
+
+def test_library_exports_every_declared_symbol():
+    from riemannengine_b200 import _build, capi
+    if not os.path.exists(_build.LIB_PATH):
+        _build.build_library()
+    handle = ctypes.CDLL(_build.LIB_PATH)
+    for name in declared_symbols():
+        assert hasattr(handle, name), f"{name} declared in rmn_b200.h but not exported"
+        assert name in capi.SIGNATURES, f"{name} has no ctypes signature"
+    assert set(capi.SIGNATURES) == set(declared_symbols())
+
+
+def test_host_only_entry_points():
+    from riemannengine_b200 import capi
+    lib = capi.lib()
+    assert lib.rmn_version() >= 100
+    assert lib.rmn_status_string(capi.ERR_PROBE_LIMIT).decode().startswith("hash probe limit")
+    assert lib.rmn_table_bytes(0) == 256 + 16 * 16
+    assert lib.rmn_table_bytes(1000) == 256 + 16 * 2048  # next power of two >= 2n + 2 slots
+
+
+def test_region_offsets_match_oracle():
+    import numpy as np
+    from oracle import oracle as O
+    from riemannengine_b200 import capi, ops
+    for rt, ks, dl, ts in [(capi.HYPER_CUBE, [3, 3, 3], [1, 1, 1], [1, 1, 1]),
+                           (capi.HYPER_CUBE, [2, 2, 2], [1, 1, 1], [2, 2, 2]),
+                           (capi.HYPER_CUBE, [3, 2, 5, 3], [1, 2, 1, 3], [1, 2, 4, 1]),
+                           (capi.HYPER_CROSS, [3, 5, 3], [1, 1, 2], [2, 1, 1])]:
+        assert (ops.region_offsets(rt, ks, dl, ts) == O.region_offsets(rt, ks, dl, ts)).all()
+    cu = np.array([[1, -2, 0], [0, 0, 3]], np.int32)
+    assert (ops.region_offsets(capi.CUSTOM, [1] * 3, [2] * 3, [4] * 3, cu) ==
+            O.region_offsets(O.CUSTOM, [1] * 3, [2] * 3, [4] * 3, cu)).all()
+
+
+def test_cpu_tensors_are_rejected():
+    import torch
+    from riemannengine_b200 import engine
+    with pytest.raises(RuntimeError, match="CUDA"):
+        engine.SparseTensor(torch.zeros(2, 3), torch.zeros(2, 4, dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="no CPU"):
+        engine.CoordinateManager(3, engine.CoordinateMapBackend.CPU)
