@@ -1,0 +1,365 @@
+"""Benchmark of the sparse-convolution hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = the whole hot path on one batch of synthetic rooms: coordinate hash
+insert (SparseTensor construction) -> 3^3 kernel map (neighbour table + pair
+lists) -> 64 -> 64 bf16 forward convolution, on a fresh coordinate manager every
+step. The metric is forward throughput in Mvoxels/s (input voxels of all ranks
+divided by the slowest rank's time). Under torchrun every rank runs its own batch
+of rooms (weak scaling by sample; the forward pass needs no collective).
+
+``--impl reference`` times the reference's own CPU implementation of the same
+path (the unmodified reference sources behind ``oracle/_ref/ref_driver``; the
+oracle's C restatement if that binary is absent) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "sparse_conv_fwd_mvoxels_per_s"
+UNIT = "Mvoxels/s"
+N_SCENES, N_VOXELS = 8, 150_000
+C_IN, C_OUT, KSIZE = 64, 64, 3
+K_VOL = KSIZE ** 3
+CPU_SAMPLE_SCENES = 2
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {
+        "workload": "indoor-room batch: 8 scenes x 150K voxels on a 200x200x60 grid per GPU, "
+                    "3^3 stride-1 conv 64->64, hash insert + kernel map + forward",
+        "scenes_per_gpu": N_SCENES, "voxels_per_scene": N_VOXELS, "kernel": "3x3x3", "stride": 1,
+        "c_in": C_IN, "c_out": C_OUT, "sharding": f"by sample, {n_gpus} rank(s), no forward collective",
+        "l2_policy": "inputs and tables (>200 MB per step) exceed the 126 MB L2; no explicit flush",
+    }
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.06)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_batch(rank: int):
+    from riemannengine_b200 import synthetic
+    coords = synthetic.indoor_batch(N_SCENES, N_VOXELS, seed=2000 + 100 * rank)
+    feats = synthetic.features(2500 + rank, len(coords), C_IN)
+    weights = synthetic.conv_weights(2600, K_VOL, C_IN, C_OUT)
+    return coords, feats, weights
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm: the reference's CPU implementation on the host cores
+# ------------------------------------------------------------------------------------------
+def cpu_reference_time(coords, feats, weights, steps: int, warmup: int):
+    """Returns (seconds for `steps` steps, voxels per step, info dict)."""
+    from oracle import refrun
+    cores = os.cpu_count() or 1
+    if refrun.available():
+        out = refrun.run(coords, feats, weights, KSIZE, 1, 1, threads=0, reps=steps, warmup=warmup,
+                         timing_only=True)
+        per_step = out["times_all"][:, 0] + out["times_all"][:, 1]  # SparseTensor ctor + first forward
+        return float(per_step.sum()) / 1e3, len(coords), {
+            "kind": "reference", "cores": int(out["info"][1]), "hardware_concurrency": int(out["info"][0]),
+            "phases_ms": {"sparse_tensor_ctor": float(out["times_ms"][0]), "first_forward": float(out["times_ms"][1]),
+                          "cached_forward": float(out["times_ms"][2]), "forward_backward": float(out["times_ms"][3])}}
+    from oracle import oracle as O
+    total = 0.0
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        mapping, _ = O.insert_and_map(coords)
+        uc = coords[mapping]
+        ptr, a, q = O.conv_kernel_map(uc, uc, O.region_offsets(O.HYPER_CUBE, [KSIZE] * 3, [1] * 3, [1] * 3))
+        O.conv_forward(feats[mapping], weights, ptr, a, q, len(uc))
+        if it >= warmup:
+            total += time.perf_counter() - t0
+    return total, len(coords), {"kind": "port", "cores": 1, "hardware_concurrency": cores}
+
+
+def cpu_sample():
+    from riemannengine_b200 import synthetic
+    coords = synthetic.indoor_batch(CPU_SAMPLE_SCENES, N_VOXELS, seed=2000)
+    feats = synthetic.features(2500, len(coords), C_IN)
+    weights = synthetic.conv_weights(2600, K_VOL, C_IN, C_OUT)
+    return coords, feats, weights
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    coords, feats, weights = cpu_sample()
+    seconds, voxels, info = cpu_reference_time(coords, feats, weights, args.steps, args.warmup)
+    value = voxels * args.steps / seconds / 1e6
+    sample = (f"{CPU_SAMPLE_SCENES} of the {N_SCENES} scenes ({voxels} voxels), fp32 features, "
+              "SparseTensor construction + first forward per step")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": info["cores"], "kind": info["kind"],
+                         "sample": sample, **{k: v for k, v in info.items() if k not in ("cores", "kind")}},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------
+# product arm
+# ------------------------------------------------------------------------------------------
+def run_product(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from riemannengine_b200 import capi, engine as E, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = capi.lib()
+
+    coords_np, feats_np, weights_np = make_batch(rank)
+    n_vox = len(coords_np)
+    coords = torch.from_numpy(coords_np).to(dev)
+    feats = torch.from_numpy(feats_np).to(dev).bfloat16()
+    conv = E.RiemannConvolution(C_IN, C_OUT, kernel_size=KSIZE, dimension=3).to(dev).bfloat16()
+    with torch.no_grad():
+        conv.kernel.copy_(torch.from_numpy(weights_np).to(dev))
+    offsets = ops.region_offsets(capi.HYPER_CUBE, [KSIZE] * 3, [1] * 3, [1] * 3)
+
+    def step():
+        """Hot path on device-resident inputs: fresh manager, hash insert, kernel map, forward."""
+        x = E.SparseTensor(feats, coords)
+        y = conv(x)
+        kmap = x.coordinate_manager.kernel_map(x.coordinate_map_key, y.coordinate_map_key, [KSIZE] * 3, [1] * 3,
+                                               [1] * 3)
+        kmap.pairs()
+        return x, y, kmap
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 3)):
+            x, y, kmap = step()
+        total_pairs = kmap.total_pairs()
+        n_unique = len(x)
+
+        # ---- headline: K steps, device-resident inputs, CUDA events on the launching stream ----
+        barrier()
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        launches0 = lib.rmn_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+        launches = lib.rmn_launch_count() - launches0
+        elapsed_ms = e0.elapsed_time(e1)
+        clocks = sampler.stop() if sampler else None
+
+        # ---- per-phase timings (median over steps; each phase bracketed by events) ----------------
+        def timed(fn, reps):
+            ts = []
+            for _ in range(reps):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                r = fn()
+                b.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b))
+            return statistics.median(ts), r
+
+        reps = max(5, min(args.steps, 20))
+        t_hash, table = timed(lambda: ops.table_build(coords), reps)
+        t_kmap, res = timed(lambda: ops.kmap_build(table, table.coords, offsets), reps)
+        cap = torch.empty(total_pairs, dtype=torch.int32, device=dev), torch.empty(total_pairs, dtype=torch.int32,
+                                                                                 device=dev)
+
+        def pairs_only():
+            capi.check(lib.rmn_kmap_pairs(ops._ptr(res.nbr), res.n_query, res.K, ops._ptr(res.offset_ptr),
+                                          ops._ptr(res.workspace), ops._ptr(cap[0]), ops._ptr(cap[1]), total_pairs,
+                                          ops._stream()), "rmn_kmap_pairs")
+        t_pairs, _ = timed(pairs_only, reps)
+        xf = x.F
+        t_fwd, _ = timed(lambda: ops.conv_forward(xf, conv.kernel, res.nbr), reps)
+
+        # ---- end to end through the public API with HOST buffers ----------------------------------
+        h_coords = torch.from_numpy(coords_np).pin_memory()
+        h_feats = torch.from_numpy(feats_np).bfloat16().pin_memory()
+        h_out = torch.empty((n_unique, C_OUT), dtype=torch.bfloat16).pin_memory()
+
+        def e2e_step():
+            dc = h_coords.to(dev, non_blocking=True)
+            df = h_feats.to(dev, non_blocking=True)
+            yy = conv(E.SparseTensor(df, dc))
+            h_out.copy_(yy.F, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        f1.record()
+        barrier()
+        e2e_ms = f0.elapsed_time(f1)
+
+    # ---- max over ranks ------------------------------------------------------------------------
+    stats = torch.tensor([elapsed_ms, e2e_ms, float(n_vox)], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        elapsed_ms, e2e_ms, total_vox = float(mx[0]), float(mx[1]), float(sm[2])
+    else:
+        total_vox = float(n_vox)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = load_peaks()
+    value = total_vox * args.steps / (elapsed_ms / 1e3) / 1e6
+    e2e_value = total_vox * args.steps / (e2e_ms / 1e3) / 1e6
+    W = 4
+    flops = 2.0 * total_pairs * C_IN * C_OUT
+    bytes_hash = n_vox * (4 * W + 32)
+    bytes_kmap = n_unique * 4 * W + n_unique * K_VOL * 32 + 8 * total_pairs
+    phases = {"hash_insert_ms": t_hash, "kmap_probe_ms": t_kmap, "kmap_pairs_ms": t_pairs, "conv_fwd_ms": t_fwd}
+    fwd_tflops = flops / (t_fwd / 1e3) / 1e12
+    kmap_gbs = bytes_kmap / ((t_kmap + t_pairs) / 1e3) / 1e9
+    hash_gbs = bytes_hash / (t_hash / 1e3) / 1e9
+    if t_fwd >= t_kmap + t_pairs:
+        roofline = {"kernel": "conv_forward", "bound": "tensor", "achieved": fwd_tflops,
+                    "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": fwd_tflops / peaks["bf16_tflops"],
+                    "traffic": None, "peak_source": peaks["source"],
+                    "algorithmic": f"2*P*Cin*Cout = {flops:.3e} flop per launch"}
+    else:
+        roofline = {"kernel": "kmap_probe+pairs", "bound": "hbm", "achieved": kmap_gbs, "peak": peaks["hbm_gbs"],
+                    "unit": "GB/s", "frac": kmap_gbs / peaks["hbm_gbs"], "traffic": None,
+                    "peak_source": peaks["source"],
+                    "algorithmic": f"N*4W + N*K*32 + 8P = {bytes_kmap:.3e} B per launch"}
+
+    coords_s, feats_s, weights_s = cpu_sample()
+    cpu_s, cpu_vox, info = cpu_reference_time(coords_s, feats_s, weights_s, steps=3, warmup=1)
+    cpu_value = cpu_vox * 3 / cpu_s / 1e6
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+        "voxels_per_step": total_vox, "pairs_per_gpu": total_pairs,
+        "phases_ms": phases,
+        "kernel_map_build_ms": t_kmap + t_pairs,
+        "fwd_cached_mvoxels_per_s": n_vox / (t_fwd / 1e3) / 1e6,
+        "roofline": roofline,
+        "roofline_all": {
+            "hash_insert": {"bound": "hbm", "achieved": hash_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": hash_gbs / peaks["hbm_gbs"]},
+            "kernel_map": {"bound": "hbm", "achieved": kmap_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                           "frac": kmap_gbs / peaks["hbm_gbs"]},
+            "conv_forward": {"bound": "tensor", "achieved": fwd_tflops, "peak": peaks["bf16_tflops"],
+                             "unit": "TFLOP/s", "frac": fwd_tflops / peaks["bf16_tflops"]},
+        },
+        "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": info["cores"], "kind": info["kind"],
+                         "sample": f"{CPU_SAMPLE_SCENES} of the {N_SCENES} scenes ({cpu_vox} voxels), fp32, "
+                                   "SparseTensor construction + first forward, 3 steps after 1 warm-up",
+                         **{k: v for k, v in info.items() if k not in ("cores", "kind")}},
+        "e2e": {"value": e2e_value, "unit": UNIT, "ms_per_step": e2e_ms / args.steps,
+                "h2d_bytes_per_step": int(h_coords.numel() * 4 + h_feats.numel() * 2),
+                "d2h_bytes_per_step": int(h_out.numel() * 2)},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_product(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -56,6 +56,9 @@ extern "C" {
 /* Library version (major*10000 + minor*100 + patch) and status text. */
 int rmn_version(void);
 const char *rmn_status_string(int status);
+/* Number of CUDA kernels this library has launched in this process so far
+ * (telemetry for benchmarks; no counterpart in the reference). */
+unsigned long long rmn_launch_count(void);
 
 /* =======================================================================
  * Coordinate hash table

@@ -19,7 +19,7 @@
 //   coords  i32 [N, W]      may contain duplicate rows
 //   feats   f32 [N, Cin]
 //   weights f32 [K, Cin, Cout]
-//   params  i32 [8] = {kernel_size, stride, dilation, chain, threads, reps, timing_only, 0}
+//   params  i32 [8] = {kernel_size, stride, dilation, chain, threads, reps, timing_only, warmup}
 //     chain = 1: after the first (strided) convolution run a transposed
 //     convolution with the same kernel_size/stride using `weights2`
 //     [K, Cout, C2] back onto the input coordinates.
@@ -29,7 +29,8 @@
 //   up_coords, up_feats, kmap2_ptr / kmap2_in / kmap2_out, grad_weights2;
 //   times_ms f64 [4] = {SparseTensor ctor, first forward (kernel map + conv),
 //   forward with cached kernel map, forward + backward}, each the median of
-//   `reps` runs; info i32 [2] = {hardware_concurrency, torch threads}.
+//   `reps` runs after `warmup` untimed ones; times_all f64 [reps, 4] holds every timed run;
+//   info i32 [2] = {hardware_concurrency, torch threads}.
 #include "engine/nn/conv.hpp"
 #include "engine/tensor/sparse_tensor.hpp"
 
@@ -154,6 +155,7 @@ int main(int argc, char** argv) {
     int threads = params[4].item<int>();
     const int reps = std::max(1, params[5].item<int>());
     const bool timing_only = params[6].item<int>() != 0;
+    const int warmup = std::max(0, params[7].item<int>());
     const int hw = static_cast<int>(std::thread::hardware_concurrency());
     if (threads <= 0) threads = std::max(hw, 1);
     torch::set_num_threads(threads);
@@ -180,32 +182,46 @@ int main(int argc, char** argv) {
 
     // --- timings (median of reps); also warms everything up -----------------
     std::vector<double> t_ctor, t_first, t_cached, t_fb;
-    for (int r = 0; r < reps + 1; ++r) {
-      auto f = feats.clone().requires_grad_(true);
-      double t0 = now_ms();
-      riemann::SparseTensor x(f, coords);
-      double t1 = now_ms();
-      auto y = conv->forward(x);
-      if (chain) y = up->forward(y);
-      double t2 = now_ms();
-      auto y2 = conv->forward(x);
-      if (chain) y2 = up->forward(y2);
-      double t3 = now_ms();
-      auto y3 = conv->forward(x);
-      if (chain) y3 = up->forward(y3);
-      (y3.F() * y3.F()).sum().mul(0.5).backward();
-      double t4 = now_ms();
+    std::vector<double> all;
+    for (int r = 0; r < reps + warmup; ++r) {
+      double t0, t1, t2, t3, t4;
+      {  // forward-only phases run without autograd recording
+        torch::NoGradGuard no_grad;
+        t0 = now_ms();
+        riemann::SparseTensor x(feats, coords);
+        t1 = now_ms();
+        auto y = conv->forward(x);
+        if (chain) y = up->forward(y);
+        t2 = now_ms();
+        auto y2 = conv->forward(x);
+        if (chain) y2 = up->forward(y2);
+        t3 = now_ms();
+      }
+      const double t_c = t1 - t0, t_f = t2 - t1, t_k = t3 - t2;
+      {  // forward + backward on a tensor whose kernel maps are already cached
+        auto f = feats.clone().requires_grad_(true);
+        riemann::SparseTensor x(f, coords);
+        conv->forward(x);
+        if (chain) up->forward(conv->forward(x));
+        t3 = now_ms();
+        auto y3 = conv->forward(x);
+        if (chain) y3 = up->forward(y3);
+        (y3.F() * y3.F()).sum().mul(0.5).backward();
+        t4 = now_ms();
+      }
       conv->zero_grad();
       if (chain) up->zero_grad();
-      if (r == 0 && reps > 1) continue;  // warm-up
-      t_ctor.push_back(t1 - t0);
-      t_first.push_back(t2 - t1);
-      t_cached.push_back(t3 - t2);
+      if (r < warmup) continue;
+      for (double v : {t_c, t_f, t_k, t4 - t3}) all.push_back(v);
+      t_ctor.push_back(t_c);
+      t_first.push_back(t_f);
+      t_cached.push_back(t_k);
       t_fb.push_back(t4 - t3);
     }
     write_array(out, "times_ms",
                 torch::tensor({median(t_ctor), median(t_first), median(t_cached), median(t_fb)},
                               torch::kFloat64));
+    write_array(out, "times_all", torch::tensor(all, torch::kFloat64).reshape({reps, 4}));
     write_array(out, "info", torch::tensor({hw, at::get_num_threads()}, torch::kInt32));
     if (timing_only) return 0;
 

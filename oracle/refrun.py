@@ -60,7 +60,7 @@ def read_arrays(path: str) -> Dict[str, np.ndarray]:
 
 def run(coords: np.ndarray, feats: np.ndarray, weights: np.ndarray, kernel_size: int, stride: int = 1,
         dilation: int = 1, weights2: Optional[np.ndarray] = None, threads: int = 0, reps: int = 1,
-        timing_only: bool = False, timeout: Optional[float] = None) -> Dict[str, np.ndarray]:
+        timing_only: bool = False, warmup: int = 0, timeout: Optional[float] = None) -> Dict[str, np.ndarray]:
     """One reference run: SparseTensor -> conv [-> transposed conv] -> backward."""
     if not available():
         raise RuntimeError("reference driver not built: make -C oracle ref")
@@ -69,7 +69,7 @@ def run(coords: np.ndarray, feats: np.ndarray, weights: np.ndarray, kernel_size:
         "feats": np.ascontiguousarray(feats, np.float32),
         "weights": np.ascontiguousarray(weights, np.float32),
         "params": np.array([kernel_size, stride, dilation, int(weights2 is not None), threads, reps,
-                            int(timing_only), 0], np.int32),
+                            int(timing_only), warmup], np.int32),
     }
     if weights2 is not None:
         arrays["weights2"] = np.ascontiguousarray(weights2, np.float32)

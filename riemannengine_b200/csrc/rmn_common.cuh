@@ -126,6 +126,8 @@ inline bool coords_aligned(const void* p, int W) {
   return W == 4 ? (a & 15) == 0 : W == 2 ? (a & 7) == 0 : (a & 3) == 0;
 }
 
+void count_launch();
+
 inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? RMN_OK : RMN_ERR_CUDA; }
 
 #define RMN_CUDA_TRY(expr)                        \
@@ -134,7 +136,13 @@ inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? RMN_OK : RMN_E
     if (_e != cudaSuccess) return RMN_ERR_CUDA;   \
   } while (0)
 
-#define RMN_LAUNCH_CHECK() RMN_CUDA_TRY(cudaGetLastError())
+// Every kernel launch of the library is followed by exactly one RMN_LAUNCH_CHECK, which also
+// feeds the launch counter read by rmn_launch_count().
+#define RMN_LAUNCH_CHECK()                 \
+  do {                                     \
+    ::rmn::count_launch();                 \
+    RMN_CUDA_TRY(cudaGetLastError());      \
+  } while (0)
 
 // Dispatch a functor templated on the coordinate width.
 #define RMN_DISPATCH_W(W_, ...)                   \
