@@ -59,6 +59,11 @@ const char *rmn_status_string(int status);
 /* Number of CUDA kernels this library has launched in this process so far
  * (telemetry for benchmarks; no counterpart in the reference). */
 unsigned long long rmn_launch_count(void);
+/* Synchronises `stream` and returns the sticky device-side status of the
+ * convolution kernels: RMN_OK, or RMN_ERR_TIMEOUT when a bounded wait inside a
+ * kernel ran out (the kernel then returned early and its output is invalid).
+ * No counterpart in the reference. */
+int rmn_device_status(void *stream);
 
 /* =======================================================================
  * Coordinate hash table

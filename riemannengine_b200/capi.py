@@ -22,6 +22,7 @@ SIGNATURES = {
     "rmn_version": (c_int, []),
     "rmn_status_string": (c_char_p, [c_int]),
     "rmn_launch_count": (ctypes.c_ulonglong, []),
+    "rmn_device_status": (c_int, [c_void_p]),
     "rmn_table_bytes": (c_size_t, [c_uint32]),
     "rmn_table_build_workspace_bytes": (c_size_t, [c_uint32]),
     "rmn_table_build": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p,

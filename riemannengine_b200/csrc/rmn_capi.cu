@@ -12,9 +12,13 @@ size_t simt_wgrad_workspace_bytes(uint32_t n_dst, int K, int c_in, int c_out);
 int simt_conv_backward_weight(const void* feats, int c_in, const void* grad_out, uint32_t n_dst,
                               int c_out, const int32_t* nbr, int K, float* dw, int dtype,
                               void* workspace, cudaStream_t stream);
+int tc_conv(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
+            int c_col, bool transposed_weights, void* out, cudaStream_t stream);
+int tc_read_status(cudaStream_t stream, uint32_t* status);
 }  // namespace rmn
 
 #include <atomic>
+#include <cstdlib>
 
 namespace rmn {
 static std::atomic<unsigned long long> g_launches{0};
@@ -43,6 +47,21 @@ extern "C" const char* rmn_status_string(int status) {
   }
 }
 
+// RMN_B200_DISABLE_TC=1 routes bf16 through the SIMT kernels (debugging aid).
+static bool use_tensor_cores() {
+  static const bool on = [] {
+    const char* e = std::getenv("RMN_B200_DISABLE_TC");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
+
+extern "C" int rmn_device_status(void* stream_) {
+  uint32_t st = 0;
+  const int rc = tc_read_status((cudaStream_t)stream_, &st);
+  return rc != RMN_OK ? rc : (int)st;
+}
+
 static bool conv_args_ok(const void* a, const void* w, const int32_t* nbr, const void* out, int K,
                          int c_in, int c_out, int dtype) {
   return a && w && nbr && out && K >= 1 && K <= 65535 && c_in >= 1 && c_out >= 1 &&
@@ -60,6 +79,10 @@ extern "C" int rmn_conv_forward(const void* d_feats, uint32_t n_src, int c_in,
     return RMN_OK;
   }
   if (!conv_args_ok(d_feats, d_weights, d_nbr, d_out, K, c_in, c_out, dtype)) return RMN_ERR_BAD_ARG;
+  if (dtype == RMN_BF16 && use_tensor_cores()) {
+    const int st = tc_conv(d_feats, d_weights, d_nbr, n_dst, K, c_in, c_out, false, d_out, stream);
+    if (st != RMN_ERR_UNSUPPORTED) return st;
+  }
   return simt_conv_forward(d_feats, c_in, d_weights, K, c_out, d_nbr, n_dst, d_out, dtype, stream);
 }
 
@@ -76,6 +99,10 @@ extern "C" int rmn_conv_backward_input(const void* d_grad_out, uint32_t n_dst, i
   }
   if (!conv_args_ok(d_grad_out, d_weights, d_nbr_t, d_grad_feats, K, c_in, c_out, dtype))
     return RMN_ERR_BAD_ARG;
+  if (dtype == RMN_BF16 && use_tensor_cores()) {
+    const int st = tc_conv(d_grad_out, d_weights, d_nbr_t, n_src, K, c_out, c_in, true, d_grad_feats, stream);
+    if (st != RMN_ERR_UNSUPPORTED) return st;
+  }
   return simt_conv_backward_input(d_grad_out, c_out, d_weights, K, c_in, d_nbr_t, n_src,
                                   d_grad_feats, dtype, stream);
 }

@@ -148,10 +148,12 @@ constexpr uint32_t pow2_at_least(uint32_t v) {
 
 template <int CR, int CC>
 struct Cfg {
-  static constexpr uint32_t A_BYTES = kTileM * CR * 2;
-  static constexpr uint32_t B_BYTES = CR * CC * 2;
+  static constexpr int KB = CR < 64 ? CR : 64;  // reduction channels per pipeline stage
+  static constexpr int NKB = CR / KB;
+  static constexpr uint32_t A_BYTES = kTileM * KB * 2;
+  static constexpr uint32_t B_BYTES = KB * CC * 2;
   static constexpr uint32_t STAGE = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (STAGE * 4 <= 200 * 1024) ? 4 : 3;
+  static constexpr int STAGES = 4;
   static constexpr uint32_t BAR_OFFSET = STAGES * STAGE;
   static constexpr uint32_t SMEM = BAR_OFFSET + 256;
   static constexpr uint32_t TMEM_COLS = pow2_at_least(2 * CC);
@@ -167,11 +169,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_conv_tc(const __nv_bfloat16* __
                                                          __nv_bfloat16* __restrict__ out,
                                                          uint32_t n_tiles) {
   using C = Cfg<CR, CC>;
-  constexpr int STAGES = C::STAGES;
+  constexpr int STAGES = C::STAGES, KB = C::KB, NKB = C::NKB;
   constexpr int CIN_W = kWT ? CC : CR, COUT_W = kWT ? CR : CC;
-  constexpr int W_C8 = COUT_W / 8;              // 16-byte chunks per weight row
-  constexpr uint32_t W_ROWGROUP = W_C8 * 128;   // bytes of 8 weight rows
-  static_assert(CR % 32 == 0 && CC % 32 == 0 && CC <= 256 && CR <= 256, "channel counts");
+  // weight image of one stage: B_ROWS rows of B_C8 16-byte chunks
+  constexpr int B_ROWS = kWT ? CC : KB, B_C8 = (kWT ? KB : CC) / 8;
+  constexpr uint32_t W_ROWGROUP = B_C8 * 128;  // bytes of 8 weight rows in the image
+  static_assert(CR % 32 == 0 && CC % 32 == 0 && CC <= 256 && CR % KB == 0, "channel counts");
 
   extern __shared__ __align__(1024) uint8_t smem[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::BAR_OFFSET);
@@ -214,40 +217,45 @@ __global__ void __launch_bounds__(kThreads, 1) k_conv_tc(const __nv_bfloat16* __
     for (uint32_t tile = blockIdx.x; tile < n_tiles && !timed_out; tile += gridDim.x) {
       const uint32_t row = tile * kTileM + warp * 32 + lane;
       int32_t idx_next = row < n_dst ? __ldg(nbr + row) : -1;
-      for (int k = 0; k < K; ++k, ++it) {
+      for (int k = 0; k < K && !timed_out; ++k) {
         const int32_t idx = idx_next;
         if (k + 1 < K) idx_next = row < n_dst ? __ldg(nbr + (size_t)(k + 1) * n_dst + row) : -1;
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-        if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
-        const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
-        // A: 8 rows x 4 chunks per warp instruction (64 contiguous bytes per source row;
-        // each quarter-warp writes 8 distinct rows of one chunk -> conflict-free)
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int r_local = g * 8 + (lane & 7);
-          const int32_t sidx = __shfl_sync(0xFFFFFFFFu, idx, r_local);
-          const __nv_bfloat16* base = src + (size_t)(sidx < 0 ? 0 : sidx) * CR;
-          const uint32_t bytes = sidx < 0 ? 0u : 16u;
-#pragma unroll
-          for (int cq = 0; cq < CR / 32; ++cq) {
-            const int chunk = cq * 4 + (lane >> 3);
-            cp_async16(a_s + chunk * (kTileM * 16) + (warp * 32 + r_local) * 16, base + chunk * 8, bytes);
-          }
-        }
-        // B: the whole W[k] image
         const __nv_bfloat16* wk = w + (size_t)k * CIN_W * COUT_W;
+#pragma unroll 1
+        for (int kb = 0; kb < NKB; ++kb, ++it) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+          if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
+          const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
+          // A: 8 rows x 4 chunks per warp instruction (64 contiguous bytes per source row;
+          // each quarter-warp writes 8 distinct rows of one chunk -> conflict-free)
 #pragma unroll
-        for (int i = 0; i < (CIN_W * W_C8) / kProducerThreads; ++i) {
-          const int u = i * 4 + warp;  // one (8-row group, 4-chunk group) per warp instruction
-          const int c8 = (u % (W_C8 / 4)) * 4 + (lane >> 3);
-          const int ci = (u / (W_C8 / 4)) * 8 + (lane & 7);
-          cp_async16(b_s + (ci >> 3) * W_ROWGROUP + c8 * 128 + (ci & 7) * 16, wk + (size_t)ci * COUT_W + c8 * 8, 16u);
-        }
-        cp_async_commit();
-        if (it >= (uint32_t)kLag) {
-          cp_async_wait<kLag>();
-          fence_proxy_async();
-          mbar_arrive(&full[(it - kLag) % STAGES]);
+          for (int g = 0; g < 4; ++g) {
+            const int r_local = g * 8 + (lane & 7);
+            const int32_t sidx = __shfl_sync(0xFFFFFFFFu, idx, r_local);
+            const __nv_bfloat16* base = src + (size_t)(sidx < 0 ? 0 : sidx) * CR + kb * KB;
+            const uint32_t bytes = sidx < 0 ? 0u : 16u;
+#pragma unroll
+            for (int cq = 0; cq < KB / 32; ++cq) {
+              const int chunk = cq * 4 + (lane >> 3);
+              cp_async16(a_s + chunk * (kTileM * 16) + (warp * 32 + r_local) * 16, base + chunk * 8, bytes);
+            }
+          }
+          // B: this stage's slice of W[k]
+#pragma unroll
+          for (int i = 0; i < (B_ROWS * B_C8) / kProducerThreads; ++i) {
+            const int u = i * 4 + warp;  // one (8-row group, 4-chunk group) per warp instruction
+            const int c8 = (u % (B_C8 / 4)) * 4 + (lane >> 3);
+            const int r = (u / (B_C8 / 4)) * 8 + (lane & 7);
+            const __nv_bfloat16* g = kWT ? wk + (size_t)r * COUT_W + kb * KB + c8 * 8
+                                         : wk + (size_t)(kb * KB + r) * COUT_W + c8 * 8;
+            cp_async16(b_s + (r >> 3) * W_ROWGROUP + c8 * 128 + (r & 7) * 16, g, 16u);
+          }
+          cp_async_commit();
+          if (it >= (uint32_t)kLag) {
+            cp_async_wait<kLag>();
+            fence_proxy_async();
+            mbar_arrive(&full[(it - kLag) % STAGES]);
+          }
         }
       }
     }
@@ -267,14 +275,15 @@ __global__ void __launch_bounds__(kThreads, 1) k_conv_tc(const __nv_bfloat16* __
       if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { timed_out = true; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * CC;
-      for (int k = 0; k < K; ++k, ++it) {
+      const uint32_t n_stage = (uint32_t)K * NKB;
+      for (uint32_t st = 0; st < n_stage; ++st, ++it) {
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
         if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
         tc_fence_after();
         if (lane == 0) {
           const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
 #pragma unroll
-          for (int j = 0; j < CR / 16; ++j) {
+          for (int j = 0; j < KB / 16; ++j) {
             // A, K-major: row groups 128 B apart (SBO), the two 8-channel chunks 2048 B apart (LBO)
             const uint64_t a_desc = smem_desc(a_s + j * 2 * (kTileM * 16), kTileM * 16, 128);
             uint64_t b_desc;
@@ -282,7 +291,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_conv_tc(const __nv_bfloat16* __
               b_desc = smem_desc(b_s + j * 2 * W_ROWGROUP, W_ROWGROUP, 128);
             else                 // K-major: N groups (weight rows) W_ROWGROUP apart (SBO), K chunks 128 B apart (LBO)
               b_desc = smem_desc(b_s + j * 2 * 128, 128, W_ROWGROUP);
-            tc_mma_bf16(d_tmem, a_desc, b_desc, IDESC, (k | j) != 0 ? 1u : 0u);
+            tc_mma_bf16(d_tmem, a_desc, b_desc, IDESC, (st | (uint32_t)j) != 0 ? 1u : 0u);
           }
           tc_commit(&empty[s]);
         }
