@@ -41,6 +41,7 @@ extern "C" {
 #define RMN_ERR_CUDA 5         /* a CUDA runtime call failed */
 #define RMN_ERR_RANGE 6        /* coordinate bounding box does not pack into 63 bits */
 #define RMN_ERR_UNSUPPORTED 7  /* shape / dtype combination has no kernel */
+#define RMN_ERR_TOO_LARGE 8    /* size exceeds the fixed capacity of an allocation-free entry point */
 
 /* ---- feature element types -------------------------------------------- */
 #define RMN_F32 0
@@ -98,6 +99,32 @@ int rmn_table_build(const int32_t *d_coords, uint32_t n_rows, int W, void *d_tab
                     size_t table_bytes, int64_t *d_mapping, int64_t *d_inverse,
                     int32_t *d_unique_coords, void *d_workspace, size_t workspace_bytes,
                     void *stream);
+
+/*
+ * rmn_table_build for callers that cannot allocate device memory. It has no
+ * counterpart in the reference. Same inputs, outputs and results as
+ * rmn_table_build, but there is no workspace argument: the build's scratch is
+ * a fixed device array inside the library (4 MiB per GPU, held from the moment
+ * the library is loaded on that GPU until the process exits).
+ * Meant for hosts with a frozen memory plan (real-time loops where cudaMalloc
+ * is banned because it synchronises the device and may fail mid-run) and for
+ * plug-ins that receive input/output buffers from their host but no allocator.
+ *  - n_rows must not exceed rmn_table_build_static_max_rows() (1 048 576);
+ *    larger inputs return RMN_ERR_TOO_LARGE and enqueue nothing.
+ *  - The first call on each device looks up the device address of the scratch
+ *    array (with that device current); make that first call outside any stream
+ *    capture. Later calls on the same device only enqueue kernels.
+ *  - The call itself performs no cudaMalloc / cudaFree and calls no allocating
+ *    library routine.
+ *  - All calls on one GPU share the one scratch array, which keeps the
+ *    previous call's contents (every word is rewritten before it is read, so
+ *    stale contents are harmless). Two calls whose kernels overlap on the same
+ *    GPU (different streams, different threads) race on it: serialise them.
+ */
+uint32_t rmn_table_build_static_max_rows(void);
+int rmn_table_build_static(const int32_t *d_coords, uint32_t n_rows, int W, void *d_table,
+                           size_t table_bytes, int64_t *d_mapping, int64_t *d_inverse,
+                           int32_t *d_unique_coords, void *stream);
 
 /*
  * Synchronising read-back: info[0] = n_unique, info[1] = device status

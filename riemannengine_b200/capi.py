@@ -12,7 +12,7 @@ from ctypes import c_char_p, c_int, c_int64, c_size_t, c_uint32, c_uint64, c_voi
 
 from . import _build
 
-OK, ERR_BAD_ARG, ERR_ALLOC, ERR_PROBE_LIMIT, ERR_TIMEOUT, ERR_CUDA, ERR_RANGE, ERR_UNSUPPORTED = range(8)
+OK, ERR_BAD_ARG, ERR_ALLOC, ERR_PROBE_LIMIT, ERR_TIMEOUT, ERR_CUDA, ERR_RANGE, ERR_UNSUPPORTED, ERR_TOO_LARGE = range(9)
 F32, BF16 = 0, 1
 HYPER_CUBE, HYPER_CROSS, CUSTOM = 0, 1, 2
 MAX_W = 8
@@ -27,6 +27,9 @@ SIGNATURES = {
     "rmn_table_build_workspace_bytes": (c_size_t, [c_uint32]),
     "rmn_table_build": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_size_t, c_void_p]),
+    "rmn_table_build_static_max_rows": (c_uint32, []),
+    "rmn_table_build_static": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p,
+                                       c_void_p]),
     "rmn_table_info": (c_int, [c_void_p, c_void_p, c_void_p]),
     "rmn_table_find": (c_int, [c_void_p, c_void_p, c_uint32, c_int, c_void_p, c_void_p]),
     "rmn_coords_stride": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_void_p, c_void_p]),

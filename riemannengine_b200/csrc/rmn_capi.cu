@@ -43,6 +43,7 @@ extern "C" const char* rmn_status_string(int status) {
     case RMN_ERR_CUDA: return "CUDA runtime error";
     case RMN_ERR_RANGE: return "coordinate bounding box does not pack into 63 bits";
     case RMN_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+    case RMN_ERR_TOO_LARGE: return "size exceeds the fixed capacity of the allocation-free entry point";
     default: return "unknown status";
   }
 }

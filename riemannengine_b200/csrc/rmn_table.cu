@@ -16,6 +16,8 @@
 
 #include <limits.h>
 
+#include <mutex>
+
 namespace rmn {
 
 constexpr int kRowsPerBlock = 256;
@@ -294,6 +296,64 @@ extern "C" int rmn_table_build(const int32_t* d_coords, uint32_t n_rows, int W, 
   k_inverse<<<nb, 256, 0, stream>>>(slots, slot_of_row, n_rows, h, d_inverse);
   RMN_LAUNCH_CHECK();
   return RMN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of rmn_table_build.
+//
+// Some hosts may not allocate device memory once they are running: a perception
+// loop with a fixed memory plan treats cudaMalloc as forbidden because it
+// synchronises the whole device and can fail from fragmentation in the middle
+// of a drive, and a plug-in loaded into somebody else's process may be handed
+// input and output buffers but no allocator to ask for scratch. Such callers
+// own the table, mapping and inverse buffers (they are outputs) yet have
+// nowhere to put the build's scratch (slot-of-row array + block counters).
+// Here that scratch lives in a file-scope device array of fixed size, so the
+// call needs nothing beyond its inputs and outputs. The price is a hard row
+// limit and 4 MiB of device memory held by every GPU that loads the library.
+//
+// The host symbol below is only a handle: kernels must be given the device
+// address obtained with cudaGetSymbolAddress, which is looked up once per
+// device (with that device current) on the first call made on it.
+// ---------------------------------------------------------------------------
+constexpr uint32_t kStaticMaxRows = 1u << 20;
+constexpr size_t kStaticScratchBytes =
+    (size_t)kStaticMaxRows * 4 + ((kStaticMaxRows + rmn::kRowsPerBlock - 1) / rmn::kRowsPerBlock + 1) * 4 + 256;
+static __device__ __align__(256) unsigned char g_table_static_scratch[kStaticScratchBytes];
+
+static int static_scratch_address(void** out) {
+  constexpr int kMaxDevices = 64;
+  static void* address[kMaxDevices] = {};
+  static std::mutex lock;
+  int dev = 0;
+  RMN_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return RMN_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> guard(lock);
+  if (!address[dev]) {
+    void* p = nullptr;
+    // the current device is `dev`: the address returned belongs to this device's copy of the array
+    RMN_CUDA_TRY(cudaGetSymbolAddress(&p, g_table_static_scratch));
+    if (!p) return RMN_ERR_CUDA;
+    address[dev] = p;
+  }
+  *out = address[dev];
+  return RMN_OK;
+}
+
+extern "C" uint32_t rmn_table_build_static_max_rows(void) { return kStaticMaxRows; }
+
+extern "C" int rmn_table_build_static(const int32_t* d_coords, uint32_t n_rows, int W, void* d_table,
+                                      size_t table_bytes, int64_t* d_mapping, int64_t* d_inverse,
+                                      int32_t* d_unique_coords, void* stream_) {
+  if (n_rows > kStaticMaxRows) return RMN_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != RMN_OK) return rc;
+  // Nothing in the scratch has to start at zero: the insert pass writes the slot of every row
+  // and the count pass writes every block counter before anything reads them, so whatever an
+  // earlier call left behind is overwritten.
+  return rmn_table_build(d_coords, n_rows, W, d_table, table_bytes, d_mapping, d_inverse,
+                         d_unique_coords, scratch, kStaticScratchBytes, stream_);
 }
 
 extern "C" int rmn_table_info(const void* d_table, uint32_t info[4], void* stream_) {
