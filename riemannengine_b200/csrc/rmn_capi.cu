@@ -15,6 +15,9 @@ int simt_conv_backward_weight(const void* feats, int c_in, const void* grad_out,
 int tc_conv(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
             int c_col, bool transposed_weights, void* out, cudaStream_t stream);
 int tc_read_status(cudaStream_t stream, uint32_t* status);
+int tc_conv_wgrad(const void* feats, const void* grad_out, const int32_t* nbr, uint32_t n_dst, int K, int c_in,
+                  int c_out, float* dw, void* workspace, size_t workspace_bytes, size_t* need,
+                  cudaStream_t stream);
 }  // namespace rmn
 
 #include <atomic>
@@ -110,8 +113,11 @@ extern "C" int rmn_conv_backward_input(const void* d_grad_out, uint32_t n_dst, i
 
 extern "C" size_t rmn_conv_backward_weight_workspace_bytes(uint32_t n_dst, int K, int c_in,
                                                            int c_out, int dtype) {
-  (void)dtype;
   if (K < 1 || c_in < 1 || c_out < 1) return 0;
+  size_t need = 0;
+  if (dtype == RMN_BF16 && use_tensor_cores() &&
+      tc_conv_wgrad(nullptr, nullptr, nullptr, n_dst, K, c_in, c_out, nullptr, nullptr, 0, &need, nullptr) == RMN_OK)
+    return need;
   return simt_wgrad_workspace_bytes(n_dst, K, c_in, c_out);
 }
 
@@ -130,6 +136,12 @@ extern "C" int rmn_conv_backward_weight(const void* d_feats, uint32_t n_src, int
     return RMN_ERR_BAD_ARG;
   if (workspace_bytes < rmn_conv_backward_weight_workspace_bytes(n_dst, K, c_in, c_out, dtype))
     return RMN_ERR_ALLOC;
+  if (dtype == RMN_BF16 && use_tensor_cores()) {
+    size_t need = 0;
+    const int st = tc_conv_wgrad(d_feats, d_grad_out, d_nbr, n_dst, K, c_in, c_out, d_grad_weights, d_workspace,
+                                 workspace_bytes, &need, stream);
+    if (st != RMN_ERR_UNSUPPORTED) return st;
+  }
   return simt_conv_backward_weight(d_feats, c_in, d_grad_out, n_dst, c_out, d_nbr, K,
                                    d_grad_weights, dtype, d_workspace, stream);
 }

@@ -1,0 +1,290 @@
+// Tensor-core weight gradient for sm_100a (bf16 features, fp32 accumulation):
+//   dW[k][ci][co] = sum_j F[nbr[k][j]][ci] * dY[j][co]
+// As a GEMM the reduction runs over destination rows j, so both operands are
+// "MN-major" (channels contiguous for a fixed row): A' = gathered feature rows,
+// B' = dY rows. G = 128 / C_in kernel offsets are stacked along M so that every
+// tcgen05.mma uses the full M = 128 (TMEM lane = offset-in-group * C_in + ci)
+// while sharing the same dY tile.
+//
+// Grid = (row chunks, offset sets). A CTA keeps the accumulators of its offset
+// set resident in TMEM (groups * C_out <= 512 columns) while it walks its row
+// chunk in blocks of 64 rows; one pipeline stage = (row block, offset group):
+// 64 x G gathered rows (16 KB) + the 64 dY rows. At the end the four producer
+// warps read the accumulators back and write an fp32 partial
+// [chunk][K][C_in][C_out]; a second kernel adds the chunks in a fixed order, so
+// the result is bit-reproducible (no atomics).
+//
+// Waits are bounded like in the forward kernel (status word g_tc_status).
+//
+// Included at the end of rmn_conv_tc.cu (one translation unit, one status word).
+#pragma once
+
+namespace rmn {
+namespace tc {
+
+constexpr int kRowsPerStage = 64;
+constexpr int kWgradThreads = 160;  // 4 producer/epilogue warps + 1 MMA warp
+
+constexpr uint32_t instr_desc_mn(int m, int n) {
+  // D fp32, A/B bf16, both operands MN-major
+  return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+
+template <int CIN, int COUT>
+struct WgradCfg {
+  static constexpr int G = 128 / CIN;                     // offsets stacked along M
+  static constexpr int MAX_GROUPS = 512 / COUT;           // accumulators resident in TMEM
+  static constexpr uint32_t A_BYTES = kRowsPerStage * 128 * 2;
+  static constexpr uint32_t B_BYTES = kRowsPerStage * COUT * 2;
+  static constexpr uint32_t STAGE = A_BYTES + B_BYTES;
+  // six stages where they fit: deeper prefetch, and > 114 KB keeps one CTA (one TMEM owner) per SM
+  static constexpr int STAGES = STAGE * 6 <= 200 * 1024 ? 6 : 4;
+  static constexpr uint32_t BAR_OFFSET = STAGES * STAGE;
+  static constexpr uint32_t SMEM = BAR_OFFSET + 256;
+};
+
+template <int CIN, int COUT>
+__global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
+    const __nv_bfloat16* __restrict__ feats, const __nv_bfloat16* __restrict__ grad_out,
+    const int32_t* __restrict__ nbr, uint32_t n_dst, int K, uint32_t chunk_rows, int groups_per_set,
+    uint32_t tmem_cols, float* __restrict__ partial) {
+  using C = WgradCfg<CIN, COUT>;
+  constexpr int STAGES = C::STAGES, G = C::G;
+  constexpr int A_C8 = 16, B_C8 = COUT / 8;           // 16-byte chunks per stage row
+  constexpr uint32_t A_KGROUP = A_C8 * 128, B_KGROUP = B_C8 * 128;  // bytes of 8 rows in the image
+  static_assert(128 % CIN == 0 && CIN >= 32 && COUT % 32 == 0 && COUT <= 256, "channel counts");
+
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::BAR_OFFSET);
+  uint64_t* empty = full + STAGES;
+  uint64_t* done = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_groups_total = (K + G - 1) / G;
+  const int group0 = blockIdx.y * groups_per_set;
+  const int n_groups = min(groups_per_set, n_groups_total - group0);
+  const uint32_t j_begin = blockIdx.x * chunk_rows;
+  const uint32_t j_end = min(n_dst, j_begin + chunk_rows);
+  const uint32_t n_blocks = j_end > j_begin ? (j_end - j_begin + kRowsPerStage - 1) / kRowsPerStage : 0;
+  const uint32_t n_stage = n_blocks * (uint32_t)n_groups;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], kProducerThreads);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(done, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    fence_proxy_async();
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  const uint32_t smem_base = smem_u32(smem);
+  bool timed_out = false;
+
+  if (warp < 4) {
+    // ------------------------------ producers ------------------------------------------
+    uint32_t it = 0;
+    for (uint32_t blk = 0; blk < n_blocks && !timed_out; ++blk) {
+      const uint32_t j0 = j_begin + blk * kRowsPerStage;
+#pragma unroll 1
+      for (int g = 0; g < n_groups; ++g, ++it) {
+        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+        if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
+        const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
+        const int k0 = (group0 + g) * G;
+        // A': 8 rows x 4 chunks per warp instruction; chunk m8 = offset-in-group * (CIN/8) + channel chunk
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int u = i * 4 + warp;
+          const int r = (u >> 2) * 8 + (lane & 7);
+          const int m8 = (u & 3) * 4 + (lane >> 3);
+          const int gg = m8 / (CIN / 8), c = m8 % (CIN / 8);
+          const uint32_t j = j0 + r;
+          int32_t idx = -1;
+          if (j < j_end && k0 + gg < K) idx = __ldg(nbr + (size_t)(k0 + gg) * n_dst + j);
+          cp_async16(a_s + (r >> 3) * A_KGROUP + m8 * 128 + (r & 7) * 16,
+                     feats + (size_t)(idx < 0 ? 0 : idx) * CIN + c * 8, idx < 0 ? 0u : 16u);
+        }
+        // B': the 64 dY rows of this block
+#pragma unroll
+        for (int i = 0; i < (kRowsPerStage * B_C8) / kProducerThreads; ++i) {
+          const int u = i * 4 + warp;
+          const int r = (u / (B_C8 / 4)) * 8 + (lane & 7);
+          const int n8 = (u % (B_C8 / 4)) * 4 + (lane >> 3);
+          const uint32_t j = j0 + r;
+          const bool ok = j < j_end;
+          cp_async16(b_s + (r >> 3) * B_KGROUP + n8 * 128 + (r & 7) * 16,
+                     grad_out + (size_t)(ok ? j : 0) * COUT + n8 * 8, ok ? 16u : 0u);
+        }
+        cp_async_commit();
+        if (it >= (uint32_t)kLag) {
+          cp_async_wait<kLag>();
+          fence_proxy_async();
+          mbar_arrive(&full[(it - kLag) % STAGES]);
+        }
+      }
+    }
+    cp_async_wait<0>();
+    fence_proxy_async();
+    if (!timed_out) {
+      const uint32_t pending = it < (uint32_t)kLag ? it : (uint32_t)kLag;
+      for (uint32_t j = it - pending; j < it; ++j) mbar_arrive(&full[j % STAGES]);
+    }
+    // ------------------------------ epilogue (same warps) -------------------------------
+    if (!timed_out && n_stage > 0 && !mbar_wait(done, 0)) timed_out = true;
+    timed_out = __any_sync(0xFFFFFFFFu, timed_out);  // the TMEM loads below are warp-collective
+    tc_fence_after();
+    const int m = warp * 32 + lane;  // TMEM lane
+    const int gg = m / CIN, ci = m % CIN;
+    for (int g = 0; g < n_groups; ++g) {
+      const int k = (group0 + g) * G + gg;
+#pragma unroll
+      for (int c0 = 0; c0 < COUT; c0 += 32) {
+        uint32_t r[32];
+        if (n_stage > 0 && !timed_out) {
+          tc_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + g * COUT + c0, r);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int v = 0; v < 32; ++v) r[v] = 0u;
+        }
+        if (k < K) {
+          float4* dst = reinterpret_cast<float4*>(partial + (((size_t)blockIdx.x * K + k) * CIN + ci) * COUT + c0);
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            dst[v] = make_float4(__uint_as_float(r[v * 4 + 0]), __uint_as_float(r[v * 4 + 1]),
+                                 __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
+        }
+      }
+    }
+  } else {
+    // ------------------------------ MMA issuer -----------------------------------------
+    constexpr uint32_t IDESC = instr_desc_mn(128, COUT);
+    uint32_t it = 0;
+    for (uint32_t blk = 0; blk < n_blocks && !timed_out; ++blk) {
+      for (int g = 0; g < n_groups; ++g, ++it) {
+        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+        if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
+#pragma unroll
+          for (int jj = 0; jj < kRowsPerStage / 16; ++jj) {
+            // MN-major operands: 8-element channel groups 128 B apart (SBO), 8-row groups one KGROUP apart (LBO)
+            const uint64_t a_desc = smem_desc(a_s + jj * 2 * A_KGROUP, A_KGROUP, 128);
+            const uint64_t b_desc = smem_desc(b_s + jj * 2 * B_KGROUP, B_KGROUP, 128);
+            tc_mma_bf16(tmem_base + g * COUT, a_desc, b_desc, IDESC, (blk | (uint32_t)jj) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[s]);
+        }
+        __syncwarp();
+      }
+    }
+    if (!timed_out && lane == 0) tc_commit(done);
+    __syncwarp();
+  }
+
+  if (timed_out) atomicExch(&g_tc_status, (uint32_t)RMN_ERR_TIMEOUT);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols)
+                 : "memory");
+  }
+}
+
+__global__ void __launch_bounds__(256) k_reduce_chunks(const float* __restrict__ partial, uint32_t n_chunks,
+                                                       size_t elems, float* __restrict__ out) {
+  const size_t e = (size_t)blockIdx.x * 256 + threadIdx.x;
+  if (e >= elems) return;
+  float s = 0.f;
+  for (uint32_t c = 0; c < n_chunks; ++c) s += partial[(size_t)c * elems + e];
+  out[e] = s;
+}
+
+struct WgradPlan {
+  uint32_t chunks, chunk_rows;
+  int sets, groups_per_set;
+  uint32_t tmem_cols;
+};
+
+template <int CIN, int COUT>
+WgradPlan plan(uint32_t n_dst, int K, int sms) {
+  using C = WgradCfg<CIN, COUT>;
+  WgradPlan p;
+  const int groups = (K + C::G - 1) / C::G;
+  p.sets = (groups + C::MAX_GROUPS - 1) / C::MAX_GROUPS;
+  p.groups_per_set = (groups + p.sets - 1) / p.sets;
+  p.tmem_cols = pow2_at_least((uint32_t)p.groups_per_set * COUT);
+  uint32_t want = (uint32_t)(sms / p.sets);
+  if (want < 1) want = 1;
+  uint32_t rows = (n_dst + want - 1) / want;
+  if (rows < 2048) rows = 2048;
+  p.chunk_rows = (rows + kRowsPerStage - 1) / kRowsPerStage * kRowsPerStage;
+  p.chunks = n_dst == 0 ? 1 : (n_dst + p.chunk_rows - 1) / p.chunk_rows;
+  return p;
+}
+
+template <int CIN, int COUT>
+int launch_wgrad(const void* feats, const void* grad_out, const int32_t* nbr, uint32_t n_dst, int K, float* dw,
+                 void* workspace, size_t workspace_bytes, size_t* need, cudaStream_t stream) {
+  using C = WgradCfg<CIN, COUT>;
+  int dev = 0, sms = 148;
+  RMN_CUDA_TRY(cudaGetDevice(&dev));
+  RMN_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const WgradPlan p = plan<CIN, COUT>(n_dst, K, sms);
+  const size_t elems = (size_t)K * CIN * COUT;
+  *need = (size_t)p.chunks * elems * sizeof(float);
+  if (!feats) return RMN_OK;  // size query
+  if (workspace_bytes < *need) return RMN_ERR_ALLOC;
+  auto kern = k_conv_tc_wgrad<CIN, COUT>;
+  static bool configured[64] = {};
+  if (dev < 64 && !configured[dev]) {
+    RMN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
+    configured[dev] = true;
+  }
+  dim3 grid(p.chunks, p.sets);
+  kern<<<grid, kWgradThreads, C::SMEM, stream>>>((const __nv_bfloat16*)feats, (const __nv_bfloat16*)grad_out, nbr,
+                                                 n_dst, K, p.chunk_rows, p.groups_per_set, p.tmem_cols,
+                                                 (float*)workspace);
+  RMN_LAUNCH_CHECK();
+  k_reduce_chunks<<<(uint32_t)((elems + 255) / 256), 256, 0, stream>>>((const float*)workspace, p.chunks, elems, dw);
+  RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}
+
+}  // namespace tc
+
+// feats == nullptr: only report the workspace bytes in *need. RMN_ERR_UNSUPPORTED when no
+// tensor-core instantiation covers the shape.
+int tc_conv_wgrad(const void* feats, const void* grad_out, const int32_t* nbr, uint32_t n_dst, int K, int c_in,
+                  int c_out, float* dw, void* workspace, size_t workspace_bytes, size_t* need,
+                  cudaStream_t stream) {
+#define RMN_WG_CASE(I, O) \
+  if (c_in == I && c_out == O) \
+    return tc::launch_wgrad<I, O>(feats, grad_out, nbr, n_dst, K, dw, workspace, workspace_bytes, need, stream);
+  RMN_WG_CASE(32, 32)
+  RMN_WG_CASE(32, 64)
+  RMN_WG_CASE(64, 32)
+  RMN_WG_CASE(64, 64)
+  RMN_WG_CASE(64, 128)
+  RMN_WG_CASE(128, 64)
+  RMN_WG_CASE(128, 128)
+  RMN_WG_CASE(128, 256)
+#undef RMN_WG_CASE
+  return RMN_ERR_UNSUPPORTED;
+}
+
+}  // namespace rmn

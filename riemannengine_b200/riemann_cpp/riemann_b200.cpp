@@ -1,0 +1,683 @@
+// Implementation of the riemann_cpp (B200) host layer: LibTorch tensors for device memory and
+// autograd, the C ABI of librmn_b200.so for every coordinate / convolution operation.
+#include "riemann_b200.hpp"
+
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+
+#include <cmath>
+#include <cstdlib>
+#include <sstream>
+#include <stdexcept>
+
+#include "rmn_b200.h"
+
+namespace riemann {
+namespace {
+
+constexpr const char* ERROR_MAP_NOT_FOUND = "CoordinateMap not found";
+
+// status -> the exception type the reference's ASSERT throws (engine/foundation/errors.hpp:113-122)
+void check(int status, const char* where) {
+  if (status != RMN_OK)
+    throw std::runtime_error(std::string(where) + ": " + rmn_status_string(status) + " (status " +
+                             std::to_string(status) + ")");
+}
+
+void* current_stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+void* ptr(const at::Tensor& t) { return t.defined() && t.numel() > 0 ? t.data_ptr() : nullptr; }
+
+int dtype_code(const at::Tensor& t) {
+  if (t.scalar_type() == at::kFloat) return RMN_F32;
+  if (t.scalar_type() == at::kBFloat16) return RMN_BF16;
+  throw std::runtime_error("unsupported feature dtype: float32 and bfloat16 only");
+}
+
+// the checks of insert_and_map_cpp (engine/grid/space_impl.hpp:268-276)
+void check_coordinates(const at::Tensor& c) {
+  TORCH_CHECK(c.is_cuda(), "coordinates must be a CUDA tensor: this library has no CPU path");
+  TORCH_CHECK(c.dim() == 2, "coordinates must be 2-D [N, 1 + D]");
+  TORCH_CHECK(c.scalar_type() == at::kInt, "coordinates must be int32");
+  TORCH_CHECK(c.is_contiguous(), "coordinates must be contiguous");
+  TORCH_CHECK(c.size(1) >= 2 && c.size(1) <= RMN_MAX_W, "coordinates must have between 2 and 8 columns");
+}
+
+std::string stride_string(const stride_type& s) {
+  std::ostringstream out;
+  out << "[";
+  for (size_t i = 0; i < s.size(); ++i) out << (i ? ", " : "") << s[i];
+  out << "]";
+  return out.str();
+}
+
+std::vector<int32_t> to_i32(const stride_type& s) { return std::vector<int32_t>(s.begin(), s.end()); }
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// CoordinateMapKey
+// ---------------------------------------------------------------------------------------------
+CoordinateMapKey::CoordinateMapKey(size_type coordinate_size, coordinate_map_key_type const& key)
+    : m_key_set(true), m_coordinate_size(coordinate_size), m_key(key) {
+  if (coordinate_size - 1 != m_key.first.size())
+    throw std::runtime_error("Invalid tensor_stride: " + stride_string(m_key.first));
+}
+
+CoordinateMapKey::CoordinateMapKey(stride_type tensor_stride, std::string string_id)
+    : m_key_set(true), m_coordinate_size(tensor_stride.size() + 1), m_key(std::move(tensor_stride), std::move(string_id)) {}
+
+void CoordinateMapKey::set_key(stride_type tensor_stride, std::string string_id) {
+  if (m_coordinate_size - 1 != tensor_stride.size())
+    throw std::runtime_error("Invalid tensor_stride size: " + stride_string(tensor_stride));
+  m_key = std::make_pair(std::move(tensor_stride), std::move(string_id));
+  m_key_set = true;
+}
+
+void CoordinateMapKey::set_key(coordinate_map_key_type const& key) { set_key(key.first, key.second); }
+
+coordinate_map_key_type CoordinateMapKey::get_key() const {
+  if (!m_key_set) throw std::runtime_error("Key not set");
+  return m_key;
+}
+
+uint64_t CoordinateMapKey::hash() const {
+  uint64_t h = UINT64_C(14695981039346656037);  // FNV-1a over stride entries and id bytes
+  for (auto s : m_key.first) { h ^= s; h *= UINT64_C(1099511628211); }
+  for (unsigned char c : m_key.second) { h ^= c; h *= UINT64_C(1099511628211); }
+  return h;
+}
+
+bool CoordinateMapKey::operator==(CoordinateMapKey const& key) const {
+  if (!m_key_set || !key.m_key_set) return false;
+  return m_key == key.m_key;
+}
+
+std::string CoordinateMapKey::to_string() const {
+  std::string out = "coordinate map key:" + stride_string(m_key.first);
+  if (!m_key.second.empty()) out += ":" + m_key.second;
+  return out;
+}
+
+// ---------------------------------------------------------------------------------------------
+// KernelMap
+// ---------------------------------------------------------------------------------------------
+at::Tensor const& KernelMap::nbr_in() {
+  if (!nbr_in_.defined()) {
+    c10::cuda::CUDAGuard guard(nbr_out.device());
+    const int64_t K = nbr_out.size(0);
+    nbr_in_ = at::empty({K, n_in}, nbr_out.options());
+    check(rmn_kmap_transpose(static_cast<const int32_t*>(ptr(nbr_out)), static_cast<uint32_t>(n_out),
+                             static_cast<int>(K), static_cast<uint32_t>(n_in),
+                             static_cast<int32_t*>(ptr(nbr_in_)), current_stream()),
+          "rmn_kmap_transpose");
+  }
+  return nbr_in_;
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> const& KernelMap::pairs() {
+  if (have_pairs_) return pairs_;
+  if (parent) {  // in <-> out of the parent's lists (engine/grid/space.cpp:104-107)
+    auto const& p = parent->pairs();
+    pairs_ = std::make_tuple(std::get<0>(p), std::get<2>(p), std::get<1>(p));
+  } else {
+    c10::cuda::CUDAGuard guard(nbr_out.device());
+    auto host_ptr = offset_ptr.cpu();
+    const int64_t K = nbr_out.size(0);
+    const int64_t total = host_ptr[K].item<int64_t>();
+    auto in_idx = at::empty({total}, nbr_out.options());
+    auto out_idx = at::empty({total}, nbr_out.options());
+    check(rmn_kmap_pairs(static_cast<const int32_t*>(ptr(nbr_out)), static_cast<uint32_t>(n_out),
+                         static_cast<int>(K), static_cast<const int64_t*>(ptr(offset_ptr)), ptr(workspace),
+                         static_cast<int32_t*>(ptr(in_idx)), static_cast<int32_t*>(ptr(out_idx)),
+                         static_cast<uint64_t>(total), current_stream()),
+          "rmn_kmap_pairs");
+    pairs_ = std::make_tuple(host_ptr, in_idx, out_idx);
+  }
+  have_pairs_ = true;
+  return pairs_;
+}
+
+std::shared_ptr<KernelMap> KernelMap::swapped(std::shared_ptr<KernelMap> const& self) {
+  auto out = std::make_shared<KernelMap>();
+  out->nbr_out = nbr_in();
+  out->nbr_in_ = nbr_out;
+  out->n_in = n_out;
+  out->n_out = n_in;
+  out->parent = self;
+  return out;
+}
+
+// ---------------------------------------------------------------------------------------------
+// CoordinateManager
+// ---------------------------------------------------------------------------------------------
+CoordinateManager::CoordinateManager(int D, CoordinateMapBackend::Type map_type, GPUMemoryAllocatorBackend::Type,
+                                     RiemannAlgorithm::Mode)
+    : D_(D), map_type_(map_type) {
+  if (map_type != CoordinateMapBackend::CUDA)
+    throw std::runtime_error("riemann_cpp (B200) has no CPU coordinate-map backend");
+}
+
+CoordinateManager::Map CoordinateManager::build(const at::Tensor& coords, const stride_type& tensor_stride,
+                                                at::Tensor* mapping_out, at::Tensor* inverse_out) {
+  c10::cuda::CUDAGuard guard(coords.device());
+  const uint32_t n = static_cast<uint32_t>(coords.size(0));
+  const int W = static_cast<int>(coords.size(1));
+  auto bytes = at::TensorOptions().dtype(at::kByte).device(coords.device());
+  auto longs = at::TensorOptions().dtype(at::kLong).device(coords.device());
+  Map m;
+  m.tensor_stride = tensor_stride;
+  const size_t table_bytes = rmn_table_bytes(n), ws_bytes = rmn_table_build_workspace_bytes(n);
+  m.table = at::empty({static_cast<int64_t>(table_bytes)}, bytes);
+  auto ws = at::empty({static_cast<int64_t>(ws_bytes)}, bytes);
+  auto mapping = at::empty({n}, longs), inverse = at::empty({n}, longs);
+  auto unique = at::empty({n, W}, coords.options());
+  check(rmn_table_build(static_cast<const int32_t*>(ptr(coords)), n, W, ptr(m.table), table_bytes,
+                        static_cast<int64_t*>(ptr(mapping)), static_cast<int64_t*>(ptr(inverse)),
+                        static_cast<int32_t*>(ptr(unique)), ptr(ws), ws_bytes, current_stream()),
+        "rmn_table_build");
+  uint32_t info[4];
+  check(rmn_table_info(ptr(m.table), info, current_stream()), "rmn_table_build");
+  m.size = info[0];
+  m.coords = unique.narrow(0, 0, m.size);
+  if (mapping_out) *mapping_out = mapping.narrow(0, 0, m.size);
+  if (inverse_out) *inverse_out = inverse;
+  return m;
+}
+
+CoordinateManager::Map const& CoordinateManager::find(const CoordinateMapKey& key, const char* what) const {
+  auto it = maps_.find(key.get_key());
+  if (it == maps_.end()) {
+    std::string msg = what && *what ? std::string(what) + " " : std::string();
+    throw std::runtime_error(msg + ERROR_MAP_NOT_FOUND);
+  }
+  return it->second;
+}
+
+bool CoordinateManager::exists(const CoordinateMapKey& key) const { return maps_.count(key.get_key()) != 0; }
+uint32_t CoordinateManager::size(const CoordinateMapKey& key) const { return find(key).size; }
+at::Tensor CoordinateManager::get_coordinates(const CoordinateMapKey& key) const { return find(key).coords; }
+
+std::pair<CoordinateMapKey, std::pair<at::Tensor, at::Tensor>>
+CoordinateManager::insert_and_map(const at::Tensor& coordinates, stride_type tensor_stride, std::string string_id) {
+  check_coordinates(coordinates);
+  const auto coordinate_size = static_cast<size_type>(coordinates.size(1));
+  if (coordinate_size - 1 != tensor_stride.size())
+    throw std::runtime_error("The coordinate dimension (coordinate_size - 1): " +
+                             std::to_string(coordinate_size - 1) +
+                             " must match the size of tensor stride: " + stride_string(tensor_stride));
+  coordinate_map_key_type map_key(tensor_stride, string_id);
+  while (maps_.count(map_key)) {  // key collision -> random string id (space_impl.hpp:284-289)
+    std::string suffix = "-";
+    for (int i = 0; i < 8; ++i) suffix.push_back(static_cast<char>('a' + std::rand() % 26));
+    map_key.second = string_id + suffix;
+  }
+  at::Tensor mapping, inverse;
+  maps_[map_key] = build(coordinates, tensor_stride, &mapping, &inverse);
+  return {CoordinateMapKey(coordinate_size, map_key), {mapping, inverse}};
+}
+
+CoordinateMapKey CoordinateManager::stride(const CoordinateMapKey& in_key, const stride_type& kernel_stride,
+                                           std::string string_id) {
+  auto const& in_map = find(in_key);
+  if (in_map.tensor_stride.size() != kernel_stride.size()) throw std::runtime_error("stride size mismatch.");
+  stride_type out_stride(in_map.tensor_stride);
+  for (size_t i = 0; i < out_stride.size(); ++i) out_stride[i] *= kernel_stride[i];
+  coordinate_map_key_type out_key(out_stride, string_id.empty() ? in_key.get_key().second : string_id);
+  if (!maps_.count(out_key)) {
+    c10::cuda::CUDAGuard guard(in_map.coords.device());
+    auto aligned = at::empty_like(in_map.coords);
+    auto st = to_i32(out_stride);
+    check(rmn_coords_stride(static_cast<const int32_t*>(ptr(in_map.coords)), in_map.size,
+                            static_cast<int>(in_map.coords.size(1)), st.data(),
+                            static_cast<int32_t*>(ptr(aligned)), current_stream()),
+          "rmn_coords_stride");
+    maps_[out_key] = build(aligned, out_stride, nullptr, nullptr);
+  }
+  return CoordinateMapKey(in_key.get_coordinate_size(), out_key);
+}
+
+std::shared_ptr<KernelMap> CoordinateManager::kernel_map(const CoordinateMapKey& in_key,
+                                                         const CoordinateMapKey& out_key,
+                                                         const stride_type& kernel_size,
+                                                         const stride_type& kernel_stride,
+                                                         const stride_type& kernel_dilation,
+                                                         RegionType::Type region_type, const at::Tensor& offsets,
+                                                         bool is_transpose, bool is_pool) {
+  const size_t kernel_dim = kernel_size.size();
+  if (kernel_dim != kernel_stride.size() || kernel_dim != kernel_dilation.size())
+    throw std::runtime_error("kernel size mismatch");
+  std::vector<int32_t> custom;
+  if (region_type == RegionType::CUSTOM) {
+    TORCH_CHECK(offsets.defined(), "CUSTOM region needs offsets");
+    auto host = offsets.to(at::kCPU, at::kInt).contiguous();
+    custom.assign(host.data_ptr<int32_t>(), host.data_ptr<int32_t>() + host.numel());
+    for (size_t i = 0; i < kernel_dim; ++i)
+      TORCH_CHECK(kernel_size[i] > 0 && kernel_stride[i] > 0 && kernel_dilation[i] > 0,
+                  "CUSTOM kernel size, stride and dilation must be positive");
+  }
+  auto cache_key = [&](const CoordinateMapKey& a, const CoordinateMapKey& b, bool transpose) {
+    std::ostringstream out;
+    out << a.to_string() << "|" << b.to_string() << "|" << stride_string(kernel_size) << stride_string(kernel_stride)
+        << stride_string(kernel_dilation) << "|" << int(region_type) << transpose << is_pool << "|";
+    for (auto v : custom) out << v << ",";
+    return out.str();
+  };
+  const std::string key = cache_key(in_key, out_key, is_transpose);
+  if (auto it = kernel_maps_.find(key); it != kernel_maps_.end()) return it->second;
+
+  auto const& in_map = find(in_key, "in_map");
+  auto const& out_map = find(out_key, "out_map");
+  const int W = static_cast<int>(in_map.coords.size(1));
+  if (kernel_dim + 1 != static_cast<size_t>(W) || out_map.coords.size(1) != W)
+    throw std::runtime_error("kernel size mismatch");
+
+  std::shared_ptr<KernelMap> result;
+  if (is_transpose) {
+    const std::string swapped_key = cache_key(out_key, in_key, false);
+    if (auto it = kernel_maps_.find(swapped_key); it != kernel_maps_.end()) result = it->second->swapped(it->second);
+  }
+  if (!result) {
+    // forward: region on the INPUT stride, probe the input map around every output row.
+    // transposed: region on the OUTPUT (fine) stride, out = in + off_k; probing the input map at
+    // out - off_k gives the output-stationary table directly (space_impl.hpp:649-697 builds the same
+    // pairs by probing the output map and swapping).
+    auto const& region_stride = is_transpose ? out_map.tensor_stride : in_map.tensor_stride;
+    auto ks = to_i32(kernel_size), kd = to_i32(kernel_dilation), ts = to_i32(region_stride);
+    const int D = static_cast<int>(kernel_dim);
+    const int n_custom = D ? static_cast<int>(custom.size()) / D : 0;
+    const int K = rmn_region_volume(int(region_type), D, ks.data(), n_custom);
+    if (K < 0) check(-K, "rmn_region_volume");
+    std::vector<int32_t> off(static_cast<size_t>(K) * D);
+    const int K2 = rmn_region_offsets(int(region_type), D, ks.data(), kd.data(), ts.data(),
+                                      custom.empty() ? nullptr : custom.data(), n_custom, off.data());
+    if (K2 < 0) check(-K2, "rmn_region_offsets");
+    if (is_transpose)
+      for (auto& v : off) v = -v;
+
+    c10::cuda::CUDAGuard guard(in_map.coords.device());
+    auto ints = in_map.coords.options();
+    auto d_off = at::from_blob(off.data(), {static_cast<int64_t>(off.size())}, at::kInt).to(in_map.coords.device());
+    result = std::make_shared<KernelMap>();
+    result->n_in = in_map.size;
+    result->n_out = out_map.size;
+    result->nbr_out = at::empty({K, static_cast<int64_t>(out_map.size)}, ints);
+    result->offset_ptr = at::empty({K + 1}, ints.dtype(at::kLong));
+    const size_t ws_bytes = rmn_kmap_workspace_bytes(out_map.size, K);
+    result->workspace = at::empty({static_cast<int64_t>(ws_bytes)}, ints.dtype(at::kByte));
+    check(rmn_kmap_build(ptr(in_map.table), static_cast<const int32_t*>(ptr(out_map.coords)), out_map.size, W,
+                         static_cast<const int32_t*>(ptr(d_off)), K, static_cast<int32_t*>(ptr(result->nbr_out)),
+                         static_cast<int64_t*>(ptr(result->offset_ptr)), ptr(result->workspace), ws_bytes,
+                         current_stream()),
+          "rmn_kmap_build");
+  }
+  kernel_maps_[key] = result;
+  return result;
+}
+
+std::map<int64_t, at::Tensor> CoordinateManager::kernel_map_th(
+    const CoordinateMapKey& in_key, const CoordinateMapKey& out_key, const stride_type& kernel_size,
+    const stride_type& kernel_stride, const stride_type& kernel_dilation, RegionType::Type region_type,
+    const at::Tensor& offsets, bool is_transpose, bool is_pool) {
+  auto kmap = kernel_map(in_key, out_key, kernel_size, kernel_stride, kernel_dilation, region_type, offsets,
+                         is_transpose, is_pool);
+  auto const& [host_ptr, in_idx, out_idx] = kmap->pairs();
+  std::map<int64_t, at::Tensor> out;
+  auto acc = host_ptr.accessor<int64_t, 1>();
+  for (int64_t k = 0; k + 1 < host_ptr.size(0); ++k)
+    if (acc[k + 1] > acc[k])
+      out[k] = at::stack({in_idx.slice(0, acc[k], acc[k + 1]), out_idx.slice(0, acc[k], acc[k + 1])});
+  return out;
+}
+
+// ---------------------------------------------------------------------------------------------
+// SparseTensor (engine/tensor/sparse_tensor.cpp:62-120, 447-481)
+// ---------------------------------------------------------------------------------------------
+namespace {
+at::Tensor quantize_features(const at::Tensor& features, const at::Tensor& first_rows,
+                             const at::Tensor& row_to_unique, int64_t unique_count,
+                             SparseTensorQuantizationMode::Type mode) {
+  switch (mode) {
+    case SparseTensorQuantizationMode::RANDOM_SUBSAMPLE:
+      // all rows unique <=> first rows are 0..N-1 (first-occurrence numbering)
+      if (features.size(0) == unique_count) return features;
+      return features.index_select(0, first_rows);
+    case SparseTensorQuantizationMode::NO_QUANTIZATION:
+      return features;
+    case SparseTensorQuantizationMode::UNWEIGHTED_SUM:
+    case SparseTensorQuantizationMode::UNWEIGHTED_AVERAGE: {
+      auto result = torch::zeros({unique_count, features.size(1)}, features.options());
+      result.index_add_(0, row_to_unique, features);
+      if (mode == SparseTensorQuantizationMode::UNWEIGHTED_SUM) return result;
+      auto counts = torch::zeros({unique_count}, features.options());
+      counts.index_add_(0, row_to_unique, torch::ones({features.size(0)}, features.options()));
+      return result / counts.clamp_min(1).unsqueeze(1);
+    }
+    case SparseTensorQuantizationMode::MAX_POOL: {
+      auto result = torch::zeros({unique_count, features.size(1)}, features.options());
+      return at::scatter_reduce(result, 0, row_to_unique.unsqueeze(1).expand_as(features), features, "amax", false);
+    }
+    default:
+      throw std::runtime_error("Unknown quantization mode");
+  }
+}
+}  // namespace
+
+SparseTensor::SparseTensor(at::Tensor features, at::Tensor coordinates, std::shared_ptr<CoordinateManager> manager,
+                           SparseTensorQuantizationMode::Type quantization_mode,
+                           GPUMemoryAllocatorBackend::Type alloc_type, RiemannAlgorithm::Mode algo)
+    : features_(std::move(features)), key_(static_cast<size_type>(coordinates.dim() == 2 ? coordinates.size(1) : 0)),
+      dimension_(0) {
+  TORCH_CHECK(features_.dim() == 2, "Features must be a 2D tensor");
+  TORCH_CHECK(coordinates.dim() == 2, "Coordinates must be a 2D tensor");
+  TORCH_CHECK(features_.size(0) == coordinates.size(0), "Features and coordinates must have same number of rows");
+  TORCH_CHECK(coordinates.size(1) >= 2, "Coordinates must contain a batch column and spatial columns");
+  TORCH_CHECK(coordinates.is_cuda(), "coordinates must be a CUDA tensor: this library has no CPU path");
+  dimension_ = static_cast<int>(coordinates.size(1) - 1);
+  if (!manager)
+    manager = std::make_shared<CoordinateManager>(dimension_, CoordinateMapBackend::CUDA, alloc_type, algo);
+  TORCH_CHECK(manager->D() == dimension_, "Coordinate manager dimension does not match coordinates");
+  manager_ = std::move(manager);
+  stride_type unit_stride(static_cast<size_t>(dimension_), 1);
+  auto inserted = manager_->insert_and_map(coordinates.contiguous(), unit_stride);
+  key_ = std::move(inserted.first);
+  features_ = quantize_features(features_, inserted.second.first, inserted.second.second, manager_->size(key_),
+                                quantization_mode);
+}
+
+SparseTensor::SparseTensor(at::Tensor features, CoordinateMapKey coordinate_map_key,
+                           std::shared_ptr<CoordinateManager> manager)
+    : features_(std::move(features)), key_(std::move(coordinate_map_key)), manager_(std::move(manager)),
+      dimension_(static_cast<int>(key_.get_coordinate_size()) - 1) {
+  TORCH_CHECK(manager_, "Manager must not be null");
+  TORCH_CHECK(features_.dim() == 2, "Features must be 2D");
+  TORCH_CHECK(key_.is_key_set(), "Coordinate map key must be set");
+  TORCH_CHECK(manager_->D() == dimension_, "Coordinate manager dimension does not match coordinate key");
+  TORCH_CHECK(features_.size(0) == manager_->size(key_), "Feature row count must match coordinate map size");
+}
+
+at::Tensor SparseTensor::C() const {
+  if (!coordinates_.has_value()) coordinates_ = manager_->get_coordinates(key_);
+  return coordinates_.value();
+}
+
+SparseTensor SparseTensor::to(c10::ScalarType dtype) const { return SparseTensor(features_.to(dtype), key_, manager_); }
+SparseTensor SparseTensor::detach() const { return SparseTensor(features_.detach(), key_, manager_); }
+
+// ---------------------------------------------------------------------------------------------
+// KernelGenerator (engine/grid/stencil.cpp:81-193)
+// ---------------------------------------------------------------------------------------------
+namespace {
+stride_type to_stride_vector(torch::IntArrayRef v) {
+  stride_type out;
+  for (auto x : v) {
+    TORCH_CHECK(x > 0, "kernel parameters must be positive");
+    out.push_back(static_cast<uint32_t>(x));
+  }
+  return out;
+}
+}  // namespace
+
+KernelGenerator::KernelGenerator(torch::IntArrayRef kernel_size, torch::IntArrayRef stride, torch::IntArrayRef dilation,
+                                 bool is_transpose, RegionType::Type region_type, at::Tensor region_offsets,
+                                 bool expand_coordinates, std::vector<RegionType::Type> axis_types, int dimension)
+    : kernel_size_(to_stride_vector(kernel_size)), kernel_stride_(to_stride_vector(stride)),
+      kernel_dilation_(to_stride_vector(dilation)), is_transpose_(is_transpose), region_type_(region_type),
+      region_offsets_(std::move(region_offsets)), expand_coordinates_(expand_coordinates), D_(dimension),
+      kernel_volume_(0) {
+  if (D_ <= 0) D_ = static_cast<int>(kernel_size_.size());
+  if (kernel_size_.size() == 1 && D_ > 1) kernel_size_.assign(D_, kernel_size_[0]);
+  if (kernel_stride_.size() == 1 && D_ > 1) kernel_stride_.assign(D_, kernel_stride_[0]);
+  if (kernel_dilation_.size() == 1 && D_ > 1) kernel_dilation_.assign(D_, kernel_dilation_[0]);
+  TORCH_CHECK(kernel_size_.size() == static_cast<size_t>(D_), "kernel_size dimension mismatch");
+  TORCH_CHECK(kernel_stride_.size() == static_cast<size_t>(D_), "kernel_stride dimension mismatch");
+  TORCH_CHECK(kernel_dilation_.size() == static_cast<size_t>(D_), "kernel_dilation dimension mismatch");
+  TORCH_CHECK(axis_types.empty(), "axis_types must be empty");
+  if (region_type_ == RegionType::CUSTOM) {
+    TORCH_CHECK(region_offsets_.defined(), "CUSTOM region needs region_offsets");
+    region_offsets_ = region_offsets_.to(at::kCPU, at::kInt).reshape({-1, D_}).contiguous();
+  } else if (region_offsets_.defined()) {
+    TORCH_CHECK(region_offsets_.numel() == 0, "region_offsets must be empty for HYPER_CUBE/HYPER_CROSS");
+  }
+  auto ks = to_i32(kernel_size_);
+  kernel_volume_ = rmn_region_volume(int(region_type_), D_, ks.data(),
+                                     region_type_ == RegionType::CUSTOM ? static_cast<int>(region_offsets_.size(0)) : 0);
+  TORCH_CHECK(kernel_volume_ > 0, "invalid kernel region");
+}
+
+KernelGenerator::KernelParams KernelGenerator::get_kernel(const stride_type& tensor_stride, bool) const {
+  TORCH_CHECK(tensor_stride.size() == static_cast<size_t>(D_), "tensor_stride dimension mismatch");
+  for (auto s : tensor_stride) TORCH_CHECK(s > 0, "tensor_stride must be positive");
+  KernelParams params;
+  params.kernel_size = kernel_size_;
+  params.kernel_stride = kernel_stride_;
+  params.kernel_dilation = kernel_dilation_;
+  params.region_type = region_type_;
+  params.region_offsets = region_offsets_.defined() ? region_offsets_.clone() : at::Tensor{};
+  params.expand_coordinates = expand_coordinates_;
+  params.D = D_;
+  return params;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Convolution with a hand-written backward (the reference differentiates the
+// index_select / matmul / index_add_ chain through torch autograd, engine/nn/conv.cpp:47-64)
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+at::Tensor conv_forward(const at::Tensor& feats_in, const at::Tensor& kernel_in, const at::Tensor& nbr) {
+  TORCH_CHECK(feats_in.is_cuda() && kernel_in.is_cuda(), "features and kernel must be CUDA tensors");
+  TORCH_CHECK(feats_in.scalar_type() == kernel_in.scalar_type(), "expected features and kernel to have the same dtype");
+  auto feats = feats_in.contiguous(), kernel = kernel_in.contiguous();
+  c10::cuda::CUDAGuard guard(feats.device());
+  const int K = static_cast<int>(kernel.size(0)), c_in = static_cast<int>(kernel.size(1)),
+            c_out = static_cast<int>(kernel.size(2));
+  auto out = at::empty({nbr.size(1), c_out}, feats.options());
+  check(rmn_conv_forward(ptr(feats), static_cast<uint32_t>(feats.size(0)), c_in, ptr(kernel), K, c_out,
+                         static_cast<const int32_t*>(ptr(nbr)), static_cast<uint32_t>(nbr.size(1)), ptr(out),
+                         dtype_code(feats), current_stream()),
+        "rmn_conv_forward");
+  return out;
+}
+
+at::Tensor conv_backward_input(const at::Tensor& grad_in, const at::Tensor& kernel_in, const at::Tensor& nbr_t) {
+  auto grad = grad_in.contiguous(), kernel = kernel_in.contiguous();
+  c10::cuda::CUDAGuard guard(grad.device());
+  const int K = static_cast<int>(kernel.size(0)), c_in = static_cast<int>(kernel.size(1)),
+            c_out = static_cast<int>(kernel.size(2));
+  auto out = at::empty({nbr_t.size(1), c_in}, grad.options());
+  check(rmn_conv_backward_input(ptr(grad), static_cast<uint32_t>(grad.size(0)), c_out, ptr(kernel), K, c_in,
+                                static_cast<const int32_t*>(ptr(nbr_t)), static_cast<uint32_t>(nbr_t.size(1)),
+                                ptr(out), dtype_code(grad), current_stream()),
+        "rmn_conv_backward_input");
+  return out;
+}
+
+at::Tensor conv_backward_weight(const at::Tensor& feats_in, const at::Tensor& grad_in, const at::Tensor& nbr) {
+  auto feats = feats_in.contiguous(), grad = grad_in.contiguous();
+  c10::cuda::CUDAGuard guard(feats.device());
+  const int K = static_cast<int>(nbr.size(0)), c_in = static_cast<int>(feats.size(1)),
+            c_out = static_cast<int>(grad.size(1));
+  const uint32_t n_dst = static_cast<uint32_t>(nbr.size(1));
+  const int code = dtype_code(feats);
+  auto dw = at::empty({K, c_in, c_out}, feats.options().dtype(at::kFloat));
+  const size_t ws_bytes = rmn_conv_backward_weight_workspace_bytes(n_dst, K, c_in, c_out, code);
+  auto ws = at::empty({static_cast<int64_t>(ws_bytes ? ws_bytes : 16)}, feats.options().dtype(at::kByte));
+  check(rmn_conv_backward_weight(ptr(feats), static_cast<uint32_t>(feats.size(0)), c_in, ptr(grad), n_dst, c_out,
+                                 static_cast<const int32_t*>(ptr(nbr)), K, static_cast<float*>(ptr(dw)), code,
+                                 ptr(ws), ws_bytes, current_stream()),
+        "rmn_conv_backward_weight");
+  return dw;
+}
+
+struct KernelMapHolder : torch::CustomClassHolder {
+  std::shared_ptr<KernelMap> map;
+};
+
+class SparseConvolutionAutograd : public torch::autograd::Function<SparseConvolutionAutograd> {
+public:
+  static at::Tensor forward(torch::autograd::AutogradContext* ctx, at::Tensor features, at::Tensor kernel,
+                            c10::intrusive_ptr<KernelMapHolder> holder) {
+    ctx->save_for_backward({features, kernel});
+    ctx->saved_data["kmap"] = holder;
+    return conv_forward(features, kernel, holder->map->nbr_out);
+  }
+  static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::variable_list grad_outputs) {
+    auto saved = ctx->get_saved_variables();
+    auto holder = ctx->saved_data["kmap"].toCustomClass<KernelMapHolder>();
+    auto grad = grad_outputs[0].contiguous();
+    at::Tensor g_feat, g_kernel;
+    if (ctx->needs_input_grad(0)) g_feat = conv_backward_input(grad, saved[1], holder->map->nbr_in());
+    if (ctx->needs_input_grad(1))
+      g_kernel = conv_backward_weight(saved[0], grad, holder->map->nbr_out).to(saved[1].scalar_type());
+    return {g_feat, g_kernel, at::Tensor()};
+  }
+};
+
+}  // namespace
+
+at::Tensor sparse_convolution(const at::Tensor& features, const at::Tensor& kernel,
+                              const std::shared_ptr<KernelMap>& kmap) {
+  auto holder = c10::make_intrusive<KernelMapHolder>();
+  holder->map = kmap;
+  return SparseConvolutionAutograd::apply(features, kernel, holder);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Layers (engine/nn/conv.cpp:70-189)
+// ---------------------------------------------------------------------------------------------
+RiemannConvolutionBaseImpl::RiemannConvolutionBaseImpl(int in_channels, int out_channels, int kernel_size, int stride,
+                                                       int dilation, bool bias, bool is_transpose,
+                                                       bool expand_coordinates, ConvolutionMode::Type convolution_mode,
+                                                       int dimension, RegionType::Type region_type)
+    : in_channels_(in_channels), out_channels_(out_channels), is_transpose_(is_transpose), use_mm_(false),
+      dimension_(dimension), convolution_mode_(convolution_mode),
+      kernel_generator_({kernel_size}, {stride}, {dilation}, is_transpose, region_type, {}, expand_coordinates, {},
+                        dimension) {
+  TORCH_CHECK(in_channels > 0 && out_channels > 0, "Convolution channel counts must be positive");
+  const auto volume = kernel_generator_.kernel_volume();
+  kernel_ = register_parameter("kernel", torch::empty({volume, in_channels_, out_channels_}));
+  if (bias) bias_ = register_parameter("bias", torch::empty({1, out_channels_}));
+  reset_parameters(is_transpose);
+}
+
+void RiemannConvolutionBaseImpl::reset() { reset_parameters(is_transpose_); }
+
+void RiemannConvolutionBaseImpl::reset_parameters(bool is_transpose) {
+  torch::NoGradGuard guard;
+  const auto fan = (is_transpose ? out_channels_ : in_channels_) * kernel_generator_.kernel_volume();
+  const auto bound = 1.0 / std::sqrt(static_cast<double>(fan));
+  kernel_.uniform_(-bound, bound);
+  if (bias_.defined()) bias_.uniform_(-bound, bound);
+}
+
+SparseTensor RiemannConvolutionBaseImpl::forward(const SparseTensor& input) {
+  TORCH_CHECK(input.dimension() == dimension_, "Input dimension mismatch");
+  TORCH_CHECK(input.F().size(1) == in_channels_, "Input channel count does not match convolution");
+  const auto params = kernel_generator_.get_kernel(input.tensor_stride(), is_transpose_);
+  const auto input_key = input.coordinate_map_key().get_key();
+  auto output_stride = input_key.first;
+  for (size_t axis = 0; axis < output_stride.size(); ++axis) {
+    const auto step = params.kernel_stride[axis];
+    if (is_transpose_) {
+      TORCH_CHECK(step != 0 && output_stride[axis] % step == 0,
+                  "Transpose convolution stride must divide tensor stride");
+      output_stride[axis] /= step;
+    } else {
+      output_stride[axis] *= step;
+    }
+  }
+  CoordinateMapKey output_key(static_cast<size_type>(input.coordinate_map_key().get_coordinate_size()),
+                              {output_stride, input_key.second});
+  auto manager = input.coordinate_manager();
+  if (!is_transpose_ && params.kernel_stride != stride_type(dimension_, 1))
+    output_key = manager->stride(input.coordinate_map_key(), params.kernel_stride);
+  auto kmap = manager->kernel_map(input.coordinate_map_key(), output_key, params.kernel_size, params.kernel_stride,
+                                  params.kernel_dilation, params.region_type, params.region_offsets, is_transpose_,
+                                  false);
+  auto result = sparse_convolution(input.F(), kernel_, kmap);
+  if (bias_.defined()) result = result + bias_;
+  return SparseTensor(std::move(result), output_key, std::move(manager));
+}
+
+RiemannConvolutionImpl::RiemannConvolutionImpl(int in_channels, int out_channels, int kernel_size, int stride,
+                                               int dilation, bool bias, bool expand_coordinates,
+                                               ConvolutionMode::Type convolution_mode, int dimension) {
+  base_ = std::make_shared<RiemannConvolutionBaseImpl>(in_channels, out_channels, kernel_size, stride, dilation, bias,
+                                                       false, expand_coordinates, convolution_mode, dimension);
+  register_module("base", base_);
+}
+
+RiemannConvolutionTransposeImpl::RiemannConvolutionTransposeImpl(int in_channels, int out_channels, int kernel_size,
+                                                                 int stride, int dilation, bool bias,
+                                                                 bool expand_coordinates,
+                                                                 ConvolutionMode::Type convolution_mode,
+                                                                 int dimension) {
+  base_ = std::make_shared<RiemannConvolutionBaseImpl>(in_channels, out_channels, kernel_size, stride, dilation, bias,
+                                                       true, expand_coordinates, convolution_mode, dimension);
+  register_module("base", base_);
+}
+
+RiemannGenerativeConvolutionTransposeImpl::RiemannGenerativeConvolutionTransposeImpl(
+    int in_channels, int out_channels, int kernel_size, int stride, int dilation, bool bias,
+    ConvolutionMode::Type convolution_mode, int dimension) {
+  base_ = std::make_shared<RiemannConvolutionBaseImpl>(in_channels, out_channels, kernel_size, stride, dilation, bias,
+                                                       true, true, convolution_mode, dimension);
+  register_module("base", base_);
+}
+
+// ---------------------------------------------------------------------------------------------
+// ConvolutionFunction helpers (autodiff/compat.hpp:86-156)
+// ---------------------------------------------------------------------------------------------
+namespace {
+std::vector<int64_t> to_int64(const stride_type& s) { return std::vector<int64_t>(s.begin(), s.end()); }
+
+at::Tensor run_function(bool transpose, at::Tensor input_features, at::Tensor kernel, const stride_type& kernel_size,
+                        const stride_type& kernel_stride, const stride_type& kernel_dilation,
+                        RegionType::Type region_type, at::Tensor region_offsets, bool expand_coordinates,
+                        ConvolutionMode::Type conv_mode, std::shared_ptr<CoordinateMapKey> in_key,
+                        std::shared_ptr<CoordinateMapKey> out_key, std::shared_ptr<CoordinateManager> manager) {
+  TORCH_CHECK(kernel.dim() == 3, "Convolution kernel must have shape [kernel, in, out]");
+  TORCH_CHECK(kernel.size(1) == input_features.size(1), "Convolution kernel input channels do not match features");
+  TORCH_CHECK(in_key && in_key->is_key_set(), "input key must be set");
+  const int dimension = static_cast<int>(in_key->get_coordinate_size()) - 1;
+  SparseTensor input(input_features, *in_key, manager);
+  RiemannConvolutionBaseImpl layer(static_cast<int>(input_features.size(1)), static_cast<int>(kernel.size(2)), 1, 1,
+                                   1, false, transpose, expand_coordinates, conv_mode, dimension, region_type);
+  layer.kernel_generator_ = KernelGenerator(to_int64(kernel_size), to_int64(kernel_stride), to_int64(kernel_dilation),
+                                            transpose, region_type, std::move(region_offsets), expand_coordinates, {},
+                                            dimension);
+  TORCH_CHECK(kernel.size(0) == layer.kernel_generator_.kernel_volume(),
+              "Convolution kernel volume does not match its geometry");
+  layer.kernel_ = std::move(kernel);
+  auto output = layer.forward(input);
+  if (out_key) out_key->set_key(output.coordinate_map_key().get_key());
+  return output.F();
+}
+}  // namespace
+
+at::Tensor ConvolutionFunction::apply(at::Tensor input_features, at::Tensor kernel, stride_type kernel_size,
+                                      stride_type kernel_stride, stride_type kernel_dilation,
+                                      RegionType::Type region_type, at::Tensor region_offsets, bool expand_coordinates,
+                                      ConvolutionMode::Type conv_mode, std::shared_ptr<CoordinateMapKey> in_key,
+                                      std::shared_ptr<CoordinateMapKey> out_key,
+                                      std::shared_ptr<CoordinateManager> manager) {
+  return run_function(false, std::move(input_features), std::move(kernel), kernel_size, kernel_stride, kernel_dilation,
+                      region_type, std::move(region_offsets), expand_coordinates, conv_mode, std::move(in_key),
+                      std::move(out_key), std::move(manager));
+}
+
+at::Tensor ConvolutionTransposeFunction::apply(at::Tensor input_features, at::Tensor kernel, stride_type kernel_size,
+                                               stride_type kernel_stride, stride_type kernel_dilation,
+                                               RegionType::Type region_type, at::Tensor region_offsets,
+                                               bool expand_coordinates, ConvolutionMode::Type conv_mode,
+                                               std::shared_ptr<CoordinateMapKey> in_key,
+                                               std::shared_ptr<CoordinateMapKey> out_key,
+                                               std::shared_ptr<CoordinateManager> manager) {
+  return run_function(true, std::move(input_features), std::move(kernel), kernel_size, kernel_stride, kernel_dilation,
+                      region_type, std::move(region_offsets), expand_coordinates, conv_mode, std::move(in_key),
+                      std::move(out_key), std::move(manager));
+}
+
+}  // namespace riemann

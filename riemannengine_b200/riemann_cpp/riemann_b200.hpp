@@ -1,0 +1,278 @@
+// riemann_cpp (B200): C++20 / LibTorch host layer of the sparse-convolution hot path.
+//
+// Same names, constructor argument order, defaults and exception behaviour as
+// the reference's public classes, so that networks written against the
+// reference compile unchanged:
+//   CoordinateMapKey                 engine/grid/key.hpp:18-99
+//   CoordinateManager                engine/grid/space.hpp:817-906
+//   SparseTensor                     engine/tensor/sparse_tensor.hpp:16-80
+//   KernelGenerator                  engine/grid/stencil.hpp:533-598
+//   RiemannConvolution{,Transpose,GenerativeTranspose} (TORCH_MODULE)
+//                                    engine/nn/conv.hpp:13-90
+//   ConvolutionFunction / ConvolutionTransposeFunction
+//                                    autodiff/compat.hpp:86-156
+// Every coordinate and convolution operation is one or more calls into the C
+// ABI of librmn_b200.so (include/rmn_b200.h) on the current CUDA stream; there
+// is no CPU backend.
+#pragma once
+
+#include <torch/torch.h>
+
+#include <map>
+#include <memory>
+#include <string>
+#include <tuple>
+#include <utility>
+#include <vector>
+
+namespace riemann {
+
+using stride_type = std::vector<uint32_t>;
+using size_type = uint32_t;
+using coordinate_map_key_type = std::pair<stride_type, std::string>;
+
+namespace SparseTensorQuantizationMode {
+enum Type { RANDOM_SUBSAMPLE = 0, UNWEIGHTED_AVERAGE = 1, UNWEIGHTED_SUM = 2, MAX_POOL = 3, NO_QUANTIZATION = 4 };
+}
+namespace GPUMemoryAllocatorBackend {
+enum Type { PYTORCH = 0, CUDA = 1 };
+}
+namespace RiemannAlgorithm {
+enum Mode { DEFAULT = 0, MEMORY_EFFICIENT = 1, SPEED_OPTIMIZED = 2 };
+}
+namespace CoordinateMapBackend {
+enum Type { CPU = 0, CUDA = 1 };
+}
+namespace RegionType {
+enum Type { HYPER_CUBE, HYPER_CROSS, CUSTOM };
+}
+namespace ConvolutionMode {
+enum Type { DEFAULT, DIRECT_GEMM, COPY_GEMM };
+}
+
+class CoordinateMapKey {
+public:
+  CoordinateMapKey() = delete;
+  explicit CoordinateMapKey(size_type coordinate_size) : m_key_set(false), m_coordinate_size(coordinate_size) {}
+  CoordinateMapKey(size_type coordinate_size, coordinate_map_key_type const& key);
+  CoordinateMapKey(stride_type tensor_stride, std::string string_id = "");
+
+  size_type get_coordinate_size() const { return m_coordinate_size; }
+  void set_key(stride_type tensor_stride, std::string string_id);
+  void set_key(coordinate_map_key_type const& key);
+  coordinate_map_key_type get_key() const;
+  uint64_t hash() const;
+  bool is_key_set() const noexcept { return m_key_set; }
+  stride_type get_tensor_stride() const { return m_key.first; }
+  bool operator==(CoordinateMapKey const& key) const;
+  std::string to_string() const;
+
+private:
+  bool m_key_set;
+  size_type m_coordinate_size;
+  coordinate_map_key_type m_key;
+};
+
+// One cached kernel map. nbr_out [K, N_out] holds the input row (or -1) of every (offset,
+// output row); nbr_in [K, N_in] is its inverse, built on first use. The pair lists are the
+// reference's representation (engine/grid/maps.hpp:19-79).
+struct KernelMap {
+  at::Tensor nbr_out;
+  int64_t n_in = 0, n_out = 0;
+  at::Tensor offset_ptr;  // int64 [K+1] device, of the probe that produced nbr_out (undefined on a swapped view)
+  at::Tensor workspace;
+  std::shared_ptr<KernelMap> parent;  // set on a swapped view
+
+  at::Tensor const& nbr_in();
+  // (offset_ptr on the host, in rows, out rows)
+  std::tuple<at::Tensor, at::Tensor, at::Tensor> const& pairs();
+  std::shared_ptr<KernelMap> swapped(std::shared_ptr<KernelMap> const& self);
+
+private:
+  at::Tensor nbr_in_;
+  bool have_pairs_ = false;
+  std::tuple<at::Tensor, at::Tensor, at::Tensor> pairs_;
+};
+
+class CoordinateManager {
+public:
+  CoordinateManager(int D, CoordinateMapBackend::Type map_type = CoordinateMapBackend::CUDA,
+                    GPUMemoryAllocatorBackend::Type alloc_type = GPUMemoryAllocatorBackend::PYTORCH,
+                    RiemannAlgorithm::Mode algo = RiemannAlgorithm::DEFAULT);
+
+  std::pair<CoordinateMapKey, std::pair<at::Tensor, at::Tensor>>
+  insert_and_map(const at::Tensor& coordinates, stride_type tensor_stride, std::string string_id = "");
+
+  CoordinateMapKey stride(const CoordinateMapKey& in_key, const stride_type& kernel_stride,
+                          std::string string_id = "");
+
+  at::Tensor get_coordinates(const CoordinateMapKey& key) const;
+  uint32_t size(const CoordinateMapKey& key) const;
+  bool exists(const CoordinateMapKey& key) const;
+
+  // Cached kernel map (engine/grid/space_impl.hpp:499-706).
+  std::shared_ptr<KernelMap> kernel_map(const CoordinateMapKey& in_key, const CoordinateMapKey& out_key,
+                                        const stride_type& kernel_size, const stride_type& kernel_stride,
+                                        const stride_type& kernel_dilation, RegionType::Type region_type,
+                                        const at::Tensor& offsets, bool is_transpose, bool is_pool);
+  // {offset index -> int32 [2, P_k]} (engine/grid/space.cpp:202-228)
+  std::map<int64_t, at::Tensor> kernel_map_th(const CoordinateMapKey& in_key, const CoordinateMapKey& out_key,
+                                              const stride_type& kernel_size, const stride_type& kernel_stride,
+                                              const stride_type& kernel_dilation, RegionType::Type region_type,
+                                              const at::Tensor& offsets, bool is_transpose, bool is_pool);
+
+  int D() const { return D_; }
+  CoordinateMapBackend::Type backend() const { return map_type_; }
+
+private:
+  struct Map {
+    at::Tensor table;   // uint8, device
+    at::Tensor coords;  // int32 [n, W]
+    stride_type tensor_stride;
+    uint32_t size = 0;
+  };
+  Map const& find(const CoordinateMapKey& key, const char* what = "") const;
+  Map build(const at::Tensor& coords, const stride_type& tensor_stride, at::Tensor* mapping, at::Tensor* inverse);
+
+  int D_;
+  CoordinateMapBackend::Type map_type_;
+  std::map<coordinate_map_key_type, Map> maps_;
+  std::map<std::string, std::shared_ptr<KernelMap>> kernel_maps_;
+};
+
+class SparseTensor {
+public:
+  SparseTensor(at::Tensor features, at::Tensor coordinates, std::shared_ptr<CoordinateManager> manager = nullptr,
+               SparseTensorQuantizationMode::Type quantization_mode = SparseTensorQuantizationMode::RANDOM_SUBSAMPLE,
+               GPUMemoryAllocatorBackend::Type alloc_type = GPUMemoryAllocatorBackend::PYTORCH,
+               RiemannAlgorithm::Mode algo = RiemannAlgorithm::DEFAULT);
+  SparseTensor(at::Tensor features, CoordinateMapKey coordinate_map_key, std::shared_ptr<CoordinateManager> manager);
+
+  const at::Tensor& F() const noexcept { return features_; }
+  at::Tensor C() const;
+  const CoordinateMapKey& coordinate_map_key() const noexcept { return key_; }
+  std::shared_ptr<CoordinateManager> coordinate_manager() const noexcept { return manager_; }
+  stride_type tensor_stride() const { return key_.get_tensor_stride(); }
+  int dimension() const noexcept { return dimension_; }
+  torch::Device device() const { return features_.device(); }
+  c10::ScalarType dtype() const { return features_.scalar_type(); }
+  bool requires_grad() const { return features_.requires_grad(); }
+  SparseTensor to(c10::ScalarType dtype) const;
+  SparseTensor detach() const;
+
+private:
+  at::Tensor features_;
+  mutable c10::optional<at::Tensor> coordinates_;
+  CoordinateMapKey key_;
+  std::shared_ptr<CoordinateManager> manager_;
+  int dimension_;
+};
+
+class KernelGenerator {
+public:
+  struct KernelParams {
+    stride_type kernel_size, kernel_stride, kernel_dilation;
+    RegionType::Type region_type;
+    at::Tensor region_offsets;
+    bool expand_coordinates;
+    int D;
+  };
+  KernelGenerator(torch::IntArrayRef kernel_size, torch::IntArrayRef stride = {1}, torch::IntArrayRef dilation = {1},
+                  bool is_transpose = false, RegionType::Type region_type = RegionType::HYPER_CUBE,
+                  at::Tensor region_offsets = {}, bool expand_coordinates = false,
+                  std::vector<RegionType::Type> axis_types = {}, int dimension = -1);
+  int kernel_volume() const { return kernel_volume_; }
+  const stride_type& kernel_size() const { return kernel_size_; }
+  const stride_type& kernel_stride() const { return kernel_stride_; }
+  const stride_type& kernel_dilation() const { return kernel_dilation_; }
+  RegionType::Type region_type() const { return region_type_; }
+  bool expand_coordinates() const { return expand_coordinates_; }
+  int dimension() const { return D_; }
+  KernelParams get_kernel(const stride_type& tensor_stride, bool is_transpose) const;
+
+private:
+  stride_type kernel_size_, kernel_stride_, kernel_dilation_;
+  bool is_transpose_;
+  RegionType::Type region_type_;
+  at::Tensor region_offsets_;
+  bool expand_coordinates_;
+  int D_;
+  int kernel_volume_;
+};
+
+// out = sum_k F[in_k] @ W[k] scattered to out_k, with a hand-written backward.
+at::Tensor sparse_convolution(const at::Tensor& features, const at::Tensor& kernel,
+                              const std::shared_ptr<KernelMap>& kmap);
+
+// Helpers with the reference's argument list (autodiff/compat.hpp:89-96, 125-132): run one
+// (transposed) convolution over explicit keys and write the resulting key into *out_key.
+struct ConvolutionFunction {
+  static at::Tensor apply(at::Tensor input_features, at::Tensor kernel, stride_type kernel_size,
+                          stride_type kernel_stride, stride_type kernel_dilation, RegionType::Type region_type,
+                          at::Tensor region_offsets, bool expand_coordinates, ConvolutionMode::Type conv_mode,
+                          std::shared_ptr<CoordinateMapKey> in_key, std::shared_ptr<CoordinateMapKey> out_key,
+                          std::shared_ptr<CoordinateManager> manager);
+};
+struct ConvolutionTransposeFunction {
+  static at::Tensor apply(at::Tensor input_features, at::Tensor kernel, stride_type kernel_size,
+                          stride_type kernel_stride, stride_type kernel_dilation, RegionType::Type region_type,
+                          at::Tensor region_offsets, bool expand_coordinates, ConvolutionMode::Type conv_mode,
+                          std::shared_ptr<CoordinateMapKey> in_key, std::shared_ptr<CoordinateMapKey> out_key,
+                          std::shared_ptr<CoordinateManager> manager);
+};
+
+class RiemannConvolutionBaseImpl : public torch::nn::Cloneable<RiemannConvolutionBaseImpl> {
+public:
+  RiemannConvolutionBaseImpl(int in_channels, int out_channels, int kernel_size = 3, int stride = 1,
+                             int dilation = 1, bool bias = false, bool is_transpose = false,
+                             bool expand_coordinates = false,
+                             ConvolutionMode::Type convolution_mode = ConvolutionMode::DEFAULT, int dimension = 3,
+                             RegionType::Type region_type = RegionType::HYPER_CUBE);
+  void reset() override;
+  void reset_parameters(bool is_transpose = false);
+  SparseTensor forward(const SparseTensor& input);
+
+  int in_channels_, out_channels_;
+  bool is_transpose_, use_mm_;
+  int dimension_;
+  ConvolutionMode::Type convolution_mode_;
+  KernelGenerator kernel_generator_;
+  torch::Tensor kernel_{nullptr};
+  torch::Tensor bias_{nullptr};
+};
+
+#define RIEMANN_B200_CONV_WRAPPER(Name)                                                                   \
+  class Name##Impl : public torch::nn::Cloneable<Name##Impl> {                                            \
+  public:                                                                                                 \
+    Name##Impl(int in_channels, int out_channels, int kernel_size = 3, int stride = 1, int dilation = 1,  \
+               bool bias = false, bool expand_coordinates = false,                                        \
+               ConvolutionMode::Type convolution_mode = ConvolutionMode::DEFAULT, int dimension = 3);     \
+    void reset() override { base_->reset(); }                                                             \
+    SparseTensor forward(const SparseTensor& input) { return base_->forward(input); }                     \
+    std::shared_ptr<RiemannConvolutionBaseImpl> base() { return base_; }                                  \
+                                                                                                          \
+  private:                                                                                                \
+    std::shared_ptr<RiemannConvolutionBaseImpl> base_{nullptr};                                           \
+  };                                                                                                      \
+  TORCH_MODULE(Name)
+
+RIEMANN_B200_CONV_WRAPPER(RiemannConvolution);
+RIEMANN_B200_CONV_WRAPPER(RiemannConvolutionTranspose);
+
+class RiemannGenerativeConvolutionTransposeImpl
+    : public torch::nn::Cloneable<RiemannGenerativeConvolutionTransposeImpl> {
+public:
+  RiemannGenerativeConvolutionTransposeImpl(int in_channels, int out_channels, int kernel_size = 3, int stride = 1,
+                                            int dilation = 1, bool bias = false,
+                                            ConvolutionMode::Type convolution_mode = ConvolutionMode::DEFAULT,
+                                            int dimension = 3);
+  void reset() override { base_->reset(); }
+  SparseTensor forward(const SparseTensor& input) { return base_->forward(input); }
+  std::shared_ptr<RiemannConvolutionBaseImpl> base() { return base_; }
+
+private:
+  std::shared_ptr<RiemannConvolutionBaseImpl> base_{nullptr};
+};
+TORCH_MODULE(RiemannGenerativeConvolutionTranspose);
+
+}  // namespace riemann
