@@ -79,3 +79,59 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
 
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv))
+
+
+# ------------------------------------------------------------------------------------------
+# C++20 / LibTorch host layer (riemann_cpp) + its pybind11 module
+# ------------------------------------------------------------------------------------------
+HOST_DIR = os.path.join(PKG, "riemann_cpp")
+HOST_LIB = os.path.join(LIB_DIR, "_C.so")
+
+
+def build_host_extension(force: bool = False, verbose: bool = False) -> str:
+    """Compile ``riemann_cpp/*.cpp`` with g++ against LibTorch and link them to librmn_b200.so."""
+    import sysconfig
+
+    import torch
+
+    build_library()
+    srcs = sorted(os.path.join(HOST_DIR, f) for f in os.listdir(HOST_DIR) if f.endswith(".cpp"))
+    deps = srcs + [os.path.join(HOST_DIR, f) for f in os.listdir(HOST_DIR) if f.endswith(".hpp")]
+    deps.append(os.path.join(INCLUDE, "rmn_b200.h"))
+    if not force and os.path.exists(HOST_LIB) and os.path.getmtime(HOST_LIB) >= max(os.path.getmtime(f) for f in deps):
+        return HOST_LIB
+    tdir = os.path.dirname(torch.__file__)
+    cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(_nvcc())), "include")
+    flags = ["-std=c++20", "-O2", "-fPIC", "-w", "-DTORCH_EXTENSION_NAME=_C",
+             f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+             "-I" + INCLUDE, "-I" + HOST_DIR, "-isystem", os.path.join(tdir, "include"),
+             "-isystem", os.path.join(tdir, "include", "torch", "csrc", "api", "include"),
+             "-isystem", sysconfig.get_paths()["include"], "-isystem", cuda_inc]
+    os.makedirs(OBJ_DIR, exist_ok=True)
+
+    def compile_one(src: str) -> str:
+        obj = os.path.join(OBJ_DIR, "host_" + os.path.basename(src)[:-4] + ".o")
+        newest = max(os.path.getmtime(f) for f in deps if not f.endswith(".cpp"))
+        if not force and os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src), newest):
+            return obj
+        cmd = [cxx] + flags + ["-c", src, "-o", obj]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if verbose or res.returncode != 0:
+            sys.stderr.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
+        if res.returncode != 0:
+            raise RuntimeError(f"g++ failed on {src}")
+        return obj
+
+    with ThreadPoolExecutor(max_workers=len(srcs)) as ex:
+        objs = list(ex.map(compile_one, srcs))
+    tmp = HOST_LIB + f".tmp{os.getpid()}"
+    cmd = [cxx, "-shared", "-o", tmp] + objs + [
+        "-L" + os.path.join(tdir, "lib"), "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
+        "-ltorch_python", "-L" + LIB_DIR, "-lrmn_b200", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(tdir, "lib")]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(" ".join(cmd) + "\n" + res.stdout + res.stderr)
+        raise RuntimeError("host extension link failed")
+    os.replace(tmp, HOST_LIB)
+    return HOST_LIB

@@ -6,23 +6,26 @@
 //   forward         out[j] = sum_k F[nbr[k][j]]    . W[k]      B = W[k]   read MN-major
 //   backward input  dF[i]  = sum_k dY[nbr_t[k][i]] . W[k]^T    B = W[k]   read K-major
 //
-// One persistent CTA per SM slot loops over tiles of 128 destination rows.
-// Warp roles (288 threads):
-//   warps 0-3  producers: for every offset k gather the 128 source rows named
-//              by nbr[k][tile] (16-byte cp.async, zero-fill for -1) and copy
-//              W[k] into a ring of shared-memory stages;
-//   warp  4    issues tcgen05.mma for each stage (one elected lane), commits
-//              the stage back to the producers and the finished accumulator to
-//              the epilogue;
-//   warps 5-8  epilogue: tcgen05.ld the fp32 accumulator (double-buffered in
-//              TMEM so it overlaps the next tile's MMAs), convert to bf16,
-//              store.
+// One persistent CTA per SM loops over super-tiles of T x 128 destination rows
+// (T = 2 where TMEM allows) so that one copy of W[k] in shared memory serves
+// T row tiles. Warp roles (416 threads):
+//   warps 0-7   producers: for every offset k (and 64-channel block of the
+//               reduction) gather the source rows named by nbr[k][super-tile]
+//               (16-byte cp.async, zero-fill for -1) and copy the W[k] slice
+//               into a ring of shared-memory stages;
+//   warp  8     issues tcgen05.mma for each stage (one lane), commits the stage
+//               back to the producers and the finished accumulators to the
+//               epilogue;
+//   warps 9-12  epilogue: tcgen05.ld the fp32 accumulators (double-buffered in
+//               TMEM, so it overlaps the next super-tile's MMAs), convert to
+//               bf16, store.
 //
-// Shared-memory operand image (no swizzle, "core matrices" of 8 x 16 bytes):
-//   A  [chunk c = channel/8][row r]      : c * 2048 + r * 16            (K-major)
-//   B  [ci / 8][c8 = co/8][ci % 8]       : (ci/8) * (C8*128) + c8*128 + (ci%8)*16
-// The same B image is read MN-major (reduction over ci, forward) or K-major
-// (reduction over co, backward input) by choosing the descriptor strides.
+// Shared-memory operand images are the swizzled canonical layouts: a line of
+// 128 bytes (64 bf16; 64 bytes when only 32 channels) per matrix row, 16-byte
+// chunk c of row r stored at chunk position c ^ (r % 8) (64-byte lines:
+// c ^ ((r / 2) % 4)). Eight consecutive lanes copy the eight chunks of ONE
+// source row: the global read is a whole 128-byte line and the shared-memory
+// write is conflict-free.
 //
 // Every mbarrier wait is bounded: after ~2 s without progress a role records
 // RMN_ERR_TIMEOUT in a device status word and leaves; all roles then meet at
@@ -39,36 +42,56 @@ __device__ uint32_t g_tc_status = 0;
 namespace tc {
 
 constexpr int kTileM = 128;
-constexpr int kThreads = 288;
+constexpr int kFwdProducerWarps = 8;
+constexpr int kFwdProducers = kFwdProducerWarps * 32;
+constexpr int kFwdThreads = kFwdProducers + 32 + 128;
+
+// chunk position of 16-byte chunk c in row r of a swizzled image with SW-byte lines
+template <int SW>
+__device__ __forceinline__ uint32_t swz(uint32_t r, uint32_t c) {
+  if constexpr (SW == 128) return c ^ (r & 7u);
+  else return c ^ ((r >> 1) & 3u);
+}
 
 template <int CR, int CC>
 struct Cfg {
   static constexpr int KB = CR < 64 ? CR : 64;  // reduction channels per pipeline stage
   static constexpr int NKB = CR / KB;
-  static constexpr uint32_t A_BYTES = kTileM * KB * 2;
+  static constexpr int T = CC <= 128 ? 2 : 1;   // row tiles sharing one W[k] stage
+  static constexpr int SWA = KB * 2;            // bytes per A line
+  static constexpr uint32_t A_TILE = kTileM * SWA;
+  static constexpr uint32_t A_BYTES = T * A_TILE;
   static constexpr uint32_t B_BYTES = KB * CC * 2;
   static constexpr uint32_t STAGE = A_BYTES + B_BYTES;
-  static constexpr int STAGES = 4;
+  static constexpr int STAGES = STAGE * 5 <= 200 * 1024 ? 5 : 4;
+  static constexpr int LAG = STAGES - 2;        // cp.async groups in flight per producer thread
   static constexpr uint32_t BAR_OFFSET = STAGES * STAGE;
   static constexpr uint32_t SMEM = BAR_OFFSET + 256;
-  static constexpr uint32_t TMEM_COLS = pow2_at_least(2 * CC);
+  static constexpr uint32_t TMEM_COLS = pow2_at_least(2 * T * CC);
 };
 
 // CR: reduction channels per offset; CC: output channels; kWT: weights are read transposed
 // (backward input). Weight tensor is [K][CIN_w][COUT_w] with (CIN_w, COUT_w) = kWT ? (CC, CR) : (CR, CC).
 template <int CR, int CC, bool kWT>
-__global__ void __launch_bounds__(kThreads, 1) k_conv_tc(const __nv_bfloat16* __restrict__ src,
-                                                         const __nv_bfloat16* __restrict__ w,
-                                                         const int32_t* __restrict__ nbr,
-                                                         uint32_t n_dst, int K,
-                                                         __nv_bfloat16* __restrict__ out,
-                                                         uint32_t n_tiles) {
+__global__ void __launch_bounds__(kFwdThreads, 1) k_conv_tc(const __nv_bfloat16* __restrict__ src,
+                                                            const __nv_bfloat16* __restrict__ w,
+                                                            const int32_t* __restrict__ nbr,
+                                                            uint32_t n_dst, int K,
+                                                            __nv_bfloat16* __restrict__ out,
+                                                            uint32_t n_super) {
   using C = Cfg<CR, CC>;
-  constexpr int STAGES = C::STAGES, KB = C::KB, NKB = C::NKB;
+  constexpr int STAGES = C::STAGES, KB = C::KB, NKB = C::NKB, T = C::T, LAG = C::LAG, SWA = C::SWA;
   constexpr int CIN_W = kWT ? CC : CR, COUT_W = kWT ? CR : CC;
-  // weight image of one stage: B_ROWS rows of B_C8 16-byte chunks
-  constexpr int B_ROWS = kWT ? CC : KB, B_C8 = (kWT ? KB : CC) / 8;
-  constexpr uint32_t W_ROWGROUP = B_C8 * 128;  // bytes of 8 weight rows in the image
+  // Weight image of one stage: lines of SWB bytes.
+  //   forward (MN-major): one line per reduction row ci (KB lines) and 64-column atom;
+  //   backward input (K-major): one line per output row ci (CC lines) holding the KB reduction channels.
+  constexpr int SWB = kWT ? KB * 2 : (CC < 64 ? CC : 64) * 2;
+  constexpr int B_LINES = kWT ? CC : KB;
+  constexpr int B_ATOMS = kWT ? 1 : (CC * 2) / SWB;
+  constexpr int B_CPL = SWB / 16;                   // chunks per line
+  constexpr uint32_t B_ATOM_BYTES = B_LINES * SWB;  // forward: distance between 64-column atoms
+  constexpr int A_CPL = SWA / 16;
+  constexpr uint32_t LT_A = SWA == 128 ? 2u : 4u, LT_B = SWB == 128 ? 2u : 4u;
   static_assert(CR % 32 == 0 && CC % 32 == 0 && CC <= 256 && CR % KB == 0, "channel counts");
 
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -82,7 +105,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_conv_tc(const __nv_bfloat16* __
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], kProducerThreads);
+      mbar_init(&full[s], kFwdProducers);
       mbar_init(&empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -92,7 +115,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_conv_tc(const __nv_bfloat16* __
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
   }
-  if (warp == 4) {
+  if (warp == kFwdProducerWarps) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(C::TMEM_COLS)
@@ -106,50 +129,55 @@ __global__ void __launch_bounds__(kThreads, 1) k_conv_tc(const __nv_bfloat16* __
   const uint32_t smem_base = smem_u32(smem);
   bool timed_out = false;
 
-  if (warp < 4) {
+  if (warp < kFwdProducerWarps) {
     // ------------------------------ producers ------------------------------------------
+    // warp w owns rows [32w, 32w + 32) of the (T * 128)-row super-tile; warps beyond T * 4 only copy weights
+    const bool has_rows = warp < T * 4;
+    const uint32_t a_tile_off = (uint32_t)(warp >> 2) * C::A_TILE;
+    const uint32_t row_in_tile0 = (uint32_t)(warp & 3) * 32;
+    constexpr int ROWS_PER_INSTR = 32 / A_CPL;
+    const uint32_t a_chunk = lane % A_CPL, a_row_sub = lane / A_CPL;
     uint32_t it = 0;
-    for (uint32_t tile = blockIdx.x; tile < n_tiles && !timed_out; tile += gridDim.x) {
-      const uint32_t row = tile * kTileM + warp * 32 + lane;
-      int32_t idx_next = row < n_dst ? __ldg(nbr + row) : -1;
+    for (uint32_t st = blockIdx.x; st < n_super && !timed_out; st += gridDim.x) {
+      const uint32_t row = st * (kTileM * T) + warp * 32 + lane;
+      const bool row_ok = has_rows && row < n_dst;
+      int32_t idx_next = row_ok ? __ldg(nbr + row) : -1;
       for (int k = 0; k < K && !timed_out; ++k) {
         const int32_t idx = idx_next;
-        if (k + 1 < K) idx_next = row < n_dst ? __ldg(nbr + (size_t)(k + 1) * n_dst + row) : -1;
+        if (k + 1 < K) idx_next = row_ok ? __ldg(nbr + (size_t)(k + 1) * n_dst + row) : -1;
         const __nv_bfloat16* wk = w + (size_t)k * CIN_W * COUT_W;
 #pragma unroll 1
         for (int kb = 0; kb < NKB; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
           if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
           const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
-          // A: 8 rows x 4 chunks per warp instruction (64 contiguous bytes per source row;
-          // each quarter-warp writes 8 distinct rows of one chunk -> conflict-free)
+          if (has_rows) {
+            // A: a quarter-warp copies the whole line of one gathered row
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int r_local = g * 8 + (lane & 7);
-            const int32_t sidx = __shfl_sync(0xFFFFFFFFu, idx, r_local);
-            const __nv_bfloat16* base = src + (size_t)(sidx < 0 ? 0 : sidx) * CR + kb * KB;
-            const uint32_t bytes = sidx < 0 ? 0u : 16u;
-#pragma unroll
-            for (int cq = 0; cq < KB / 32; ++cq) {
-              const int chunk = cq * 4 + (lane >> 3);
-              cp_async16(a_s + chunk * (kTileM * 16) + (warp * 32 + r_local) * 16, base + chunk * 8, bytes);
+            for (int g = 0; g < 32 / ROWS_PER_INSTR; ++g) {
+              const uint32_t r_local = g * ROWS_PER_INSTR + a_row_sub;
+              const int32_t sidx = __shfl_sync(0xFFFFFFFFu, idx, r_local);
+              const uint32_t r = row_in_tile0 + r_local;
+              cp_async16(a_s + a_tile_off + r * SWA + (swz<SWA>(r, a_chunk) << 4),
+                         src + (size_t)(sidx < 0 ? 0 : sidx) * CR + kb * KB + a_chunk * 8, sidx < 0 ? 0u : 16u);
             }
+          } else {
+            __syncwarp();
           }
-          // B: this stage's slice of W[k]
+          // B: this stage's slice of W[k], one line (and atom) per B_CPL consecutive threads
 #pragma unroll
-          for (int i = 0; i < (B_ROWS * B_C8) / kProducerThreads; ++i) {
-            const int u = i * 4 + warp;  // one (8-row group, 4-chunk group) per warp instruction
-            const int c8 = (u % (B_C8 / 4)) * 4 + (lane >> 3);
-            const int r = (u / (B_C8 / 4)) * 8 + (lane & 7);
-            const __nv_bfloat16* g = kWT ? wk + (size_t)r * COUT_W + kb * KB + c8 * 8
-                                         : wk + (size_t)(kb * KB + r) * COUT_W + c8 * 8;
-            cp_async16(b_s + (r >> 3) * W_ROWGROUP + c8 * 128 + (r & 7) * 16, g, 16u);
+          for (int q = tid; q < B_LINES * B_ATOMS * B_CPL; q += kFwdProducers) {
+            const uint32_t c = q % B_CPL, unit = q / B_CPL;
+            const uint32_t line = unit % B_LINES, atom = unit / B_LINES;
+            const __nv_bfloat16* g = kWT ? wk + (size_t)line * COUT_W + kb * KB + c * 8
+                                         : wk + (size_t)(kb * KB + line) * COUT_W + atom * (SWB / 2) + c * 8;
+            cp_async16(b_s + atom * B_ATOM_BYTES + line * SWB + (swz<SWB>(line, c) << 4), g, 16u);
           }
           cp_async_commit();
-          if (it >= (uint32_t)kLag) {
-            cp_async_wait<kLag>();
+          if (it >= (uint32_t)LAG) {
+            cp_async_wait<LAG>();
             fence_proxy_async();
-            mbar_arrive(&full[(it - kLag) % STAGES]);
+            mbar_arrive(&full[(it - LAG) % STAGES]);
           }
         }
       }
@@ -158,35 +186,38 @@ __global__ void __launch_bounds__(kThreads, 1) k_conv_tc(const __nv_bfloat16* __
     cp_async_wait<0>();
     fence_proxy_async();
     if (!timed_out) {
-      const uint32_t pending = it < (uint32_t)kLag ? it : (uint32_t)kLag;
+      const uint32_t pending = it < (uint32_t)LAG ? it : (uint32_t)LAG;
       for (uint32_t j = it - pending; j < it; ++j) mbar_arrive(&full[j % STAGES]);
     }
-  } else if (warp == 4) {
+  } else if (warp == kFwdProducerWarps) {
     // ------------------------------ MMA issuer -----------------------------------------
     constexpr uint32_t IDESC = instr_desc(kTileM, CC, !kWT);
     uint32_t it = 0, tile_iter = 0;
-    for (uint32_t tile = blockIdx.x; tile < n_tiles && !timed_out; tile += gridDim.x, ++tile_iter) {
+    for (uint32_t st = blockIdx.x; st < n_super && !timed_out; st += gridDim.x, ++tile_iter) {
       const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
       if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { timed_out = true; break; }
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * CC;
+      const uint32_t d_tmem = tmem_base + acc * (T * CC);
       const uint32_t n_stage = (uint32_t)K * NKB;
-      for (uint32_t st = 0; st < n_stage; ++st, ++it) {
+      for (uint32_t sg = 0; sg < n_stage; ++sg, ++it) {
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
         if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
         tc_fence_after();
         if (lane == 0) {
           const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
 #pragma unroll
-          for (int j = 0; j < KB / 16; ++j) {
-            // A, K-major: row groups 128 B apart (SBO), the two 8-channel chunks 2048 B apart (LBO)
-            const uint64_t a_desc = smem_desc(a_s + j * 2 * (kTileM * 16), kTileM * 16, 128);
-            uint64_t b_desc;
-            if constexpr (!kWT)  // MN-major: column groups 128 B apart (SBO), 8-row groups W_ROWGROUP apart (LBO)
-              b_desc = smem_desc(b_s + j * 2 * W_ROWGROUP, W_ROWGROUP, 128);
-            else                 // K-major: N groups (weight rows) W_ROWGROUP apart (SBO), K chunks 128 B apart (LBO)
-              b_desc = smem_desc(b_s + j * 2 * 128, 128, W_ROWGROUP);
-            tc_mma_bf16(d_tmem, a_desc, b_desc, IDESC, (st | (uint32_t)j) != 0 ? 1u : 0u);
+          for (int t = 0; t < T; ++t) {
+#pragma unroll
+            for (int j = 0; j < KB / 16; ++j) {
+              // A, K-major swizzled: 8-row groups 8 * SWA apart (SBO); a K step of 16 channels is 32 bytes
+              const uint64_t a_desc = smem_desc_sw(a_s + t * C::A_TILE + j * 32, 16, 8 * SWA, LT_A);
+              uint64_t b_desc;
+              if constexpr (!kWT)  // MN-major: 8-row K groups 8 * SWB apart (SBO), 64-column atoms B_ATOM_BYTES apart (LBO)
+                b_desc = smem_desc_sw(b_s + j * 16 * SWB, B_ATOM_BYTES, 8 * SWB, LT_B);
+              else                 // K-major: 8-row N groups 8 * SWB apart (SBO), K step 32 bytes
+                b_desc = smem_desc_sw(b_s + j * 32, 16, 8 * SWB, LT_B);
+              tc_mma_bf16(d_tmem + t * CC, a_desc, b_desc, IDESC, (sg | (uint32_t)j) != 0 ? 1u : 0u);
+            }
           }
           tc_commit(&empty[s]);
         }
@@ -200,30 +231,33 @@ __global__ void __launch_bounds__(kThreads, 1) k_conv_tc(const __nv_bfloat16* __
     // ------------------------------ epilogue -------------------------------------------
     const uint32_t quad = warp & 3;  // TMEM lanes [32*quad, 32*quad + 32)
     uint32_t tile_iter = 0;
-    for (uint32_t tile = blockIdx.x; tile < n_tiles && !timed_out; tile += gridDim.x, ++tile_iter) {
+    for (uint32_t st = blockIdx.x; st < n_super && !timed_out; st += gridDim.x, ++tile_iter) {
       const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
       if (!mbar_wait(&tmem_full[acc], acc_ph)) { timed_out = true; break; }
       tc_fence_after();
-      const uint32_t row = tile * kTileM + quad * 32 + lane;
 #pragma unroll
-      for (int c0 = 0; c0 < CC; c0 += 32) {
-        uint32_t r[32];
-        tc_ld32(tmem_base + ((quad * 32u) << 16) + acc * CC + c0, r);
-        tc_wait_ld();
-        if (row < n_dst) {
-          uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * CC + c0);
+      for (int t = 0; t < T; ++t) {
+        const uint32_t row = st * (kTileM * T) + t * kTileM + quad * 32 + lane;
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 o;
-            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-            o.x = *reinterpret_cast<uint32_t*>(&p0);
-            o.y = *reinterpret_cast<uint32_t*>(&p1);
-            o.z = *reinterpret_cast<uint32_t*>(&p2);
-            o.w = *reinterpret_cast<uint32_t*>(&p3);
-            dst[v] = o;
+        for (int c0 = 0; c0 < CC; c0 += 32) {
+          uint32_t r[32];
+          tc_ld32(tmem_base + ((quad * 32u) << 16) + acc * (T * CC) + t * CC + c0, r);
+          tc_wait_ld();
+          if (row < n_dst) {
+            uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * CC + c0);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+              __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              o.x = *reinterpret_cast<uint32_t*>(&p0);
+              o.y = *reinterpret_cast<uint32_t*>(&p1);
+              o.z = *reinterpret_cast<uint32_t*>(&p2);
+              o.w = *reinterpret_cast<uint32_t*>(&p3);
+              dst[v] = o;
+            }
           }
         }
       }
@@ -235,7 +269,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_conv_tc(const __nv_bfloat16* __
   if (timed_out) atomicExch(&g_tc_status, (uint32_t)RMN_ERR_TIMEOUT);
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kFwdProducerWarps) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS)
                  : "memory");
@@ -256,12 +290,14 @@ int launch(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, i
   }
   int sms = 148;
   RMN_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const uint32_t n_tiles = (n_dst + kTileM - 1) / kTileM;
+  const uint32_t rows_per_super = kTileM * C::T;
+  const uint32_t n_super = (n_dst + rows_per_super - 1) / rows_per_super;
+  // one CTA per SM unless two fit (shared memory and TMEM columns)
   const uint32_t per_sm = (C::SMEM <= 110 * 1024 && C::TMEM_COLS <= 256) ? 2u : 1u;
   uint32_t grid = (uint32_t)sms * per_sm;
-  if (grid > n_tiles) grid = n_tiles;
-  kern<<<grid, kThreads, C::SMEM, stream>>>((const __nv_bfloat16*)src, (const __nv_bfloat16*)w, nbr, n_dst, K,
-                                            (__nv_bfloat16*)out, n_tiles);
+  if (grid > n_super) grid = n_super;
+  kern<<<grid, kFwdThreads, C::SMEM, stream>>>((const __nv_bfloat16*)src, (const __nv_bfloat16*)w, nbr, n_dst, K,
+                                               (__nv_bfloat16*)out, n_super);
   RMN_LAUNCH_CHECK();
   return RMN_OK;
 }

@@ -102,6 +102,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
          ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46);
 }
 
+// Same with a swizzled layout: layout_type 2 = 128-byte swizzle, 4 = 64-byte, 6 = 32-byte.
+__device__ __forceinline__ uint64_t smem_desc_sw(uint32_t addr, uint32_t lbo, uint32_t sbo, uint32_t layout_type) {
+  return smem_desc(addr, lbo, sbo) | ((uint64_t)layout_type << 61);
+}
+
 // Instruction descriptor of kind::f16: D fp32, A/B bf16, A K-major, B K- or MN-major.
 constexpr uint32_t instr_desc(int m, int n, bool b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) |

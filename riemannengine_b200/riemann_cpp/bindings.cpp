@@ -1,0 +1,154 @@
+// pybind11 module `_C`: re-exports the C++ host layer with the names and keyword arguments of
+// the reference's Python module (python/src/sparse_bindings.cpp:79-199,
+// python/src/nn_bindings.cpp:91-117), so that the C++ classes can be driven from pytest.
+#include <torch/extension.h>
+
+#include "riemann_b200.hpp"
+
+namespace py = pybind11;
+using namespace riemann;
+
+namespace {
+
+template <typename Impl>
+py::class_<Impl, std::shared_ptr<Impl>> bind_conv(py::module_& m, const char* name) {
+  py::class_<Impl, std::shared_ptr<Impl>> cls(m, name);
+  cls.def("forward", [](Impl& self, const SparseTensor& input) { return self.forward(input); }, py::arg("input"),
+          py::call_guard<py::gil_scoped_release>());
+  cls.def("__call__", [](Impl& self, const SparseTensor& input) { return self.forward(input); }, py::arg("input"),
+          py::call_guard<py::gil_scoped_release>());
+  cls.def_property_readonly("kernel", [](Impl& self) { return self.base()->kernel_; });
+  cls.def_property_readonly("bias", [](Impl& self) { return self.base()->bias_; });
+  cls.def("parameters", [](Impl& self) { return self.parameters(); });
+  cls.def("named_parameters", [](Impl& self) {
+    py::dict out;
+    for (auto& p : self.named_parameters()) out[py::str(p.key())] = p.value();
+    return out;
+  });
+  cls.def("to", [](Impl& self, py::object dtype_or_device) {
+    if (THPDtype_Check(dtype_or_device.ptr()))
+      self.to(reinterpret_cast<THPDtype*>(dtype_or_device.ptr())->scalar_type);
+    else
+      self.to(torch::Device(py::cast<std::string>(py::str(dtype_or_device))));
+  });
+  cls.def("zero_grad", [](Impl& self) { self.zero_grad(); });
+  return cls;
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "riemann_cpp (B200) host layer";
+
+  py::enum_<CoordinateMapBackend::Type>(m, "CoordinateMapBackend")
+      .value("CPU", CoordinateMapBackend::CPU)
+      .value("CUDA", CoordinateMapBackend::CUDA);
+  py::enum_<RiemannAlgorithm::Mode>(m, "RiemannAlgorithm")
+      .value("DEFAULT", RiemannAlgorithm::DEFAULT)
+      .value("MEMORY_EFFICIENT", RiemannAlgorithm::MEMORY_EFFICIENT)
+      .value("SPEED_OPTIMIZED", RiemannAlgorithm::SPEED_OPTIMIZED);
+  py::enum_<SparseTensorQuantizationMode::Type>(m, "SparseTensorQuantizationMode")
+      .value("RANDOM_SUBSAMPLE", SparseTensorQuantizationMode::RANDOM_SUBSAMPLE)
+      .value("UNWEIGHTED_AVERAGE", SparseTensorQuantizationMode::UNWEIGHTED_AVERAGE)
+      .value("UNWEIGHTED_SUM", SparseTensorQuantizationMode::UNWEIGHTED_SUM)
+      .value("MAX_POOL", SparseTensorQuantizationMode::MAX_POOL)
+      .value("NO_QUANTIZATION", SparseTensorQuantizationMode::NO_QUANTIZATION);
+  py::enum_<RegionType::Type>(m, "RegionType")
+      .value("HYPER_CUBE", RegionType::HYPER_CUBE)
+      .value("HYPER_CROSS", RegionType::HYPER_CROSS)
+      .value("CUSTOM", RegionType::CUSTOM);
+  py::enum_<ConvolutionMode::Type>(m, "ConvolutionMode")
+      .value("DEFAULT", ConvolutionMode::DEFAULT)
+      .value("DIRECT_GEMM", ConvolutionMode::DIRECT_GEMM)
+      .value("COPY_GEMM", ConvolutionMode::COPY_GEMM);
+
+  py::class_<CoordinateMapKey>(m, "CoordinateMapKey")
+      .def(py::init<stride_type, std::string>(), py::arg("tensor_stride"), py::arg("string_id") = "")
+      .def_property_readonly("tensor_stride", &CoordinateMapKey::get_tensor_stride)
+      .def_property_readonly("coordinate_size", &CoordinateMapKey::get_coordinate_size)
+      .def("is_key_set", &CoordinateMapKey::is_key_set)
+      .def("__eq__", [](const CoordinateMapKey& a, const CoordinateMapKey& b) { return a == b; })
+      .def("__hash__", &CoordinateMapKey::hash)
+      .def("__repr__", &CoordinateMapKey::to_string);
+
+  py::class_<CoordinateManager, std::shared_ptr<CoordinateManager>>(m, "CoordinateManager")
+      .def(py::init([](int dimension, CoordinateMapBackend::Type backend, RiemannAlgorithm::Mode algorithm) {
+             return std::make_shared<CoordinateManager>(dimension, backend, GPUMemoryAllocatorBackend::PYTORCH,
+                                                        algorithm);
+           }),
+           py::arg("dimension"), py::arg("backend") = CoordinateMapBackend::CUDA,
+           py::arg("algorithm") = RiemannAlgorithm::DEFAULT)
+      .def_property_readonly("dimension", &CoordinateManager::D)
+      .def("size", [](const CoordinateManager& self, const CoordinateMapKey& key) { return self.size(key); },
+           py::arg("coordinate_map_key"))
+      .def("get_coordinates", &CoordinateManager::get_coordinates, py::arg("coordinate_map_key"))
+      .def("insert_and_map", &CoordinateManager::insert_and_map, py::arg("coordinates"), py::arg("tensor_stride"),
+           py::arg("string_id") = "")
+      .def("stride", &CoordinateManager::stride, py::arg("in_key"), py::arg("kernel_stride"),
+           py::arg("string_id") = "")
+      .def("kernel_map_th",
+           [](CoordinateManager& self, const CoordinateMapKey& in_key, const CoordinateMapKey& out_key,
+              stride_type kernel_size, stride_type kernel_stride, stride_type kernel_dilation,
+              RegionType::Type region_type, bool is_transpose) {
+             return self.kernel_map_th(in_key, out_key, kernel_size, kernel_stride, kernel_dilation, region_type,
+                                       at::Tensor(), is_transpose, false);
+           },
+           py::arg("in_key"), py::arg("out_key"), py::arg("kernel_size"), py::arg("kernel_stride"),
+           py::arg("kernel_dilation"), py::arg("region_type") = RegionType::HYPER_CUBE,
+           py::arg("is_transpose") = false);
+
+  py::class_<SparseTensor>(m, "SparseTensor")
+      .def(py::init([](at::Tensor features, at::Tensor coordinates, std::shared_ptr<CoordinateManager> manager,
+                       SparseTensorQuantizationMode::Type quantization_mode, RiemannAlgorithm::Mode algorithm) {
+             return SparseTensor(std::move(features), std::move(coordinates), std::move(manager), quantization_mode,
+                                 GPUMemoryAllocatorBackend::PYTORCH, algorithm);
+           }),
+           py::arg("features"), py::arg("coordinates"),
+           py::arg("coordinate_manager") = std::shared_ptr<CoordinateManager>(),
+           py::arg("quantization_mode") = SparseTensorQuantizationMode::RANDOM_SUBSAMPLE,
+           py::arg("algorithm") = RiemannAlgorithm::DEFAULT)
+      .def(py::init<at::Tensor, CoordinateMapKey, std::shared_ptr<CoordinateManager>>(), py::arg("features"),
+           py::arg("coordinate_map_key"), py::arg("coordinate_manager"))
+      .def_property_readonly("F", &SparseTensor::F)
+      .def_property_readonly("C", &SparseTensor::C)
+      .def_property_readonly("features", &SparseTensor::F)
+      .def_property_readonly("coordinates", &SparseTensor::C)
+      .def_property_readonly("coordinate_map_key", &SparseTensor::coordinate_map_key)
+      .def_property_readonly("coordinate_manager", &SparseTensor::coordinate_manager)
+      .def_property_readonly("tensor_stride", &SparseTensor::tensor_stride)
+      .def_property_readonly("dimension", &SparseTensor::dimension)
+      .def_property_readonly("requires_grad", &SparseTensor::requires_grad)
+      .def_property_readonly("shape",
+                             [](const SparseTensor& self) { return py::make_tuple(self.F().size(0), self.F().size(1)); })
+      .def("__len__", [](const SparseTensor& self) { return self.F().size(0); })
+      .def("detach", &SparseTensor::detach);
+
+  bind_conv<RiemannConvolutionImpl>(m, "RiemannConvolution")
+      .def(py::init([](int in_channels, int out_channels, int kernel_size, int stride, int dilation, bool bias,
+                       bool expand_coordinates, ConvolutionMode::Type convolution_mode, int dimension) {
+             return std::make_shared<RiemannConvolutionImpl>(in_channels, out_channels, kernel_size, stride, dilation,
+                                                             bias, expand_coordinates, convolution_mode, dimension);
+           }),
+           py::arg("in_channels"), py::arg("out_channels"), py::arg("kernel_size") = 3, py::arg("stride") = 1,
+           py::arg("dilation") = 1, py::arg("bias") = false, py::arg("expand_coordinates") = false,
+           py::arg("convolution_mode") = ConvolutionMode::DEFAULT, py::arg("dimension") = 3);
+  bind_conv<RiemannConvolutionTransposeImpl>(m, "RiemannConvolutionTranspose")
+      .def(py::init([](int in_channels, int out_channels, int kernel_size, int stride, int dilation, bool bias,
+                       bool expand_coordinates, ConvolutionMode::Type convolution_mode, int dimension) {
+             return std::make_shared<RiemannConvolutionTransposeImpl>(in_channels, out_channels, kernel_size, stride,
+                                                                      dilation, bias, expand_coordinates,
+                                                                      convolution_mode, dimension);
+           }),
+           py::arg("in_channels"), py::arg("out_channels"), py::arg("kernel_size") = 3, py::arg("stride") = 1,
+           py::arg("dilation") = 1, py::arg("bias") = false, py::arg("expand_coordinates") = false,
+           py::arg("convolution_mode") = ConvolutionMode::DEFAULT, py::arg("dimension") = 3);
+  bind_conv<RiemannGenerativeConvolutionTransposeImpl>(m, "RiemannGenerativeConvolutionTranspose")
+      .def(py::init([](int in_channels, int out_channels, int kernel_size, int stride, int dilation, bool bias,
+                       ConvolutionMode::Type convolution_mode, int dimension) {
+             return std::make_shared<RiemannGenerativeConvolutionTransposeImpl>(
+                 in_channels, out_channels, kernel_size, stride, dilation, bias, convolution_mode, dimension);
+           }),
+           py::arg("in_channels"), py::arg("out_channels"), py::arg("kernel_size") = 3, py::arg("stride") = 1,
+           py::arg("dilation") = 1, py::arg("bias") = false, py::arg("convolution_mode") = ConvolutionMode::DEFAULT,
+           py::arg("dimension") = 3);
+}

@@ -7,7 +7,6 @@
 
 #include <cmath>
 #include <cstdlib>
-#include <sstream>
 #include <stdexcept>
 
 #include "rmn_b200.h"
@@ -43,12 +42,16 @@ void check_coordinates(const at::Tensor& c) {
   TORCH_CHECK(c.size(1) >= 2 && c.size(1) <= RMN_MAX_W, "coordinates must have between 2 and 8 columns");
 }
 
+// (plain string appends: iostreams are avoided on purpose, the extension shares a process with
+// libraries that carry their own copies of the stream templates)
 std::string stride_string(const stride_type& s) {
-  std::ostringstream out;
-  out << "[";
-  for (size_t i = 0; i < s.size(); ++i) out << (i ? ", " : "") << s[i];
-  out << "]";
-  return out.str();
+  std::string out = "[";
+  for (size_t i = 0; i < s.size(); ++i) {
+    if (i) out += ", ";
+    out += std::to_string(s[i]);
+  }
+  out += "]";
+  return out;
 }
 
 std::vector<int32_t> to_i32(const stride_type& s) { return std::vector<int32_t>(s.begin(), s.end()); }
@@ -257,11 +260,11 @@ std::shared_ptr<KernelMap> CoordinateManager::kernel_map(const CoordinateMapKey&
                   "CUSTOM kernel size, stride and dilation must be positive");
   }
   auto cache_key = [&](const CoordinateMapKey& a, const CoordinateMapKey& b, bool transpose) {
-    std::ostringstream out;
-    out << a.to_string() << "|" << b.to_string() << "|" << stride_string(kernel_size) << stride_string(kernel_stride)
-        << stride_string(kernel_dilation) << "|" << int(region_type) << transpose << is_pool << "|";
-    for (auto v : custom) out << v << ",";
-    return out.str();
+    std::string out = a.to_string() + "|" + b.to_string() + "|" + stride_string(kernel_size) +
+                      stride_string(kernel_stride) + stride_string(kernel_dilation) + "|" +
+                      std::to_string(int(region_type)) + (transpose ? "T" : "F") + (is_pool ? "P" : "C") + "|";
+    for (auto v : custom) out += std::to_string(v) + ",";
+    return out;
   };
   const std::string key = cache_key(in_key, out_key, is_transpose);
   if (auto it = kernel_maps_.find(key); it != kernel_maps_.end()) return it->second;

@@ -62,3 +62,23 @@ def test_cpu_tensors_are_rejected():
         engine.SparseTensor(torch.zeros(2, 3), torch.zeros(2, 4, dtype=torch.int32))
     with pytest.raises(RuntimeError, match="no CPU"):
         engine.CoordinateManager(3, engine.CoordinateMapBackend.CPU)
+
+
+def test_cpp_host_module_loads_on_cpu():
+    """The C++ host layer builds against LibTorch and mirrors the reference's class names."""
+    import os
+    from riemannengine_b200 import _build, cpp
+    if not os.path.exists(_build.HOST_LIB):
+        pytest.skip("host extension not built (python -c 'import __graft_entry__ as g; g.build()')")
+    C = cpp.load()
+    for name in ("CoordinateMapKey", "CoordinateManager", "SparseTensor", "RiemannConvolution",
+                 "RiemannConvolutionTranspose", "RiemannGenerativeConvolutionTranspose"):
+        assert hasattr(C, name)
+    k = C.CoordinateMapKey([2, 2, 2], "a")
+    assert k.tensor_stride == [2, 2, 2] and k.coordinate_size == 4 and repr(k) == "coordinate map key:[2, 2, 2]:a"
+    conv = C.RiemannConvolution(4, 8, kernel_size=3, bias=True)
+    assert tuple(conv.kernel.shape) == (27, 4, 8) and tuple(conv.bias.shape) == (1, 8)
+    bound = 1.0 / (4 * 27) ** 0.5
+    assert float(conv.kernel.abs().max()) <= bound
+    with pytest.raises(RuntimeError, match="no CPU"):
+        C.CoordinateManager(3, C.CoordinateMapBackend.CPU)

@@ -1,0 +1,91 @@
+"""GPU tests of the C++20 / LibTorch host layer (riemann_cpp) through its pybind11 module: the
+same structural checks the reference makes on its layers (tests/engine/test_layers.cpp:132-148,
+python/tests/test_bindings.py:73-124) and value/gradient parity with the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from tests import parity
+from tests.parity import OracleBackend, rel_max
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def C():
+    from riemannengine_b200 import cpp
+    return cpp.load()
+
+
+def _inputs(n=800, c=5, seed=3):
+    rng = np.random.default_rng(seed)
+    coords = np.concatenate([rng.integers(0, 2, (n, 1)), rng.integers(-6, 7, (n, 3))], 1).astype(np.int32)
+    feats = rng.standard_normal((n, c)).astype(np.float32)
+    return coords, feats
+
+
+def test_cpp_sparse_tensor_and_conv_match_oracle(C):
+    coords, feats = _inputs()
+    f = torch.from_numpy(feats).cuda().requires_grad_(True)
+    x = C.SparseTensor(f, torch.from_numpy(coords).cuda())
+    conv = C.RiemannConvolution(5, 7, kernel_size=3, dimension=3)
+    conv.to("cuda")
+    y = conv(x)
+    ((y.F * y.F).sum() * 0.5).backward()
+    w = conv.kernel.detach().cpu().numpy()
+    r = parity.run_pipeline(OracleBackend(f64=True), coords, feats, w, 3, 3, 1, 1)
+    assert (x.C.cpu().numpy() == r["in_coords"]).all()
+    assert rel_max(y.F.detach().cpu().numpy(), r["out_feats"]) <= 1e-4
+    assert rel_max(f.grad.cpu().numpy(), r["grad_feats"]) <= 1e-4
+    assert rel_max(conv.kernel.grad.cpu().numpy(), r["grad_weights"]) <= 1e-4
+    th = x.coordinate_manager.kernel_map_th(x.coordinate_map_key, y.coordinate_map_key, [3] * 3, [1] * 3, [1] * 3)
+    assert sum(v.shape[1] for v in th.values()) == int(r["kmap_ptr"][-1])
+    for k, v in th.items():
+        want = parity.sorted_pairs(r["kmap_ptr"], r["kmap_in"], r["kmap_out"], k)
+        got = v.cpu().numpy().T.astype(np.int64)
+        got = got[np.lexsort((got[:, 1], got[:, 0]))]
+        assert (got == want).all()
+
+
+def test_cpp_down_up_chain(C):
+    coords, feats = _inputs(c=4, seed=5)
+    f = torch.from_numpy(feats).cuda().requires_grad_(True)
+    x = C.SparseTensor(f, torch.from_numpy(coords).cuda())
+    down = C.RiemannConvolution(4, 6, kernel_size=2, stride=2, dimension=3)
+    up = C.RiemannConvolutionTranspose(6, 3, kernel_size=2, stride=2, dimension=3)
+    down.to("cuda")
+    up.to("cuda")
+    y = down(x)
+    assert y.tensor_stride == [2, 2, 2] and len(y) < len(x) and y.F.shape[1] == 6
+    z = up(y)
+    assert z.tensor_stride == [1, 1, 1] and len(z) == len(x) and z.coordinate_map_key == x.coordinate_map_key
+    ((z.F * z.F).sum() * 0.5).backward()
+    r = parity.run_pipeline(OracleBackend(f64=True), coords, feats, down.kernel.detach().cpu().numpy(), 3, 2, 2, 1,
+                            up.kernel.detach().cpu().numpy())
+    assert (y.C.cpu().numpy() == r["out_coords"]).all()
+    assert rel_max(z.F.detach().cpu().numpy(), r["up_feats"]) <= 1e-4
+    assert rel_max(f.grad.cpu().numpy(), r["grad_feats"]) <= 1e-4
+    assert rel_max(down.kernel.grad.cpu().numpy(), r["grad_weights"]) <= 1e-4
+    assert rel_max(up.kernel.grad.cpu().numpy(), r["grad_weights2"]) <= 1e-4
+
+
+def test_cpp_transposed_needs_existing_map(C):
+    coords, feats = _inputs(c=3)
+    x = C.SparseTensor(torch.from_numpy(feats).cuda(), torch.from_numpy(coords).cuda())
+    up = C.RiemannConvolutionTranspose(3, 2, kernel_size=2, stride=2, dimension=3)
+    up.to("cuda")
+    with pytest.raises(RuntimeError, match="must divide"):
+        up(x)
+
+
+def test_cpp_bf16_layer(C):
+    coords, feats = _inputs(n=3000, c=32, seed=9)
+    x = C.SparseTensor(torch.from_numpy(feats).cuda().bfloat16(), torch.from_numpy(coords).cuda())
+    conv = C.RiemannConvolution(32, 64, kernel_size=3, dimension=3)
+    conv.to("cuda")
+    conv.to(torch.bfloat16)
+    y = conv(x)
+    w = conv.kernel.detach().float().cpu().numpy()
+    fb = torch.from_numpy(feats).bfloat16().float().numpy()
+    r = parity.run_pipeline(OracleBackend(f64=True), coords, fb, w, 3, 3, 1, 1)
+    assert parity.rel_l2(y.F.float().cpu().numpy(), r["out_feats"]) <= 1e-2
