@@ -32,7 +32,7 @@ struct __align__(16) TableHeader {
   uint32_t n_rows;
   uint32_t n_unique;
   uint32_t status;
-  uint32_t cap_log2;
+  uint32_t capacity;   // number of slots (a multiple of 32, about 2 x n_rows)
   uint32_t total_bits;
   uint32_t reserved;
   int32_t mn[RMN_MAX_W];
@@ -73,13 +73,14 @@ struct Packer {
   }
 };
 
-__device__ __forceinline__ uint32_t hash_key(unsigned long long k, uint32_t mask) {
-  k ^= k >> 33;
-  k *= 0xff51afd7ed558ccdull;
-  k ^= k >> 33;
-  k *= 0xc4ceb9fe1a85ec53ull;
-  k ^= k >> 33;
-  return (uint32_t)k & mask;
+// 32-bit mix of the packed key, then Lemire's multiply-shift range reduction onto [0, capacity).
+__device__ __forceinline__ uint32_t hash_key(unsigned long long k, uint32_t capacity) {
+  uint32_t h = (uint32_t)k ^ ((uint32_t)(k >> 32) * 0x9E3779B1u);
+  h *= 0x85ebca6bu;
+  h ^= h >> 13;
+  h *= 0xc2b2ae35u;
+  h ^= h >> 16;
+  return __umulhi(h, capacity);
 }
 
 __device__ __forceinline__ ulonglong2 load_slot(const Slot* s) {
@@ -87,14 +88,14 @@ __device__ __forceinline__ ulonglong2 load_slot(const Slot* s) {
 }
 
 // Lookup; returns uid or 0xFFFFFFFF. Probing is bounded by the slot count.
-__device__ __forceinline__ uint32_t table_find(const Slot* slots, uint32_t mask,
+__device__ __forceinline__ uint32_t table_find(const Slot* slots, uint32_t capacity,
                                                unsigned long long key) {
-  uint32_t s = hash_key(key, mask);
-  for (uint32_t probe = 0; probe <= mask; ++probe) {
+  uint32_t s = hash_key(key, capacity);
+  for (uint32_t probe = 0; probe < capacity; ++probe) {
     ulonglong2 v = load_slot(slots + s);
     if (v.x == key) return (uint32_t)(v.y >> 32);
     if (v.x == kEmptyKey) return 0xFFFFFFFFu;
-    s = (s + 1) & mask;
+    s = s + 1 == capacity ? 0u : s + 1;
   }
   return 0xFFFFFFFFu;
 }
@@ -114,10 +115,10 @@ __device__ __forceinline__ void load_row(const int32_t* __restrict__ coords, uin
   }
 }
 
-inline uint32_t table_cap_log2(uint32_t n_rows) {
-  uint32_t lg = 4;
-  while ((1ull << lg) < 2ull * n_rows + 2ull) ++lg;
-  return lg;
+// Slot count for n_rows inserted rows: load factor <= 50 %, multiple of 32, at least 32.
+inline uint32_t table_capacity(uint32_t n_rows) {
+  const unsigned long long want = 2ull * n_rows + 32ull;
+  return (uint32_t)((want + 31ull) / 32ull * 32ull);
 }
 
 // load_row uses 16-byte (W == 4) / 8-byte (W == 2) vector loads

@@ -20,22 +20,30 @@ namespace rmn {
 
 constexpr int kKmapBlock = 256;
 
+// The packed key is linear in the coordinates: key(c + off) = key(c) + sum_i (off_i << shift_i)
+// in 64-bit modular arithmetic, so each probe costs one 64-bit add on top of the range test
+// (a neighbour outside the table's bounding box is a miss without touching memory).
 template <int W>
 __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe(
     const TableHeader* __restrict__ h, const Slot* __restrict__ slots,
     const int32_t* __restrict__ query, uint32_t n_query, const int32_t* __restrict__ offsets,
     int K, int32_t* __restrict__ nbr, uint32_t* __restrict__ block_counts, uint32_t n_blocks) {
-  extern __shared__ int32_t smem[];
-  int32_t* s_off = smem;                                       // [K][W-1]
-  uint32_t* s_cnt = reinterpret_cast<uint32_t*>(smem + K * (W - 1));  // [K]
+  extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int D = W - 1;
+  long long* s_delta = reinterpret_cast<long long*>(smem_raw);           // [K]
+  int32_t* s_off = reinterpret_cast<int32_t*>(s_delta + K);              // [K][D]
+  uint32_t* s_cnt = reinterpret_cast<uint32_t*>(s_off + K * D);          // [K]
   for (int i = threadIdx.x; i < K * D; i += kKmapBlock) s_off[i] = offsets[i];
-  for (int i = threadIdx.x; i < K; i += kKmapBlock) s_cnt[i] = 0;
+  for (int k = threadIdx.x; k < K; k += kKmapBlock) {
+    long long d = 0;
+#pragma unroll
+    for (int a = 0; a < D; ++a) d += (long long)offsets[k * D + a] << h->shift[a + 1];
+    s_delta[k] = d;
+    s_cnt[k] = 0;
+  }
   __syncthreads();
 
-  Packer<W> pk;
-  pk.load(h);
-  const uint32_t mask = (1u << h->cap_log2) - 1u;
+  const uint32_t capacity = h->capacity;
   const uint32_t q = blockIdx.x * kKmapBlock + threadIdx.x;
   const bool active = q < n_query;
   int32_t c[W];
@@ -45,18 +53,27 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe(
 #pragma unroll
     for (int i = 0; i < W; ++i) c[i] = 0;
   }
+  // distance from the box minimum per column, the packed centre key, and the box spans
+  uint32_t dist[W], span[W];
+  long long ckey = 0;
+#pragma unroll
+  for (int i = 0; i < W; ++i) {
+    const int32_t mn = h->mn[i];
+    dist[i] = (uint32_t)c[i] - (uint32_t)mn;
+    span[i] = (uint32_t)(h->mx[i] - mn);
+    ckey += (long long)((long long)c[i] - (long long)mn) << h->shift[i];
+  }
+  const bool batch_ok = active && dist[0] <= span[0];
   const int lane = threadIdx.x & 31;
   for (int k = 0; k < K; ++k) {
-    int32_t nb[W];
-    nb[0] = c[0];
+    bool in_box = batch_ok;
 #pragma unroll
-    for (int a = 0; a < D; ++a) nb[a + 1] = c[a + 1] + s_off[k * D + a];
-    unsigned long long key;
+    for (int a = 0; a < D; ++a) in_box = in_box && (dist[a + 1] + (uint32_t)s_off[k * D + a] <= span[a + 1]);
     uint32_t uid = 0xFFFFFFFFu;
-    if (active && pk.pack(nb, key)) uid = table_find(slots, mask, key);
-    if (active) nbr[(size_t)k * n_query + q] = (int32_t)uid;
+    if (in_box) uid = table_find(slots, capacity, (unsigned long long)(ckey + s_delta[k]));
+    if (active) __stcs(nbr + (size_t)k * n_query + q, (int32_t)uid);
     const uint32_t hits = __ballot_sync(0xFFFFFFFFu, uid != 0xFFFFFFFFu);
-    if (lane == 0 && hits) atomicAdd(&s_cnt[k], (uint32_t)__popc(hits));
+    if (lane == 0) atomicAdd(&s_cnt[k], (uint32_t)__popc(hits));
   }
   __syncthreads();
   for (int k = threadIdx.x; k < K; k += kKmapBlock)
@@ -243,7 +260,7 @@ extern "C" int rmn_kmap_build(const void* d_table, const int32_t* d_query, uint3
   auto* h = reinterpret_cast<const TableHeader*>(d_table);
   auto* slots =
       reinterpret_cast<const Slot*>(reinterpret_cast<const char*>(d_table) + sizeof(TableHeader));
-  const size_t smem = (size_t)K * (W - 1) * 4 + (size_t)K * 4;
+  const size_t smem = (size_t)K * 8 + (size_t)K * (W - 1) * 4 + (size_t)K * 4;
   RMN_DISPATCH_W(W, k_kmap_probe<kW><<<nb, kKmapBlock, smem, stream>>>(
                         h, slots, d_query, n_query, d_offsets, K, d_nbr, block_counts, nb));
   RMN_LAUNCH_CHECK();

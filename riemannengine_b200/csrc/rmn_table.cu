@@ -22,14 +22,14 @@ namespace rmn {
 
 constexpr int kRowsPerBlock = 256;
 
-__global__ void k_header_init(TableHeader* h, uint32_t W, uint32_t n_rows, uint32_t cap_log2) {
+__global__ void k_header_init(TableHeader* h, uint32_t W, uint32_t n_rows, uint32_t capacity) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   h->magic = kTableMagic;
   h->W = W;
   h->n_rows = n_rows;
   h->n_unique = 0;
   h->status = RMN_OK;
-  h->cap_log2 = cap_log2;
+  h->capacity = capacity;
   h->total_bits = 0;
   h->reserved = 0;
   for (int c = 0; c < RMN_MAX_W; ++c) {
@@ -43,6 +43,7 @@ __global__ void k_header_init(TableHeader* h, uint32_t W, uint32_t n_rows, uint3
 template <int W>
 __global__ void __launch_bounds__(256) k_range(const int32_t* __restrict__ coords, uint32_t n,
                                                TableHeader* h) {
+  __shared__ int32_t s_mn[8][W], s_mx[8][W];
   int32_t mn[W], mx[W];
 #pragma unroll
   for (int c = 0; c < W; ++c) { mn[c] = INT_MAX; mx[c] = INT_MIN; }
@@ -52,14 +53,21 @@ __global__ void __launch_bounds__(256) k_range(const int32_t* __restrict__ coord
 #pragma unroll
     for (int c = 0; c < W; ++c) { mn[c] = min(mn[c], v[c]); mx[c] = max(mx[c], v[c]); }
   }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int c = 0; c < W; ++c) {
-    int32_t a = __reduce_min_sync(0xFFFFFFFFu, mn[c]);
-    int32_t b = __reduce_max_sync(0xFFFFFFFFu, mx[c]);
-    if ((threadIdx.x & 31) == 0) {
-      atomicMin(&h->mn[c], a);
-      atomicMax(&h->mx[c], b);
-    }
+    const int32_t a = __reduce_min_sync(0xFFFFFFFFu, mn[c]);
+    const int32_t b = __reduce_max_sync(0xFFFFFFFFu, mx[c]);
+    if (lane == 0) { s_mn[warp][c] = a; s_mx[warp][c] = b; }
+  }
+  __syncthreads();
+  // one atomic per block and column (per-warp atomics on eight addresses serialise badly)
+  if (threadIdx.x < W) {
+    int32_t a = s_mn[0][threadIdx.x], b = s_mx[0][threadIdx.x];
+#pragma unroll
+    for (int w2 = 1; w2 < 8; ++w2) { a = min(a, s_mn[w2][threadIdx.x]); b = max(b, s_mx[w2][threadIdx.x]); }
+    atomicMin(&h->mn[threadIdx.x], a);
+    atomicMax(&h->mx[threadIdx.x], b);
   }
 }
 
@@ -92,14 +100,14 @@ __global__ void __launch_bounds__(256) k_insert(const int32_t* __restrict__ coor
   if (row >= n) return;
   Packer<W> pk;
   pk.load(h);
-  const uint32_t mask = (1u << h->cap_log2) - 1u;
+  const uint32_t capacity = h->capacity;
   int32_t c[W];
   load_row<W>(coords, row, c);
   unsigned long long key;
   pk.pack(c, key);
-  uint32_t s = hash_key(key, mask);
+  uint32_t s = hash_key(key, capacity);
   bool placed = false;
-  for (uint32_t probe = 0; probe <= mask; ++probe) {
+  for (uint32_t probe = 0; probe < capacity; ++probe) {
     unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(&slots[s].key);
     if (cur == kEmptyKey) cur = atomicCAS(&slots[s].key, kEmptyKey, key);
     if (cur == kEmptyKey || cur == key) {
@@ -108,7 +116,7 @@ __global__ void __launch_bounds__(256) k_insert(const int32_t* __restrict__ coor
       placed = true;
       break;
     }
-    s = (s + 1) & mask;
+    s = s + 1 == capacity ? 0u : s + 1;
   }
   if (!placed) atomicExch(&h->status, (uint32_t)RMN_ERR_PROBE_LIMIT);
 }
@@ -212,12 +220,12 @@ __global__ void __launch_bounds__(256) k_find(const TableHeader* __restrict__ h,
   if (q >= n) return;
   Packer<W> pk;
   pk.load(h);
-  const uint32_t mask = (1u << h->cap_log2) - 1u;
+  const uint32_t capacity = h->capacity;
   int32_t c[W];
   load_row<W>(query, q, c);
   unsigned long long key;
   uint32_t uid = 0xFFFFFFFFu;
-  if (pk.pack(c, key)) uid = table_find(slots, mask, key);
+  if (pk.pack(c, key)) uid = table_find(slots, capacity, key);
   rows[q] = (int32_t)uid;
 }
 
@@ -245,7 +253,7 @@ __global__ void __launch_bounds__(256) k_stride(const int32_t* __restrict__ coor
 using namespace rmn;
 
 extern "C" size_t rmn_table_bytes(uint32_t n_rows) {
-  return sizeof(TableHeader) + (sizeof(Slot) << table_cap_log2(n_rows));
+  return sizeof(TableHeader) + sizeof(Slot) * (size_t)table_capacity(n_rows);
 }
 
 extern "C" size_t rmn_table_build_workspace_bytes(uint32_t n_rows) {
@@ -266,10 +274,10 @@ extern "C" int rmn_table_build(const int32_t* d_coords, uint32_t n_rows, int W, 
     return RMN_ERR_ALLOC;
   auto* h = reinterpret_cast<TableHeader*>(d_table);
   auto* slots = reinterpret_cast<Slot*>(reinterpret_cast<char*>(d_table) + sizeof(TableHeader));
-  const uint32_t cap_log2 = table_cap_log2(n_rows);
-  k_header_init<<<1, 32, 0, stream>>>(h, (uint32_t)W, n_rows, cap_log2);
+  const uint32_t capacity = table_capacity(n_rows);
+  k_header_init<<<1, 32, 0, stream>>>(h, (uint32_t)W, n_rows, capacity);
   RMN_LAUNCH_CHECK();
-  RMN_CUDA_TRY(cudaMemsetAsync(slots, 0xFF, sizeof(Slot) << cap_log2, stream));
+  RMN_CUDA_TRY(cudaMemsetAsync(slots, 0xFF, sizeof(Slot) * (size_t)capacity, stream));
   if (n_rows == 0) {
     k_plan<<<1, 32, 0, stream>>>(h);
     RMN_LAUNCH_CHECK();
@@ -365,7 +373,7 @@ extern "C" int rmn_table_info(const void* d_table, uint32_t info[4], void* strea
   if (h.magic != kTableMagic) return RMN_ERR_BAD_ARG;
   info[0] = h.n_unique;
   info[1] = h.status;
-  info[2] = 1u << h.cap_log2;
+  info[2] = h.capacity;
   info[3] = h.n_rows;
   return (int)h.status;
 }

@@ -1,0 +1,79 @@
+"""Sample sharding and weight-gradient all-reduce for data-parallel runs.
+
+The hot path shards by sample: the batch index is column 0 of every coordinate and no kernel-map
+pair crosses samples, so each rank hashes, maps and convolves its own samples with no forward
+communication. The one collective of a training step is a sum of the weight gradients, done as a
+single flat (bucketed) all-reduce per step: NCCL over NVLink on GPUs, gloo in the CPU tests of
+this host logic. The reference has no distributed code at all (its ``RiemannSyncBatchNorm`` is an
+alias of the plain layer, engine/nn/normalization.hpp:36-37).
+"""
+from __future__ import annotations
+
+from typing import Iterable, List, Optional, Sequence
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def assign_samples(voxels_per_sample: Sequence[int], world_size: int) -> List[List[int]]:
+    """Greedy longest-processing-time assignment of whole samples to ranks, balanced by voxel
+    count. Returns, per rank, the sorted list of sample (batch) indices it owns."""
+    order = sorted(range(len(voxels_per_sample)), key=lambda i: (-int(voxels_per_sample[i]), i))
+    loads = [0] * world_size
+    owned: List[List[int]] = [[] for _ in range(world_size)]
+    for i in order:
+        r = min(range(world_size), key=lambda j: (loads[j], j))
+        owned[r].append(i)
+        loads[r] += int(voxels_per_sample[i])
+    return [sorted(o) for o in owned]
+
+
+def shard_rows(coords: np.ndarray, rank: int, world_size: int) -> np.ndarray:
+    """Row indices of ``coords`` [N, 1 + D] (batch index in column 0) that belong to ``rank``."""
+    batch = np.asarray(coords)[:, 0]
+    n_samples = int(batch.max()) + 1 if len(batch) else 0
+    counts = np.bincount(batch, minlength=n_samples)
+    mine = assign_samples(counts.tolist(), world_size)[rank]
+    return np.nonzero(np.isin(batch, mine))[0]
+
+
+def allreduce_gradients(params: Iterable[torch.nn.Parameter], group: Optional[dist.ProcessGroup] = None,
+                        average: bool = False, bucket_bytes: int = 64 << 20) -> int:
+    """Sum (or average) the gradients of ``params`` over the ranks with as few collectives as
+    possible: gradients are packed into flat fp32 buckets of at most ``bucket_bytes``.
+    Returns the number of collectives issued. A no-op outside an initialised process group."""
+    if not (dist.is_available() and dist.is_initialized()):
+        return 0
+    world = dist.get_world_size(group)
+    grads = [p.grad for p in params if p.grad is not None]
+    if world == 1 or not grads:
+        return 0
+    calls = 0
+    bucket: List[torch.Tensor] = []
+    size = 0
+
+    def flush():
+        nonlocal bucket, size, calls
+        if not bucket:
+            return
+        flat = torch.cat([g.reshape(-1).float() for g in bucket])
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+        if average:
+            flat /= world
+        off = 0
+        for g in bucket:
+            n = g.numel()
+            g.copy_(flat[off:off + n].view_as(g))
+            off += n
+        calls += 1
+        bucket, size = [], 0
+
+    for g in grads:
+        nbytes = g.numel() * 4
+        if bucket and size + nbytes > bucket_bytes:
+            flush()
+        bucket.append(g)
+        size += nbytes
+    flush()
+    return calls

@@ -513,28 +513,27 @@ at::Tensor conv_backward_weight(const at::Tensor& feats_in, const at::Tensor& gr
   return dw;
 }
 
-struct KernelMapHolder : torch::CustomClassHolder {
-  std::shared_ptr<KernelMap> map;
-};
-
+// The neighbour tables travel through autograd as plain (non-differentiable) int32 tensors:
+// nbr_out for the forward pass and the weight gradient, nbr_in for the input gradient.
 class SparseConvolutionAutograd : public torch::autograd::Function<SparseConvolutionAutograd> {
 public:
   static at::Tensor forward(torch::autograd::AutogradContext* ctx, at::Tensor features, at::Tensor kernel,
-                            c10::intrusive_ptr<KernelMapHolder> holder) {
+                            at::Tensor nbr_out, at::Tensor nbr_in) {
     ctx->save_for_backward({features, kernel});
-    ctx->saved_data["kmap"] = holder;
-    return conv_forward(features, kernel, holder->map->nbr_out);
+    ctx->saved_data["nbr_out"] = nbr_out;
+    ctx->saved_data["nbr_in"] = nbr_in;
+    return conv_forward(features, kernel, nbr_out);
   }
   static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
                                                  torch::autograd::variable_list grad_outputs) {
     auto saved = ctx->get_saved_variables();
-    auto holder = ctx->saved_data["kmap"].toCustomClass<KernelMapHolder>();
+    auto nbr_out = ctx->saved_data["nbr_out"].toTensor();
+    auto nbr_in = ctx->saved_data["nbr_in"].toTensor();
     auto grad = grad_outputs[0].contiguous();
     at::Tensor g_feat, g_kernel;
-    if (ctx->needs_input_grad(0)) g_feat = conv_backward_input(grad, saved[1], holder->map->nbr_in());
-    if (ctx->needs_input_grad(1))
-      g_kernel = conv_backward_weight(saved[0], grad, holder->map->nbr_out).to(saved[1].scalar_type());
-    return {g_feat, g_kernel, at::Tensor()};
+    if (ctx->needs_input_grad(0)) g_feat = conv_backward_input(grad, saved[1], nbr_in);
+    if (ctx->needs_input_grad(1)) g_kernel = conv_backward_weight(saved[0], grad, nbr_out).to(saved[1].scalar_type());
+    return {g_feat, g_kernel, at::Tensor(), at::Tensor()};
   }
 };
 
@@ -542,9 +541,9 @@ public:
 
 at::Tensor sparse_convolution(const at::Tensor& features, const at::Tensor& kernel,
                               const std::shared_ptr<KernelMap>& kmap) {
-  auto holder = c10::make_intrusive<KernelMapHolder>();
-  holder->map = kmap;
-  return SparseConvolutionAutograd::apply(features, kernel, holder);
+  // the inverse table is cached in the kernel map; it is only needed when the features want a gradient
+  at::Tensor nbr_in = features.requires_grad() ? kmap->nbr_in() : at::empty({0}, kmap->nbr_out.options());
+  return SparseConvolutionAutograd::apply(features, kernel, kmap->nbr_out, nbr_in);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -1,0 +1,74 @@
+"""world_size-2 gloo tests (CPU) of the multi-rank host logic: sample sharding and the bucketed
+weight-gradient all-reduce."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from riemannengine_b200 import distributed as D
+
+
+def test_assign_samples_is_a_balanced_partition():
+    counts = [150, 90, 120, 30, 150, 60, 100, 100]
+    for world in (1, 2, 4, 8):
+        owned = D.assign_samples(counts, world)
+        flat = sorted(i for o in owned for i in o)
+        assert flat == list(range(len(counts)))
+        loads = [sum(counts[i] for i in o) for o in owned]
+        assert max(loads) - min(loads) <= max(counts)
+
+
+def test_shard_rows_keeps_samples_whole():
+    rng = np.random.default_rng(0)
+    coords = np.concatenate([rng.integers(0, 5, (1000, 1)), rng.integers(0, 9, (1000, 3))], 1).astype(np.int32)
+    rows = [D.shard_rows(coords, r, 2) for r in range(2)]
+    assert sorted(np.concatenate(rows).tolist()) == list(range(1000))
+    b0, b1 = set(coords[rows[0], 0].tolist()), set(coords[rows[1], 0].tolist())
+    assert not (b0 & b1)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.manual_seed(0)
+    params = [torch.nn.Parameter(torch.zeros(27, 8, 8)), torch.nn.Parameter(torch.zeros(8, 4, 16)),
+              torch.nn.Parameter(torch.zeros(1, 16)), torch.nn.Parameter(torch.zeros(3))]
+    for i, p in enumerate(params[:3]):
+        p.grad = torch.full_like(p, float(rank + 1) * (i + 1))
+    calls_one = D.allreduce_gradients(params)  # the parameter without a gradient is skipped
+    ok = all(torch.equal(p.grad, torch.full_like(p, 3.0 * (i + 1))) for i, p in enumerate(params[:3]))
+    for i, p in enumerate(params[:3]):
+        p.grad = torch.full_like(p, float(rank + 1))
+    calls_many = D.allreduce_gradients(params, average=True, bucket_bytes=4096)
+    ok = ok and all(torch.allclose(p.grad, torch.full_like(p, 1.5)) for p in params[:3])
+    out[rank] = (ok, calls_one, calls_many)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_bucketed_allreduce_two_ranks_gloo():
+    world = 2
+    with mp.Manager() as m:
+        out = m.dict()
+        mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+        for r in range(world):
+            ok, calls_one, calls_many = out[r]
+            assert ok
+            assert calls_one == 1          # everything fits one bucket
+            assert calls_many >= 2         # small buckets -> several collectives, same result
+
+
+def test_allreduce_is_noop_without_process_group():
+    p = torch.nn.Parameter(torch.ones(3))
+    p.grad = torch.ones(3)
+    assert D.allreduce_gradients([p]) == 0
+    assert torch.equal(p.grad, torch.ones(3))
