@@ -193,8 +193,32 @@ def run_product(args) -> None:
         conv.kernel.copy_(torch.from_numpy(weights_np).to(dev))
     offsets = ops.region_offsets(capi.HYPER_CUBE, [KSIZE] * 3, [1] * 3, [1] * 3)
 
+    # The step runs through the C++ host layer (riemann_cpp) when it is built, else through the
+    # Python mirror; both call the same C ABI.
+    cpp_host = None
+    if args.host != "py":
+        try:
+            from riemannengine_b200 import cpp as cpp_loader
+            cpp_host = cpp_loader.load()
+        except Exception as exc:  # pragma: no cover
+            if args.host == "cpp":
+                raise
+            sys.stderr.write(f"C++ host layer unavailable ({exc}); using the Python host layer\n")
+    if cpp_host is not None:
+        cconv = cpp_host.RiemannConvolution(C_IN, C_OUT, kernel_size=KSIZE, dimension=3)
+        cconv.to(f"cuda:{local_rank}")
+        cconv.to(torch.bfloat16)
+        with torch.no_grad():
+            cconv.kernel.copy_(torch.from_numpy(weights_np).to(dev))
+
     def step():
         """Hot path on device-resident inputs: fresh manager, hash insert, kernel map, forward."""
+        if cpp_host is not None:
+            x = cpp_host.SparseTensor(feats, coords)
+            y = cconv(x)
+            x.coordinate_manager.kernel_map_pairs(x.coordinate_map_key, y.coordinate_map_key, [KSIZE] * 3, [1] * 3,
+                                                  [1] * 3)
+            return x, y, None
         x = E.SparseTensor(feats, coords)
         y = conv(x)
         kmap = x.coordinate_manager.kernel_map(x.coordinate_map_key, y.coordinate_map_key, [KSIZE] * 3, [1] * 3,
@@ -210,8 +234,10 @@ def run_product(args) -> None:
     with torch.no_grad():
         for _ in range(max(args.warmup, 3)):
             x, y, kmap = step()
-        total_pairs = kmap.total_pairs()
         n_unique = len(x)
+        table0 = ops.table_build(coords)
+        total_pairs = int(ops.kmap_build(table0, table0.coords, offsets).pairs()[0][-1])
+        del table0
 
         # ---- headline: K steps, device-resident inputs, CUDA events on the launching stream ----
         barrier()
@@ -261,7 +287,7 @@ def run_product(args) -> None:
         def e2e_step():
             dc = h_coords.to(dev, non_blocking=True)
             df = h_feats.to(dev, non_blocking=True)
-            yy = conv(E.SparseTensor(df, dc))
+            yy = cconv(cpp_host.SparseTensor(df, dc)) if cpp_host is not None else conv(E.SparseTensor(df, dc))
             h_out.copy_(yy.F, non_blocking=True)
 
         for _ in range(3):
@@ -320,6 +346,7 @@ def run_product(args) -> None:
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+        "host_layer": "riemann_cpp (C++/LibTorch)" if cpp_host is not None else "python",
         "voxels_per_step": total_vox, "pairs_per_gpu": total_pairs,
         "phases_ms": phases,
         "kernel_map_build_ms": t_kmap + t_pairs,
@@ -354,6 +381,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--host", default="auto", choices=["auto", "cpp", "py"],
+                    help="host layer driving the step: the C++/LibTorch riemann_cpp module or the Python mirror")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -32,7 +32,7 @@ struct __align__(16) TableHeader {
   uint32_t n_rows;
   uint32_t n_unique;
   uint32_t status;
-  uint32_t capacity;   // number of slots (a multiple of 32, about 2 x n_rows)
+  uint32_t capacity;   // number of slots (a multiple of 32, about 3 x n_rows)
   uint32_t total_bits;
   uint32_t reserved;
   int32_t mn[RMN_MAX_W];
@@ -73,29 +73,39 @@ struct Packer {
   }
 };
 
-// 32-bit mix of the packed key, then Lemire's multiply-shift range reduction onto [0, capacity).
+// Slot of a key: the low three bits of the key (the low bits of the first spatial column, which
+// is packed first) select the position inside an 8-slot (128-byte) bucket; the remaining bits
+// are mixed to 32 bits and range-reduced (multiply-shift) onto the bucket index. Eight voxels
+// that are consecutive along the first spatial axis therefore share one 128-byte line, so the
+// x-1 / x / x+1 probes of a kernel map hit the line the thread has just pulled into L1.
+// Collisions step to the same position of the next bucket.
 __device__ __forceinline__ uint32_t hash_key(unsigned long long k, uint32_t capacity) {
-  uint32_t h = (uint32_t)k ^ ((uint32_t)(k >> 32) * 0x9E3779B1u);
+  const unsigned long long b = k >> 3;
+  uint32_t h = (uint32_t)b ^ ((uint32_t)(b >> 32) * 0x9E3779B1u);
   h *= 0x85ebca6bu;
   h ^= h >> 13;
   h *= 0xc2b2ae35u;
   h ^= h >> 16;
-  return __umulhi(h, capacity);
+  return __umulhi(h, capacity >> 3) * 8u + ((uint32_t)k & 7u);
+}
+__device__ __forceinline__ uint32_t next_slot(uint32_t s, uint32_t capacity) {
+  s += 8u;
+  return s >= capacity ? s - capacity : s;
 }
 
 __device__ __forceinline__ ulonglong2 load_slot(const Slot* s) {
   return __ldg(reinterpret_cast<const ulonglong2*>(s));
 }
 
-// Lookup; returns uid or 0xFFFFFFFF. Probing is bounded by the slot count.
+// Lookup; returns uid or 0xFFFFFFFF. Probing is bounded by the bucket count.
 __device__ __forceinline__ uint32_t table_find(const Slot* slots, uint32_t capacity,
                                                unsigned long long key) {
   uint32_t s = hash_key(key, capacity);
-  for (uint32_t probe = 0; probe < capacity; ++probe) {
+  for (uint32_t probe = 0; probe < (capacity >> 3); ++probe) {
     ulonglong2 v = load_slot(slots + s);
     if (v.x == key) return (uint32_t)(v.y >> 32);
     if (v.x == kEmptyKey) return 0xFFFFFFFFu;
-    s = s + 1 == capacity ? 0u : s + 1;
+    s = next_slot(s, capacity);
   }
   return 0xFFFFFFFFu;
 }
@@ -115,9 +125,9 @@ __device__ __forceinline__ void load_row(const int32_t* __restrict__ coords, uin
   }
 }
 
-// Slot count for n_rows inserted rows: load factor <= 50 %, multiple of 32, at least 32.
+// Slot count for n_rows inserted rows: load factor <= 1/3, a multiple of 32, at least 64.
 inline uint32_t table_capacity(uint32_t n_rows) {
-  const unsigned long long want = 2ull * n_rows + 32ull;
+  const unsigned long long want = 3ull * n_rows + 64ull;
   return (uint32_t)((want + 31ull) / 32ull * 32ull);
 }
 

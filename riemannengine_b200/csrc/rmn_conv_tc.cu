@@ -7,9 +7,9 @@
 //   backward input  dF[i]  = sum_k dY[nbr_t[k][i]] . W[k]^T    B = W[k]   read K-major
 //
 // One persistent CTA per SM loops over super-tiles of T x 128 destination rows
-// (T = 2 where TMEM allows) so that one copy of W[k] in shared memory serves
-// T row tiles. Warp roles (416 threads):
-//   warps 0-7   producers: for every offset k (and 64-channel block of the
+// (T = 4 for up to 64 output channels, 2 up to 128) so that one copy of W[k] in shared memory serves
+// T row tiles. Warp roles (4T producer warps + 1 + 4):
+//   first 4T    producers: for every offset k (and 64-channel block of the
 //               reduction) gather the source rows named by nbr[k][super-tile]
 //               (16-byte cp.async, zero-fill for -1) and copy the W[k] slice
 //               into a ring of shared-memory stages;
@@ -42,9 +42,6 @@ __device__ uint32_t g_tc_status = 0;
 namespace tc {
 
 constexpr int kTileM = 128;
-constexpr int kFwdProducerWarps = 8;
-constexpr int kFwdProducers = kFwdProducerWarps * 32;
-constexpr int kFwdThreads = kFwdProducers + 32 + 128;
 
 // chunk position of 16-byte chunk c in row r of a swizzled image with SW-byte lines
 template <int SW>
@@ -57,14 +54,18 @@ template <int CR, int CC>
 struct Cfg {
   static constexpr int KB = CR < 64 ? CR : 64;  // reduction channels per pipeline stage
   static constexpr int NKB = CR / KB;
-  static constexpr int T = CC <= 128 ? 2 : 1;   // row tiles sharing one W[k] stage
+  // row tiles sharing one W[k] stage: as many as the 512 TMEM columns allow with two accumulator sets
+  static constexpr int T = CC <= 64 ? 4 : (CC <= 128 ? 2 : 1);
+  static constexpr int PRODUCER_WARPS = T < 2 ? 8 : 4 * T;  // one warp per 32 gathered rows (>= 8 for the weights)
+  static constexpr int PRODUCERS = PRODUCER_WARPS * 32;
+  static constexpr int THREADS = PRODUCERS + 32 + 128;
   static constexpr int SWA = KB * 2;            // bytes per A line
   static constexpr uint32_t A_TILE = kTileM * SWA;
   static constexpr uint32_t A_BYTES = T * A_TILE;
   static constexpr uint32_t B_BYTES = KB * CC * 2;
   static constexpr uint32_t STAGE = A_BYTES + B_BYTES;
-  static constexpr int STAGES = STAGE * 5 <= 200 * 1024 ? 5 : 4;
-  static constexpr int LAG = STAGES - 2;        // cp.async groups in flight per producer thread
+  static constexpr int STAGES = STAGE * 5 <= 216 * 1024 ? 5 : (STAGE * 4 <= 216 * 1024 ? 4 : 3);
+  static constexpr int LAG = STAGES > 3 ? STAGES - 2 : 1;  // cp.async groups in flight per producer thread
   static constexpr uint32_t BAR_OFFSET = STAGES * STAGE;
   static constexpr uint32_t SMEM = BAR_OFFSET + 256;
   static constexpr uint32_t TMEM_COLS = pow2_at_least(2 * T * CC);
@@ -73,7 +74,7 @@ struct Cfg {
 // CR: reduction channels per offset; CC: output channels; kWT: weights are read transposed
 // (backward input). Weight tensor is [K][CIN_w][COUT_w] with (CIN_w, COUT_w) = kWT ? (CC, CR) : (CR, CC).
 template <int CR, int CC, bool kWT>
-__global__ void __launch_bounds__(kFwdThreads, 1) k_conv_tc(const __nv_bfloat16* __restrict__ src,
+__global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_bfloat16* __restrict__ src,
                                                             const __nv_bfloat16* __restrict__ w,
                                                             const int32_t* __restrict__ nbr,
                                                             uint32_t n_dst, int K,
@@ -81,6 +82,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1) k_conv_tc(const __nv_bfloat16*
                                                             uint32_t n_super) {
   using C = Cfg<CR, CC>;
   constexpr int STAGES = C::STAGES, KB = C::KB, NKB = C::NKB, T = C::T, LAG = C::LAG, SWA = C::SWA;
+  constexpr int kFwdProducerWarps = C::PRODUCER_WARPS, kFwdProducers = C::PRODUCERS;
   constexpr int CIN_W = kWT ? CC : CR, COUT_W = kWT ? CR : CC;
   // Weight image of one stage: lines of SWB bytes.
   //   forward (MN-major): one line per reduction row ci (KB lines) and 64-column atom;
@@ -296,7 +298,7 @@ int launch(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, i
   const uint32_t per_sm = (C::SMEM <= 110 * 1024 && C::TMEM_COLS <= 256) ? 2u : 1u;
   uint32_t grid = (uint32_t)sms * per_sm;
   if (grid > n_super) grid = n_super;
-  kern<<<grid, kFwdThreads, C::SMEM, stream>>>((const __nv_bfloat16*)src, (const __nv_bfloat16*)w, nbr, n_dst, K,
+  kern<<<grid, C::THREADS, C::SMEM, stream>>>((const __nv_bfloat16*)src, (const __nv_bfloat16*)w, nbr, n_dst, K,
                                                (__nv_bfloat16*)out, n_super);
   RMN_LAUNCH_CHECK();
   return RMN_OK;

@@ -65,15 +65,47 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe(
   }
   const bool batch_ok = active && dist[0] <= span[0];
   const int lane = threadIdx.x & 31;
-  for (int k = 0; k < K; ++k) {
-    bool in_box = batch_ok;
+  // Offsets are handled kUnroll at a time: the first-probe loads of a batch are issued before any
+  // is examined, so a thread keeps several table reads in flight. With the region's first axis
+  // varying fastest, a batch of three is the x-1 / x / x+1 triple that shares one table line.
+  constexpr int kUnroll = 3;
+  for (int k0 = 0; k0 < K; k0 += kUnroll) {
+    unsigned long long key[kUnroll];
+    uint32_t slot[kUnroll];
+    ulonglong2 first[kUnroll];
+    bool valid[kUnroll];
 #pragma unroll
-    for (int a = 0; a < D; ++a) in_box = in_box && (dist[a + 1] + (uint32_t)s_off[k * D + a] <= span[a + 1]);
-    uint32_t uid = 0xFFFFFFFFu;
-    if (in_box) uid = table_find(slots, capacity, (unsigned long long)(ckey + s_delta[k]));
-    if (active) __stcs(nbr + (size_t)k * n_query + q, (int32_t)uid);
-    const uint32_t hits = __ballot_sync(0xFFFFFFFFu, uid != 0xFFFFFFFFu);
-    if (lane == 0) atomicAdd(&s_cnt[k], (uint32_t)__popc(hits));
+    for (int u = 0; u < kUnroll; ++u) {
+      const int k = min(k0 + u, K - 1);
+      bool in_box = batch_ok && (k0 + u < K);
+#pragma unroll
+      for (int a = 0; a < D; ++a) in_box = in_box && (dist[a + 1] + (uint32_t)s_off[k * D + a] <= span[a + 1]);
+      valid[u] = in_box;
+      key[u] = (unsigned long long)(ckey + s_delta[k]);
+      slot[u] = hash_key(key[u], capacity);
+      first[u] = make_ulonglong2(kEmptyKey, 0ull);
+      if (in_box) first[u] = load_slot(slots + slot[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int k = k0 + u;
+      uint32_t uid = 0xFFFFFFFFu;
+      if (valid[u]) {
+        ulonglong2 v = first[u];
+        uint32_t s = slot[u];
+        for (uint32_t probe = 0; probe < (capacity >> 3); ++probe) {
+          if (v.x == key[u]) { uid = (uint32_t)(v.y >> 32); break; }
+          if (v.x == kEmptyKey) break;
+          s = next_slot(s, capacity);
+          v = load_slot(slots + s);
+        }
+      }
+      if (k < K) {  // uniform across the block
+        if (active) __stcs(nbr + (size_t)k * n_query + q, (int32_t)uid);
+        const uint32_t hits = __ballot_sync(0xFFFFFFFFu, uid != 0xFFFFFFFFu);
+        if (lane == 0) atomicAdd(&s_cnt[k], (uint32_t)__popc(hits));
+      }
+    }
   }
   __syncthreads();
   for (int k = threadIdx.x; k < K; k += kKmapBlock)
@@ -144,17 +176,23 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_pairs(
   for (int k = warp; k < K; k += kKmapBlock / 32) {
     unsigned long long pos =
         (unsigned long long)offset_ptr[k] + block_prefix[(size_t)k * n_blocks + blockIdx.x];
+    // all eight row groups are loaded before the first ballot (eight independent 128-byte reads in flight)
+    int32_t av[kKmapBlock / 32];
 #pragma unroll
     for (int g = 0; g < kKmapBlock / 32; ++g) {
       const uint32_t q = row0 + g * 32 + lane;
-      int32_t a = -1;
-      if (q < n_query) a = __ldg(nbr + (size_t)k * n_query + q);
+      av[g] = q < n_query ? __ldcs(nbr + (size_t)k * n_query + q) : -1;
+    }
+#pragma unroll
+    for (int g = 0; g < kKmapBlock / 32; ++g) {
+      const uint32_t q = row0 + g * 32 + lane;
+      const int32_t a = av[g];
       const uint32_t hits = __ballot_sync(0xFFFFFFFFu, a >= 0);
       if (a >= 0) {
         const unsigned long long p = pos + __popc(hits & ((1u << lane) - 1u));
         if (p < capacity) {
-          a_idx[p] = a;
-          q_idx[p] = (int32_t)q;
+          __stcs(a_idx + p, a);
+          __stcs(q_idx + p, (int32_t)q);
         } else {
           *overflow = 1;
         }

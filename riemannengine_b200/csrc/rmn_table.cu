@@ -74,7 +74,10 @@ __global__ void __launch_bounds__(256) k_range(const int32_t* __restrict__ coord
 __global__ void k_plan(TableHeader* h) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   uint32_t total = 0;
-  for (uint32_t c = 0; c < h->W; ++c) {
+  // packing order: spatial columns first (column 1 in the lowest bits: its low three bits pick
+  // the position inside a bucket), the batch column last
+  for (uint32_t i = 0; i < h->W; ++i) {
+    const uint32_t c = i + 1 < h->W ? i + 1 : 0;
     uint32_t b = 0;
     if (h->n_rows > 0) {
       uint32_t span = (uint32_t)h->mx[c] - (uint32_t)h->mn[c];
@@ -107,7 +110,7 @@ __global__ void __launch_bounds__(256) k_insert(const int32_t* __restrict__ coor
   pk.pack(c, key);
   uint32_t s = hash_key(key, capacity);
   bool placed = false;
-  for (uint32_t probe = 0; probe < capacity; ++probe) {
+  for (uint32_t probe = 0; probe < (capacity >> 3); ++probe) {
     unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(&slots[s].key);
     if (cur == kEmptyKey) cur = atomicCAS(&slots[s].key, kEmptyKey, key);
     if (cur == kEmptyKey || cur == key) {
@@ -116,7 +119,7 @@ __global__ void __launch_bounds__(256) k_insert(const int32_t* __restrict__ coor
       placed = true;
       break;
     }
-    s = s + 1 == capacity ? 0u : s + 1;
+    s = next_slot(s, capacity);
   }
   if (!placed) atomicExch(&h->status, (uint32_t)RMN_ERR_PROBE_LIMIT);
 }

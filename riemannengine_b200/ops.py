@@ -159,6 +159,22 @@ class NeighbourTable:
         return ptr_host, a, q
 
 
+_OFFSET_CACHE: dict = {}
+
+
+def _device_offsets(off: np.ndarray, dev: torch.device) -> torch.Tensor:
+    """Device copy of a region's offsets; cached so that repeated kernel-map builds with the same
+    region do not pay a synchronous host-to-device copy each time."""
+    key = (dev.index, off.shape, off.tobytes())
+    hit = _OFFSET_CACHE.get(key)
+    if hit is None:
+        if len(_OFFSET_CACHE) > 256:
+            _OFFSET_CACHE.clear()
+        hit = torch.from_numpy(off.reshape(-1).copy()).to(dev)
+        _OFFSET_CACHE[key] = hit
+    return hit
+
+
 def kmap_build(table: CoordinateTable, query: torch.Tensor, offsets: np.ndarray) -> NeighbourTable:
     """Probe ``table`` at ``query[q] + offsets[k]`` for all (k, q) (rmn_kmap_build)."""
     _check_coords(query, "query coordinates")
@@ -170,7 +186,7 @@ def kmap_build(table: CoordinateTable, query: torch.Tensor, offsets: np.ndarray)
     dev = query.device
     lib = capi.lib()
     with torch.cuda.device(dev):
-        d_off = torch.from_numpy(off.reshape(-1).copy()).to(dev)
+        d_off = _device_offsets(off, dev)
         nbr = torch.empty((K, nq), dtype=torch.int32, device=dev)
         ptr = torch.empty(K + 1, dtype=torch.int64, device=dev)
         wbytes = lib.rmn_kmap_workspace_bytes(nq, K)

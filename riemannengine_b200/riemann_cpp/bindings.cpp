@@ -86,6 +86,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("string_id") = "")
       .def("stride", &CoordinateManager::stride, py::arg("in_key"), py::arg("kernel_stride"),
            py::arg("string_id") = "")
+      .def("kernel_map_pairs",
+           [](CoordinateManager& self, const CoordinateMapKey& in_key, const CoordinateMapKey& out_key,
+              stride_type kernel_size, stride_type kernel_stride, stride_type kernel_dilation,
+              RegionType::Type region_type, bool is_transpose) {
+             // (offset_ptr int64 [K+1] on the host, in rows int32 [P], out rows int32 [P]) of the cached map
+             auto kmap = self.kernel_map(in_key, out_key, kernel_size, kernel_stride, kernel_dilation, region_type,
+                                         at::Tensor(), is_transpose, false);
+             return kmap->pairs();
+           },
+           py::arg("in_key"), py::arg("out_key"), py::arg("kernel_size"), py::arg("kernel_stride"),
+           py::arg("kernel_dilation"), py::arg("region_type") = RegionType::HYPER_CUBE,
+           py::arg("is_transpose") = false, py::call_guard<py::gil_scoped_release>())
       .def("kernel_map_th",
            [](CoordinateManager& self, const CoordinateMapKey& in_key, const CoordinateMapKey& out_key,
               stride_type kernel_size, stride_type kernel_stride, stride_type kernel_dilation,

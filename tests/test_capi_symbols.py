@@ -37,9 +37,9 @@ def test_host_only_entry_points():
     lib = capi.lib()
     assert lib.rmn_version() >= 100
     assert lib.rmn_status_string(capi.ERR_PROBE_LIMIT).decode().startswith("hash probe limit")
-    assert lib.rmn_table_bytes(0) == 256 + 16 * 32
-    assert lib.rmn_table_bytes(1000) == 256 + 16 * 2048  # 2n + 32 slots rounded up to a multiple of 32
-    assert lib.rmn_table_bytes(1 << 20) == 256 + 16 * ((2 << 20) + 32)
+    assert lib.rmn_table_bytes(0) == 256 + 16 * 64
+    assert lib.rmn_table_bytes(1000) == 256 + 16 * 3072  # 3n + 64 slots rounded up to a multiple of 32
+    assert lib.rmn_table_bytes(1 << 20) == 256 + 16 * ((3 << 20) + 64)
 
 
 def test_region_offsets_match_oracle():

@@ -88,4 +88,4 @@ def test_cpp_bf16_layer(C):
     w = conv.kernel.detach().float().cpu().numpy()
     fb = torch.from_numpy(feats).bfloat16().float().numpy()
     r = parity.run_pipeline(OracleBackend(f64=True), coords, fb, w, 3, 3, 1, 1)
-    assert parity.rel_l2(y.F.float().cpu().numpy(), r["out_feats"]) <= 1e-2
+    assert parity.rel_l2(y.F.detach().float().cpu().numpy(), r["out_feats"]) <= 1e-2
