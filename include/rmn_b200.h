@@ -196,6 +196,20 @@ int rmn_kmap_build(const void *d_table, const int32_t *d_query, uint32_t n_query
                    void *d_workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * rmn_kmap_build for the self map of a stride-1 convolution: `d_coords` must be exactly the
+ * unique coordinates of `d_table` in row order (row q of the query IS row q of the table), K
+ * must be odd and the offsets point-symmetric (offsets[K-1-k] == -offsets[k], offsets[K/2] == 0;
+ * the caller checks this on its host copy). Same outputs as rmn_kmap_build, about half the
+ * probes: a hit (q -> a) at offset k also fills (a -> q) at offset K-1-k, and the centre offset
+ * is the identity. Every region of CoordinateMapCPU::kernel_map
+ * (engine/grid/lattice_cpu.hpp:606-673) with odd kernel sizes is of this kind when input and
+ * output maps coincide (engine/nn/conv.cpp:111-125).
+ */
+int rmn_kmap_build_self(const void *d_table, const int32_t *d_coords, uint32_t n_rows, int W,
+                        const int32_t *d_offsets, int K, int32_t *d_nbr, int64_t *d_offset_ptr,
+                        void *d_workspace, size_t workspace_bytes, void *stream);
+
+/*
  * Materialise the pair lists of the last rmn_kmap_build (same d_nbr,
  * d_offset_ptr and d_workspace): d_a_idx[p], d_q_idx[p] for p < ptr[K],
  * pairs of one offset sorted by query row. `capacity` = entries available in

@@ -38,6 +38,8 @@ SIGNATURES = {
     "rmn_kmap_workspace_bytes": (c_size_t, [c_uint32, c_int]),
     "rmn_kmap_build": (c_int, [c_void_p, c_void_p, c_uint32, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                c_void_p, c_size_t, c_void_p]),
+    "rmn_kmap_build_self": (c_int, [c_void_p, c_void_p, c_uint32, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                    c_void_p, c_size_t, c_void_p]),
     "rmn_kmap_pairs": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_uint64,
                                c_void_p]),
     "rmn_kmap_transpose": (c_int, [c_void_p, c_uint32, c_int, c_uint32, c_void_p, c_void_p]),

@@ -12,7 +12,7 @@ size_t simt_wgrad_workspace_bytes(uint32_t n_dst, int K, int c_in, int c_out);
 int simt_conv_backward_weight(const void* feats, int c_in, const void* grad_out, uint32_t n_dst,
                               int c_out, const int32_t* nbr, int K, float* dw, int dtype,
                               void* workspace, cudaStream_t stream);
-int tc_conv(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
+int tc_conv(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
             int c_col, bool transposed_weights, void* out, cudaStream_t stream);
 int tc_read_status(cudaStream_t stream, uint32_t* status);
 int tc_conv_wgrad(const void* feats, const void* grad_out, const int32_t* nbr, uint32_t n_dst, int K, int c_in,
@@ -84,7 +84,7 @@ extern "C" int rmn_conv_forward(const void* d_feats, uint32_t n_src, int c_in,
   }
   if (!conv_args_ok(d_feats, d_weights, d_nbr, d_out, K, c_in, c_out, dtype)) return RMN_ERR_BAD_ARG;
   if (dtype == RMN_BF16 && use_tensor_cores()) {
-    const int st = tc_conv(d_feats, d_weights, d_nbr, n_dst, K, c_in, c_out, false, d_out, stream);
+    const int st = tc_conv(d_feats, n_src, d_weights, d_nbr, n_dst, K, c_in, c_out, false, d_out, stream);
     if (st != RMN_ERR_UNSUPPORTED) return st;
   }
   return simt_conv_forward(d_feats, c_in, d_weights, K, c_out, d_nbr, n_dst, d_out, dtype, stream);
@@ -104,7 +104,7 @@ extern "C" int rmn_conv_backward_input(const void* d_grad_out, uint32_t n_dst, i
   if (!conv_args_ok(d_grad_out, d_weights, d_nbr_t, d_grad_feats, K, c_in, c_out, dtype))
     return RMN_ERR_BAD_ARG;
   if (dtype == RMN_BF16 && use_tensor_cores()) {
-    const int st = tc_conv(d_grad_out, d_weights, d_nbr_t, n_src, K, c_out, c_in, true, d_grad_feats, stream);
+    const int st = tc_conv(d_grad_out, n_dst, d_weights, d_nbr_t, n_src, K, c_out, c_in, true, d_grad_feats, stream);
     if (st != RMN_ERR_UNSUPPORTED) return st;
   }
   return simt_conv_backward_input(d_grad_out, c_out, d_weights, K, c_in, d_nbr_t, n_src,

@@ -65,7 +65,6 @@ struct Cfg {
   static constexpr uint32_t B_BYTES = KB * CC * 2;
   static constexpr uint32_t STAGE = A_BYTES + B_BYTES;
   static constexpr int STAGES = STAGE * 5 <= 216 * 1024 ? 5 : (STAGE * 4 <= 216 * 1024 ? 4 : 3);
-  static constexpr int LAG = STAGES > 3 ? STAGES - 2 : 1;  // cp.async groups in flight per producer thread
   static constexpr uint32_t BAR_OFFSET = STAGES * STAGE;
   static constexpr uint32_t SMEM = BAR_OFFSET + 256;
   static constexpr uint32_t TMEM_COLS = pow2_at_least(2 * T * CC);
@@ -81,7 +80,7 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
                                                             __nv_bfloat16* __restrict__ out,
                                                             uint32_t n_super) {
   using C = Cfg<CR, CC>;
-  constexpr int STAGES = C::STAGES, KB = C::KB, NKB = C::NKB, T = C::T, LAG = C::LAG, SWA = C::SWA;
+  constexpr int STAGES = C::STAGES, KB = C::KB, NKB = C::NKB, T = C::T, SWA = C::SWA;
   constexpr int kFwdProducerWarps = C::PRODUCER_WARPS, kFwdProducers = C::PRODUCERS;
   constexpr int CIN_W = kWT ? CC : CR, COUT_W = kWT ? CR : CC;
   // Weight image of one stage: lines of SWB bytes.
@@ -175,22 +174,14 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
                                          : wk + (size_t)(kb * KB + line) * COUT_W + atom * (SWB / 2) + c * 8;
             cp_async16(b_s + atom * B_ATOM_BYTES + line * SWB + (swz<SWB>(line, c) << 4), g, 16u);
           }
-          cp_async_commit();
-          if (it >= (uint32_t)LAG) {
-            cp_async_wait<LAG>();
-            fence_proxy_async();
-            mbar_arrive(&full[(it - LAG) % STAGES]);
-          }
+          // The stage's "full" barrier fires by itself once this thread's copies have landed
+          // (cp.async.mbarrier.arrive.noinc), so producers never wait for data: they run ahead
+          // until the ring is full and every stage of shared memory can be in flight.
+          cp_async_arrive_noinc(&full[s]);
         }
       }
     }
-    // drain the stages still in flight
-    cp_async_wait<0>();
-    fence_proxy_async();
-    if (!timed_out) {
-      const uint32_t pending = it < (uint32_t)LAG ? it : (uint32_t)LAG;
-      for (uint32_t j = it - pending; j < it; ++j) mbar_arrive(&full[j % STAGES]);
-    }
+    cp_async_wait<0>();  // nothing may still be writing shared memory when the CTA exits
   } else if (warp == kFwdProducerWarps) {
     // ------------------------------ MMA issuer -----------------------------------------
     constexpr uint32_t IDESC = instr_desc(kTileM, CC, !kWT);
@@ -204,6 +195,8 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
       for (uint32_t sg = 0; sg < n_stage; ++sg, ++it) {
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
         if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
+        // the copies were generic-proxy writes; the tensor core reads through the async proxy
+        fence_proxy_async();
         tc_fence_after();
         if (lane == 0) {
           const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
@@ -308,17 +301,39 @@ int launch(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, i
 
 }  // namespace rmn
 
+#include "rmn_conv_tc_tma.cuh"
 #include "rmn_conv_tc_wgrad.cuh"
+
+#include <cstdlib>
 
 namespace rmn {
 
+// RMN_B200_CONV_TMA=1 selects the TMA gather4 producers. They are correct but, measured on the
+// 1.2 M-voxel 64 -> 64 workload, 2.4x slower than the cp.async producers (1.13 ms vs 0.47 ms):
+// the TMA engine retires one four-row gather (512 B) every ~38 cycles per SM, well below what the
+// load/store unit sustains for the same rows. Read on every call so that tests can toggle it.
+static bool use_tma() {
+  const char* e = std::getenv("RMN_B200_CONV_TMA");
+  return e && e[0] == '1';
+}
+
+template <int CR, int CC, bool kWT>
+static int launch_best(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, uint32_t n_dst, int K,
+                       void* out, cudaStream_t stream) {
+  if (use_tma()) {
+    const int st = tc::launch_tma<CR, CC, kWT>(src, n_src, w, nbr, n_dst, K, out, stream);
+    if (st != RMN_ERR_UNSUPPORTED) return st;
+  }
+  return tc::launch<CR, CC, kWT>(src, w, nbr, n_dst, K, out, stream);
+}
+
 // Returns RMN_ERR_UNSUPPORTED when no tensor-core instantiation covers the shape.
-int tc_conv(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
+int tc_conv(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
             int c_col, bool transposed_weights, void* out, cudaStream_t stream) {
-#define RMN_TC_CASE(R, Cc)                                                                      \
-  if (c_red == R && c_col == Cc)                                                                \
-    return transposed_weights ? tc::launch<R, Cc, true>(src, w, nbr, n_dst, K, out, stream)     \
-                              : tc::launch<R, Cc, false>(src, w, nbr, n_dst, K, out, stream);
+#define RMN_TC_CASE(R, Cc)                                                                            \
+  if (c_red == R && c_col == Cc)                                                                      \
+    return transposed_weights ? launch_best<R, Cc, true>(src, n_src, w, nbr, n_dst, K, out, stream)   \
+                              : launch_best<R, Cc, false>(src, n_src, w, nbr, n_dst, K, out, stream);
   RMN_TC_CASE(32, 32)
   RMN_TC_CASE(32, 64)
   RMN_TC_CASE(64, 32)

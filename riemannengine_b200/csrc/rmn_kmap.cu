@@ -112,6 +112,94 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe(
     block_counts[(size_t)k * n_blocks + blockIdx.x] = s_cnt[k];
 }
 
+// Self map with a point-symmetric region (stride-1 convolution: the query rows ARE the table's
+// rows, offsets[K-1-k] == -offsets[k], offsets[K/2] == 0). A pair (q -> a) at offset k implies
+// (a -> q) at offset K-1-k, so only the first K/2 offsets are probed; every hit also fills its
+// mirror entry (one scattered 4-byte store instead of a second probe) and the centre offset is
+// the identity. The mirrored half of nbr must hold -1 before the launch.
+template <int W>
+__global__ void __launch_bounds__(kKmapBlock) k_kmap_probe_self(
+    const TableHeader* __restrict__ h, const Slot* __restrict__ slots,
+    const int32_t* __restrict__ coords, uint32_t n, const int32_t* __restrict__ offsets, int K,
+    int32_t* __restrict__ nbr, uint32_t* __restrict__ block_counts, uint32_t n_blocks) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int D = W - 1;
+  const int half = K / 2;
+  long long* s_delta = reinterpret_cast<long long*>(smem_raw);   // [half]
+  int32_t* s_off = reinterpret_cast<int32_t*>(s_delta + (half > 0 ? half : 1));  // [half][D]
+  uint32_t* s_cnt = reinterpret_cast<uint32_t*>(s_off + (half > 0 ? half : 1) * D);  // [half]
+  for (int i = threadIdx.x; i < half * D; i += kKmapBlock) s_off[i] = offsets[i];
+  for (int k = threadIdx.x; k < half; k += kKmapBlock) {
+    long long d = 0;
+#pragma unroll
+    for (int a = 0; a < D; ++a) d += (long long)offsets[k * D + a] << h->shift[a + 1];
+    s_delta[k] = d;
+    s_cnt[k] = 0;
+  }
+  __syncthreads();
+
+  const uint32_t capacity = h->capacity;
+  const uint32_t q = blockIdx.x * kKmapBlock + threadIdx.x;
+  const bool active = q < n;
+  int32_t c[W];
+  if (active) {
+    load_row<W>(coords, q, c);
+  } else {
+#pragma unroll
+    for (int i = 0; i < W; ++i) c[i] = 0;
+  }
+  uint32_t dist[W], span[W];
+  long long ckey = 0;
+#pragma unroll
+  for (int i = 0; i < W; ++i) {
+    const int32_t mn = h->mn[i];
+    dist[i] = (uint32_t)c[i] - (uint32_t)mn;
+    span[i] = (uint32_t)(h->mx[i] - mn);
+    ckey += (long long)((long long)c[i] - (long long)mn) << h->shift[i];
+  }
+  const int lane = threadIdx.x & 31;
+  if (active) __stcs(nbr + (size_t)half * n + q, (int32_t)q);  // centre offset: identity
+  for (int k = 0; k < half; ++k) {
+    bool in_box = active;
+#pragma unroll
+    for (int a = 0; a < D; ++a) in_box = in_box && (dist[a + 1] + (uint32_t)s_off[k * D + a] <= span[a + 1]);
+    uint32_t uid = 0xFFFFFFFFu;
+    if (in_box) uid = table_find(slots, capacity, (unsigned long long)(ckey + s_delta[k]));
+    if (active) {
+      __stcs(nbr + (size_t)k * n + q, (int32_t)uid);
+      if (uid != 0xFFFFFFFFu) nbr[(size_t)(K - 1 - k) * n + uid] = (int32_t)q;  // mirror entry
+    }
+    const uint32_t hits = __ballot_sync(0xFFFFFFFFu, uid != 0xFFFFFFFFu);
+    if (lane == 0) atomicAdd(&s_cnt[k], (uint32_t)__popc(hits));
+  }
+  __syncthreads();
+  for (int k = threadIdx.x; k < half; k += kKmapBlock)
+    block_counts[(size_t)k * n_blocks + blockIdx.x] = s_cnt[k];
+  if (threadIdx.x == 0) {
+    const uint32_t row0 = blockIdx.x * kKmapBlock;
+    block_counts[(size_t)half * n_blocks + blockIdx.x] = row0 < n ? min((uint32_t)kKmapBlock, n - row0) : 0u;
+  }
+}
+
+// Hit counts per (offset, 256-row block) for `n_off` offset rows of a neighbour table
+// (the mirrored half of a self map, whose entries were scattered by other blocks).
+__global__ void __launch_bounds__(kKmapBlock) k_kmap_count_rows(const int32_t* __restrict__ nbr, uint32_t n,
+                                                              int n_off, uint32_t* __restrict__ block_counts,
+                                                              uint32_t n_blocks) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t row0 = blockIdx.x * kKmapBlock;
+  for (int k = warp; k < n_off; k += kKmapBlock / 32) {
+    uint32_t cnt = 0;
+#pragma unroll
+    for (int g = 0; g < kKmapBlock / 32; ++g) {
+      const uint32_t q = row0 + g * 32 + lane;
+      const int32_t a = q < n ? __ldg(nbr + (size_t)k * n + q) : -1;
+      cnt += __popc(__ballot_sync(0xFFFFFFFFu, a >= 0));
+    }
+    if (lane == 0) block_counts[(size_t)k * n_blocks + blockIdx.x] = cnt;
+  }
+}
+
 // grid = K blocks of 1024 threads: exclusive scan of block_counts[k][0..n_blocks) in place,
 // totals[k] = number of pairs of offset k.
 __global__ void __launch_bounds__(1024) k_kmap_scan_blocks(uint32_t* __restrict__ block_counts,
@@ -302,6 +390,46 @@ extern "C" int rmn_kmap_build(const void* d_table, const int32_t* d_query, uint3
   RMN_DISPATCH_W(W, k_kmap_probe<kW><<<nb, kKmapBlock, smem, stream>>>(
                         h, slots, d_query, n_query, d_offsets, K, d_nbr, block_counts, nb));
   RMN_LAUNCH_CHECK();
+  k_kmap_scan_blocks<<<K, 1024, 0, stream>>>(block_counts, nb, totals);
+  RMN_LAUNCH_CHECK();
+  k_kmap_offset_ptr<<<1, 32, 0, stream>>>(totals, K, d_offset_ptr);
+  RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}
+
+extern "C" int rmn_kmap_build_self(const void* d_table, const int32_t* d_coords, uint32_t n_rows, int W,
+                                   const int32_t* d_offsets, int K, int32_t* d_nbr, int64_t* d_offset_ptr,
+                                   void* d_workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!d_table || W < 2 || W > RMN_MAX_W || K < 1 || K > 4096 || (K & 1) == 0 || !d_offsets || !d_offset_ptr ||
+      !d_workspace)
+    return RMN_ERR_BAD_ARG;
+  if (workspace_bytes < rmn_kmap_workspace_bytes(n_rows, K)) return RMN_ERR_ALLOC;
+  const uint32_t nb = kmap_blocks(n_rows);
+  uint32_t* block_counts = reinterpret_cast<uint32_t*>(d_workspace);
+  uint32_t* totals = block_counts + (size_t)K * nb;
+  if (n_rows == 0) {
+    RMN_CUDA_TRY(cudaMemsetAsync(d_offset_ptr, 0, sizeof(int64_t) * (K + 1), stream));
+    return RMN_OK;
+  }
+  if (!d_coords || !d_nbr || !coords_aligned(d_coords, W)) return RMN_ERR_BAD_ARG;
+  auto* h = reinterpret_cast<const TableHeader*>(d_table);
+  auto* slots =
+      reinterpret_cast<const Slot*>(reinterpret_cast<const char*>(d_table) + sizeof(TableHeader));
+  const int half = K / 2;
+  if (half > 0)  // the mirrored half starts as "no neighbour"
+    RMN_CUDA_TRY(cudaMemsetAsync(d_nbr + (size_t)(half + 1) * n_rows, 0xFF, (size_t)half * n_rows * sizeof(int32_t),
+                                 stream));
+  const int hs = half > 0 ? half : 1;
+  const size_t smem = (size_t)hs * 8 + (size_t)hs * (W - 1) * 4 + (size_t)hs * 4;
+  RMN_DISPATCH_W(W, k_kmap_probe_self<kW><<<nb, kKmapBlock, smem, stream>>>(
+                        h, slots, d_coords, n_rows, d_offsets, K, d_nbr, block_counts, nb));
+  RMN_LAUNCH_CHECK();
+  if (half > 0) {
+    k_kmap_count_rows<<<nb, kKmapBlock, 0, stream>>>(d_nbr + (size_t)(half + 1) * n_rows, n_rows, half,
+                                                     block_counts + (size_t)(half + 1) * nb, nb);
+    RMN_LAUNCH_CHECK();
+  }
   k_kmap_scan_blocks<<<K, 1024, 0, stream>>>(block_counts, nb, totals);
   RMN_LAUNCH_CHECK();
   k_kmap_offset_ptr<<<1, 32, 0, stream>>>(totals, K, d_offset_ptr);

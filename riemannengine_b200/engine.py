@@ -268,7 +268,7 @@ class CoordinateManager:
         if not is_transpose:
             # region on the INPUT tensor stride; probe the input map around every output row
             off = ops.region_offsets(region_type, ks, kd, in_map.tensor_stride, custom)
-            res = ops.kmap_build(in_map.table, out_map.coords, off)
+            res = ops.kmap_build(in_map.table, out_map.coords, off, self_map=in_map is out_map)
             kmap = KernelMap(res.nbr, in_map.size, out_map.size, res)
         else:
             swapped_key = (out_key.get_key(), in_key.get_key(), tuple(ks), tuple(kst), tuple(kd), region_type,

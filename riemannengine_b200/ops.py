@@ -175,8 +175,19 @@ def _device_offsets(off: np.ndarray, dev: torch.device) -> torch.Tensor:
     return hit
 
 
-def kmap_build(table: CoordinateTable, query: torch.Tensor, offsets: np.ndarray) -> NeighbourTable:
-    """Probe ``table`` at ``query[q] + offsets[k]`` for all (k, q) (rmn_kmap_build)."""
+def offsets_point_symmetric(offsets: np.ndarray) -> bool:
+    """True when K is odd, offsets[K-1-k] == -offsets[k] and the centre offset is zero."""
+    off = np.asarray(offsets)
+    k = off.shape[0]
+    return k % 2 == 1 and bool((off[::-1] == -off).all()) and not off[k // 2].any()
+
+
+def kmap_build(table: CoordinateTable, query: torch.Tensor, offsets: np.ndarray,
+               self_map: bool = False) -> NeighbourTable:
+    """Probe ``table`` at ``query[q] + offsets[k]`` for all (k, q) (rmn_kmap_build).
+
+    ``self_map=True`` promises that ``query`` is ``table.coords`` itself; with point-symmetric
+    offsets the half-probe builder (rmn_kmap_build_self) is used."""
     _check_coords(query, "query coordinates")
     if query.size(1) != table.width:
         raise RuntimeError("kernel size mismatch")
@@ -191,8 +202,11 @@ def kmap_build(table: CoordinateTable, query: torch.Tensor, offsets: np.ndarray)
         ptr = torch.empty(K + 1, dtype=torch.int64, device=dev)
         wbytes = lib.rmn_kmap_workspace_bytes(nq, K)
         ws = torch.empty(wbytes, dtype=torch.uint8, device=dev)
-        capi.check(lib.rmn_kmap_build(_ptr(table.buffer), _ptr(query), nq, table.width, _ptr(d_off), K, _ptr(nbr),
-                                      _ptr(ptr), _ptr(ws), wbytes, _stream()), "rmn_kmap_build")
+        fn, name = lib.rmn_kmap_build, "rmn_kmap_build"
+        if self_map and nq == table.n_unique and offsets_point_symmetric(off):
+            fn, name = lib.rmn_kmap_build_self, "rmn_kmap_build_self"
+        capi.check(fn(_ptr(table.buffer), _ptr(query), nq, table.width, _ptr(d_off), K, _ptr(nbr), _ptr(ptr),
+                      _ptr(ws), wbytes, _stream()), name)
     return NeighbourTable(nbr, ptr, ws, nq, K, table.n_unique)
 
 

@@ -308,11 +308,16 @@ std::shared_ptr<KernelMap> CoordinateManager::kernel_map(const CoordinateMapKey&
     result->offset_ptr = at::empty({K + 1}, ints.dtype(at::kLong));
     const size_t ws_bytes = rmn_kmap_workspace_bytes(out_map.size, K);
     result->workspace = at::empty({static_cast<int64_t>(ws_bytes)}, ints.dtype(at::kByte));
-    check(rmn_kmap_build(ptr(in_map.table), static_cast<const int32_t*>(ptr(out_map.coords)), out_map.size, W,
-                         static_cast<const int32_t*>(ptr(d_off)), K, static_cast<int32_t*>(ptr(result->nbr_out)),
-                         static_cast<int64_t*>(ptr(result->offset_ptr)), ptr(result->workspace), ws_bytes,
-                         current_stream()),
-          "rmn_kmap_build");
+    // self map (stride-1 convolution) with a point-symmetric region: half the probes
+    bool self_symmetric = !is_transpose && in_key.get_key() == out_key.get_key() && (K % 2 == 1);
+    for (int k = 0; self_symmetric && k < K; ++k)
+      for (int a = 0; a < D; ++a)
+        if (off[static_cast<size_t>(k) * D + a] != -off[static_cast<size_t>(K - 1 - k) * D + a]) self_symmetric = false;
+    auto build = self_symmetric ? rmn_kmap_build_self : rmn_kmap_build;
+    check(build(ptr(in_map.table), static_cast<const int32_t*>(ptr(out_map.coords)), out_map.size, W,
+                static_cast<const int32_t*>(ptr(d_off)), K, static_cast<int32_t*>(ptr(result->nbr_out)),
+                static_cast<int64_t*>(ptr(result->offset_ptr)), ptr(result->workspace), ws_bytes, current_stream()),
+          self_symmetric ? "rmn_kmap_build_self" : "rmn_kmap_build");
   }
   kernel_maps_[key] = result;
   return result;

@@ -260,3 +260,54 @@ def test_large_batch_properties(gpu):
     # <conv_w(x), g> is linear in w: d/dw matches backward_weight
     dw = ops.conv_backward_weight(x1, gy, nbr)
     assert abs(float((dw.double() * w.double()).sum() - lhs)) / abs(float(lhs)) < 1e-5
+
+
+@pytest.mark.parametrize("D,ks,dil,n", [(3, 3, 1, 20000), (3, 5, 1, 3000), (2, 3, 2, 4000), (4, 3, 1, 2500), (3, 1, 1, 500)])
+def test_self_map_builder_equals_general_builder(gpu, D, ks, dil, n):
+    """The half-probe builder for stride-1 self maps gives the same neighbour table, CSR pointer
+    and pair lists as the general builder."""
+    from riemannengine_b200 import ops
+    from tests.gpu_backend import dev_coords
+    O = OracleBackend()
+    c = _random_cloud(50 + D, n, D, -9, 9, 2, dup_frac=0)
+    c = c[O.insert_and_map(c)[0]]
+    off = O.region_offsets([ks] * D, [dil] * D, [1] * D)
+    assert ops.offsets_point_symmetric(off)
+    t = ops.table_build(dev_coords(c))
+    a = ops.kmap_build(t, t.coords, off)
+    b = ops.kmap_build(t, t.coords, off, self_map=True)
+    assert torch.equal(a.nbr, b.nbr)
+    assert torch.equal(a.offset_ptr, b.offset_ptr)
+    pa, pb = a.pairs(), b.pairs()
+    assert torch.equal(pa[0], pb[0]) and torch.equal(pa[1], pb[1]) and torch.equal(pa[2], pb[2])
+    assert not ops.offsets_point_symmetric(O.region_offsets([2] * D, [1] * D, [1] * D))
+
+
+def test_tma_gather4_producers_match_cp_async(gpu, monkeypatch):
+    """The optional TMA (tile::gather4) producers of the tensor-core kernel give the same
+    output as the default cp.async producers, bit for bit (same MMA order)."""
+    from riemannengine_b200 import ops, synthetic
+    from tests.gpu_backend import dev_coords
+    c = synthetic.indoor_scene(91, 30000)
+    c = np.concatenate([np.zeros((len(c), 1), np.int32), c], 1)
+    t = ops.table_build(dev_coords(c))
+    nbr = ops.kmap_build(t, t.coords, ops.region_offsets(0, [3] * 3, [1] * 3, [1] * 3), self_map=True).nbr
+    g = torch.Generator(device="cuda").manual_seed(3)
+    for c_in, c_out in ((64, 64), (32, 64), (128, 128)):
+        x = torch.randn(len(c), c_in, device="cuda", generator=g).bfloat16()
+        w = (torch.randn(27, c_in, c_out, device="cuda", generator=g) * 0.05).bfloat16()
+        monkeypatch.delenv("RMN_B200_CONV_TMA", raising=False)
+        y0 = ops.conv_forward(x, w, nbr)
+        d0 = ops.conv_backward_input(y0, w, ops.kmap_transpose(nbr, len(c)))
+        monkeypatch.setenv("RMN_B200_CONV_TMA", "1")
+        y1 = ops.conv_forward(x, w, nbr)
+        d1 = ops.conv_backward_input(y0, w, ops.kmap_transpose(nbr, len(c)))
+        assert torch.equal(y0, y1) and torch.equal(d0, d1)
+    monkeypatch.delenv("RMN_B200_CONV_TMA", raising=False)
+    assert capi_status_ok()
+
+
+def capi_status_ok():
+    import ctypes
+    from riemannengine_b200 import capi
+    return capi.lib().rmn_device_status(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == capi.OK
