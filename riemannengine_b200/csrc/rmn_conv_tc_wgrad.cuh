@@ -51,8 +51,11 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
     uint32_t tmem_cols, float* __restrict__ partial) {
   using C = WgradCfg<CIN, COUT>;
   constexpr int STAGES = C::STAGES, G = C::G;
-  constexpr int A_C8 = 16, B_C8 = COUT / 8;           // 16-byte chunks per stage row
-  constexpr uint32_t A_KGROUP = A_C8 * 128, B_KGROUP = B_C8 * 128;  // bytes of 8 rows in the image
+  constexpr int SWB = (COUT < 64 ? COUT : 64) * 2;     // bytes per dY line
+  constexpr int B_CPL = SWB / 16;                      // chunks per dY line
+  constexpr uint32_t A_ATOM = kRowsPerStage * 128;     // bytes of one 64-channel atom of A' (all stage rows)
+  constexpr uint32_t B_ATOM = kRowsPerStage * SWB;
+  constexpr uint32_t LT_B = SWB == 128 ? 2u : 4u;
   static_assert(128 % CIN == 0 && CIN >= 32 && COUT % 32 == 0 && COUT <= 256, "channel counts");
 
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -94,53 +97,60 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
 
   if (warp < 4) {
     // ------------------------------ producers ------------------------------------------
+    // A' image: one 128-byte swizzled line per (stage row, 64-channel atom of the stacked M axis);
+    // eight consecutive lanes copy one line, i.e. one (CIN >= 64) or two (CIN = 32) gathered rows.
+    // The neighbour indices of a stage are fetched while the previous stage is being issued.
     uint32_t it = 0;
+    auto stage_index = [&](uint32_t blk_, int g_, int i_) -> int32_t {
+      const int unit = (i_ * 4 + warp) * 4 + (lane >> 3);
+      const int r = unit & (kRowsPerStage - 1), atom = unit / kRowsPerStage;
+      const int gg = (atom * 8 + (lane & 7)) / (CIN / 8);
+      const uint32_t j = j_begin + blk_ * kRowsPerStage + r;
+      const int k = (group0 + g_) * G + gg;
+      return (blk_ < n_blocks && j < j_end && k < K) ? __ldg(nbr + (size_t)k * n_dst + j) : -1;
+    };
+    int32_t nxt[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) nxt[i] = n_groups > 0 ? stage_index(0, 0, i) : -1;
     for (uint32_t blk = 0; blk < n_blocks && !timed_out; ++blk) {
       const uint32_t j0 = j_begin + blk * kRowsPerStage;
 #pragma unroll 1
       for (int g = 0; g < n_groups; ++g, ++it) {
+        int32_t idx[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) idx[i] = nxt[i];
+        {
+          const bool last_g = g + 1 == n_groups;
+          const uint32_t nb = last_g ? blk + 1 : blk;
+          const int ng = last_g ? 0 : g + 1;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) nxt[i] = stage_index(nb, ng, i);
+        }
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
         if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
         const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
-        const int k0 = (group0 + g) * G;
-        // A': 8 rows x 4 chunks per warp instruction; chunk m8 = offset-in-group * (CIN/8) + channel chunk
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const int u = i * 4 + warp;
-          const int r = (u >> 2) * 8 + (lane & 7);
-          const int m8 = (u & 3) * 4 + (lane >> 3);
-          const int gg = m8 / (CIN / 8), c = m8 % (CIN / 8);
-          const uint32_t j = j0 + r;
-          int32_t idx = -1;
-          if (j < j_end && k0 + gg < K) idx = __ldg(nbr + (size_t)(k0 + gg) * n_dst + j);
-          cp_async16(a_s + (r >> 3) * A_KGROUP + m8 * 128 + (r & 7) * 16,
-                     feats + (size_t)(idx < 0 ? 0 : idx) * CIN + c * 8, idx < 0 ? 0u : 16u);
+          const int unit = (i * 4 + warp) * 4 + (lane >> 3);
+          const uint32_t r = unit & (kRowsPerStage - 1), atom = unit / kRowsPerStage, c = lane & 7;
+          const int cch = (atom * 8 + c) % (CIN / 8);
+          cp_async16(a_s + atom * A_ATOM + r * 128 + (swz<128>(r, c) << 4),
+                     feats + (size_t)(idx[i] < 0 ? 0 : idx[i]) * CIN + cch * 8, idx[i] < 0 ? 0u : 16u);
         }
-        // B': the 64 dY rows of this block
+        // B': the 64 dY rows of this block, one swizzled line per (row, 64-column atom)
 #pragma unroll
-        for (int i = 0; i < (kRowsPerStage * B_C8) / kProducerThreads; ++i) {
-          const int u = i * 4 + warp;
-          const int r = (u / (B_C8 / 4)) * 8 + (lane & 7);
-          const int n8 = (u % (B_C8 / 4)) * 4 + (lane >> 3);
+        for (int q = tid; q < kRowsPerStage * (COUT / 8); q += kProducerThreads) {
+          const uint32_t c = q % B_CPL, unit = q / B_CPL;
+          const uint32_t r = unit & (kRowsPerStage - 1), atom = unit / kRowsPerStage;
           const uint32_t j = j0 + r;
           const bool ok = j < j_end;
-          cp_async16(b_s + (r >> 3) * B_KGROUP + n8 * 128 + (r & 7) * 16,
-                     grad_out + (size_t)(ok ? j : 0) * COUT + n8 * 8, ok ? 16u : 0u);
+          cp_async16(b_s + atom * B_ATOM + r * SWB + (swz<SWB>(r, c) << 4),
+                     grad_out + (size_t)(ok ? j : 0) * COUT + atom * (SWB / 2) + c * 8, ok ? 16u : 0u);
         }
-        cp_async_commit();
-        if (it >= (uint32_t)kLag) {
-          cp_async_wait<kLag>();
-          fence_proxy_async();
-          mbar_arrive(&full[(it - kLag) % STAGES]);
-        }
+        cp_async_arrive_noinc(&full[s]);  // fires when this thread's copies have landed
       }
     }
     cp_async_wait<0>();
-    fence_proxy_async();
-    if (!timed_out) {
-      const uint32_t pending = it < (uint32_t)kLag ? it : (uint32_t)kLag;
-      for (uint32_t j = it - pending; j < it; ++j) mbar_arrive(&full[j % STAGES]);
-    }
     // ------------------------------ epilogue (same warps) -------------------------------
     if (!timed_out && n_stage > 0 && !mbar_wait(done, 0)) timed_out = true;
     timed_out = __any_sync(0xFFFFFFFFu, timed_out);  // the TMEM loads below are warp-collective
@@ -176,14 +186,15 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
       for (int g = 0; g < n_groups; ++g, ++it) {
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
         if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
+        fence_proxy_async();  // cp.async wrote through the generic proxy; the MMA reads through the async proxy
         tc_fence_after();
         if (lane == 0) {
           const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
 #pragma unroll
           for (int jj = 0; jj < kRowsPerStage / 16; ++jj) {
-            // MN-major operands: 8-element channel groups 128 B apart (SBO), 8-row groups one KGROUP apart (LBO)
-            const uint64_t a_desc = smem_desc(a_s + jj * 2 * A_KGROUP, A_KGROUP, 128);
-            const uint64_t b_desc = smem_desc(b_s + jj * 2 * B_KGROUP, B_KGROUP, 128);
+            // MN-major swizzled operands: 8-row K groups 8 lines apart (SBO), 64-channel atoms one ATOM apart (LBO)
+            const uint64_t a_desc = smem_desc_sw(a_s + jj * 16 * 128, A_ATOM, 8 * 128, 2u);
+            const uint64_t b_desc = smem_desc_sw(b_s + jj * 16 * SWB, B_ATOM, 8 * SWB, LT_B);
             tc_mma_bf16(tmem_base + g * COUT, a_desc, b_desc, IDESC, (blk | (uint32_t)jj) != 0 ? 1u : 0u);
           }
           tc_commit(&empty[s]);
