@@ -428,8 +428,77 @@ def run_product(args) -> None:
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------
+# training step (side measurement, not the headline): hash + kernel map + forward + backward
+# (input and weight gradients) + all-reduce of the weight gradients over the ranks
+# ------------------------------------------------------------------------------------------
+def run_train(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from riemannengine_b200 import capi, distributed as D, engine as E
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = capi.lib()
+    coords_np, feats_np, weights_np = make_batch(rank)
+    coords = torch.from_numpy(coords_np).to(dev)
+    feats = torch.from_numpy(feats_np).to(dev).bfloat16().requires_grad_(True)
+    conv = E.RiemannConvolution(C_IN, C_OUT, kernel_size=KSIZE, dimension=3).to(dev).bfloat16()
+    with torch.no_grad():
+        conv.kernel.copy_(torch.from_numpy(weights_np).to(dev))
+
+    def step():
+        conv.zero_grad(set_to_none=True)
+        feats.grad = None
+        y = conv(E.SparseTensor(feats, coords))
+        y.F.float().square().mean().backward()
+        D.allreduce_gradients(conv.parameters(), average=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    l0 = lib.rmn_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    stats = torch.tensor([e0.elapsed_time(e1), float(len(coords_np))], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx, sm = stats.clone(), stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, vox = float(mx[0]), float(sm[1])
+    else:
+        ms, vox = float(stats[0]), float(stats[1])
+    if rank == 0:
+        print(json.dumps({
+            "metric": "sparse_conv_fwd_bwd_mvoxels_per_s", "value": vox * args.steps / (ms / 1e3) / 1e6, "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
+            "config": dict(workload_config(world), workload="indoor-room batch, 3^3 64->64: hash insert + kernel map + "
+                           "forward + backward (dX, dW) + weight-gradient all-reduce"),
+            "gpu_launches": int(lib.rmn_launch_count() - l0)}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--mode", default="fwd", choices=["fwd", "train"],
+                    help="fwd: the headline forward metric; train: forward + backward + gradient all-reduce")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
@@ -439,6 +508,8 @@ def main() -> None:
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.mode == "train":
+        run_train(args)
     else:
         run_product(args)
 
