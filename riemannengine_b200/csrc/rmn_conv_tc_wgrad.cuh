@@ -41,7 +41,10 @@ struct WgradCfg {
   // six stages where they fit: deeper prefetch, and > 114 KB keeps one CTA (one TMEM owner) per SM
   static constexpr int STAGES = STAGE * 6 <= 200 * 1024 ? 6 : 4;
   static constexpr uint32_t BAR_OFFSET = STAGES * STAGE;
-  static constexpr uint32_t SMEM = BAR_OFFSET + 256;
+  static constexpr int IDX_AHEAD = 3;   // stages of lead of the neighbour-index prefetch
+  static constexpr int IDX_SLOTS = 4;   // ring slots (> IDX_AHEAD)
+  static constexpr uint32_t IDX_OFFSET = BAR_OFFSET + 256;
+  static constexpr uint32_t SMEM = IDX_OFFSET + IDX_SLOTS * kProducerThreads * 8 * 4;
 };
 
 template <int CIN, int COUT>
@@ -99,32 +102,41 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
     // ------------------------------ producers ------------------------------------------
     // A' image: one 128-byte swizzled line per (stage row, 64-channel atom of the stacked M axis);
     // eight consecutive lanes copy one line, i.e. one (CIN >= 64) or two (CIN = 32) gathered rows.
-    // The neighbour indices of a stage are fetched while the previous stage is being issued.
+    // The neighbour indices a thread needs for a stage are copied (4-byte cp.async) into a private
+    // slot of a small shared-memory ring kIdxAhead stages before that stage is issued: the table
+    // read is a streaming DRAM access and must not sit on the critical path of the gathers.
     uint32_t it = 0;
-    auto stage_index = [&](uint32_t blk_, int g_, int i_) -> int32_t {
-      const int unit = (i_ * 4 + warp) * 4 + (lane >> 3);
-      const int r = unit & (kRowsPerStage - 1), atom = unit / kRowsPerStage;
-      const int gg = (atom * 8 + (lane & 7)) / (CIN / 8);
-      const uint32_t j = j_begin + blk_ * kRowsPerStage + r;
-      const int k = (group0 + g_) * G + gg;
-      return (blk_ < n_blocks && j < j_end && k < K) ? __ldg(nbr + (size_t)k * n_dst + j) : -1;
-    };
-    int32_t nxt[8];
+    int32_t* idx_ring = reinterpret_cast<int32_t*>(smem + C::IDX_OFFSET);
+    auto issue_indices = [&](uint32_t v) {
+      const uint32_t blk_ = v / (uint32_t)n_groups;
+      const int g_ = (int)(v - blk_ * (uint32_t)n_groups);
+      int32_t* slot = idx_ring + (v % C::IDX_SLOTS) * (kProducerThreads * 8) + tid * 8;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) nxt[i] = n_groups > 0 ? stage_index(0, 0, i) : -1;
+      for (int i = 0; i < 8; ++i) {
+        const int unit = (i * 4 + warp) * 4 + (lane >> 3);
+        const int r = unit & (kRowsPerStage - 1), atom = unit / kRowsPerStage;
+        const int gg = (atom * 8 + (lane & 7)) / (CIN / 8);
+        const uint32_t j = j_begin + blk_ * kRowsPerStage + r;
+        const int k = (group0 + g_) * G + gg;
+        if (blk_ < n_blocks && j < j_end && k < K)
+          cp_async4(smem_u32(slot + i), nbr + (size_t)k * n_dst + j);
+        else
+          slot[i] = -1;
+      }
+      cp_async_commit();
+    };
+    for (uint32_t v = 0; v < (uint32_t)C::IDX_AHEAD; ++v) issue_indices(v);
     for (uint32_t blk = 0; blk < n_blocks && !timed_out; ++blk) {
       const uint32_t j0 = j_begin + blk * kRowsPerStage;
 #pragma unroll 1
       for (int g = 0; g < n_groups; ++g, ++it) {
+        issue_indices(it + C::IDX_AHEAD);
+        cp_async_wait<C::IDX_AHEAD>();  // the indices of stage `it` (and all older copies) have landed
         int32_t idx[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) idx[i] = nxt[i];
         {
-          const bool last_g = g + 1 == n_groups;
-          const uint32_t nb = last_g ? blk + 1 : blk;
-          const int ng = last_g ? 0 : g + 1;
+          const int32_t* slot = idx_ring + (it % C::IDX_SLOTS) * (kProducerThreads * 8) + tid * 8;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) nxt[i] = stage_index(nb, ng, i);
+          for (int i = 0; i < 8; ++i) idx[i] = slot[i];
         }
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
         if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }

@@ -115,6 +115,9 @@ class KernelMap:
         self._nbr_in = nbr_in
         self._parent = parent               # set on a swapped view
         self._pairs = None
+        # stride-1 self map with a point-symmetric region: nbr_in[k] == nbr_out[K-1-k], so the
+        # input-gradient pass reuses nbr_out with the kernel flipped along its offset axis
+        self.self_symmetric = False
 
     @property
     def nbr_in(self) -> torch.Tensor:
@@ -270,6 +273,7 @@ class CoordinateManager:
             off = ops.region_offsets(region_type, ks, kd, in_map.tensor_stride, custom)
             res = ops.kmap_build(in_map.table, out_map.coords, off, self_map=in_map is out_map)
             kmap = KernelMap(res.nbr, in_map.size, out_map.size, res)
+            kmap.self_symmetric = in_map is out_map and ops.offsets_point_symmetric(off)
         else:
             swapped_key = (out_key.get_key(), in_key.get_key(), tuple(ks), tuple(kst), tuple(kd), region_type,
                            False, bool(is_pool), None if custom is None else custom.tobytes())
@@ -520,7 +524,10 @@ class _SparseConvolutionFunction(torch.autograd.Function):
         grad_out = grad_out.contiguous()
         g_feat = g_kernel = None
         if ctx.needs_input_grad[0]:
-            g_feat = ops.conv_backward_input(grad_out, kernel, kmap.nbr_in)
+            if kmap.self_symmetric:
+                g_feat = ops.conv_backward_input(grad_out, kernel.flip(0), kmap.nbr_out)
+            else:
+                g_feat = ops.conv_backward_input(grad_out, kernel, kmap.nbr_in)
         if ctx.needs_input_grad[1]:
             g_kernel = ops.conv_backward_weight(features, grad_out, kmap.nbr_out).to(kernel.dtype)
         return g_feat, g_kernel, None

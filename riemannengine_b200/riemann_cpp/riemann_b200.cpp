@@ -318,6 +318,7 @@ std::shared_ptr<KernelMap> CoordinateManager::kernel_map(const CoordinateMapKey&
                 static_cast<const int32_t*>(ptr(d_off)), K, static_cast<int32_t*>(ptr(result->nbr_out)),
                 static_cast<int64_t*>(ptr(result->offset_ptr)), ptr(result->workspace), ws_bytes, current_stream()),
           self_symmetric ? "rmn_kmap_build_self" : "rmn_kmap_build");
+    result->self_symmetric = self_symmetric;
   }
   kernel_maps_[key] = result;
   return result;
@@ -523,10 +524,11 @@ at::Tensor conv_backward_weight(const at::Tensor& feats_in, const at::Tensor& gr
 class SparseConvolutionAutograd : public torch::autograd::Function<SparseConvolutionAutograd> {
 public:
   static at::Tensor forward(torch::autograd::AutogradContext* ctx, at::Tensor features, at::Tensor kernel,
-                            at::Tensor nbr_out, at::Tensor nbr_in) {
+                            at::Tensor nbr_out, at::Tensor nbr_in, bool flip_kernel) {
     ctx->save_for_backward({features, kernel});
     ctx->saved_data["nbr_out"] = nbr_out;
     ctx->saved_data["nbr_in"] = nbr_in;
+    ctx->saved_data["flip_kernel"] = flip_kernel;
     return conv_forward(features, kernel, nbr_out);
   }
   static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
@@ -536,9 +538,10 @@ public:
     auto nbr_in = ctx->saved_data["nbr_in"].toTensor();
     auto grad = grad_outputs[0].contiguous();
     at::Tensor g_feat, g_kernel;
-    if (ctx->needs_input_grad(0)) g_feat = conv_backward_input(grad, saved[1], nbr_in);
+    if (ctx->needs_input_grad(0))
+      g_feat = conv_backward_input(grad, ctx->saved_data["flip_kernel"].toBool() ? saved[1].flip(0) : saved[1], nbr_in);
     if (ctx->needs_input_grad(1)) g_kernel = conv_backward_weight(saved[0], grad, nbr_out).to(saved[1].scalar_type());
-    return {g_feat, g_kernel, at::Tensor(), at::Tensor()};
+    return {g_feat, g_kernel, at::Tensor(), at::Tensor(), at::Tensor()};
   }
 };
 
@@ -547,8 +550,10 @@ public:
 at::Tensor sparse_convolution(const at::Tensor& features, const at::Tensor& kernel,
                               const std::shared_ptr<KernelMap>& kmap) {
   // the inverse table is cached in the kernel map; it is only needed when the features want a gradient
-  at::Tensor nbr_in = features.requires_grad() ? kmap->nbr_in() : at::empty({0}, kmap->nbr_out.options());
-  return SparseConvolutionAutograd::apply(features, kernel, kmap->nbr_out, nbr_in);
+  at::Tensor nbr_in = kmap->self_symmetric
+                          ? kmap->nbr_out
+                          : (features.requires_grad() ? kmap->nbr_in() : at::empty({0}, kmap->nbr_out.options()));
+  return SparseConvolutionAutograd::apply(features, kernel, kmap->nbr_out, nbr_in, kmap->self_symmetric);
 }
 
 // ---------------------------------------------------------------------------------------------

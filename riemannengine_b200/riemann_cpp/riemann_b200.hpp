@@ -82,6 +82,9 @@ struct KernelMap {
   at::Tensor offset_ptr;  // int64 [K+1] device, of the probe that produced nbr_out (undefined on a swapped view)
   at::Tensor workspace;
   std::shared_ptr<KernelMap> parent;  // set on a swapped view
+  // stride-1 self map with a point-symmetric region: nbr_in[k] == nbr_out[K-1-k], so the input
+  // gradient reuses nbr_out with the kernel flipped along its offset axis
+  bool self_symmetric = false;
 
   at::Tensor const& nbr_in();
   // (offset_ptr on the host, in rows, out rows)
