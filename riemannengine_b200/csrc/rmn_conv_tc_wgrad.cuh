@@ -23,7 +23,10 @@ namespace rmn {
 namespace tc {
 
 constexpr int kRowsPerStage = 64;
-constexpr int kWgradThreads = 160;  // 4 producer/epilogue warps + 1 MMA warp
+constexpr int kWgProducerWarps = 16;  // gather warps (the first four also run the epilogue)
+constexpr int kWgProducers = kWgProducerWarps * 32;
+constexpr int kWgIdxPerThread = 32 / kWgProducerWarps * 4 / 4;  // A' lines per thread and stage
+constexpr int kWgradThreads = kWgProducers + 32;
 
 constexpr uint32_t instr_desc_mn(int m, int n) {
   // D fp32, A/B bf16, both operands MN-major
@@ -44,7 +47,7 @@ struct WgradCfg {
   static constexpr int IDX_AHEAD = 3;   // stages of lead of the neighbour-index prefetch
   static constexpr int IDX_SLOTS = 4;   // ring slots (> IDX_AHEAD)
   static constexpr uint32_t IDX_OFFSET = BAR_OFFSET + 256;
-  static constexpr uint32_t SMEM = IDX_OFFSET + IDX_SLOTS * kProducerThreads * 8 * 4;
+  static constexpr uint32_t SMEM = IDX_OFFSET + IDX_SLOTS * kWgProducers * kWgIdxPerThread * 4;
 };
 
 template <int CIN, int COUT>
@@ -78,14 +81,14 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full[s], kProducerThreads);
+      mbar_init(&full[s], kWgProducers);
       mbar_init(&empty[s], 1);
     }
     mbar_init(done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     fence_proxy_async();
   }
-  if (warp == 4) {
+  if (warp == kWgProducerWarps) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
                  "r"(tmem_cols)
                  : "memory");
@@ -98,7 +101,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
   const uint32_t smem_base = smem_u32(smem);
   bool timed_out = false;
 
-  if (warp < 4) {
+  if (warp < kWgProducerWarps) {
     // ------------------------------ producers ------------------------------------------
     // A' image: one 128-byte swizzled line per (stage row, 64-channel atom of the stacked M axis);
     // eight consecutive lanes copy one line, i.e. one (CIN >= 64) or two (CIN = 32) gathered rows.
@@ -110,10 +113,10 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
     auto issue_indices = [&](uint32_t v) {
       const uint32_t blk_ = v / (uint32_t)n_groups;
       const int g_ = (int)(v - blk_ * (uint32_t)n_groups);
-      int32_t* slot = idx_ring + (v % C::IDX_SLOTS) * (kProducerThreads * 8) + tid * 8;
+      int32_t* slot = idx_ring + (v % C::IDX_SLOTS) * (kWgProducers * kWgIdxPerThread) + tid * kWgIdxPerThread;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int unit = (i * 4 + warp) * 4 + (lane >> 3);
+      for (int i = 0; i < kWgIdxPerThread; ++i) {
+        const int unit = (i * kWgProducerWarps + warp) * 4 + (lane >> 3);
         const int r = unit & (kRowsPerStage - 1), atom = unit / kRowsPerStage;
         const int gg = (atom * 8 + (lane & 7)) / (CIN / 8);
         const uint32_t j = j_begin + blk_ * kRowsPerStage + r;
@@ -132,18 +135,19 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
       for (int g = 0; g < n_groups; ++g, ++it) {
         issue_indices(it + C::IDX_AHEAD);
         cp_async_wait<C::IDX_AHEAD>();  // the indices of stage `it` (and all older copies) have landed
-        int32_t idx[8];
+        int32_t idx[kWgIdxPerThread];
         {
-          const int32_t* slot = idx_ring + (it % C::IDX_SLOTS) * (kProducerThreads * 8) + tid * 8;
+          const int32_t* slot =
+              idx_ring + (it % C::IDX_SLOTS) * (kWgProducers * kWgIdxPerThread) + tid * kWgIdxPerThread;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) idx[i] = slot[i];
+          for (int i = 0; i < kWgIdxPerThread; ++i) idx[i] = slot[i];
         }
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
         if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
         const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int unit = (i * 4 + warp) * 4 + (lane >> 3);
+        for (int i = 0; i < kWgIdxPerThread; ++i) {
+          const int unit = (i * kWgProducerWarps + warp) * 4 + (lane >> 3);
           const uint32_t r = unit & (kRowsPerStage - 1), atom = unit / kRowsPerStage, c = lane & 7;
           const int cch = (atom * 8 + c) % (CIN / 8);
           cp_async16(a_s + atom * A_ATOM + r * 128 + (swz<128>(r, c) << 4),
@@ -151,7 +155,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
         }
         // B': the 64 dY rows of this block, one swizzled line per (row, 64-column atom)
 #pragma unroll
-        for (int q = tid; q < kRowsPerStage * (COUT / 8); q += kProducerThreads) {
+        for (int q = tid; q < kRowsPerStage * (COUT / 8); q += kWgProducers) {
           const uint32_t c = q % B_CPL, unit = q / B_CPL;
           const uint32_t r = unit & (kRowsPerStage - 1), atom = unit / kRowsPerStage;
           const uint32_t j = j0 + r;
@@ -163,7 +167,8 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
       }
     }
     cp_async_wait<0>();
-    // ------------------------------ epilogue (same warps) -------------------------------
+    // ------------------------------ epilogue (first four producer warps) ----------------
+    if (warp < 4) {
     if (!timed_out && n_stage > 0 && !mbar_wait(done, 0)) timed_out = true;
     timed_out = __any_sync(0xFFFFFFFFu, timed_out);  // the TMEM loads below are warp-collective
     tc_fence_after();
@@ -189,6 +194,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
                                  __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
         }
       }
+    }
     }
   } else {
     // ------------------------------ MMA issuer -----------------------------------------
@@ -221,7 +227,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
   if (timed_out) atomicExch(&g_tc_status, (uint32_t)RMN_ERR_TIMEOUT);
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kWgProducerWarps) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols)
                  : "memory");
