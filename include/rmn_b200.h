@@ -247,6 +247,17 @@ int rmn_conv_forward(const void *d_feats, uint32_t n_src, int c_in, const void *
                      int c_out, const int32_t *d_nbr, uint32_t n_dst, void *d_out, int dtype,
                      void *stream);
 
+/* rmn_conv_forward with a fused per-channel epilogue:
+ *   out[j, c] = act((sum_k feats[nbr[k, j], :] @ weights[k])[c] * scale[c] + shift[c])
+ * d_scale / d_shift: fp32 [c_out] device arrays or NULL (1 / 0); relu != 0 applies max(., 0).
+ * shift alone is the layer's bias add (engine/nn/conv.cpp:135-136); scale + shift is an
+ * inference-mode batch norm folded with the bias (engine/nn/normalization.hpp:11-34), relu the
+ * activation that follows it in the reference's blocks (engine/nn/residual.cpp:44-52). The
+ * reference runs these as separate passes over [N, C]. */
+int rmn_conv_forward_fused(const void *d_feats, uint32_t n_src, int c_in, const void *d_weights, int K,
+                           int c_out, const int32_t *d_nbr, uint32_t n_dst, void *d_out, int dtype,
+                           const float *d_scale, const float *d_shift, int relu, void *stream);
+
 /* grad_feats[i, :] = sum_k grad_out[nbr_t[k, i], :] @ weights[k]^T
  * d_nbr_t: [K, n_src] of destination rows (rmn_kmap_transpose of the forward table). */
 int rmn_conv_backward_input(const void *d_grad_out, uint32_t n_dst, int c_out,

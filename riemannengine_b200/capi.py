@@ -45,6 +45,8 @@ SIGNATURES = {
     "rmn_kmap_transpose": (c_int, [c_void_p, c_uint32, c_int, c_uint32, c_void_p, c_void_p]),
     "rmn_conv_forward": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_int, c_void_p, c_uint32,
                                  c_void_p, c_int, c_void_p]),
+    "rmn_conv_forward_fused": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_int, c_void_p, c_uint32,
+                                       c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "rmn_conv_backward_input": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_int, c_void_p, c_uint32,
                                         c_void_p, c_int, c_void_p]),
     "rmn_conv_backward_weight_workspace_bytes": (c_size_t, [c_uint32, c_int, c_int, c_int, c_int]),

@@ -4,7 +4,8 @@
 
 namespace rmn {
 int simt_conv_forward(const void* feats, int c_in, const void* w, int K, int c_out,
-                      const int32_t* nbr, uint32_t n_dst, void* out, int dtype, cudaStream_t stream);
+                      const int32_t* nbr, uint32_t n_dst, void* out, int dtype, const float* ep_scale,
+                      const float* ep_shift, int ep_relu, cudaStream_t stream);
 int simt_conv_backward_input(const void* grad_out, int c_out, const void* w, int K, int c_in,
                              const int32_t* nbr_t, uint32_t n_src, void* grad_feats, int dtype,
                              cudaStream_t stream);
@@ -13,7 +14,8 @@ int simt_conv_backward_weight(const void* feats, int c_in, const void* grad_out,
                               int c_out, const int32_t* nbr, int K, float* dw, int dtype,
                               void* workspace, cudaStream_t stream);
 int tc_conv(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
-            int c_col, bool transposed_weights, void* out, cudaStream_t stream);
+            int c_col, bool transposed_weights, void* out, const float* ep_scale, const float* ep_shift, int ep_relu,
+            cudaStream_t stream);
 int tc_read_status(cudaStream_t stream, uint32_t* status);
 int tc_conv_wgrad(const void* feats, const void* grad_out, const int32_t* nbr, uint32_t n_dst, int K, int c_in,
                   int c_out, float* dw, void* workspace, size_t workspace_bytes, size_t* need,
@@ -72,22 +74,27 @@ static bool conv_args_ok(const void* a, const void* w, const int32_t* nbr, const
          c_in <= 65536 && c_out <= 65536 && (dtype == RMN_F32 || dtype == RMN_BF16);
 }
 
+extern "C" int rmn_conv_forward_fused(const void* d_feats, uint32_t n_src, int c_in, const void* d_weights, int K,
+                                      int c_out, const int32_t* d_nbr, uint32_t n_dst, void* d_out, int dtype,
+                                      const float* d_scale, const float* d_shift, int relu, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (n_dst == 0) return RMN_OK;
+  if (!conv_args_ok(n_src ? d_feats : d_out, d_weights, d_nbr, d_out, K, c_in, c_out, dtype)) return RMN_ERR_BAD_ARG;
+  if (dtype == RMN_BF16 && use_tensor_cores() && n_src > 0) {
+    const int st = tc_conv(d_feats, n_src, d_weights, d_nbr, n_dst, K, c_in, c_out, false, d_out, d_scale, d_shift,
+                           relu, stream);
+    if (st != RMN_ERR_UNSUPPORTED) return st;
+  }
+  // (with no source rows every neighbour entry is -1: the SIMT kernel then writes act(shift))
+  return simt_conv_forward(d_feats, c_in, d_weights, K, c_out, d_nbr, n_dst, d_out, dtype, d_scale, d_shift, relu,
+                           stream);
+}
+
 extern "C" int rmn_conv_forward(const void* d_feats, uint32_t n_src, int c_in,
                                 const void* d_weights, int K, int c_out, const int32_t* d_nbr,
                                 uint32_t n_dst, void* d_out, int dtype, void* stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
-  if (n_dst == 0) return RMN_OK;
-  if (n_src == 0) {
-    if (!d_out || (dtype != RMN_F32 && dtype != RMN_BF16)) return RMN_ERR_BAD_ARG;
-    RMN_CUDA_TRY(cudaMemsetAsync(d_out, 0, (size_t)n_dst * c_out * (dtype == RMN_F32 ? 4 : 2), stream));
-    return RMN_OK;
-  }
-  if (!conv_args_ok(d_feats, d_weights, d_nbr, d_out, K, c_in, c_out, dtype)) return RMN_ERR_BAD_ARG;
-  if (dtype == RMN_BF16 && use_tensor_cores()) {
-    const int st = tc_conv(d_feats, n_src, d_weights, d_nbr, n_dst, K, c_in, c_out, false, d_out, stream);
-    if (st != RMN_ERR_UNSUPPORTED) return st;
-  }
-  return simt_conv_forward(d_feats, c_in, d_weights, K, c_out, d_nbr, n_dst, d_out, dtype, stream);
+  return rmn_conv_forward_fused(d_feats, n_src, c_in, d_weights, K, c_out, d_nbr, n_dst, d_out, dtype, nullptr,
+                                nullptr, 0, stream_);
 }
 
 extern "C" int rmn_conv_backward_input(const void* d_grad_out, uint32_t n_dst, int c_out,
@@ -104,7 +111,8 @@ extern "C" int rmn_conv_backward_input(const void* d_grad_out, uint32_t n_dst, i
   if (!conv_args_ok(d_grad_out, d_weights, d_nbr_t, d_grad_feats, K, c_in, c_out, dtype))
     return RMN_ERR_BAD_ARG;
   if (dtype == RMN_BF16 && use_tensor_cores()) {
-    const int st = tc_conv(d_grad_out, n_dst, d_weights, d_nbr_t, n_src, K, c_out, c_in, true, d_grad_feats, stream);
+    const int st = tc_conv(d_grad_out, n_dst, d_weights, d_nbr_t, n_src, K, c_out, c_in, true, d_grad_feats, nullptr, nullptr, 0,
+                           stream);
     if (st != RMN_ERR_UNSUPPORTED) return st;
   }
   return simt_conv_backward_input(d_grad_out, c_out, d_weights, K, c_in, d_nbr_t, n_src,

@@ -31,7 +31,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) k_conv_gather_gemm(
     const T* __restrict__ src, const T* __restrict__ w, const int32_t* __restrict__ nbr,
     uint32_t n_dst, int K, int c_red, int c_col, long long ws_k, int ws_red, int ws_col,
-    T* __restrict__ out) {
+    T* __restrict__ out, const float* __restrict__ ep_scale, const float* __restrict__ ep_shift, int ep_relu) {
   __shared__ float As[TK][TM + 4];
   __shared__ float Bs[TK][TN + 4];
   __shared__ int32_t s_idx[TM];
@@ -96,7 +96,14 @@ __global__ void __launch_bounds__(256) k_conv_gather_gemm(
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
-      if (n < c_col) out[(size_t)row * c_col + n] = from_f32<T>(acc[i][j]);
+      if (n < c_col) {
+        // fused epilogue: out = act(acc * scale + shift)
+        float f = acc[i][j];
+        if (ep_scale) f *= __ldg(ep_scale + n);
+        if (ep_shift) f += __ldg(ep_shift + n);
+        if (ep_relu) f = fmaxf(f, 0.f);
+        out[(size_t)row * c_col + n] = from_f32<T>(f);
+      }
     }
   }
 }
@@ -194,21 +201,23 @@ inline uint32_t wgrad_chunks(uint32_t n_dst) {
 template <typename T>
 int launch_gather_gemm(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, int K,
                        int c_red, int c_col, long long ws_k, int ws_red, int ws_col, void* out,
-                       cudaStream_t stream) {
+                       const float* ep_scale, const float* ep_shift, int ep_relu, cudaStream_t stream) {
   dim3 grid((n_dst + TM - 1) / TM, (c_col + TN - 1) / TN);
   k_conv_gather_gemm<T><<<grid, 256, 0, stream>>>((const T*)src, (const T*)w, nbr, n_dst, K, c_red,
-                                                  c_col, ws_k, ws_red, ws_col, (T*)out);
+                                                  c_col, ws_k, ws_red, ws_col, (T*)out, ep_scale, ep_shift, ep_relu);
   RMN_LAUNCH_CHECK();
   return RMN_OK;
 }
 
 int simt_conv_forward(const void* feats, int c_in, const void* w, int K, int c_out,
-                      const int32_t* nbr, uint32_t n_dst, void* out, int dtype,
-                      cudaStream_t stream) {
+                      const int32_t* nbr, uint32_t n_dst, void* out, int dtype, const float* ep_scale,
+                      const float* ep_shift, int ep_relu, cudaStream_t stream) {
   const long long ws_k = (long long)c_in * c_out;
   if (dtype == RMN_F32)
-    return launch_gather_gemm<float>(feats, w, nbr, n_dst, K, c_in, c_out, ws_k, c_out, 1, out, stream);
-  return launch_gather_gemm<__nv_bfloat16>(feats, w, nbr, n_dst, K, c_in, c_out, ws_k, c_out, 1, out, stream);
+    return launch_gather_gemm<float>(feats, w, nbr, n_dst, K, c_in, c_out, ws_k, c_out, 1, out, ep_scale, ep_shift,
+                                     ep_relu, stream);
+  return launch_gather_gemm<__nv_bfloat16>(feats, w, nbr, n_dst, K, c_in, c_out, ws_k, c_out, 1, out, ep_scale,
+                                           ep_shift, ep_relu, stream);
 }
 
 int simt_conv_backward_input(const void* grad_out, int c_out, const void* w, int K, int c_in,
@@ -216,8 +225,10 @@ int simt_conv_backward_input(const void* grad_out, int c_out, const void* w, int
                              cudaStream_t stream) {
   const long long ws_k = (long long)c_in * c_out;
   if (dtype == RMN_F32)
-    return launch_gather_gemm<float>(grad_out, w, nbr_t, n_src, K, c_out, c_in, ws_k, 1, c_out, grad_feats, stream);
-  return launch_gather_gemm<__nv_bfloat16>(grad_out, w, nbr_t, n_src, K, c_out, c_in, ws_k, 1, c_out, grad_feats, stream);
+    return launch_gather_gemm<float>(grad_out, w, nbr_t, n_src, K, c_out, c_in, ws_k, 1, c_out, grad_feats, nullptr,
+                                     nullptr, 0, stream);
+  return launch_gather_gemm<__nv_bfloat16>(grad_out, w, nbr_t, n_src, K, c_out, c_in, ws_k, 1, c_out, grad_feats,
+                                           nullptr, nullptr, 0, stream);
 }
 
 size_t simt_wgrad_workspace_bytes(uint32_t n_dst, int K, int c_in, int c_out) {

@@ -66,7 +66,8 @@ struct Cfg {
   static constexpr uint32_t STAGE = A_BYTES + B_BYTES;
   static constexpr int STAGES = STAGE * 5 <= 216 * 1024 ? 5 : (STAGE * 4 <= 216 * 1024 ? 4 : 3);
   static constexpr uint32_t BAR_OFFSET = STAGES * STAGE;
-  static constexpr uint32_t SMEM = BAR_OFFSET + 256;
+  static constexpr uint32_t EP_OFFSET = BAR_OFFSET + 256;  // 2 * 256 floats of epilogue scale / shift
+  static constexpr uint32_t SMEM = EP_OFFSET + 2 * 256 * 4;
   static constexpr uint32_t TMEM_COLS = pow2_at_least(2 * T * CC);
 };
 
@@ -78,7 +79,9 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
                                                             const int32_t* __restrict__ nbr,
                                                             uint32_t n_dst, int K,
                                                             __nv_bfloat16* __restrict__ out,
-                                                            uint32_t n_super) {
+                                                            uint32_t n_super,
+                                                            const float* __restrict__ ep_scale,
+                                                            const float* __restrict__ ep_shift, int ep_relu) {
   using C = Cfg<CR, CC>;
   constexpr int STAGES = C::STAGES, KB = C::KB, NKB = C::NKB, T = C::T, SWA = C::SWA;
   constexpr int kFwdProducerWarps = C::PRODUCER_WARPS, kFwdProducers = C::PRODUCERS;
@@ -101,8 +104,15 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
   uint64_t* tmem_full = empty + STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  // fused epilogue out = act(acc * scale + shift): per-channel scale | shift, staged once per CTA
+  float* s_ep = reinterpret_cast<float*>(smem + C::EP_OFFSET);
+  const bool has_ep = ep_scale != nullptr || ep_shift != nullptr || ep_relu != 0;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (has_ep && tid < CC) {
+    s_ep[tid] = ep_scale ? __ldg(ep_scale + tid) : 1.f;
+    s_ep[CC + tid] = ep_shift ? __ldg(ep_shift + tid) : 0.f;
+  }
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -238,6 +248,14 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
           uint32_t r[32];
           tc_ld32(tmem_base + ((quad * 32u) << 16) + acc * (T * CC) + t * CC + c0, r);
           tc_wait_ld();
+          if (has_ep) {
+#pragma unroll
+            for (int v = 0; v < 32; ++v) {
+              float f = fmaf(__uint_as_float(r[v]), s_ep[c0 + v], s_ep[CC + c0 + v]);
+              if (ep_relu) f = fmaxf(f, 0.f);
+              r[v] = __float_as_uint(f);
+            }
+          }
           if (row < n_dst) {
             uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * CC + c0);
 #pragma unroll
@@ -273,7 +291,7 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
 
 template <int CR, int CC, bool kWT>
 int launch(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, void* out,
-           cudaStream_t stream) {
+           const float* ep_scale, const float* ep_shift, int ep_relu, cudaStream_t stream) {
   using C = Cfg<CR, CC>;
   auto kern = k_conv_tc<CR, CC, kWT>;
   static bool configured[64] = {};
@@ -292,7 +310,7 @@ int launch(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, i
   uint32_t grid = (uint32_t)sms * per_sm;
   if (grid > n_super) grid = n_super;
   kern<<<grid, C::THREADS, C::SMEM, stream>>>((const __nv_bfloat16*)src, (const __nv_bfloat16*)w, nbr, n_dst, K,
-                                               (__nv_bfloat16*)out, n_super);
+                                               (__nv_bfloat16*)out, n_super, ep_scale, ep_shift, ep_relu);
   RMN_LAUNCH_CHECK();
   return RMN_OK;
 }
@@ -319,21 +337,23 @@ static bool use_tma() {
 
 template <int CR, int CC, bool kWT>
 static int launch_best(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, uint32_t n_dst, int K,
-                       void* out, cudaStream_t stream) {
-  if (use_tma()) {
+                       void* out, const float* ep_scale, const float* ep_shift, int ep_relu, cudaStream_t stream) {
+  if (use_tma() && !ep_scale && !ep_shift && !ep_relu) {
     const int st = tc::launch_tma<CR, CC, kWT>(src, n_src, w, nbr, n_dst, K, out, stream);
     if (st != RMN_ERR_UNSUPPORTED) return st;
   }
-  return tc::launch<CR, CC, kWT>(src, w, nbr, n_dst, K, out, stream);
+  return tc::launch<CR, CC, kWT>(src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream);
 }
 
 // Returns RMN_ERR_UNSUPPORTED when no tensor-core instantiation covers the shape.
 int tc_conv(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
-            int c_col, bool transposed_weights, void* out, cudaStream_t stream) {
+            int c_col, bool transposed_weights, void* out, const float* ep_scale, const float* ep_shift, int ep_relu,
+            cudaStream_t stream) {
 #define RMN_TC_CASE(R, Cc)                                                                            \
   if (c_red == R && c_col == Cc)                                                                      \
-    return transposed_weights ? launch_best<R, Cc, true>(src, n_src, w, nbr, n_dst, K, out, stream)   \
-                              : launch_best<R, Cc, false>(src, n_src, w, nbr, n_dst, K, out, stream);
+    return transposed_weights                                                                         \
+               ? launch_best<R, Cc, true>(src, n_src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream)  \
+               : launch_best<R, Cc, false>(src, n_src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream);
   RMN_TC_CASE(32, 32)
   RMN_TC_CASE(32, 64)
   RMN_TC_CASE(64, 32)

@@ -512,10 +512,12 @@ class _SparseConvolutionFunction(torch.autograd.Function):
     engine/nn/conv.cpp:47-64)."""
 
     @staticmethod
-    def forward(ctx, features, kernel, kmap: KernelMap):
+    def forward(ctx, features, kernel, kmap: KernelMap, bias=None):
         ctx.kmap = kmap
+        ctx.has_bias = bias is not None
         ctx.save_for_backward(features, kernel)
-        return ops.conv_forward(features, kernel, kmap.nbr_out)
+        # the bias add is fused into the convolution's epilogue
+        return ops.conv_forward(features, kernel, kmap.nbr_out, shift=bias)
 
     @staticmethod
     def backward(ctx, grad_out):
@@ -530,11 +532,42 @@ class _SparseConvolutionFunction(torch.autograd.Function):
                 g_feat = ops.conv_backward_input(grad_out, kernel, kmap.nbr_in)
         if ctx.needs_input_grad[1]:
             g_kernel = ops.conv_backward_weight(features, grad_out, kmap.nbr_out).to(kernel.dtype)
-        return g_feat, g_kernel, None
+        g_bias = None
+        if ctx.has_bias and ctx.needs_input_grad[3]:
+            g_bias = grad_out.sum(0, keepdim=True)
+        return g_feat, g_kernel, None, g_bias
 
 
-def sparse_convolution(features: torch.Tensor, kernel: torch.Tensor, kmap: KernelMap) -> torch.Tensor:
-    return _SparseConvolutionFunction.apply(features, kernel, kmap)
+def sparse_convolution(features: torch.Tensor, kernel: torch.Tensor, kmap: KernelMap,
+                       bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    return _SparseConvolutionFunction.apply(features, kernel, kmap, bias)
+
+
+def fused_conv_bn_relu(input: "SparseTensor", conv, bn: Optional[torch.nn.BatchNorm1d] = None,
+                       relu: bool = True) -> "SparseTensor":
+    """Inference-only conv -> batch norm (running statistics) -> ReLU as ONE kernel: the norm's
+    affine and the layer's bias are folded into the convolution epilogue. Equals
+    ``relu(bn(conv(input).F))`` with ``bn`` in eval mode (the reference's blocks run these as
+    three passes, engine/nn/residual.cpp:44-52)."""
+    base = conv.base if hasattr(conv, "base") else conv
+    with torch.no_grad():
+        scale = shift = None
+        bias = base.bias.reshape(-1).float() if base.bias is not None else None
+        if bn is not None:
+            if bn.training:
+                raise RuntimeError("fused_conv_bn_relu folds running statistics: call bn.eval() first")
+            inv = torch.rsqrt(bn.running_var.float() + bn.eps)
+            scale = inv * (bn.weight.float() if bn.weight is not None else 1.0)
+            shift = -bn.running_mean.float() * scale
+            if bn.bias is not None:
+                shift = shift + bn.bias.float()
+            if bias is not None:
+                shift = shift + bias * scale
+        else:
+            shift = bias
+        out_key, kmap = base._output_key_and_map(input)
+        feats = ops.conv_forward(input.F, base.kernel, kmap.nbr_out, scale=scale, shift=shift, relu=relu)
+    return SparseTensor(feats, out_key, input.coordinate_manager)
 
 
 class RiemannConvolutionBase(torch.nn.Module):
@@ -570,7 +603,8 @@ class RiemannConvolutionBase(torch.nn.Module):
             if self.bias is not None:
                 self.bias.uniform_(-bound, bound)
 
-    def forward(self, input: SparseTensor) -> SparseTensor:
+    def _output_key_and_map(self, input: SparseTensor):
+        """Key arithmetic of conv.cpp:104-132 plus the (cached) kernel map."""
         if input.dimension != self.dimension:
             raise RuntimeError("Input dimension mismatch")
         if input.F.size(1) != self.in_channels:
@@ -592,10 +626,12 @@ class RiemannConvolutionBase(torch.nn.Module):
         kmap = manager.kernel_map(input.coordinate_map_key, out_key, params.kernel_size, params.kernel_stride,
                                   params.kernel_dilation, params.region_type, params.region_offsets,
                                   self.is_transpose, False)
-        result = sparse_convolution(input.F, self.kernel, kmap)
-        if self.bias is not None:
-            result = result + self.bias
-        return SparseTensor(result, out_key, manager)
+        return out_key, kmap
+
+    def forward(self, input: SparseTensor) -> SparseTensor:
+        out_key, kmap = self._output_key_and_map(input)
+        result = sparse_convolution(input.F, self.kernel, kmap, self.bias)
+        return SparseTensor(result, out_key, input.coordinate_manager)
 
 
 class _ConvWrapper(torch.nn.Module):

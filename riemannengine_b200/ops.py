@@ -229,8 +229,11 @@ def _check_conv(feats: torch.Tensor, weights: torch.Tensor, what: str) -> None:
         raise RuntimeError(f"expected {what} and weights to have the same dtype, got {feats.dtype} and {weights.dtype}")
 
 
-def conv_forward(feats: torch.Tensor, weights: torch.Tensor, nbr: torch.Tensor) -> torch.Tensor:
-    """out[j] = sum_k feats[nbr[k, j]] @ weights[k] (rmn_conv_forward)."""
+def conv_forward(feats: torch.Tensor, weights: torch.Tensor, nbr: torch.Tensor,
+                 scale: Optional[torch.Tensor] = None, shift: Optional[torch.Tensor] = None,
+                 relu: bool = False) -> torch.Tensor:
+    """out[j] = act((sum_k feats[nbr[k, j]] @ weights[k]) * scale + shift) (rmn_conv_forward_fused);
+    ``scale`` / ``shift`` are per-output-channel vectors (any float dtype, used as fp32) or None."""
     _check_conv(feats, weights, "features")
     feats, weights = feats.contiguous(), weights.contiguous()
     K, c_in, c_out = (int(s) for s in weights.shape)
@@ -238,10 +241,21 @@ def conv_forward(feats: torch.Tensor, weights: torch.Tensor, nbr: torch.Tensor) 
         raise RuntimeError("Input channel count does not match convolution")
     n_dst = int(nbr.size(1))
     out = torch.empty((n_dst, c_out), dtype=feats.dtype, device=feats.device)
+
+    def vec(v):
+        if v is None:
+            return None
+        v = v.detach().reshape(-1).to(device=feats.device, dtype=torch.float32).contiguous()
+        if v.numel() != c_out:
+            raise RuntimeError("epilogue vectors must have one entry per output channel")
+        return v
+
+    sc, sh = vec(scale), vec(shift)
     with torch.cuda.device(feats.device):
-        capi.check(capi.lib().rmn_conv_forward(_ptr(feats), int(feats.size(0)), c_in, _ptr(weights), K, c_out,
-                                               _ptr(nbr), n_dst, _ptr(out), _dtype_code(feats), _stream()),
-                   "rmn_conv_forward")
+        capi.check(capi.lib().rmn_conv_forward_fused(_ptr(feats), int(feats.size(0)), c_in, _ptr(weights), K, c_out,
+                                                     _ptr(nbr), n_dst, _ptr(out), _dtype_code(feats), _ptr(sc),
+                                                     _ptr(sh), int(bool(relu)), _stream()),
+                   "rmn_conv_forward_fused")
     return out
 
 

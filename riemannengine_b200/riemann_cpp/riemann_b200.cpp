@@ -474,7 +474,9 @@ KernelGenerator::KernelParams KernelGenerator::get_kernel(const stride_type& ten
 // ---------------------------------------------------------------------------------------------
 namespace {
 
-at::Tensor conv_forward(const at::Tensor& feats_in, const at::Tensor& kernel_in, const at::Tensor& nbr) {
+// bias (if defined) is folded into the kernel's epilogue as a per-channel shift
+at::Tensor conv_forward(const at::Tensor& feats_in, const at::Tensor& kernel_in, const at::Tensor& nbr,
+                        const at::Tensor& bias = at::Tensor()) {
   TORCH_CHECK(feats_in.is_cuda() && kernel_in.is_cuda(), "features and kernel must be CUDA tensors");
   TORCH_CHECK(feats_in.scalar_type() == kernel_in.scalar_type(), "expected features and kernel to have the same dtype");
   auto feats = feats_in.contiguous(), kernel = kernel_in.contiguous();
@@ -482,10 +484,16 @@ at::Tensor conv_forward(const at::Tensor& feats_in, const at::Tensor& kernel_in,
   const int K = static_cast<int>(kernel.size(0)), c_in = static_cast<int>(kernel.size(1)),
             c_out = static_cast<int>(kernel.size(2));
   auto out = at::empty({nbr.size(1), c_out}, feats.options());
-  check(rmn_conv_forward(ptr(feats), static_cast<uint32_t>(feats.size(0)), c_in, ptr(kernel), K, c_out,
-                         static_cast<const int32_t*>(ptr(nbr)), static_cast<uint32_t>(nbr.size(1)), ptr(out),
-                         dtype_code(feats), current_stream()),
-        "rmn_conv_forward");
+  at::Tensor shift;
+  if (bias.defined()) {
+    shift = bias.detach().reshape({-1}).to(at::kFloat).contiguous();
+    TORCH_CHECK(shift.numel() == c_out, "bias must have one entry per output channel");
+  }
+  check(rmn_conv_forward_fused(ptr(feats), static_cast<uint32_t>(feats.size(0)), c_in, ptr(kernel), K, c_out,
+                               static_cast<const int32_t*>(ptr(nbr)), static_cast<uint32_t>(nbr.size(1)), ptr(out),
+                               dtype_code(feats), nullptr, static_cast<const float*>(ptr(shift)), 0,
+                               current_stream()),
+        "rmn_conv_forward_fused");
   return out;
 }
 
@@ -524,12 +532,13 @@ at::Tensor conv_backward_weight(const at::Tensor& feats_in, const at::Tensor& gr
 class SparseConvolutionAutograd : public torch::autograd::Function<SparseConvolutionAutograd> {
 public:
   static at::Tensor forward(torch::autograd::AutogradContext* ctx, at::Tensor features, at::Tensor kernel,
-                            at::Tensor nbr_out, at::Tensor nbr_in, bool flip_kernel) {
+                            at::Tensor nbr_out, at::Tensor nbr_in, bool flip_kernel, at::Tensor bias) {
     ctx->save_for_backward({features, kernel});
+    ctx->saved_data["has_bias"] = bias.defined();
     ctx->saved_data["nbr_out"] = nbr_out;
     ctx->saved_data["nbr_in"] = nbr_in;
     ctx->saved_data["flip_kernel"] = flip_kernel;
-    return conv_forward(features, kernel, nbr_out);
+    return conv_forward(features, kernel, nbr_out, bias);
   }
   static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
                                                  torch::autograd::variable_list grad_outputs) {
@@ -541,19 +550,21 @@ public:
     if (ctx->needs_input_grad(0))
       g_feat = conv_backward_input(grad, ctx->saved_data["flip_kernel"].toBool() ? saved[1].flip(0) : saved[1], nbr_in);
     if (ctx->needs_input_grad(1)) g_kernel = conv_backward_weight(saved[0], grad, nbr_out).to(saved[1].scalar_type());
-    return {g_feat, g_kernel, at::Tensor(), at::Tensor(), at::Tensor()};
+    at::Tensor g_bias;
+    if (ctx->saved_data["has_bias"].toBool() && ctx->needs_input_grad(5)) g_bias = grad.sum(0, /*keepdim=*/true);
+    return {g_feat, g_kernel, at::Tensor(), at::Tensor(), at::Tensor(), g_bias};
   }
 };
 
 }  // namespace
 
 at::Tensor sparse_convolution(const at::Tensor& features, const at::Tensor& kernel,
-                              const std::shared_ptr<KernelMap>& kmap) {
+                              const std::shared_ptr<KernelMap>& kmap, const at::Tensor& bias) {
   // the inverse table is cached in the kernel map; it is only needed when the features want a gradient
   at::Tensor nbr_in = kmap->self_symmetric
                           ? kmap->nbr_out
                           : (features.requires_grad() ? kmap->nbr_in() : at::empty({0}, kmap->nbr_out.options()));
-  return SparseConvolutionAutograd::apply(features, kernel, kmap->nbr_out, nbr_in, kmap->self_symmetric);
+  return SparseConvolutionAutograd::apply(features, kernel, kmap->nbr_out, nbr_in, kmap->self_symmetric, bias);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -608,8 +619,7 @@ SparseTensor RiemannConvolutionBaseImpl::forward(const SparseTensor& input) {
   auto kmap = manager->kernel_map(input.coordinate_map_key(), output_key, params.kernel_size, params.kernel_stride,
                                   params.kernel_dilation, params.region_type, params.region_offsets, is_transpose_,
                                   false);
-  auto result = sparse_convolution(input.F(), kernel_, kmap);
-  if (bias_.defined()) result = result + bias_;
+  auto result = sparse_convolution(input.F(), kernel_, kmap, bias_);  // the bias add is fused into the epilogue
   return SparseTensor(std::move(result), output_key, std::move(manager));
 }
 

@@ -204,8 +204,9 @@ private:
 };
 
 // out = sum_k F[in_k] @ W[k] scattered to out_k, with a hand-written backward.
+// (an optional bias [1, C_out] is added inside the kernel's epilogue)
 at::Tensor sparse_convolution(const at::Tensor& features, const at::Tensor& kernel,
-                              const std::shared_ptr<KernelMap>& kmap);
+                              const std::shared_ptr<KernelMap>& kmap, const at::Tensor& bias = at::Tensor());
 
 // Helpers with the reference's argument list (autodiff/compat.hpp:89-96, 125-132): run one
 // (transposed) convolution over explicit keys and write the resulting key into *out_key.

@@ -89,3 +89,17 @@ def test_cpp_bf16_layer(C):
     fb = torch.from_numpy(feats).bfloat16().float().numpy()
     r = parity.run_pipeline(OracleBackend(f64=True), coords, fb, w, 3, 3, 1, 1)
     assert parity.rel_l2(y.F.detach().float().cpu().numpy(), r["out_feats"]) <= 1e-2
+
+
+def test_cpp_bias_is_fused_and_has_gradient(C):
+    coords, feats = _inputs(c=4, seed=12)
+    f = torch.from_numpy(feats).cuda().requires_grad_(True)
+    x = C.SparseTensor(f, torch.from_numpy(coords).cuda())
+    conv = C.RiemannConvolution(4, 6, kernel_size=3, bias=True, dimension=3)
+    conv.to("cuda")
+    y = conv(x)
+    y.F.sum().backward()
+    r = parity.run_pipeline(OracleBackend(f64=True), coords, feats, conv.kernel.detach().cpu().numpy(), 3, 3, 1, 1)
+    want = r["out_feats"] + conv.bias.detach().cpu().numpy().astype(np.float64)
+    assert rel_max(y.F.detach().cpu().numpy(), want) <= 1e-4
+    assert torch.allclose(conv.bias.grad, torch.full_like(conv.bias.grad, float(len(y))))

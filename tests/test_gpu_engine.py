@@ -151,3 +151,37 @@ def test_state_dict_round_trip_reproduces_output():
     assert set(a.state_dict()) == {"base.kernel", "base.bias"}
     b.load_state_dict(a.state_dict())
     assert torch.allclose(a(x).F, b(x).F, atol=1e-6)
+
+
+@pytest.mark.parametrize("dtype,c_in,c_out,tol", [(torch.float32, 6, 10, 1e-5), (torch.bfloat16, 64, 64, 2e-2),
+                                                  (torch.bfloat16, 32, 128, 2e-2)])
+def test_fused_conv_bn_relu_matches_unfused(dtype, c_in, c_out, tol):
+    """conv -> BatchNorm1d(eval) -> ReLU folded into the convolution epilogue equals the three
+    separate passes (reference blocks: engine/nn/residual.cpp:44-52)."""
+    from riemannengine_b200 import engine as E
+    torch.manual_seed(1)
+    x, _, _, _ = _make(n=2500, c=c_in, seed=21)
+    x = x.to(dtype)
+    conv = E.RiemannConvolution(c_in, c_out, kernel_size=3, bias=True, dimension=3).cuda().to(dtype)
+    bn = torch.nn.BatchNorm1d(c_out).cuda()
+    with torch.no_grad():
+        bn.running_mean.uniform_(-0.5, 0.5)
+        bn.running_var.uniform_(0.5, 2.0)
+        bn.weight.uniform_(0.5, 1.5)
+        bn.bias.uniform_(-0.3, 0.3)
+    bn.eval()
+    with torch.no_grad():
+        plain = E.RiemannConvolution(c_in, c_out, kernel_size=3, bias=False, dimension=3).cuda().to(dtype)
+        plain.kernel.copy_(conv.kernel)
+        acc = plain(x).F.float() + conv.bias.float()
+        want = torch.relu(bn(acc))
+        got = E.fused_conv_bn_relu(x, conv, bn, relu=True)
+        assert got.coordinate_map_key == x.coordinate_map_key
+        err = (got.F.float() - want).norm() / want.norm()
+        assert float(err) <= tol
+        # bias-only epilogue is what the layer's own forward uses
+        y = conv(x).F.float()
+        assert float((y - acc).norm() / acc.norm()) <= tol
+    bn.train()
+    with pytest.raises(RuntimeError, match="eval"):
+        E.fused_conv_bn_relu(x, conv, bn)
