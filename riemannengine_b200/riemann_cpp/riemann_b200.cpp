@@ -485,7 +485,7 @@ at::Tensor conv_forward(const at::Tensor& feats_in, const at::Tensor& kernel_in,
             c_out = static_cast<int>(kernel.size(2));
   auto out = at::empty({nbr.size(1), c_out}, feats.options());
   at::Tensor shift;
-  if (bias.defined()) {
+  if (bias.defined() && bias.numel() > 0) {
     shift = bias.detach().reshape({-1}).to(at::kFloat).contiguous();
     TORCH_CHECK(shift.numel() == c_out, "bias must have one entry per output channel");
   }
@@ -534,7 +534,7 @@ public:
   static at::Tensor forward(torch::autograd::AutogradContext* ctx, at::Tensor features, at::Tensor kernel,
                             at::Tensor nbr_out, at::Tensor nbr_in, bool flip_kernel, at::Tensor bias) {
     ctx->save_for_backward({features, kernel});
-    ctx->saved_data["has_bias"] = bias.defined();
+    ctx->saved_data["has_bias"] = bias.numel() > 0;
     ctx->saved_data["nbr_out"] = nbr_out;
     ctx->saved_data["nbr_in"] = nbr_in;
     ctx->saved_data["flip_kernel"] = flip_kernel;
@@ -551,7 +551,7 @@ public:
       g_feat = conv_backward_input(grad, ctx->saved_data["flip_kernel"].toBool() ? saved[1].flip(0) : saved[1], nbr_in);
     if (ctx->needs_input_grad(1)) g_kernel = conv_backward_weight(saved[0], grad, nbr_out).to(saved[1].scalar_type());
     at::Tensor g_bias;
-    if (ctx->saved_data["has_bias"].toBool() && ctx->needs_input_grad(5)) g_bias = grad.sum(0, /*keepdim=*/true);
+    if (ctx->saved_data["has_bias"].toBool() && ctx->needs_input_grad(4)) g_bias = grad.sum(0, /*keepdim=*/true);
     return {g_feat, g_kernel, at::Tensor(), at::Tensor(), at::Tensor(), g_bias};
   }
 };
@@ -564,7 +564,9 @@ at::Tensor sparse_convolution(const at::Tensor& features, const at::Tensor& kern
   at::Tensor nbr_in = kmap->self_symmetric
                           ? kmap->nbr_out
                           : (features.requires_grad() ? kmap->nbr_in() : at::empty({0}, kmap->nbr_out.options()));
-  return SparseConvolutionAutograd::apply(features, kernel, kmap->nbr_out, nbr_in, kmap->self_symmetric, bias);
+  // (autograd functions take defined tensors only: an empty tensor stands for "no bias")
+  at::Tensor bias_arg = bias.defined() ? bias : at::empty({0}, kernel.options());
+  return SparseConvolutionAutograd::apply(features, kernel, kmap->nbr_out, nbr_in, kmap->self_symmetric, bias_arg);
 }
 
 // ---------------------------------------------------------------------------------------------
