@@ -46,6 +46,18 @@ def workload_config(n_gpus: int) -> dict:
     }
 
 
+def captured_traffic(*names: str):
+    """DRAM bytes per launch (read + write) of the named kernels from the committed ncu capture of
+    this exact workload (profiles/dram_traffic_indoor8x150k.json); None if the file is missing."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic_indoor8x150k.json")
+    try:
+        with open(path) as f:
+            t = json.load(f)
+        return int(sum(t[n]["dram_read_bytes"] + t[n]["dram_write_bytes"] for n in names))
+    except (OSError, KeyError, ValueError):
+        return None
+
+
 def load_peaks() -> dict:
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -380,11 +392,12 @@ def run_product(args) -> None:
     if t_fwd >= t_kmap + t_pairs:
         roofline = {"kernel": "conv_forward", "bound": "tensor", "achieved": fwd_tflops,
                     "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": fwd_tflops / peaks["bf16_tflops"],
-                    "traffic": None, "peak_source": peaks["source"],
+                    "traffic": captured_traffic("conv_forward"), "peak_source": peaks["source"],
                     "algorithmic": f"2*P*Cin*Cout = {flops:.3e} flop per launch"}
     else:
         roofline = {"kernel": "kmap_probe+pairs", "bound": "hbm", "achieved": kmap_gbs, "peak": peaks["hbm_gbs"],
-                    "unit": "GB/s", "frac": kmap_gbs / peaks["hbm_gbs"], "traffic": None,
+                    "unit": "GB/s", "frac": kmap_gbs / peaks["hbm_gbs"],
+                    "traffic": captured_traffic("kmap_probe", "kmap_pairs"),
                     "peak_source": peaks["source"],
                     "algorithmic": f"N*4W + N*K*32 + 8P = {bytes_kmap:.3e} B per launch"}
 
