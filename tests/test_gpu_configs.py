@@ -1,0 +1,107 @@
+"""Parity on seeded stand-ins of the other benchmark configurations, at sizes the oracle finishes
+in seconds: LiDAR-like sweeps (very sparse, large coordinate range, 4 input channels, strided
+down + transposed up with weight gradients) and the 4-D spatio-temporal 3^4 = 81-offset kernel."""
+import numpy as np
+import pytest
+import torch
+
+from tests import parity
+from tests.parity import OracleBackend, rel_l2, rel_max
+
+pytestmark = pytest.mark.gpu
+
+
+def test_lidar_sweep_network_fp32_matches_oracle():
+    """3^3 4->32 on a 120K-point sweep voxelised at 0.1 m, then 2^3 stride-2 down 32->64 and the
+    transposed 2^3 up 64->32 (kernel maps, outputs and all gradients)."""
+    from riemannengine_b200 import synthetic
+    from tests.gpu_backend import GpuBackend
+    pts = synthetic.lidar_sweep(3001)
+    c = np.concatenate([np.zeros((len(pts), 1), np.int32), pts], 1)
+    assert 100_000 < len(c) < 125_000 and c[:, 1:].min() < -600 and c[:, 1:].max() > 600
+    O, G = OracleBackend(f64=True), GpuBackend(torch.float32)
+    f = synthetic.features(3100, len(c), 4)
+    w = synthetic.conv_weights(3101, 27, 4, 32)
+    r0 = parity.run_pipeline(O, c, f, w, 3, 3, 1, 1)
+    r1 = parity.run_pipeline(G, c, f, w, 3, 3, 1, 1)
+    parity.assert_kernel_maps_equal(tuple(r1[k] for k in ("kmap_ptr", "kmap_in", "kmap_out")),
+                                    tuple(r0[k] for k in ("kmap_ptr", "kmap_in", "kmap_out")))
+    for key in ("out_feats", "grad_feats", "grad_weights"):
+        assert rel_max(r1[key], r0[key]) <= 1e-4, key
+    f2 = synthetic.features(3102, len(c), 32)
+    wd = synthetic.conv_weights(3103, 8, 32, 64)
+    wu = synthetic.conv_weights(3104, 8, 64, 32, transpose=True)
+    d0 = parity.run_pipeline(O, c, f2, wd, 3, 2, 2, 1, wu)
+    d1 = parity.run_pipeline(G, c, f2, wd, 3, 2, 2, 1, wu)
+    assert (d0["out_coords"] == d1["out_coords"]).all()
+    for a in ("kmap", "kmap2"):
+        parity.assert_kernel_maps_equal(tuple(d1[a + s] for s in ("_ptr", "_in", "_out")),
+                                        tuple(d0[a + s] for s in ("_ptr", "_in", "_out")))
+    for key in ("out_feats", "up_feats", "grad_feats", "grad_weights", "grad_weights2"):
+        assert rel_max(d1[key], d0[key]) <= 1e-4, key
+
+
+def test_lidar_sweep_bf16_tensor_core_layers():
+    """The bf16 layers of the sweep network that run on the tensor cores: 3^3 32->64, 2^3 s2
+    64->64 down and the transposed 2^3 128->64 up, against the fp64 oracle on rounded inputs."""
+    from riemannengine_b200 import synthetic
+    from tests.gpu_backend import GpuBackend
+    pts = synthetic.lidar_sweep(3002, n_points=40_000)
+    c = np.concatenate([np.zeros((len(pts), 1), np.int32), pts], 1)
+    O, G = OracleBackend(f64=True), GpuBackend(torch.bfloat16)
+    rnd = lambda a: torch.from_numpy(a).bfloat16().float().numpy()  # noqa: E731
+    f = synthetic.features(3200, len(c), 32)
+    w = synthetic.conv_weights(3201, 27, 32, 64)
+    r0 = parity.run_pipeline(O, c, rnd(f), rnd(w), 3, 3, 1, 1)
+    r1 = parity.run_pipeline(G, c, f, w, 3, 3, 1, 1)
+    assert rel_l2(r1["out_feats"], r0["out_feats"]) <= 1e-2
+    f2 = synthetic.features(3202, len(c), 64)
+    wd = synthetic.conv_weights(3203, 8, 64, 128)
+    wu = synthetic.conv_weights(3204, 8, 128, 64, transpose=True)
+    d0 = parity.run_pipeline(O, c, rnd(f2), rnd(wd), 3, 2, 2, 1, rnd(wu))
+    d1 = parity.run_pipeline(G, c, f2, wd, 3, 2, 2, 1, wu)
+    assert rel_l2(d1["out_feats"], d0["out_feats"]) <= 1e-2
+    assert rel_l2(d1["up_feats"], d0["up_feats"]) <= 2e-2  # two bf16 layers deep
+
+
+def test_spatiotemporal_4d_81_offsets():
+    """(b, x, y, z, t) coordinates, 3^4 kernel, 32 -> 32: maps exact, fp32 within 1e-4, bf16 within 1e-2."""
+    from riemannengine_b200 import synthetic
+    from tests.gpu_backend import GpuBackend
+    c = synthetic.spatiotemporal_batch(n_batch=2, n_frames=4, n_voxels=3000, seed=4000)
+    assert c.shape[1] == 5
+    O = OracleBackend(f64=True)
+    f = synthetic.features(4100, len(c), 32)
+    w = synthetic.conv_weights(4101, 81, 32, 32)
+    r0 = parity.run_pipeline(O, c, f, w, 4, 3, 1, 1)
+    assert len(r0["kmap_ptr"]) == 82
+    r1 = parity.run_pipeline(GpuBackend(torch.float32), c, f, w, 4, 3, 1, 1)
+    parity.assert_kernel_maps_equal(tuple(r1[k] for k in ("kmap_ptr", "kmap_in", "kmap_out")),
+                                    tuple(r0[k] for k in ("kmap_ptr", "kmap_in", "kmap_out")))
+    for key in ("out_feats", "grad_feats", "grad_weights"):
+        assert rel_max(r1[key], r0[key]) <= 1e-4, key
+    rnd = lambda a: torch.from_numpy(a).bfloat16().float().numpy()  # noqa: E731
+    rb0 = parity.run_pipeline(O, c, rnd(f), rnd(w), 4, 3, 1, 1)
+    rb1 = parity.run_pipeline(GpuBackend(torch.bfloat16), c, f, w, 4, 3, 1, 1)
+    assert rel_l2(rb1["out_feats"], rb0["out_feats"]) <= 1e-2
+
+
+def test_engine_lidar_unet_slice_runs_and_backpropagates():
+    """conv 4->32 -> conv 32->64 -> down 64->64 -> conv 64->128 -> transposed up 128->64 through the layer
+    interface in bf16 (the shape of the sweep configuration), with finite gradients everywhere."""
+    from riemannengine_b200 import engine as E, synthetic
+    coords = torch.from_numpy(synthetic.lidar_batch(2, seed=3000)).cuda()
+    feats = torch.randn(len(coords), 4, device="cuda").bfloat16().requires_grad_(True)
+    layers = [E.RiemannConvolution(4, 32, 3), E.RiemannConvolution(32, 64, 3), E.RiemannConvolution(64, 64, 2, stride=2),
+              E.RiemannConvolution(64, 128, 3), E.RiemannConvolutionTranspose(128, 64, 2, stride=2)]
+    layers = [m.cuda().bfloat16() for m in layers]
+    x = E.SparseTensor(feats, coords)
+    n0 = len(x)
+    for m in layers:
+        x = m(x)
+        x = E.SparseTensor(torch.relu(x.F), x.coordinate_map_key, x.coordinate_manager)
+    assert len(x) == n0 and x.tensor_stride == [1, 1, 1] and x.F.shape[1] == 64
+    x.F.float().square().mean().backward()
+    assert torch.isfinite(feats.grad.float()).all()
+    for m in layers:
+        assert m.kernel.grad is not None and torch.isfinite(m.kernel.grad.float()).all()
