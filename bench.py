@@ -69,22 +69,64 @@ def load_peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and clock-event (throttle) reasons while the timed region runs: an NVML
+    polling thread (read-only queries, every 2 ms), or nvidia-smi if NVML cannot be loaded."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
+        import threading
         self.proc = None
+        self.thread = None
+        self.samples = []          # (sm_mhz, reasons bitmask)
+        self.max_mhz = None
+        self._stop = threading.Event()
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
-                 "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            # LOCAL_RANK indexes CUDA_VISIBLE_DEVICES; map it to the NVML index
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            nvml_index = int(visible.split(",")[index]) if visible and visible.split(",")[index].isdigit() else index
+            handle = pynvml.nvmlDeviceGetHandleByIndex(nvml_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+
+            def poll():
+                while not self._stop.is_set():
+                    try:
+                        mhz = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                        why = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                        self.samples.append((float(mhz), int(why)))
+                    except Exception:
+                        break
+                    time.sleep(0.002)
+
+            self.thread = threading.Thread(target=poll, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.thread = None
+            try:
+                self.proc = subprocess.Popen(
+                    ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
+                     "-i", str(index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            except OSError:
+                self.proc = None
 
     def stop(self) -> dict:
+        if self.thread is not None:
+            self._stop.set()
+            self.thread.join(timeout=2)
+            n = self._nvml
+            flags = {"hw_slowdown": n.nvmlClocksEventReasonHwSlowdown,
+                     "hw_thermal_slowdown": n.nvmlClocksEventReasonHwThermalSlowdown,
+                     "sw_thermal_slowdown": n.nvmlClocksEventReasonSwThermalSlowdown,
+                     "sw_power_cap": n.nvmlClocksEventReasonSwPowerCap}
+            sm = [s[0] for s in self.samples]
+            reasons = sorted(name for name, bit in flags.items() if any(s[1] & bit for s in self.samples))
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz,
+                    "samples": len(sm), "reasons": reasons, "source": "nvml"}
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock sampling unavailable"]}
         time.sleep(0.06)
         self.proc.terminate()
         try:
@@ -107,7 +149,7 @@ class ClockSampler:
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
 
 
 def make_batch(rank: int):

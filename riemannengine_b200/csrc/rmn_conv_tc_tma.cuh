@@ -7,7 +7,7 @@
 // the tensor), and the W[k] slice is one or two ordinary tiled TMA loads. Completion is
 // tracked by the stage's mbarrier transaction count, so the four producer warps only read
 // indices and issue one instruction per lane and stage, and every stage of shared memory can
-// be in flight. No multicast is used and only this GPU's memory is addressed.
+// be in flight. Every load is CTA-local (one destination CTA) and addresses this GPU's memory only.
 //
 // Included by rmn_conv_tc.cu (needs Cfg<>, swz<> and the helpers of rmn_tc.cuh).
 #pragma once
