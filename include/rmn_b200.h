@@ -89,7 +89,7 @@ size_t rmn_table_build_workspace_bytes(uint32_t n_rows);
  *   (engine/grid/lattice_gpu.cu:160-230) and the uint32->int64 widening of
  *   engine/grid/space.cu:60-80.
  *  d_mapping  [n_rows] int64: first n_unique entries = first-occurrence rows
- *  d_inverse  [n_rows] int64: unique row of every input row
+ *  d_inverse  [n_rows] int64: unique row of every input row; may be NULL (not produced)
  *  d_unique_coords [n_rows, W] int32 or NULL: unique rows in map order
  *    (what CoordinateMapManager::get_coordinates returns,
  *     engine/grid/space_impl.hpp:947-975)

@@ -34,7 +34,7 @@ struct __align__(16) TableHeader {
   uint32_t status;
   uint32_t capacity;   // number of slots (a multiple of 32, about 3 x n_rows)
   uint32_t total_bits;
-  uint32_t reserved;
+  uint32_t n_dups;     // rows that found their key already present (0: unique rows == input rows)
   int32_t mn[RMN_MAX_W];
   int32_t mx[RMN_MAX_W];
   uint32_t bits[RMN_MAX_W];

@@ -31,7 +31,7 @@ __global__ void k_header_init(TableHeader* h, uint32_t W, uint32_t n_rows, uint3
   h->status = RMN_OK;
   h->capacity = capacity;
   h->total_bits = 0;
-  h->reserved = 0;
+  h->n_dups = 0;
   for (int c = 0; c < RMN_MAX_W; ++c) {
     h->mn[c] = INT_MAX;
     h->mx[c] = INT_MIN;
@@ -94,6 +94,21 @@ __global__ void k_plan(TableHeader* h) {
   if (total > 63) h->status = RMN_ERR_RANGE;
 }
 
+// 16-byte atomic compare-and-swap of a whole slot against the empty pattern (all ones); returns
+// the slot's previous content.
+__device__ __forceinline__ void cas_slot(Slot* slot, unsigned long long key, unsigned long long rows,
+                                         unsigned long long& old_key, unsigned long long& old_rows) {
+  asm volatile(
+      "{\n\t.reg .b128 c, d, o;\n\t"
+      "mov.b128 c, {%2, %2};\n\t"
+      "mov.b128 d, {%3, %4};\n\t"
+      "atom.relaxed.gpu.global.cas.b128 o, [%5], c, d;\n\t"
+      "mov.b128 {%0, %1}, o;\n\t}"
+      : "=l"(old_key), "=l"(old_rows)
+      : "l"(~0ull), "l"(key), "l"(rows), "l"(slot)
+      : "memory");
+}
+
 template <int W>
 __global__ void __launch_bounds__(256) k_insert(const int32_t* __restrict__ coords, uint32_t n,
                                                 TableHeader* h, Slot* slots,
@@ -110,11 +125,19 @@ __global__ void __launch_bounds__(256) k_insert(const int32_t* __restrict__ coor
   pk.pack(c, key);
   uint32_t s = hash_key(key, capacity);
   bool placed = false;
+  // One 16-byte compare-and-swap claims a free slot (all ones) with {key, first_row = row,
+  // uid = row}: without duplicates the unique numbering is the row numbering and the slot is
+  // final after this single memory operation. A row that finds its key taken lowers first_row
+  // and counts itself as a duplicate (k_finalize then renumbers).
+  const unsigned long long mine = (unsigned long long)row | ((unsigned long long)row << 32);
   for (uint32_t probe = 0; probe < (capacity >> 3); ++probe) {
-    unsigned long long cur = *reinterpret_cast<volatile unsigned long long*>(&slots[s].key);
-    if (cur == kEmptyKey) cur = atomicCAS(&slots[s].key, kEmptyKey, key);
-    if (cur == kEmptyKey || cur == key) {
-      atomicMin(&slots[s].first_row, row);
+    unsigned long long cur_key, cur_rows;
+    cas_slot(&slots[s], key, mine, cur_key, cur_rows);
+    if (cur_key == kEmptyKey || cur_key == key) {
+      if (cur_key == key) {
+        atomicMin(&slots[s].first_row, row);
+        atomicAdd(&h->n_dups, 1u);
+      }
       slot_of_row[row] = s;
       placed = true;
       break;
@@ -128,6 +151,7 @@ __global__ void __launch_bounds__(kRowsPerBlock) k_count_first(const Slot* __res
                                                               const uint32_t* __restrict__ slot_of_row,
                                                               uint32_t n, const TableHeader* h,
                                                               uint32_t* __restrict__ block_counts) {
+  if (h->n_dups == 0) return;  // no duplicates: nothing to compact (see k_finalize)
   const uint32_t row = blockIdx.x * kRowsPerBlock + threadIdx.x;
   int flag = 0;
   if (row < n && h->status == RMN_OK) flag = slots[slot_of_row[row]].first_row == row;
@@ -135,9 +159,8 @@ __global__ void __launch_bounds__(kRowsPerBlock) k_count_first(const Slot* __res
   if (threadIdx.x == 0) block_counts[blockIdx.x] = (uint32_t)total;
 }
 
-// One block: in-place exclusive scan of counts[n]; the total goes to *total_out.
-__global__ void __launch_bounds__(1024) k_scan_u32(uint32_t* __restrict__ counts, uint32_t n,
-                                                   uint32_t* total_out) {
+// One block of 1024 threads: in-place exclusive scan of counts[n]; the total goes to *total_out.
+__device__ __forceinline__ void scan_u32_block(uint32_t* __restrict__ counts, uint32_t n, uint32_t* total_out) {
   __shared__ uint32_t warp_sums[32];
   const uint32_t per = (n + 1023u) / 1024u;
   const uint32_t begin = min(n, threadIdx.x * per), end = min(n, begin + per);
@@ -172,6 +195,14 @@ __global__ void __launch_bounds__(1024) k_scan_u32(uint32_t* __restrict__ counts
   }
 }
 
+// Exclusive scan of the per-block first-occurrence counts; skipped when there are no duplicates
+// (the counts were not produced then and k_finalize takes its fast path).
+__global__ void __launch_bounds__(1024) k_scan_first_counts(uint32_t* __restrict__ counts, uint32_t n,
+                                                            TableHeader* h) {
+  if (h->n_dups == 0 || h->status != RMN_OK) return;
+  scan_u32_block(counts, n, &h->n_unique);
+}
+
 template <int W>
 __global__ void __launch_bounds__(kRowsPerBlock) k_finalize(
     const int32_t* __restrict__ coords, uint32_t n, const TableHeader* h, Slot* slots,
@@ -180,6 +211,21 @@ __global__ void __launch_bounds__(kRowsPerBlock) k_finalize(
   __shared__ uint32_t warp_counts[kRowsPerBlock / 32];
   if (h->status != RMN_OK) return;
   const uint32_t row = blockIdx.x * kRowsPerBlock + threadIdx.x;
+  if (h->n_dups == 0) {
+    // Fast path (all rows distinct): unique row == input row, already stored in the slots by
+    // k_insert; only the identity mapping and the coordinate copy remain (both streaming).
+    if (row < n) {
+      mapping[row] = (int64_t)row;
+      if (unique_coords) {
+        int32_t c[W];
+        load_row<W>(coords, row, c);
+#pragma unroll
+        for (int i = 0; i < W; ++i) unique_coords[(size_t)row * W + i] = c[i];
+      }
+    }
+    if (row == 0) const_cast<TableHeader*>(h)->n_unique = n;
+    return;
+  }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   uint32_t s = 0;
   int flag = 0;
@@ -211,7 +257,7 @@ __global__ void __launch_bounds__(256) k_inverse(const Slot* __restrict__ slots,
                                                  int64_t* __restrict__ inverse) {
   const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= n || h->status != RMN_OK) return;
-  inverse[row] = (int64_t)slots[slot_of_row[row]].uid;
+  inverse[row] = h->n_dups == 0 ? (int64_t)row : (int64_t)slots[slot_of_row[row]].uid;
 }
 
 template <int W>
@@ -270,7 +316,7 @@ extern "C" int rmn_table_build(const int32_t* d_coords, uint32_t n_rows, int W, 
                                size_t workspace_bytes, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (!d_table || W < 2 || W > RMN_MAX_W || n_rows >= 0x7FFFFFFFu) return RMN_ERR_BAD_ARG;
-  if (n_rows > 0 && (!d_coords || !d_mapping || !d_inverse || !d_workspace)) return RMN_ERR_BAD_ARG;
+  if (n_rows > 0 && (!d_coords || !d_mapping || !d_workspace)) return RMN_ERR_BAD_ARG;
   if (((uintptr_t)d_table & 15) || !coords_aligned(d_coords, W)) return RMN_ERR_BAD_ARG;
   if (table_bytes < rmn_table_bytes(n_rows) ||
       (n_rows > 0 && workspace_bytes < rmn_table_build_workspace_bytes(n_rows)))
@@ -298,14 +344,16 @@ extern "C" int rmn_table_build(const int32_t* d_coords, uint32_t n_rows, int W, 
   RMN_LAUNCH_CHECK();
   k_count_first<<<nb, kRowsPerBlock, 0, stream>>>(slots, slot_of_row, n_rows, h, block_counts);
   RMN_LAUNCH_CHECK();
-  k_scan_u32<<<1, 1024, 0, stream>>>(block_counts, nb, &h->n_unique);
+  k_scan_first_counts<<<1, 1024, 0, stream>>>(block_counts, nb, h);
   RMN_LAUNCH_CHECK();
   RMN_DISPATCH_W(W, k_finalize<kW><<<nb, kRowsPerBlock, 0, stream>>>(
                         d_coords, n_rows, h, slots, slot_of_row, block_counts, d_mapping,
                         d_unique_coords));
   RMN_LAUNCH_CHECK();
-  k_inverse<<<nb, 256, 0, stream>>>(slots, slot_of_row, n_rows, h, d_inverse);
-  RMN_LAUNCH_CHECK();
+  if (d_inverse) {  // optional: only the quantisation modes that average or sample features read it
+    k_inverse<<<nb, 256, 0, stream>>>(slots, slot_of_row, n_rows, h, d_inverse);
+    RMN_LAUNCH_CHECK();
+  }
   return RMN_OK;
 }
 
