@@ -38,6 +38,19 @@
 namespace rmn {
 
 __device__ uint32_t g_tc_status = 0;
+#ifdef RMN_PROF
+__device__ unsigned long long g_prof[16];
+extern "C" int rmn_debug_prof(unsigned long long* out, int reset) {
+  if (out) cudaMemcpyFromSymbol(out, g_prof, sizeof(g_prof));
+  if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(g_prof, z, sizeof(z)); }
+  return 0;
+}
+#define PROF_T0() const long long _t0 = clock64()
+#define PROF_ADD(var) var += clock64() - _t0
+#else
+#define PROF_T0()
+#define PROF_ADD(var)
+#endif
 
 namespace tc {
 
@@ -149,19 +162,34 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
     constexpr int ROWS_PER_INSTR = 32 / A_CPL;
     const uint32_t a_chunk = lane % A_CPL, a_row_sub = lane / A_CPL;
     uint32_t it = 0;
+#ifdef RMN_PROF
+    long long prof_wait = 0; const long long prof_start = clock64();
+#endif
+
     for (uint32_t st = blockIdx.x; st < n_super && !timed_out; st += gridDim.x) {
       const uint32_t row = st * (kTileM * T) + warp * 32 + lane;
       const bool row_ok = has_rows && row < n_dst;
-      int32_t idx_next = row_ok ? __ldg(nbr + row) : -1;
+      // Neighbour indices are fetched four offsets ahead of their use (an L2 round trip is about
+      // one stage long). The window rotates through named registers: no dynamic indexing.
+      auto load_idx = [&](int kk) -> int32_t {
+        return (row_ok && kk < K) ? __ldg(nbr + (size_t)kk * n_dst + row) : -1;
+      };
+      int32_t idx_w0 = load_idx(0), idx_w1 = load_idx(1), idx_w2 = load_idx(2), idx_w3 = load_idx(3);
       for (int k = 0; k < K && !timed_out; ++k) {
-        const int32_t idx = idx_next;
-        if (k + 1 < K) idx_next = row_ok ? __ldg(nbr + (size_t)(k + 1) * n_dst + row) : -1;
+        const int32_t idx = idx_w0;
+        idx_w0 = idx_w1; idx_w1 = idx_w2; idx_w2 = idx_w3;
+        idx_w3 = load_idx(k + 4);
         const __nv_bfloat16* wk = w + (size_t)k * CIN_W * COUT_W;
 #pragma unroll 1
         for (int kb = 0; kb < NKB; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-          if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
+          {
+            PROF_T0();
+            if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
+            PROF_ADD(prof_wait);
+          }
           const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
+
           if (has_rows) {
             // A: a quarter-warp copies the whole line of one gathered row
 #pragma unroll
@@ -175,6 +203,7 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
           } else {
             __syncwarp();
           }
+
           // B: this stage's slice of W[k], one line (and atom) per B_CPL consecutive threads
 #pragma unroll
           for (int q = tid; q < B_LINES * B_ATOMS * B_CPL; q += kFwdProducers) {
@@ -191,47 +220,75 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
         }
       }
     }
+#ifdef RMN_PROF
+    if (lane == 0 && warp == 0) { atomicAdd(&g_prof[0], (unsigned long long)prof_wait); atomicAdd(&g_prof[1], (unsigned long long)(clock64() - prof_start)); }
+#endif
     cp_async_wait<0>();  // nothing may still be writing shared memory when the CTA exits
   } else if (warp == kFwdProducerWarps) {
     // ------------------------------ MMA issuer -----------------------------------------
     constexpr uint32_t IDESC = instr_desc(kTileM, CC, !kWT);
+    // descriptors with a zero start address
+    constexpr uint64_t A_DESC0 = smem_desc_sw_const(16, 8 * SWA, LT_A);
+    constexpr uint64_t B_DESC0 = kWT ? smem_desc_sw_const(16, 8 * SWB, LT_B) : smem_desc_sw_const(B_ATOM_BYTES, 8 * SWB, LT_B);
+    constexpr uint32_t A_DESC_HI = (uint32_t)(A_DESC0 >> 32), B_DESC_HI = (uint32_t)(B_DESC0 >> 32);
     uint32_t it = 0, tile_iter = 0;
+#ifdef RMN_PROF
+    long long prof_wait = 0, prof_wait_acc = 0; const long long prof_start = clock64();
+#endif
     for (uint32_t st = blockIdx.x; st < n_super && !timed_out; st += gridDim.x, ++tile_iter) {
       const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
-      if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { timed_out = true; break; }
+      {
+        PROF_T0();
+        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { timed_out = true; break; }
+        PROF_ADD(prof_wait_acc);
+      }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * (T * CC);
       const uint32_t n_stage = (uint32_t)K * NKB;
       for (uint32_t sg = 0; sg < n_stage; ++sg, ++it) {
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-        if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
+        {
+          PROF_T0();
+          if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
+          PROF_ADD(prof_wait);
+        }
         // the copies were generic-proxy writes; the tensor core reads through the async proxy
         fence_proxy_async();
         tc_fence_after();
-        if (lane == 0) {
-          const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
-#pragma unroll
-          for (int t = 0; t < T; ++t) {
-#pragma unroll
-            for (int j = 0; j < KB / 16; ++j) {
-              // A, K-major swizzled: 8-row groups 8 * SWA apart (SBO); a K step of 16 channels is 32 bytes
-              const uint64_t a_desc = smem_desc_sw(a_s + t * C::A_TILE + j * 32, 16, 8 * SWA, LT_A);
-              uint64_t b_desc;
-              if constexpr (!kWT)  // MN-major: 8-row K groups 8 * SWB apart (SBO), 64-column atoms B_ATOM_BYTES apart (LBO)
-                b_desc = smem_desc_sw(b_s + j * 16 * SWB, B_ATOM_BYTES, 8 * SWB, LT_B);
-              else                 // K-major: 8-row N groups 8 * SWB apart (SBO), K step 32 bytes
-                b_desc = smem_desc_sw(b_s + j * 32, 16, 8 * SWB, LT_B);
-              tc_mma_bf16(d_tmem + t * CC, a_desc, b_desc, IDESC, (sg | (uint32_t)j) != 0 ? 1u : 0u);
+        {
+          // Warp-uniform code, one elected lane issues. Descriptors differ from stage to stage (and
+          // from MMA to MMA) only in the 14-bit start address field: everything else is folded
+          // into constants, one add per operand.
+          const uint32_t a_s = smem_base + s * C::STAGE;
+          const uint32_t a_lo = (a_s >> 4) + (uint32_t)(A_DESC0 & 0xFFFFFFFFu);
+          const uint32_t b_lo = ((a_s + C::A_BYTES) >> 4) + (uint32_t)(B_DESC0 & 0xFFFFFFFFu);
+          static_for<T * (KB / 16)>([&](auto tj) {
+            constexpr int t = decltype(tj)::value / (KB / 16), j = decltype(tj)::value % (KB / 16);
+            {
+              // A, K-major swizzled: 8-row groups 8 * SWA apart (SBO); a K step of 16 channels is 32 bytes.
+              // B forward, MN-major: 8-row K groups 8 * SWB apart (SBO), 64-column atoms B_ATOM_BYTES apart
+              // (LBO), a K step is 16 lines; B backward input, K-major: a K step is 32 bytes.
+              const uint64_t a_desc = ((uint64_t)A_DESC_HI << 32) | (a_lo + (uint32_t)((t * C::A_TILE + j * 32) >> 4));
+              const uint64_t b_desc = ((uint64_t)B_DESC_HI << 32) | (b_lo + (uint32_t)((kWT ? j * 32 : j * 16 * SWB) >> 4));
+              const uint32_t accumulate = (sg | (uint32_t)j) != 0 ? 1u : 0u;
+              // Row tile 0 reads the K slice j of W[k] from shared memory into collector buffer j;
+              // the other row tiles of the stage reuse it (shared-memory bandwidth, which the
+              // gathers and the operand fetches compete for, bounds this kernel).
+              if constexpr (T > 1 && (CC == 64 || CC == 128) && KB / 16 <= 4)  // .ws takes N = 64, 128, 256
+                tc_mma_bf16_ws_elect<j, t == 0 ? 0 : (t == T - 1 ? 2 : 1)>(d_tmem + t * CC, a_desc, b_desc, IDESC, accumulate);
+              else
+                tc_mma_bf16_elect(d_tmem + t * CC, a_desc, b_desc, IDESC, accumulate);
             }
-          }
-          tc_commit(&empty[s]);
+          });
+          tc_commit_elect(&empty[s]);
         }
-        __syncwarp();
       }
       if (timed_out) break;
-      if (lane == 0) tc_commit(&tmem_full[acc]);
-      __syncwarp();
+      tc_commit_elect(&tmem_full[acc]);
     }
+#ifdef RMN_PROF
+    if (lane == 0) { atomicAdd(&g_prof[2], (unsigned long long)prof_wait); atomicAdd(&g_prof[3], (unsigned long long)prof_wait_acc); atomicAdd(&g_prof[4], (unsigned long long)(clock64() - prof_start)); }
+#endif
   } else {
     // ------------------------------ epilogue -------------------------------------------
     const uint32_t quad = warp & 3;  // TMEM lanes [32*quad, 32*quad + 32)

@@ -199,6 +199,9 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
   } else {
     // ------------------------------ MMA issuer -----------------------------------------
     constexpr uint32_t IDESC = instr_desc_mn(128, COUT);
+    constexpr uint64_t A_DESC0 = smem_desc_sw_const(A_ATOM, 8 * 128, 2u);
+    constexpr uint64_t B_DESC0 = smem_desc_sw_const(B_ATOM, 8 * SWB, LT_B);
+    constexpr uint32_t A_DESC_HI = (uint32_t)(A_DESC0 >> 32), B_DESC_HI = (uint32_t)(B_DESC0 >> 32);
     uint32_t it = 0;
     for (uint32_t blk = 0; blk < n_blocks && !timed_out; ++blk) {
       for (int g = 0; g < n_groups; ++g, ++it) {
@@ -206,22 +209,24 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
         if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
         fence_proxy_async();  // cp.async wrote through the generic proxy; the MMA reads through the async proxy
         tc_fence_after();
-        if (lane == 0) {
-          const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
+        {
+          // warp-uniform code, one elected lane issues; descriptors are a constant plus the
+          // operand's start address field
+          const uint32_t a_s = smem_base + s * C::STAGE;
+          const uint32_t a_lo = (a_s >> 4) + (uint32_t)(A_DESC0 & 0xFFFFFFFFu);
+          const uint32_t b_lo = ((a_s + C::A_BYTES) >> 4) + (uint32_t)(B_DESC0 & 0xFFFFFFFFu);
 #pragma unroll
           for (int jj = 0; jj < kRowsPerStage / 16; ++jj) {
             // MN-major swizzled operands: 8-row K groups 8 lines apart (SBO), 64-channel atoms one ATOM apart (LBO)
-            const uint64_t a_desc = smem_desc_sw(a_s + jj * 16 * 128, A_ATOM, 8 * 128, 2u);
-            const uint64_t b_desc = smem_desc_sw(b_s + jj * 16 * SWB, B_ATOM, 8 * SWB, LT_B);
-            tc_mma_bf16(tmem_base + g * COUT, a_desc, b_desc, IDESC, (blk | (uint32_t)jj) != 0 ? 1u : 0u);
+            const uint64_t a_desc = ((uint64_t)A_DESC_HI << 32) | (a_lo + (uint32_t)((jj * 16 * 128) >> 4));
+            const uint64_t b_desc = ((uint64_t)B_DESC_HI << 32) | (b_lo + (uint32_t)((jj * 16 * SWB) >> 4));
+            tc_mma_bf16_elect(tmem_base + g * COUT, a_desc, b_desc, IDESC, (blk | (uint32_t)jj) != 0 ? 1u : 0u);
           }
-          tc_commit(&empty[s]);
+          tc_commit_elect(&empty[s]);
         }
-        __syncwarp();
       }
     }
-    if (!timed_out && lane == 0) tc_commit(done);
-    __syncwarp();
+    if (!timed_out) tc_commit_elect(done);
   }
 
   if (timed_out) atomicExch(&g_tc_status, (uint32_t)RMN_ERR_TIMEOUT);

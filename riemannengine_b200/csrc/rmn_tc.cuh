@@ -4,6 +4,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+#include <utility>
+
 namespace rmn {
 namespace tc {
 
@@ -79,6 +82,46 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
                    smem_u32(bar))
                : "memory");
 }
+// Warp-wide forms: executed by all 32 lanes in converged code, one elected lane issues. With
+// every operand warp-uniform the compiler keeps descriptors in uniform registers; inside an
+// `if (lane == 0)` branch it has to rebuild them in per-thread registers and move each operand
+// across for every instruction.
+__device__ __forceinline__ void tc_commit_elect(uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                  uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Weight-stationary form of the elected MMA: the B operand is kept in collector buffer BUF
+// between instructions, so that row tiles sharing one W[k] slice read it from shared memory once.
+// OP 0 = fill (read B and keep it), 1 = use (reuse the kept B), 2 = lastuse (reuse and release).
+// N must be 64, 128 or 256.
+template <int BUF, int OP>
+__device__ __forceinline__ void tc_mma_bf16_ws_elect(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                     uint32_t idesc, uint32_t accumulate) {
+#define RMN_WS_CASE(B, O, TXT)                                                                       \
+  if constexpr (BUF == B && OP == O)                                                                 \
+    asm volatile("{\n\t.reg .pred p, e;\n\telect.sync _|e, 0xffffffff;\n\tsetp.ne.b32 p, %4, 0;\n\t"    \
+                 "@e tcgen05.mma.ws.cta_group::1.kind::f16.collector::" TXT " [%0], %1, %2, %3, p;\n\t}" \
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)                 \
+                 : "memory");
+  RMN_WS_CASE(0, 0, "b0::fill") RMN_WS_CASE(0, 1, "b0::use") RMN_WS_CASE(0, 2, "b0::lastuse")
+  RMN_WS_CASE(1, 0, "b1::fill") RMN_WS_CASE(1, 1, "b1::use") RMN_WS_CASE(1, 2, "b1::lastuse")
+  RMN_WS_CASE(2, 0, "b2::fill") RMN_WS_CASE(2, 1, "b2::use") RMN_WS_CASE(2, 2, "b2::lastuse")
+  RMN_WS_CASE(3, 0, "b3::fill") RMN_WS_CASE(3, 1, "b3::use") RMN_WS_CASE(3, 2, "b3::lastuse")
+#undef RMN_WS_CASE
+}
 __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                             uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -115,10 +158,28 @@ __device__ __forceinline__ uint64_t smem_desc_sw(uint32_t addr, uint32_t lbo, ui
   return smem_desc(addr, lbo, sbo) | ((uint64_t)layout_type << 61);
 }
 
+// The same descriptor with a zero start address, as a compile-time constant: adding
+// (address >> 4) to its low word gives the descriptor of an operand below 256 KB.
+constexpr uint64_t smem_desc_sw_const(uint32_t lbo, uint32_t sbo, uint32_t layout_type) {
+  return ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) | (1ull << 46) |
+         ((uint64_t)layout_type << 61);
+}
+
 // Instruction descriptor of kind::f16: D fp32, A/B bf16, A K-major, B K- or MN-major.
 constexpr uint32_t instr_desc(int m, int n, bool b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) |
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// f(std::integral_constant<int, 0>{}) ... f(std::integral_constant<int, N - 1>{}): a loop whose
+// index is a constant expression inside the body.
+template <class F, int... I>
+__device__ __forceinline__ void static_for_impl(F&& f, std::integer_sequence<int, I...>) {
+  (f(std::integral_constant<int, I>{}), ...);
+}
+template <int N, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+  static_for_impl(f, std::make_integer_sequence<int, N>{});
 }
 
 constexpr uint32_t pow2_at_least(uint32_t v) {
