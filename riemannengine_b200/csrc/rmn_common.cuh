@@ -39,7 +39,8 @@ struct __align__(16) TableHeader {
   int32_t mx[RMN_MAX_W];
   uint32_t bits[RMN_MAX_W];
   uint32_t shift[RMN_MAX_W];
-  uint32_t pad[24];
+  uint32_t range_blocks_done;  // ticket counter of the range kernel (its last block plans the packing)
+  uint32_t pad[23];
 };
 static_assert(sizeof(TableHeader) == 256, "header must be 256 bytes");
 

@@ -183,9 +183,11 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe_self(
 
 // Hit counts per (offset, 256-row block) for `n_off` offset rows of a neighbour table
 // (the mirrored half of a self map, whose entries were scattered by other blocks).
+// The launch is a no-op unless *pending != 0 (see rmn_kmap_build_self).
 __global__ void __launch_bounds__(kKmapBlock) k_kmap_count_rows(const int32_t* __restrict__ nbr, uint32_t n,
                                                               int n_off, uint32_t* __restrict__ block_counts,
-                                                              uint32_t n_blocks) {
+                                                              uint32_t n_blocks, const uint32_t* pending) {
+  if (*pending == 0) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t row0 = blockIdx.x * kKmapBlock;
   for (int k = warp; k < n_off; k += kKmapBlock / 32) {
@@ -202,10 +204,13 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_count_rows(const int32_t* _
 
 // grid = K blocks of 1024 threads: exclusive scan of block_counts[k][0..n_blocks) in place,
 // totals[k] = number of pairs of offset k.
+// With `pending` given, the launch is a no-op unless *pending != 0.
 __global__ void __launch_bounds__(1024) k_kmap_scan_blocks(uint32_t* __restrict__ block_counts,
                                                            uint32_t n_blocks,
-                                                           uint32_t* __restrict__ totals) {
+                                                           uint32_t* __restrict__ totals,
+                                                           const uint32_t* pending) {
   __shared__ uint32_t warp_sums[32];
+  if (pending && *pending == 0) return;
   uint32_t* counts = block_counts + (size_t)blockIdx.x * n_blocks;
   const uint32_t per = (n_blocks + 1023u) / 1024u;
   const uint32_t begin = min(n_blocks, threadIdx.x * per), end = min(n_blocks, begin + per);
@@ -240,9 +245,14 @@ __global__ void __launch_bounds__(1024) k_kmap_scan_blocks(uint32_t* __restrict_
 }
 
 // one thread: offset_ptr[0..K] = exclusive scan of totals (K is small)
-__global__ void k_kmap_offset_ptr(const uint32_t* __restrict__ totals, int K,
-                                  int64_t* __restrict__ offset_ptr) {
+// mirror_half > 0 (self map): offsets K-1-k and k hold the same number of pairs, so the totals of
+// the mirrored half are copied from the probed half and *pending is set: the per-block counts of
+// the mirrored half, which only the pair lists need, are produced when pair lists are first asked for.
+__global__ void k_kmap_offset_ptr(uint32_t* __restrict__ totals, int K, int64_t* __restrict__ offset_ptr,
+                                  int mirror_half, uint32_t* pending) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  for (int k = K - mirror_half; k < K; ++k) totals[k] = totals[K - 1 - k];
+  *pending = (uint32_t)mirror_half;
   int64_t run = 0;
   for (int k = 0; k < K; ++k) {
     offset_ptr[k] = run;
@@ -261,6 +271,7 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_pairs(
     unsigned long long capacity, uint32_t* __restrict__ overflow) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t row0 = blockIdx.x * kKmapBlock;
+  if (blockIdx.x == 0 && threadIdx.x == 0) overflow[1] = 0;  // the pending block counts were produced before this launch
   for (int k = warp; k < K; k += kKmapBlock / 32) {
     unsigned long long pos =
         (unsigned long long)offset_ptr[k] + block_prefix[(size_t)k * n_blocks + blockIdx.x];
@@ -390,9 +401,9 @@ extern "C" int rmn_kmap_build(const void* d_table, const int32_t* d_query, uint3
   RMN_DISPATCH_W(W, k_kmap_probe<kW><<<nb, kKmapBlock, smem, stream>>>(
                         h, slots, d_query, n_query, d_offsets, K, d_nbr, block_counts, nb));
   RMN_LAUNCH_CHECK();
-  k_kmap_scan_blocks<<<K, 1024, 0, stream>>>(block_counts, nb, totals);
+  k_kmap_scan_blocks<<<K, 1024, 0, stream>>>(block_counts, nb, totals, nullptr);
   RMN_LAUNCH_CHECK();
-  k_kmap_offset_ptr<<<1, 32, 0, stream>>>(totals, K, d_offset_ptr);
+  k_kmap_offset_ptr<<<1, 32, 0, stream>>>(totals, K, d_offset_ptr, 0, totals + K + 1);
   RMN_LAUNCH_CHECK();
   return RMN_OK;
 }
@@ -425,14 +436,10 @@ extern "C" int rmn_kmap_build_self(const void* d_table, const int32_t* d_coords,
   RMN_DISPATCH_W(W, k_kmap_probe_self<kW><<<nb, kKmapBlock, smem, stream>>>(
                         h, slots, d_coords, n_rows, d_offsets, K, d_nbr, block_counts, nb));
   RMN_LAUNCH_CHECK();
-  if (half > 0) {
-    k_kmap_count_rows<<<nb, kKmapBlock, 0, stream>>>(d_nbr + (size_t)(half + 1) * n_rows, n_rows, half,
-                                                     block_counts + (size_t)(half + 1) * nb, nb);
-    RMN_LAUNCH_CHECK();
-  }
-  k_kmap_scan_blocks<<<K, 1024, 0, stream>>>(block_counts, nb, totals);
+  // only the probed half (and the centre) is scanned here; see k_kmap_offset_ptr
+  k_kmap_scan_blocks<<<half + 1, 1024, 0, stream>>>(block_counts, nb, totals, nullptr);
   RMN_LAUNCH_CHECK();
-  k_kmap_offset_ptr<<<1, 32, 0, stream>>>(totals, K, d_offset_ptr);
+  k_kmap_offset_ptr<<<1, 32, 0, stream>>>(totals, K, d_offset_ptr, half, totals + K + 1);
   RMN_LAUNCH_CHECK();
   return RMN_OK;
 }
@@ -449,6 +456,19 @@ extern "C" int rmn_kmap_pairs(const int32_t* d_nbr, uint32_t n_query, int K,
   const uint32_t* block_prefix = reinterpret_cast<const uint32_t*>(d_workspace);
   // the word after the totals flags a capacity overflow (kept for debugging reads)
   uint32_t* overflow = const_cast<uint32_t*>(block_prefix) + (size_t)K * nb + K;
+  // A self map leaves the per-block counts of its mirrored half pending (flag word after the
+  // overflow word): count and scan them now. Both launches return at once for any other map.
+  uint32_t* pending = overflow + 1;
+  const int half = K / 2;
+  if (half > 0) {
+    uint32_t* counts = const_cast<uint32_t*>(block_prefix);
+    k_kmap_count_rows<<<nb, kKmapBlock, 0, stream>>>(d_nbr + (size_t)(K - half) * n_query, n_query, half,
+                                                     counts + (size_t)(K - half) * nb, nb, pending);
+    RMN_LAUNCH_CHECK();
+    k_kmap_scan_blocks<<<half, 1024, 0, stream>>>(counts + (size_t)(K - half) * nb, nb,
+                                                  counts + (size_t)K * nb + (K - half), pending);
+    RMN_LAUNCH_CHECK();
+  }
   k_kmap_pairs<<<nb, kKmapBlock, 0, stream>>>(d_nbr, n_query, K, d_offset_ptr, block_prefix, nb,
                                               d_a_idx, d_q_idx, capacity, overflow);
   RMN_LAUNCH_CHECK();

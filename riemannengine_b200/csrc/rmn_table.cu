@@ -22,7 +22,12 @@ namespace rmn {
 
 constexpr int kRowsPerBlock = 256;
 
-__global__ void k_header_init(TableHeader* h, uint32_t W, uint32_t n_rows, uint32_t capacity) {
+// Fills the slots with the empty pattern (all ones) and initialises the header.
+__global__ void __launch_bounds__(256) k_table_init(TableHeader* h, uint4* __restrict__ slots, uint32_t W,
+                                                    uint32_t n_rows, uint32_t capacity) {
+  const uint4 ones = make_uint4(~0u, ~0u, ~0u, ~0u);
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < capacity; i += gridDim.x * blockDim.x)
+    slots[i] = ones;
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   h->magic = kTableMagic;
   h->W = W;
@@ -32,6 +37,7 @@ __global__ void k_header_init(TableHeader* h, uint32_t W, uint32_t n_rows, uint3
   h->capacity = capacity;
   h->total_bits = 0;
   h->n_dups = 0;
+  h->range_blocks_done = 0;
   for (int c = 0; c < RMN_MAX_W; ++c) {
     h->mn[c] = INT_MAX;
     h->mx[c] = INT_MIN;
@@ -39,6 +45,8 @@ __global__ void k_header_init(TableHeader* h, uint32_t W, uint32_t n_rows, uint3
     h->shift[c] = 0;
   }
 }
+
+__device__ void plan_packing(TableHeader* h);
 
 template <int W>
 __global__ void __launch_bounds__(256) k_range(const int32_t* __restrict__ coords, uint32_t n,
@@ -69,10 +77,21 @@ __global__ void __launch_bounds__(256) k_range(const int32_t* __restrict__ coord
     atomicMin(&h->mn[threadIdx.x], a);
     atomicMax(&h->mx[threadIdx.x], b);
   }
+  // the last block to finish plans the key packing (one launch less than a separate kernel)
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0 && atomicAdd(&h->range_blocks_done, 1u) == gridDim.x - 1) {
+    __threadfence();
+    plan_packing(h);
+  }
 }
 
 __global__ void k_plan(TableHeader* h) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  if (threadIdx.x == 0 && blockIdx.x == 0) plan_packing(h);
+}
+
+// One thread: bit widths and shifts of the packed key from the bounding box in the header.
+__device__ void plan_packing(TableHeader* h) {
   uint32_t total = 0;
   // packing order: spatial columns first (column 1 in the lowest bits: its low three bits pick
   // the position inside a bucket), the batch column last
@@ -80,7 +99,8 @@ __global__ void k_plan(TableHeader* h) {
     const uint32_t c = i + 1 < h->W ? i + 1 : 0;
     uint32_t b = 0;
     if (h->n_rows > 0) {
-      uint32_t span = (uint32_t)h->mx[c] - (uint32_t)h->mn[c];
+      // volatile: the bounds were written by other blocks' atomics
+      uint32_t span = (uint32_t) * (volatile int32_t*)&h->mx[c] - (uint32_t) * (volatile int32_t*)&h->mn[c];
       b = span == 0 ? 0 : 32 - __clz(span);
     } else {
       h->mn[c] = 0;
@@ -324,9 +344,12 @@ extern "C" int rmn_table_build(const int32_t* d_coords, uint32_t n_rows, int W, 
   auto* h = reinterpret_cast<TableHeader*>(d_table);
   auto* slots = reinterpret_cast<Slot*>(reinterpret_cast<char*>(d_table) + sizeof(TableHeader));
   const uint32_t capacity = table_capacity(n_rows);
-  k_header_init<<<1, 32, 0, stream>>>(h, (uint32_t)W, n_rows, capacity);
-  RMN_LAUNCH_CHECK();
-  RMN_CUDA_TRY(cudaMemsetAsync(slots, 0xFF, sizeof(Slot) * (size_t)capacity, stream));
+  {
+    const uint32_t fill_blocks = (capacity + 255u) / 256u;
+    k_table_init<<<fill_blocks < 148u * 8u ? fill_blocks : 148u * 8u, 256, 0, stream>>>(
+        h, reinterpret_cast<uint4*>(slots), (uint32_t)W, n_rows, capacity);
+    RMN_LAUNCH_CHECK();
+  }
   if (n_rows == 0) {
     k_plan<<<1, 32, 0, stream>>>(h);
     RMN_LAUNCH_CHECK();
@@ -337,8 +360,6 @@ extern "C" int rmn_table_build(const int32_t* d_coords, uint32_t n_rows, int W, 
   const uint32_t nb = (n_rows + kRowsPerBlock - 1) / kRowsPerBlock;
   const uint32_t range_blocks = nb < 148u * 8u ? nb : 148u * 8u;
   RMN_DISPATCH_W(W, k_range<kW><<<range_blocks, 256, 0, stream>>>(d_coords, n_rows, h));
-  RMN_LAUNCH_CHECK();
-  k_plan<<<1, 32, 0, stream>>>(h);
   RMN_LAUNCH_CHECK();
   RMN_DISPATCH_W(W, k_insert<kW><<<nb, 256, 0, stream>>>(d_coords, n_rows, h, slots, slot_of_row));
   RMN_LAUNCH_CHECK();

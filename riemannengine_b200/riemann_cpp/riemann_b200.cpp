@@ -125,7 +125,13 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> const& KernelMap::pairs() {
     pairs_ = std::make_tuple(std::get<0>(p), std::get<2>(p), std::get<1>(p));
   } else {
     c10::cuda::CUDAGuard guard(nbr_out.device());
-    auto host_ptr = offset_ptr.cpu();
+    at::Tensor host_ptr;
+    if (offset_ptr_ready.has_value()) {
+      offset_ptr_ready->synchronize();  // the copy was queued before the convolution: normally long done
+      host_ptr = host_offset_ptr.clone();
+    } else {
+      host_ptr = offset_ptr.cpu();
+    }
     const int64_t K = nbr_out.size(0);
     const int64_t total = host_ptr[K].item<int64_t>();
     auto in_idx = at::empty({total}, nbr_out.options());
@@ -319,6 +325,10 @@ std::shared_ptr<KernelMap> CoordinateManager::kernel_map(const CoordinateMapKey&
                 static_cast<int64_t*>(ptr(result->offset_ptr)), ptr(result->workspace), ws_bytes, current_stream()),
           self_symmetric ? "rmn_kmap_build_self" : "rmn_kmap_build");
     result->self_symmetric = self_symmetric;
+    result->host_offset_ptr = at::empty({K + 1}, at::TensorOptions().dtype(at::kLong).pinned_memory(true));
+    result->host_offset_ptr.copy_(result->offset_ptr, /*non_blocking=*/true);
+    result->offset_ptr_ready.emplace(c10::DeviceType::CUDA);
+    result->offset_ptr_ready->record(c10::cuda::getCurrentCUDAStream());
   }
   kernel_maps_[key] = result;
   return result;

@@ -20,6 +20,7 @@
 
 #include <map>
 #include <memory>
+#include <optional>
 #include <string>
 #include <tuple>
 #include <utility>
@@ -81,6 +82,10 @@ struct KernelMap {
   int64_t n_in = 0, n_out = 0;
   at::Tensor offset_ptr;  // int64 [K+1] device, of the probe that produced nbr_out (undefined on a swapped view)
   at::Tensor workspace;
+  // offset_ptr copied to pinned host memory right after the probe, and the event after that copy:
+  // by the time pair lists are asked for, the sizes are on the host without draining the stream
+  at::Tensor host_offset_ptr;
+  std::optional<c10::Event> offset_ptr_ready;
   std::shared_ptr<KernelMap> parent;  // set on a swapped view
   // stride-1 self map with a point-symmetric region: nbr_in[k] == nbr_out[K-1-k], so the input
   // gradient reuses nbr_out with the kernel flipped along its offset axis
