@@ -459,7 +459,7 @@ def run_product(args) -> None:
     else:
         roofline = {"kernel": "kmap_probe+pairs", "bound": "hbm", "achieved": kmap_gbs, "peak": peaks["hbm_gbs"],
                     "unit": "GB/s", "frac": kmap_gbs / peaks["hbm_gbs"],
-                    "traffic": captured_traffic("kmap_probe", "kmap_pairs"),
+                    "traffic": captured_traffic("kmap_probe_self", "kmap_pairs"),
                     "peak_source": peaks["source"],
                     "algorithmic": f"N*4W + N*K*32 + 8P = {bytes_kmap:.3e} B per launch"}
 
