@@ -281,6 +281,39 @@ int rmn_conv_backward_weight(const void *d_feats, uint32_t n_src, int c_in,
                              const int32_t *d_nbr, int K, float *d_grad_weights, int dtype,
                              void *d_workspace, size_t workspace_bytes, void *stream);
 
+/* ----------------------------- local pooling --------------------------------
+ * Pooling modes of rmn_pool_forward / rmn_pool_backward: the three local modes of
+ * PoolingMode (engine/foundation/types.hpp), i.e. RiemannSumPooling / RiemannAvgPooling /
+ * RiemannMaxPooling (engine/nn/pooling.hpp:30-77). */
+#define RMN_POOL_SUM 0
+#define RMN_POOL_AVG 1
+#define RMN_POOL_MAX 2
+
+/*
+ * out[j][c] = reduce over the offsets k with d_nbr[k][j] >= 0 of feats[d_nbr[k][j]][c]
+ * (sum, mean over the rows present, or maximum); an output row without any neighbour is zero.
+ * d_nbr is the neighbour table of rmn_kmap_build for (input map, output map, pooling region).
+ * d_aux (may be NULL when no backward pass follows): average -> int32 [n_dst] rows present;
+ * maximum -> int32 [n_dst, channels] input row that supplied each value (-1 none); unused for sum.
+ * Features fp32 or bf16 (accumulated in fp32).
+ * Replaces: evaluate_pooling (engine/nn/pooling.cpp:80-144): regrouping of the kernel-map pairs by
+ *   output row on the host and one index_select + sum / mean / amax per output row.
+ */
+int rmn_pool_forward(const void *d_feats, uint32_t n_src, int channels, const int32_t *d_nbr, int K,
+                     uint32_t n_dst, int mode, void *d_out, int32_t *d_aux, int dtype, void *stream);
+
+/*
+ * Gradient of rmn_pool_forward w.r.t. the input features: grad_in[i] = sum over (k, j = d_nbr_in[k][i])
+ * of grad_out[j] (sum), grad_out[j] / count[j] (average) or grad_out[j][c] where row i supplied the
+ * maximum (ties: the first offset wins; torch's amax splits ties evenly). d_nbr_in is the inverse
+ * table (rmn_kmap_transpose of the forward table), d_aux the array the forward pass wrote.
+ * Replaces: torch autograd through the index_select / sum / mean / amax chain of
+ *   engine/nn/pooling.cpp:113-126.
+ */
+int rmn_pool_backward(const void *d_grad_out, uint32_t n_dst, int channels, const int32_t *d_nbr_in, int K,
+                      uint32_t n_src, int mode, const int32_t *d_aux, void *d_grad_in, int dtype,
+                      void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -183,3 +183,47 @@ def conv_backward(feats, grad_out, weights, offset_ptr, in_idx, out_idx, f64: bo
     fn(_p(f), _p(gi), ctypes.c_int(cin), _p(g), ctypes.c_int(cout), ctypes.c_int64(f.shape[0]),
        ctypes.c_int64(g.shape[0]), _p(w), _p(gw), ctypes.c_int(k), _p(ptr), _p(ii), _p(oi))
     return gi, gw
+
+
+# ---------------------------------------------------------------------------------------------
+# Local pooling (reference engine/nn/pooling.cpp:80-144): every output row reduces the input rows
+# its kernel-map pairs name, over all offsets; an output row without pairs is zero. Average divides
+# by the number of rows present (values.mean(0)), not by the kernel volume.
+# ---------------------------------------------------------------------------------------------
+POOL_SUM, POOL_AVG, POOL_MAX = 0, 1, 2
+
+
+def pool_forward(feats, in_idx, out_idx, n_out: int, mode: int) -> np.ndarray:
+    f = np.asarray(feats, dtype=np.float64)
+    ii, oi = _i32(in_idx).astype(np.int64), _i32(out_idx).astype(np.int64)
+    c = f.shape[1]
+    if mode == POOL_MAX:
+        out = np.full((n_out, c), -np.inf)
+        np.maximum.at(out, oi, f[ii])
+        out[np.isneginf(out)] = 0.0  # rows without any pair
+        return out
+    out = np.zeros((n_out, c))
+    np.add.at(out, oi, f[ii])
+    if mode == POOL_AVG:
+        cnt = np.bincount(oi, minlength=n_out).astype(np.float64)
+        out /= np.maximum(cnt, 1.0)[:, None]
+    return out
+
+
+def pool_backward(feats, grad_out, in_idx, out_idx, mode: int) -> np.ndarray:
+    """Gradient w.r.t. the input features (what torch autograd yields through the reference's
+    index_select / sum / mean / amax chain; amax ties are assumed absent)."""
+    f = np.asarray(feats, dtype=np.float64)
+    g = np.asarray(grad_out, dtype=np.float64)
+    ii, oi = _i32(in_idx).astype(np.int64), _i32(out_idx).astype(np.int64)
+    n_out = g.shape[0]
+    gi = np.zeros_like(f)
+    if mode == POOL_SUM:
+        np.add.at(gi, ii, g[oi])
+    elif mode == POOL_AVG:
+        cnt = np.maximum(np.bincount(oi, minlength=n_out).astype(np.float64), 1.0)
+        np.add.at(gi, ii, g[oi] / cnt[oi][:, None])
+    else:
+        mx = pool_forward(f, in_idx, out_idx, n_out, POOL_MAX)
+        np.add.at(gi, ii, g[oi] * (f[ii] == mx[oi]))
+    return gi

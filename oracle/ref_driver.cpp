@@ -24,6 +24,10 @@
 //     convolution with the same kernel_size/stride using `weights2`
 //     [K, Cout, C2] back onto the input coordinates.
 //   weights2 f32 (only when chain = 1)
+//   pool    i32 [3] = {mode (1 sum, 2 average, 3 maximum), kernel_size, stride}  (optional):
+//     also run the reference's local pooling layer on the input tensor
+//     (engine/nn/pooling.cpp:17-144) and write pool_coords, pool_feats and
+//     pool_grad_feats (gradient of 0.5 * sum(pool_feats^2) w.r.t. the input features).
 // Output arrays: mapping, inverse, in_coords, out_coords, out_feats,
 //   kmap_ptr / kmap_in / kmap_out, grad_feats, grad_weights, and for chain = 1
 //   up_coords, up_feats, kmap2_ptr / kmap2_in / kmap2_out, grad_weights2;
@@ -32,6 +36,7 @@
 //   `reps` runs after `warmup` untimed ones; times_all f64 [reps, 4] holds every timed run;
 //   info i32 [2] = {hardware_concurrency, torch threads}.
 #include "engine/nn/conv.hpp"
+#include "engine/nn/pooling.hpp"
 #include "engine/tensor/sparse_tensor.hpp"
 
 #include <torch/torch.h>
@@ -264,6 +269,22 @@ int main(int argc, char** argv) {
     write_array(out, "grad_feats", f.grad());
     write_array(out, "grad_weights", conv->base()->kernel_.grad());
     if (chain) write_array(out, "grad_weights2", up->base()->kernel_.grad());
+
+    if (arrays.count("pool")) {
+      auto pool = to_tensor(arrays.at("pool"));
+      const int pmode = pool[0].item<int>(), pk = pool[1].item<int>(), ps = pool[2].item<int>();
+      const auto mode = pmode == 1   ? riemann::PoolingMode::LOCAL_SUM_POOLING
+                        : pmode == 2 ? riemann::PoolingMode::LOCAL_AVG_POOLING
+                                     : riemann::PoolingMode::LOCAL_MAX_POOLING;
+      riemann::RiemannPoolingBaseImpl pooling(pk, ps, 1, mode, D);
+      auto fp = feats.clone().requires_grad_(true);
+      riemann::SparseTensor xp(fp, coords);
+      auto yp = pooling.forward(xp);
+      write_array(out, "pool_coords", yp.C());
+      write_array(out, "pool_feats", yp.F());
+      (yp.F() * yp.F()).sum().mul(0.5).backward();
+      write_array(out, "pool_grad_feats", fp.grad());
+    }
     return 0;
   } catch (const std::exception& e) {
     std::fprintf(stderr, "ref_driver: %s\n", e.what());

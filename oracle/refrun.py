@@ -60,8 +60,12 @@ def read_arrays(path: str) -> Dict[str, np.ndarray]:
 
 def run(coords: np.ndarray, feats: np.ndarray, weights: np.ndarray, kernel_size: int, stride: int = 1,
         dilation: int = 1, weights2: Optional[np.ndarray] = None, threads: int = 0, reps: int = 1,
-        timing_only: bool = False, warmup: int = 0, timeout: Optional[float] = None) -> Dict[str, np.ndarray]:
-    """One reference run: SparseTensor -> conv [-> transposed conv] -> backward."""
+        timing_only: bool = False, warmup: int = 0, timeout: Optional[float] = None,
+        pool: Optional[tuple] = None) -> Dict[str, np.ndarray]:
+    """One reference run: SparseTensor -> conv [-> transposed conv] -> backward.
+
+    ``pool = (mode, kernel_size, stride)`` with mode 1 sum / 2 average / 3 maximum also runs the
+    reference's local pooling layer on the input tensor (outputs ``pool_*``)."""
     if not available():
         raise RuntimeError("reference driver not built: make -C oracle ref")
     arrays = {
@@ -73,6 +77,8 @@ def run(coords: np.ndarray, feats: np.ndarray, weights: np.ndarray, kernel_size:
     }
     if weights2 is not None:
         arrays["weights2"] = np.ascontiguousarray(weights2, np.float32)
+    if pool is not None:
+        arrays["pool"] = np.array(list(pool), np.int32)
     with tempfile.TemporaryDirectory() as d:
         fin, fout = os.path.join(d, "in.rmna"), os.path.join(d, "out.rmna")
         write_arrays(fin, arrays)

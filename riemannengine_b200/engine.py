@@ -41,6 +41,22 @@ class RegionType:
     HYPER_CUBE, HYPER_CROSS, CUSTOM = 0, 1, 2
 
 
+class PoolingMode:
+    """engine/foundation/types.hpp:121-136 (same numbering)."""
+    LOCAL_SUM_POOLING = 0
+    LOCAL_AVG_POOLING = 1
+    LOCAL_MAX_POOLING = 2
+    GLOBAL_SUM_POOLING_DEFAULT = 3
+    GLOBAL_AVG_POOLING_DEFAULT = 4
+    GLOBAL_MAX_POOLING_DEFAULT = 5
+    GLOBAL_SUM_POOLING_KERNEL = 6
+    GLOBAL_AVG_POOLING_KERNEL = 7
+    GLOBAL_MAX_POOLING_KERNEL = 8
+    GLOBAL_SUM_POOLING_PYTORCH_INDEX = 9
+    GLOBAL_AVG_POOLING_PYTORCH_INDEX = 10
+    GLOBAL_MAX_POOLING_PYTORCH_INDEX = 11
+
+
 class ConvolutionMode:
     DEFAULT, DIRECT_GEMM, COPY_GEMM = 0, 1, 2
 
@@ -678,3 +694,67 @@ class RiemannGenerativeConvolutionTranspose(_ConvWrapper):
                  bias: bool = False, convolution_mode: int = ConvolutionMode.DEFAULT, dimension: int = 3):
         super().__init__(in_channels, out_channels, kernel_size, stride, dilation, bias, True, convolution_mode,
                          dimension)
+
+
+# ---------------------------------------------------------------------------------------------
+# Local pooling (engine/nn/pooling.hpp:12-77, pooling.cpp:80-144, 166-195)
+# ---------------------------------------------------------------------------------------------
+class _SparsePoolingFunction(torch.autograd.Function):
+    """out[j] = reduce over the kernel-map neighbours of output row j; the backward pass gathers
+    through the inverse neighbour table (one store per input row, no atomics)."""
+
+    @staticmethod
+    def forward(ctx, features, kmap: KernelMap, mode: int):
+        out, aux = ops.pool_forward(features, kmap.nbr_out, mode, want_aux=features.requires_grad)
+        ctx.kmap, ctx.mode, ctx.aux = kmap, mode, aux
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        return ops.pool_backward(grad_out, ctx.kmap.nbr_in, ctx.mode, ctx.aux), None, None
+
+
+_LOCAL_POOL_MODES = {PoolingMode.LOCAL_SUM_POOLING: ops.POOL_SUM, PoolingMode.LOCAL_AVG_POOLING: ops.POOL_AVG,
+                     PoolingMode.LOCAL_MAX_POOLING: ops.POOL_MAX}
+
+
+class RiemannPoolingBase(torch.nn.Module):
+    """RiemannPoolingBaseImpl (engine/nn/pooling.cpp:166-195): the output map is the input map strided
+    by the pooling stride; every output row reduces the input rows of its kernel region that exist
+    (average = mean over the rows present; an output row without neighbours is zero)."""
+
+    def __init__(self, kernel_size=3, stride=1, dilation=1, mode: int = PoolingMode.LOCAL_AVG_POOLING,
+                 dimension: int = 3, kernel_generator: Optional["KernelGenerator"] = None):
+        super().__init__()
+        if mode not in _LOCAL_POOL_MODES:
+            raise RuntimeError("Local pooling requires a local pooling mode")
+        self.kernel_generator = kernel_generator if kernel_generator is not None else KernelGenerator(
+            kernel_size, stride, dilation, False, RegionType.HYPER_CUBE, None, False, dimension=dimension)
+        self.mode = mode
+        self.dimension = dimension
+
+    def forward(self, input: SparseTensor) -> SparseTensor:
+        if input.dimension != self.dimension:
+            raise RuntimeError("Input dimension mismatch")
+        params = self.kernel_generator.get_kernel(input.tensor_stride, False)
+        manager = input.coordinate_manager
+        out_key = manager.stride(input.coordinate_map_key, params.kernel_stride)
+        kmap = manager.kernel_map(input.coordinate_map_key, out_key, params.kernel_size, params.kernel_stride,
+                                  params.kernel_dilation, params.region_type, params.region_offsets, False, True)
+        result = _SparsePoolingFunction.apply(input.F, kmap, _LOCAL_POOL_MODES[self.mode])
+        return SparseTensor(result, out_key, manager)
+
+
+class RiemannAvgPooling(RiemannPoolingBase):
+    def __init__(self, kernel_size: int, stride: int = 1, dilation: int = 1, dimension: int = 3):
+        super().__init__(kernel_size, stride, dilation, PoolingMode.LOCAL_AVG_POOLING, dimension)
+
+
+class RiemannSumPooling(RiemannPoolingBase):
+    def __init__(self, kernel_size: int, stride: int = 1, dilation: int = 1, dimension: int = 3):
+        super().__init__(kernel_size, stride, dilation, PoolingMode.LOCAL_SUM_POOLING, dimension)
+
+
+class RiemannMaxPooling(RiemannPoolingBase):
+    def __init__(self, kernel_size: int, stride: int = 1, dilation: int = 1, dimension: int = 3):
+        super().__init__(kernel_size, stride, dilation, PoolingMode.LOCAL_MAX_POOLING, dimension)

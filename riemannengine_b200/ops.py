@@ -291,3 +291,47 @@ def conv_backward_weight(feats: torch.Tensor, grad_out: torch.Tensor, nbr: torch
                                                 _ptr(nbr), K, _ptr(dw), code, _ptr(ws), wbytes, _stream()),
                    "rmn_conv_backward_weight")
     return dw
+
+
+POOL_SUM, POOL_AVG, POOL_MAX = 0, 1, 2
+
+
+def pool_forward(feats: torch.Tensor, nbr: torch.Tensor, mode: int, want_aux: bool = True):
+    """Local pooling over a neighbour table (rmn_pool_forward): returns (out [N_out, C], aux).
+
+    ``aux`` is what the backward pass needs: None for sum, int32 counts [N_out] for average,
+    int32 argmax rows [N_out, C] for maximum (None when ``want_aux`` is false)."""
+    _require_cuda(feats, "features")
+    if feats.dim() != 2 or nbr.dim() != 2:
+        raise RuntimeError("features must be [N, C] and the neighbour table [K, N_out]")
+    if not feats.is_floating_point():
+        raise RuntimeError("Sparse pooling requires floating-point features")
+    feats = feats.contiguous()
+    K, n_dst = int(nbr.size(0)), int(nbr.size(1))
+    c = int(feats.size(1))
+    out = torch.empty((n_dst, c), dtype=feats.dtype, device=feats.device)
+    aux = None
+    if want_aux and mode == POOL_AVG:
+        aux = torch.empty(n_dst, dtype=torch.int32, device=feats.device)
+    elif want_aux and mode == POOL_MAX:
+        aux = torch.empty((n_dst, c), dtype=torch.int32, device=feats.device)
+    with torch.cuda.device(feats.device):
+        capi.check(capi.lib().rmn_pool_forward(_ptr(feats), int(feats.size(0)), c, _ptr(nbr), K, n_dst, int(mode),
+                                               _ptr(out), _ptr(aux), _dtype_code(feats), _stream()),
+                   "rmn_pool_forward")
+    return out, aux
+
+
+def pool_backward(grad_out: torch.Tensor, nbr_in: torch.Tensor, mode: int, aux: Optional[torch.Tensor]) -> torch.Tensor:
+    """Gradient of pool_forward w.r.t. the input features (rmn_pool_backward); ``nbr_in`` [K, N_in] is the
+    inverse neighbour table."""
+    _require_cuda(grad_out, "output gradient")
+    grad_out = grad_out.contiguous()
+    K, n_src = int(nbr_in.size(0)), int(nbr_in.size(1))
+    c = int(grad_out.size(1))
+    grad_in = torch.empty((n_src, c), dtype=grad_out.dtype, device=grad_out.device)
+    with torch.cuda.device(grad_out.device):
+        capi.check(capi.lib().rmn_pool_backward(_ptr(grad_out), int(grad_out.size(0)), c, _ptr(nbr_in), K, n_src,
+                                                int(mode), _ptr(aux), _ptr(grad_in), _dtype_code(grad_out),
+                                                _stream()), "rmn_pool_backward")
+    return grad_in

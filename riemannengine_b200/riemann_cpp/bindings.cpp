@@ -10,6 +10,20 @@ using namespace riemann;
 
 namespace {
 
+// local pooling layers (engine/nn/pooling.hpp:30-77): (kernel_size, stride = 1, dilation = 1, dimension = 3)
+template <typename Impl>
+void bind_pool(py::module_& m, const char* name) {
+  py::class_<Impl, std::shared_ptr<Impl>>(m, name)
+      .def(py::init([](int kernel_size, int stride, int dilation, int dimension) {
+             return std::make_shared<Impl>(kernel_size, stride, dilation, dimension);
+           }),
+           py::arg("kernel_size"), py::arg("stride") = 1, py::arg("dilation") = 1, py::arg("dimension") = 3)
+      .def("forward", [](Impl& self, const SparseTensor& input) { return self.forward(input); }, py::arg("input"),
+           py::call_guard<py::gil_scoped_release>())
+      .def("__call__", [](Impl& self, const SparseTensor& input) { return self.forward(input); }, py::arg("input"),
+           py::call_guard<py::gil_scoped_release>());
+}
+
 template <typename Impl>
 py::class_<Impl, std::shared_ptr<Impl>> bind_conv(py::module_& m, const char* name) {
   py::class_<Impl, std::shared_ptr<Impl>> cls(m, name);
@@ -163,4 +177,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("in_channels"), py::arg("out_channels"), py::arg("kernel_size") = 3, py::arg("stride") = 1,
            py::arg("dilation") = 1, py::arg("bias") = false, py::arg("convolution_mode") = ConvolutionMode::DEFAULT,
            py::arg("dimension") = 3);
+
+  py::enum_<PoolingMode::Type>(m, "PoolingMode")
+      .value("LOCAL_SUM_POOLING", PoolingMode::LOCAL_SUM_POOLING)
+      .value("LOCAL_AVG_POOLING", PoolingMode::LOCAL_AVG_POOLING)
+      .value("LOCAL_MAX_POOLING", PoolingMode::LOCAL_MAX_POOLING);
+  bind_pool<RiemannAvgPoolingImpl>(m, "RiemannAvgPooling");
+  bind_pool<RiemannSumPoolingImpl>(m, "RiemannSumPooling");
+  bind_pool<RiemannMaxPoolingImpl>(m, "RiemannMaxPooling");
 }

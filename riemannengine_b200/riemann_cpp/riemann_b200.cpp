@@ -715,3 +715,93 @@ at::Tensor ConvolutionTransposeFunction::apply(at::Tensor input_features, at::Te
 }
 
 }  // namespace riemann
+
+// ---------------------------------------------------------------------------------------------
+// Local pooling (engine/nn/pooling.cpp:80-144, 166-195)
+// ---------------------------------------------------------------------------------------------
+namespace riemann {
+namespace {
+
+int pool_code(PoolingMode::Type mode) {
+  switch (mode) {
+    case PoolingMode::LOCAL_SUM_POOLING: return RMN_POOL_SUM;
+    case PoolingMode::LOCAL_AVG_POOLING: return RMN_POOL_AVG;
+    case PoolingMode::LOCAL_MAX_POOLING: return RMN_POOL_MAX;
+    default: TORCH_CHECK(false, "Local pooling requires a local pooling mode");
+  }
+}
+
+class SparsePoolingAutograd : public torch::autograd::Function<SparsePoolingAutograd> {
+public:
+  // nbr_in is the inverse table (empty when no gradient is wanted); aux is filled by the forward kernel
+  static at::Tensor forward(torch::autograd::AutogradContext* ctx, at::Tensor features, at::Tensor nbr_out,
+                            at::Tensor nbr_in, int64_t mode) {
+    TORCH_CHECK(features.is_cuda(), "features must be CUDA tensors: this library has no CPU path");
+    TORCH_CHECK(features.is_floating_point(), "Sparse pooling requires floating-point features");
+    auto feats = features.contiguous();
+    c10::cuda::CUDAGuard guard(feats.device());
+    const int64_t n_dst = nbr_out.size(1), C = feats.size(1);
+    auto out = at::empty({n_dst, C}, feats.options());
+    at::Tensor aux;
+    if (nbr_in.numel() > 0 && mode == RMN_POOL_AVG) aux = at::empty({n_dst}, nbr_out.options());
+    if (nbr_in.numel() > 0 && mode == RMN_POOL_MAX) aux = at::empty({n_dst, C}, nbr_out.options());
+    check(rmn_pool_forward(ptr(feats), static_cast<uint32_t>(feats.size(0)), static_cast<int>(C),
+                           static_cast<const int32_t*>(ptr(nbr_out)), static_cast<int>(nbr_out.size(0)),
+                           static_cast<uint32_t>(n_dst), static_cast<int>(mode), ptr(out),
+                           aux.defined() ? static_cast<int32_t*>(ptr(aux)) : nullptr, dtype_code(feats),
+                           current_stream()),
+          "rmn_pool_forward");
+    ctx->saved_data["nbr_in"] = nbr_in;
+    ctx->saved_data["aux"] = aux.defined() ? aux : at::empty({0}, nbr_out.options());
+    ctx->saved_data["mode"] = mode;
+    return out;
+  }
+  static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::variable_list grad_outputs) {
+    auto nbr_in = ctx->saved_data["nbr_in"].toTensor();
+    auto aux = ctx->saved_data["aux"].toTensor();
+    const int64_t mode = ctx->saved_data["mode"].toInt();
+    auto grad = grad_outputs[0].contiguous();
+    c10::cuda::CUDAGuard guard(grad.device());
+    auto g_feat = at::empty({nbr_in.size(1), grad.size(1)}, grad.options());
+    check(rmn_pool_backward(ptr(grad), static_cast<uint32_t>(grad.size(0)), static_cast<int>(grad.size(1)),
+                            static_cast<const int32_t*>(ptr(nbr_in)), static_cast<int>(nbr_in.size(0)),
+                            static_cast<uint32_t>(nbr_in.size(1)), static_cast<int>(mode),
+                            aux.numel() ? static_cast<const int32_t*>(ptr(aux)) : nullptr, ptr(g_feat),
+                            dtype_code(grad), current_stream()),
+          "rmn_pool_backward");
+    return {g_feat, at::Tensor(), at::Tensor(), at::Tensor()};
+  }
+};
+
+}  // namespace
+
+at::Tensor sparse_pooling(const at::Tensor& features, const std::shared_ptr<KernelMap>& kmap, PoolingMode::Type mode) {
+  at::Tensor nbr_in = features.requires_grad() ? kmap->nbr_in() : at::empty({0}, kmap->nbr_out.options());
+  return SparsePoolingAutograd::apply(features, kmap->nbr_out, nbr_in, static_cast<int64_t>(pool_code(mode)));
+}
+
+RiemannPoolingBaseImpl::RiemannPoolingBaseImpl(int kernel_size, int stride, int dilation, PoolingMode::Type mode,
+                                               int dimension)
+    : kernel_generator_({kernel_size}, {stride}, {dilation}, false, RegionType::HYPER_CUBE, {}, false, {}, dimension),
+      mode_(mode), dimension_(dimension) {
+  pool_code(mode);
+}
+
+RiemannPoolingBaseImpl::RiemannPoolingBaseImpl(KernelGenerator kernel_generator, PoolingMode::Type mode, int dimension)
+    : kernel_generator_(std::move(kernel_generator)), mode_(mode), dimension_(dimension) {
+  pool_code(mode);
+}
+
+SparseTensor RiemannPoolingBaseImpl::forward(const SparseTensor& input) {
+  TORCH_CHECK(input.dimension() == dimension_, "Input dimension mismatch");
+  const auto params = kernel_generator_.get_kernel(input.tensor_stride(), false);
+  auto manager = input.coordinate_manager();
+  auto output_key = manager->stride(input.coordinate_map_key(), params.kernel_stride);
+  auto kmap = manager->kernel_map(input.coordinate_map_key(), output_key, params.kernel_size, params.kernel_stride,
+                                  params.kernel_dilation, params.region_type, params.region_offsets, false, true);
+  auto result = sparse_pooling(input.F(), kmap, mode_);
+  return SparseTensor(std::move(result), output_key, std::move(manager));
+}
+
+}  // namespace riemann

@@ -50,6 +50,22 @@ enum Type { HYPER_CUBE, HYPER_CROSS, CUSTOM };
 namespace ConvolutionMode {
 enum Type { DEFAULT, DIRECT_GEMM, COPY_GEMM };
 }
+namespace PoolingMode {  // engine/foundation/types.hpp:121-136
+enum Type {
+  LOCAL_SUM_POOLING,
+  LOCAL_AVG_POOLING,
+  LOCAL_MAX_POOLING,
+  GLOBAL_SUM_POOLING_DEFAULT,
+  GLOBAL_AVG_POOLING_DEFAULT,
+  GLOBAL_MAX_POOLING_DEFAULT,
+  GLOBAL_SUM_POOLING_KERNEL,
+  GLOBAL_AVG_POOLING_KERNEL,
+  GLOBAL_MAX_POOLING_KERNEL,
+  GLOBAL_SUM_POOLING_PYTORCH_INDEX,
+  GLOBAL_AVG_POOLING_PYTORCH_INDEX,
+  GLOBAL_MAX_POOLING_PYTORCH_INDEX
+};
+}
 
 class CoordinateMapKey {
 public:
@@ -283,5 +299,40 @@ private:
   std::shared_ptr<RiemannConvolutionBaseImpl> base_{nullptr};
 };
 TORCH_MODULE(RiemannGenerativeConvolutionTranspose);
+
+// Local pooling over a kernel map (engine/nn/pooling.cpp:80-144) with a hand-written backward:
+// `mode` is one of the three local pooling modes.
+at::Tensor sparse_pooling(const at::Tensor& features, const std::shared_ptr<KernelMap>& kmap, PoolingMode::Type mode);
+
+// RiemannPoolingBaseImpl and its three wrappers (engine/nn/pooling.hpp:12-77): same constructor
+// arguments; the output map is the input map strided by the pooling stride.
+class RiemannPoolingBaseImpl : public torch::nn::Module {
+public:
+  RiemannPoolingBaseImpl(int kernel_size, int stride = 1, int dilation = 1,
+                         PoolingMode::Type mode = PoolingMode::LOCAL_AVG_POOLING, int dimension = 3);
+  RiemannPoolingBaseImpl(KernelGenerator kernel_generator, PoolingMode::Type mode, int dimension);
+  SparseTensor forward(const SparseTensor& input);
+
+private:
+  KernelGenerator kernel_generator_;
+  PoolingMode::Type mode_;
+  int dimension_;
+};
+
+#define RIEMANN_B200_POOL_WRAPPER(Name, Mode)                                                  \
+  class Name##Impl : public torch::nn::Module {                                                \
+  public:                                                                                      \
+    Name##Impl(int kernel_size, int stride = 1, int dilation = 1, int dimension = 3)           \
+        : pooling_(kernel_size, stride, dilation, Mode, dimension) {}                          \
+    SparseTensor forward(const SparseTensor& input) { return pooling_.forward(input); }        \
+                                                                                               \
+  private:                                                                                     \
+    RiemannPoolingBaseImpl pooling_;                                                           \
+  };                                                                                           \
+  TORCH_MODULE(Name)
+
+RIEMANN_B200_POOL_WRAPPER(RiemannAvgPooling, PoolingMode::LOCAL_AVG_POOLING);
+RIEMANN_B200_POOL_WRAPPER(RiemannSumPooling, PoolingMode::LOCAL_SUM_POOLING);
+RIEMANN_B200_POOL_WRAPPER(RiemannMaxPooling, PoolingMode::LOCAL_MAX_POOLING);
 
 }  // namespace riemann

@@ -5,7 +5,7 @@ Runs the unmodified reference CPU path (``oracle/_ref/ref_driver``, built by
 stores inputs + reference outputs as ``<case>.npz``. The parity tests load the
 fixtures only; they never need the reference at run time.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [--pool-only]
 """
 from __future__ import annotations
 
@@ -30,6 +30,17 @@ CASES = {
     "d3_k5_s1": (17, 3, 350, 1, 0, 7, 2, 2, 5, 1, 1, None),
 }
 
+# local pooling (reference engine/nn/pooling.cpp): name: (seed, D, n_rows, batches, lo, hi, channels, mode, kernel, stride)
+# mode 1 sum, 2 average, 3 maximum
+POOL_CASES = {
+    "pool_d3_sum_k2_s2": (21, 3, 500, 2, -7, 7, 6, 1, 2, 2),
+    "pool_d3_avg_k2_s2": (22, 3, 500, 2, -7, 7, 6, 2, 2, 2),
+    "pool_d3_max_k2_s2": (23, 3, 500, 2, -7, 7, 6, 3, 2, 2),
+    "pool_d3_max_k3_s1": (24, 3, 400, 2, -5, 5, 5, 3, 3, 1),
+    "pool_d3_avg_k3_s2": (25, 3, 500, 3, -7, 8, 4, 2, 3, 2),
+    "pool_d2_sum_k3_s1": (26, 2, 300, 2, -9, 9, 3, 1, 3, 1),
+}
+
 
 def make_inputs(seed, D, n, batches, lo, hi, c_in, c_out, kernel, stride, dilation, c2):
     rng = np.random.default_rng(seed)
@@ -51,7 +62,8 @@ def make_inputs(seed, D, n, batches, lo, hi, c_in, c_out, kernel, stride, dilati
 
 
 def main() -> None:
-    for name, spec in CASES.items():
+    only_pool = "--pool-only" in sys.argv
+    for name, spec in ({} if only_pool else CASES).items():
         coords, feats, weights, weights2 = make_inputs(*spec)
         _, D, _, _, _, _, _, _, kernel, stride, dilation, _ = spec
         ref = refrun.run(coords, feats, weights, kernel, stride, dilation, weights2=weights2, threads=1)
@@ -66,6 +78,17 @@ def main() -> None:
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, **arrays)
         print(name, {k: v.shape for k, v in ref.items()}, os.path.getsize(path), "bytes")
+    for name, (seed, D, n, batches, lo, hi, C, mode, kernel, stride) in POOL_CASES.items():
+        coords, feats, _, _ = make_inputs(seed, D, n, batches, lo, hi, C, 1, 1, 1, 1, None)
+        ident = np.ones((1, C, 1), np.float32)  # the driver always runs a convolution first: 1^D kernel, unused here
+        ref = refrun.run(coords, feats, ident, 1, 1, 1, threads=1, pool=(mode, kernel, stride))
+        arrays = {"in_coords_raw": coords, "in_feats_raw": feats,
+                  "spec": np.array([D, kernel, stride, mode], np.int32)}
+        for k in ("mapping", "in_coords", "pool_coords", "pool_feats", "pool_grad_feats"):
+            arrays["ref_" + k] = ref[k]
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **arrays)
+        print(name, {k: v.shape for k, v in arrays.items() if k.startswith("ref_")}, os.path.getsize(path), "bytes")
 
 
 if __name__ == "__main__":

@@ -155,3 +155,47 @@ def check_against_reference(res, gold, tol=1e-4, metric=rel_max):
         assert metric(res["grad_weights2"], g["grad_weights2"]) <= tol
     assert metric(res["grad_weights"], g["grad_weights"]) <= tol
     assert metric(res["grad_feats"], g["grad_feats"]) <= tol
+
+
+# ---------------------------------------------------------------------------------------------
+# local pooling fixtures (reference engine/nn/pooling.cpp, generated by tests/golden/make_golden.py)
+# ---------------------------------------------------------------------------------------------
+POOL_GOLDEN_CASES = ["pool_d3_sum_k2_s2", "pool_d3_avg_k2_s2", "pool_d3_max_k2_s2", "pool_d3_max_k3_s1",
+                     "pool_d3_avg_k3_s2", "pool_d2_sum_k3_s1"]
+
+
+def oracle_pool_case(gold: Dict[str, np.ndarray]):
+    """The oracle's pooled output for a pooling fixture: (out_coords, out_feats, grad w.r.t. the raw features)
+    for the loss 0.5 * sum(out^2)."""
+    from oracle import oracle as O
+
+    D, kernel, stride, mode = (int(v) for v in gold["spec"])
+    coords, feats = gold["in_coords_raw"], gold["in_feats_raw"]
+    mapping, _ = O.insert_and_map(coords)
+    in_coords, in_feats = coords[mapping], feats[mapping]
+    if stride > 1:
+        out_coords, _ = O.stride_map(in_coords, [stride] * D)
+    else:
+        out_coords = in_coords
+    offsets = O.region_offsets(O.HYPER_CUBE, [kernel] * D, [1] * D, [1] * D)
+    _, in_idx, out_idx = O.conv_kernel_map(in_coords, out_coords, offsets)
+    out = O.pool_forward(in_feats, in_idx, out_idx, len(out_coords), mode - 1)
+    g_unique = O.pool_backward(in_feats, out, in_idx, out_idx, mode - 1)
+    g_raw = np.zeros(feats.shape, np.float64)
+    g_raw[mapping] = g_unique
+    return out_coords, out, g_raw
+
+
+def check_pool_against_reference(out_coords, out_feats, grad_raw, gold, tol: float) -> None:
+    """Pooled rows are matched to the reference's by coordinate (strided maps number rows differently)."""
+    ref_c, ref_f, ref_g = gold["ref_pool_coords"], gold["ref_pool_feats"], gold["ref_pool_grad_feats"]
+    assert out_coords.shape == ref_c.shape
+    order = np.lexsort(np.asarray(out_coords).T[::-1])
+    ref_order = np.lexsort(ref_c.T[::-1])
+    assert np.array_equal(np.asarray(out_coords)[order], ref_c[ref_order])
+    scale = max(float(np.abs(ref_f).max()), 1e-30)
+    err = float(np.abs(np.asarray(out_feats, np.float64)[order] - ref_f[ref_order]).max()) / scale
+    assert err <= tol, f"pooled features differ: {err}"
+    gscale = max(float(np.abs(ref_g).max()), 1e-30)
+    gerr = float(np.abs(np.asarray(grad_raw, np.float64) - ref_g).max()) / gscale
+    assert gerr <= tol, f"pooling gradient differs: {gerr}"

@@ -103,3 +103,17 @@ def test_cpp_bias_is_fused_and_has_gradient(C):
     want = r["out_feats"] + conv.bias.detach().cpu().numpy().astype(np.float64)
     assert rel_max(y.F.detach().cpu().numpy(), want) <= 1e-4
     assert torch.allclose(conv.bias.grad, torch.full_like(conv.bias.grad, float(len(y))))
+
+
+@pytest.mark.parametrize("name", parity.POOL_GOLDEN_CASES)
+def test_cpp_pooling_matches_reference_golden(C, name):
+    # fixtures produced by the reference's pooling layers (engine/nn/pooling.cpp); fp32 bar 1e-4
+    gold = parity.load_golden(name)
+    D, kernel, stride, mode = (int(v) for v in gold["spec"])
+    layer = {1: C.RiemannSumPooling, 2: C.RiemannAvgPooling, 3: C.RiemannMaxPooling}[mode](kernel, stride, 1, D)
+    f = torch.from_numpy(gold["in_feats_raw"]).cuda().requires_grad_(True)
+    x = C.SparseTensor(f, torch.from_numpy(gold["in_coords_raw"]).cuda())
+    y = layer(x)
+    ((y.F * y.F).sum() * 0.5).backward()
+    parity.check_pool_against_reference(y.C.cpu().numpy(), y.F.detach().cpu().numpy(), f.grad.cpu().numpy(), gold,
+                                        tol=1e-4)

@@ -91,3 +91,10 @@ def test_oracle_matches_reference_golden(name, f64):
     res = parity.run_pipeline(parity.OracleBackend(f64=f64), gold["in_coords_raw"], gold["in_feats_raw"],
                               gold["weights"], D, kernel, stride, dilation, gold.get("weights2"))
     parity.check_against_reference(res, gold, tol=1e-5)
+
+
+@pytest.mark.parametrize("name", parity.POOL_GOLDEN_CASES)
+def test_oracle_pooling_matches_reference_golden(name):
+    gold = parity.load_golden(name)
+    out_coords, out, g_raw = parity.oracle_pool_case(gold)
+    parity.check_pool_against_reference(out_coords, out, g_raw, gold, tol=1e-5)
