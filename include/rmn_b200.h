@@ -201,8 +201,8 @@ int rmn_kmap_build(const void *d_table, const int32_t *d_query, uint32_t n_query
  * must be odd and the offsets point-symmetric (offsets[K-1-k] == -offsets[k], offsets[K/2] == 0;
  * the caller checks this on its host copy). Same outputs as rmn_kmap_build, about half the
  * probes: a hit (q -> a) at offset k also fills (a -> q) at offset K-1-k, and the centre offset
- * is the identity. The per-block pair counts of the mirrored half, which only rmn_kmap_pairs
- * reads, are left pending in the workspace and produced by the first rmn_kmap_pairs call.
+ * is the identity. The workspace records that the map is a self map: rmn_kmap_pairs then emits the
+ * pairs of offset K-1-k as the pairs of offset k with input and output row exchanged.
  * Every region of CoordinateMapCPU::kernel_map
  * (engine/grid/lattice_cpu.hpp:606-673) with odd kernel sizes is of this kind when input and
  * output maps coincide (engine/nn/conv.cpp:111-125).
@@ -214,10 +214,12 @@ int rmn_kmap_build_self(const void *d_table, const int32_t *d_coords, uint32_t n
 /*
  * Materialise the pair lists of the last rmn_kmap_build (same d_nbr,
  * d_offset_ptr and d_workspace): d_a_idx[p], d_q_idx[p] for p < ptr[K],
- * pairs of one offset sorted by query row. `capacity` = entries available in
- * each index array (K * n_query always suffices; ptr[K] is exact). The
- * workspace is updated in place (pending counts of a self map, status words),
- * so two calls on one workspace must not overlap.
+ * pairs of one offset sorted by query row (for a map built by
+ * rmn_kmap_build_self the offsets above the centre are the exchanged lists of
+ * their mirror offsets and therefore sorted by table row instead; the order is
+ * deterministic either way, the reference's is not: engine/grid/lattice_cpu.hpp:657-659).
+ * `capacity` = entries available in each index array (K * n_query always
+ * suffices; ptr[K] is exact).
  * Replaces: the per-offset in/out vectors of cpu_kernel_map
  *   (engine/grid/maps.hpp:19-79) and gpu_kernel_map::decompose
  *   (engine/grid/lattice_gpu.cuh:440-488). Passing the arrays in the other

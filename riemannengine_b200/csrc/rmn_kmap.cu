@@ -181,36 +181,12 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe_self(
   }
 }
 
-// Hit counts per (offset, 256-row block) for `n_off` offset rows of a neighbour table
-// (the mirrored half of a self map, whose entries were scattered by other blocks).
-// The launch is a no-op unless *pending != 0 (see rmn_kmap_build_self).
-__global__ void __launch_bounds__(kKmapBlock) k_kmap_count_rows(const int32_t* __restrict__ nbr, uint32_t n,
-                                                              int n_off, uint32_t* __restrict__ block_counts,
-                                                              uint32_t n_blocks, const uint32_t* pending) {
-  if (*pending == 0) return;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t row0 = blockIdx.x * kKmapBlock;
-  for (int k = warp; k < n_off; k += kKmapBlock / 32) {
-    uint32_t cnt = 0;
-#pragma unroll
-    for (int g = 0; g < kKmapBlock / 32; ++g) {
-      const uint32_t q = row0 + g * 32 + lane;
-      const int32_t a = q < n ? __ldg(nbr + (size_t)k * n + q) : -1;
-      cnt += __popc(__ballot_sync(0xFFFFFFFFu, a >= 0));
-    }
-    if (lane == 0) block_counts[(size_t)k * n_blocks + blockIdx.x] = cnt;
-  }
-}
-
 // grid = K blocks of 1024 threads: exclusive scan of block_counts[k][0..n_blocks) in place,
 // totals[k] = number of pairs of offset k.
-// With `pending` given, the launch is a no-op unless *pending != 0.
 __global__ void __launch_bounds__(1024) k_kmap_scan_blocks(uint32_t* __restrict__ block_counts,
                                                            uint32_t n_blocks,
-                                                           uint32_t* __restrict__ totals,
-                                                           const uint32_t* pending) {
+                                                           uint32_t* __restrict__ totals) {
   __shared__ uint32_t warp_sums[32];
-  if (pending && *pending == 0) return;
   uint32_t* counts = block_counts + (size_t)blockIdx.x * n_blocks;
   const uint32_t per = (n_blocks + 1023u) / 1024u;
   const uint32_t begin = min(n_blocks, threadIdx.x * per), end = min(n_blocks, begin + per);
@@ -246,13 +222,14 @@ __global__ void __launch_bounds__(1024) k_kmap_scan_blocks(uint32_t* __restrict_
 
 // one thread: offset_ptr[0..K] = exclusive scan of totals (K is small)
 // mirror_half > 0 (self map): offsets K-1-k and k hold the same number of pairs, so the totals of
-// the mirrored half are copied from the probed half and *pending is set: the per-block counts of
-// the mirrored half, which only the pair lists need, are produced when pair lists are first asked for.
+// the mirrored half are copied from the probed half, and *mirror_flag records the half: the pair
+// lists of the mirrored offsets are then the swapped lists of their mirror offsets (k_kmap_pairs_mirror)
+// and need no per-block counts.
 __global__ void k_kmap_offset_ptr(uint32_t* __restrict__ totals, int K, int64_t* __restrict__ offset_ptr,
-                                  int mirror_half, uint32_t* pending) {
+                                  int mirror_half, uint32_t* mirror_flag) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   for (int k = K - mirror_half; k < K; ++k) totals[k] = totals[K - 1 - k];
-  *pending = (uint32_t)mirror_half;
+  *mirror_flag = (uint32_t)mirror_half;
   int64_t run = 0;
   for (int k = 0; k < K; ++k) {
     offset_ptr[k] = run;
@@ -271,7 +248,7 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_pairs(
     unsigned long long capacity, uint32_t* __restrict__ overflow) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t row0 = blockIdx.x * kKmapBlock;
-  if (blockIdx.x == 0 && threadIdx.x == 0) overflow[1] = 0;  // the pending block counts were produced before this launch
+  K -= (int)overflow[1];  // self map: the mirrored offsets are filled by k_kmap_pairs_mirror
   for (int k = warp; k < K; k += kKmapBlock / 32) {
     unsigned long long pos =
         (unsigned long long)offset_ptr[k] + block_prefix[(size_t)k * n_blocks + blockIdx.x];
@@ -372,6 +349,26 @@ extern "C" int rmn_region_offsets(int region_type, int D, const int32_t* kernel_
   return K;
 }
 
+// Self map: the pairs of offset K-1-k are the pairs of offset k with input and output row
+// exchanged (grid.y = offset k < half). They come out sorted by input row.
+__global__ void __launch_bounds__(256) k_kmap_pairs_mirror(const int64_t* __restrict__ offset_ptr, int K,
+                                                           const uint32_t* __restrict__ mirror_flag,
+                                                           int32_t* __restrict__ a_idx, int32_t* __restrict__ q_idx,
+                                                           unsigned long long capacity) {
+  const int half = (int)*mirror_flag, k = blockIdx.y;
+  if (k >= half) return;
+  const unsigned long long begin = (unsigned long long)offset_ptr[k], end = (unsigned long long)offset_ptr[k + 1];
+  const unsigned long long dst0 = (unsigned long long)offset_ptr[K - 1 - k];
+  for (unsigned long long p = begin + blockIdx.x * blockDim.x + threadIdx.x; p < end;
+       p += (unsigned long long)gridDim.x * blockDim.x) {
+    const unsigned long long d = dst0 + (p - begin);
+    if (p < capacity && d < capacity) {
+      a_idx[d] = q_idx[p];
+      q_idx[d] = a_idx[p];
+    }
+  }
+}
+
 extern "C" size_t rmn_kmap_workspace_bytes(uint32_t n_query, int K) {
   if (K < 1) K = 1;
   return ((size_t)K * kmap_blocks(n_query) + (size_t)K + 64) * sizeof(uint32_t);
@@ -401,7 +398,7 @@ extern "C" int rmn_kmap_build(const void* d_table, const int32_t* d_query, uint3
   RMN_DISPATCH_W(W, k_kmap_probe<kW><<<nb, kKmapBlock, smem, stream>>>(
                         h, slots, d_query, n_query, d_offsets, K, d_nbr, block_counts, nb));
   RMN_LAUNCH_CHECK();
-  k_kmap_scan_blocks<<<K, 1024, 0, stream>>>(block_counts, nb, totals, nullptr);
+  k_kmap_scan_blocks<<<K, 1024, 0, stream>>>(block_counts, nb, totals);
   RMN_LAUNCH_CHECK();
   k_kmap_offset_ptr<<<1, 32, 0, stream>>>(totals, K, d_offset_ptr, 0, totals + K + 1);
   RMN_LAUNCH_CHECK();
@@ -437,7 +434,7 @@ extern "C" int rmn_kmap_build_self(const void* d_table, const int32_t* d_coords,
                         h, slots, d_coords, n_rows, d_offsets, K, d_nbr, block_counts, nb));
   RMN_LAUNCH_CHECK();
   // only the probed half (and the centre) is scanned here; see k_kmap_offset_ptr
-  k_kmap_scan_blocks<<<half + 1, 1024, 0, stream>>>(block_counts, nb, totals, nullptr);
+  k_kmap_scan_blocks<<<half + 1, 1024, 0, stream>>>(block_counts, nb, totals);
   RMN_LAUNCH_CHECK();
   k_kmap_offset_ptr<<<1, 32, 0, stream>>>(totals, K, d_offset_ptr, half, totals + K + 1);
   RMN_LAUNCH_CHECK();
@@ -456,22 +453,15 @@ extern "C" int rmn_kmap_pairs(const int32_t* d_nbr, uint32_t n_query, int K,
   const uint32_t* block_prefix = reinterpret_cast<const uint32_t*>(d_workspace);
   // the word after the totals flags a capacity overflow (kept for debugging reads)
   uint32_t* overflow = const_cast<uint32_t*>(block_prefix) + (size_t)K * nb + K;
-  // A self map leaves the per-block counts of its mirrored half pending (flag word after the
-  // overflow word): count and scan them now. Both launches return at once for any other map.
-  uint32_t* pending = overflow + 1;
-  const int half = K / 2;
-  if (half > 0) {
-    uint32_t* counts = const_cast<uint32_t*>(block_prefix);
-    k_kmap_count_rows<<<nb, kKmapBlock, 0, stream>>>(d_nbr + (size_t)(K - half) * n_query, n_query, half,
-                                                     counts + (size_t)(K - half) * nb, nb, pending);
-    RMN_LAUNCH_CHECK();
-    k_kmap_scan_blocks<<<half, 1024, 0, stream>>>(counts + (size_t)(K - half) * nb, nb,
-                                                  counts + (size_t)K * nb + (K - half), pending);
-    RMN_LAUNCH_CHECK();
-  }
   k_kmap_pairs<<<nb, kKmapBlock, 0, stream>>>(d_nbr, n_query, K, d_offset_ptr, block_prefix, nb,
                                               d_a_idx, d_q_idx, capacity, overflow);
   RMN_LAUNCH_CHECK();
+  if (K >= 3 && (K & 1)) {  // possibly a self map (odd K): returns at once unless its flag is set
+    const uint32_t per_offset = (n_query + 255u) / 256u < 64u ? (n_query + 255u) / 256u : 64u;
+    k_kmap_pairs_mirror<<<dim3(per_offset ? per_offset : 1u, (unsigned)(K / 2)), 256, 0, stream>>>(
+        d_offset_ptr, K, overflow + 1, d_a_idx, d_q_idx, capacity);
+    RMN_LAUNCH_CHECK();
+  }
   return RMN_OK;
 }
 

@@ -118,8 +118,8 @@ def test_kernel_map_matches_oracle(gpu, D, ks, dil, transposed):
     k1 = gpu().conv_kernel_map(c, c, off, transposed)
     parity.assert_kernel_maps_equal(k1, k0)
     if not transposed:
-        # device pair lists are sorted by output row inside each offset, like the oracle's
-        # (a transposed map is built the other way round by the oracle: sorted by input row)
+        # device pair lists of the general builder are sorted by output row inside each offset, like
+        # the oracle's (a transposed map is built the other way round by the oracle: sorted by input row)
         assert (np.asarray(k1[1]) == k0[1]).all() and (np.asarray(k1[2]) == k0[2]).all()
 
 
@@ -244,6 +244,16 @@ def test_large_batch_properties(gpu):
     k = 7
     sl = slice(int(ptr[k]), int(ptr[k + 1]))
     assert (nbr[k][q[sl].long()] == a[sl]).all() and (q[sl][1:] > q[sl][:-1]).all()
+    # self-map builder: same table and pointer; mirrored offsets hold the exchanged lists (sorted by table row)
+    res_s = ops.kmap_build(t, dc, off, self_map=True)
+    assert torch.equal(res_s.nbr, nbr) and torch.equal(res_s.offset_ptr, res.offset_ptr)
+    ptr_s, a_s, q_s = res_s.pairs()
+    assert torch.equal(ptr_s, ptr)
+    for k in (7, 13, 20, 26):
+        sl = slice(int(ptr[k]), int(ptr[k + 1]))
+        assert (nbr[k][q_s[sl].long()] == a_s[sl]).all()
+        key = a_s[sl] if k > 13 else q_s[sl]
+        assert (key[1:] > key[:-1]).all()
     # linearity of the forward pass in the features (fp32)
     g = torch.Generator(device="cuda").manual_seed(5)
     w = torch.randn(K, 16, 16, device="cuda", generator=g) * 0.05
@@ -279,7 +289,20 @@ def test_self_map_builder_equals_general_builder(gpu, D, ks, dil, n):
     assert torch.equal(a.nbr, b.nbr)
     assert torch.equal(a.offset_ptr, b.offset_ptr)
     pa, pb = a.pairs(), b.pairs()
-    assert torch.equal(pa[0], pb[0]) and torch.equal(pa[1], pb[1]) and torch.equal(pa[2], pb[2])
+    assert torch.equal(pa[0], pb[0])
+    ptr, K = pa[0].tolist(), len(off)
+    # identical lists up to and including the centre offset; above it the self map emits the exchanged
+    # lists of the mirror offsets (sorted by table row instead of query row): same pair sets
+    lo = ptr[K // 2 + 1]
+    assert torch.equal(pa[1][:lo], pb[1][:lo]) and torch.equal(pa[2][:lo], pb[2][:lo])
+    for k in range(K // 2 + 1, K):
+        sa = torch.stack([pa[1][ptr[k]:ptr[k + 1]], pa[2][ptr[k]:ptr[k + 1]]], 1)
+        sb = torch.stack([pb[1][ptr[k]:ptr[k + 1]], pb[2][ptr[k]:ptr[k + 1]]], 1)
+        key = lambda t: t[:, 1].long() * (1 << 32) + t[:, 0].long()  # noqa: E731
+        assert torch.equal(sa[torch.argsort(key(sa))], sb[torch.argsort(key(sb))])
+        mk = K - 1 - k  # and literally the exchanged mirror list
+        assert torch.equal(pb[1][ptr[k]:ptr[k + 1]], pb[2][ptr[mk]:ptr[mk + 1]])
+        assert torch.equal(pb[2][ptr[k]:ptr[k + 1]], pb[1][ptr[mk]:ptr[mk + 1]])
     assert not ops.offsets_point_symmetric(O.region_offsets([2] * D, [1] * D, [1] * D))
 
 
