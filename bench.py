@@ -235,6 +235,8 @@ def run_product(args) -> None:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # NCCL writes its version banner to stdout when NCCL_DEBUG is set; stdout carries the JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     lib = capi.lib()
 
@@ -526,6 +528,8 @@ def run_train(args) -> None:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # NCCL writes its version banner to stdout when NCCL_DEBUG is set; stdout carries the JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     lib = capi.lib()
     coords_np, feats_np, weights_np = make_batch(rank)
