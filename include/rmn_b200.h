@@ -283,6 +283,40 @@ int rmn_conv_backward_weight(const void *d_feats, uint32_t n_src, int c_in,
                              const int32_t *d_nbr, int K, float *d_grad_weights, int dtype,
                              void *d_workspace, size_t workspace_bytes, void *stream);
 
+/* ------------------- batch-normalisation pieces beside the convolution -------------------
+ * The reference normalises with torch::nn::BatchNorm1d on the feature matrix after every convolution
+ * (engine/nn/normalization.hpp:11-34; conv -> norm -> ReLU in engine/nn/residual.cpp:44-52). */
+
+/* Bytes of workspace for rmn_channel_stats / rmn_conv_forward_stats with `channels` (output) channels. */
+size_t rmn_channel_stats_workspace_bytes(int channels);
+
+/*
+ * d_stats[0][c] = sum over rows of x[r][c], d_stats[1][c] = sum of squares (double [2, channels]);
+ * partial sums are added in a fixed order. Replaces: the statistics pass of BatchNorm1d in training mode.
+ */
+int rmn_channel_stats(const void *d_x, uint32_t n_rows, int channels, int dtype, double *d_stats,
+                      void *d_workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * rmn_conv_forward_fused that also returns the channel statistics of the values it stores (d_stats as in
+ * rmn_channel_stats, over the n_dst output rows): the tensor-core kernel accumulates them in its epilogue,
+ * so the batch statistics of a following normalisation cost no pass over the output.
+ * Replaces: evaluate_sparse_convolution (engine/nn/conv.cpp:9-66) + the statistics pass of the
+ *   BatchNorm1d that follows it.
+ */
+int rmn_conv_forward_stats(const void *d_feats, uint32_t n_src, int c_in, const void *d_weights, int K,
+                           int c_out, const int32_t *d_nbr, uint32_t n_dst, void *d_out, int dtype,
+                           const float *d_scale, const float *d_shift, int relu, double *d_stats,
+                           void *d_workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * out[r][c] = act(x[r][c] * scale[c] + shift[c]) (scale / shift may be NULL; act = ReLU when relu != 0);
+ * in place when d_out == d_x. With scale = gamma / sqrt(var + eps) and shift = beta - mean * scale this is
+ * the normalise + affine + ReLU of conv -> norm -> ReLU as one pass.
+ */
+int rmn_affine_act(const void *d_x, uint32_t n_rows, int channels, const float *d_scale,
+                   const float *d_shift, int relu, void *d_out, int dtype, void *stream);
+
 /* ----------------------------- local pooling --------------------------------
  * Pooling modes of rmn_pool_forward / rmn_pool_backward: the three local modes of
  * PoolingMode (engine/foundation/types.hpp), i.e. RiemannSumPooling / RiemannAvgPooling /

@@ -54,7 +54,7 @@ extern "C" const char* rmn_status_string(int status) {
 }
 
 // RMN_B200_DISABLE_TC=1 routes bf16 through the SIMT kernels (debugging aid).
-static bool use_tensor_cores() {
+bool use_tensor_cores() {
   static const bool on = [] {
     const char* e = std::getenv("RMN_B200_DISABLE_TC");
     return !(e && e[0] == '1');

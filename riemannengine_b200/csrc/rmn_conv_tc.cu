@@ -80,13 +80,33 @@ struct Cfg {
   static constexpr int STAGES = STAGE * 5 <= 216 * 1024 ? 5 : (STAGE * 4 <= 216 * 1024 ? 4 : 3);
   static constexpr uint32_t BAR_OFFSET = STAGES * STAGE;
   static constexpr uint32_t EP_OFFSET = BAR_OFFSET + 256;  // 2 * 256 floats of epilogue scale / shift
-  static constexpr uint32_t SMEM = EP_OFFSET + 2 * 256 * 4;
+  static constexpr uint32_t STATS_BYTES = 4 * 2 * CC * 4;  // per-warp channel statistics of the kStats epilogue
+  static constexpr uint32_t SMEM = EP_OFFSET + 2 * 256 * 4 + STATS_BYTES;
   static constexpr uint32_t TMEM_COLS = pow2_at_least(2 * T * CC);
 };
 
+// Sum over the 32 lanes of v[c] for c = 0..31, delivered to lane c (a transposing butterfly:
+// 31 shuffles instead of 32 five-step reductions). v is destroyed.
+__device__ __forceinline__ float warp_column_sums(float (&v)[32], int lane) {
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) {
+    const bool upper = (lane & d) != 0;
+#pragma unroll
+    for (int i = 0; i < d; ++i) {
+      const float keep = upper ? v[i + d] : v[i];
+      const float send = upper ? v[i] : v[i + d];
+      v[i] = keep + __shfl_xor_sync(0xFFFFFFFFu, send, d);
+    }
+  }
+  return v[0];
+}
+
 // CR: reduction channels per offset; CC: output channels; kWT: weights are read transposed
 // (backward input). Weight tensor is [K][CIN_w][COUT_w] with (CIN_w, COUT_w) = kWT ? (CC, CR) : (CR, CC).
-template <int CR, int CC, bool kWT>
+// kStats: the epilogue also accumulates, per output channel, the sum and the sum of squares of the
+// values it stores (the batch statistics of a following batch normalisation) and writes them to
+// stats_partial[blockIdx.x][2][CC]; a second kernel adds the per-CTA partials in a fixed order.
+template <int CR, int CC, bool kWT, bool kStats = false>
 __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_bfloat16* __restrict__ src,
                                                             const __nv_bfloat16* __restrict__ w,
                                                             const int32_t* __restrict__ nbr,
@@ -94,7 +114,8 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
                                                             __nv_bfloat16* __restrict__ out,
                                                             uint32_t n_super,
                                                             const float* __restrict__ ep_scale,
-                                                            const float* __restrict__ ep_shift, int ep_relu) {
+                                                            const float* __restrict__ ep_shift, int ep_relu,
+                                                            float* __restrict__ stats_partial = nullptr) {
   using C = Cfg<CR, CC>;
   constexpr int STAGES = C::STAGES, KB = C::KB, NKB = C::NKB, T = C::T, SWA = C::SWA;
   constexpr int kFwdProducerWarps = C::PRODUCER_WARPS, kFwdProducers = C::PRODUCERS;
@@ -293,6 +314,10 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
     // ------------------------------ epilogue -------------------------------------------
     const uint32_t quad = warp & 3;  // TMEM lanes [32*quad, 32*quad + 32)
     uint32_t tile_iter = 0;
+    // kStats: lane l of this warp accumulates channel c0 + l of every 32-channel chunk
+    float st_sum[kStats ? CC / 32 : 1], st_sq[kStats ? CC / 32 : 1];
+#pragma unroll
+    for (int i = 0; i < (kStats ? CC / 32 : 1); ++i) st_sum[i] = st_sq[i] = 0.f;
     for (uint32_t st = blockIdx.x; st < n_super && !timed_out; st += gridDim.x, ++tile_iter) {
       const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
       if (!mbar_wait(&tmem_full[acc], acc_ph)) { timed_out = true; break; }
@@ -329,10 +354,38 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
               dst[v] = o;
             }
           }
+          if constexpr (kStats) {
+            // statistics of the values as stored (rounded to bf16); rows past the end count as zero
+            float val[32], sq[32];
+#pragma unroll
+            for (int v = 0; v < 32; ++v) {
+              const float f = row < n_dst ? __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[v]))) : 0.f;
+              val[v] = f;
+              sq[v] = f * f;
+            }
+            st_sq[c0 / 32] += warp_column_sums(sq, lane);
+            st_sum[c0 / 32] += warp_column_sums(val, lane);
+          }
         }
       }
       tc_fence_before();
       mbar_arrive(&tmem_empty[acc]);
+    }
+    if constexpr (kStats) {
+      // the four epilogue warps add their partials in warp order through shared memory
+      float* s_st = s_ep + 2 * 256;  // [4 warps][2][CC]
+#pragma unroll
+      for (int i = 0; i < CC / 32; ++i) {
+        s_st[(quad * 2 + 0) * CC + i * 32 + lane] = st_sum[i];
+        s_st[(quad * 2 + 1) * CC + i * 32 + lane] = st_sq[i];
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+      for (int c = (int)(quad * 32) + lane; c < 2 * CC; c += 128) {
+        float t = 0.f;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) t += s_st[q4 * 2 * CC + c];
+        stats_partial[(size_t)blockIdx.x * 2 * CC + c] = t;
+      }
     }
   }
 
@@ -346,11 +399,14 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
   }
 }
 
-template <int CR, int CC, bool kWT>
+// stats_partial != nullptr selects the kStats instantiation (forward only); *grid_out receives the
+// number of CTAs, i.e. of [2][CC] partials written.
+template <int CR, int CC, bool kWT, bool kStats = false>
 int launch(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, void* out,
-           const float* ep_scale, const float* ep_shift, int ep_relu, cudaStream_t stream) {
+           const float* ep_scale, const float* ep_shift, int ep_relu, cudaStream_t stream,
+           float* stats_partial = nullptr, uint32_t* grid_out = nullptr) {
   using C = Cfg<CR, CC>;
-  auto kern = k_conv_tc<CR, CC, kWT>;
+  auto kern = k_conv_tc<CR, CC, kWT, kStats>;
   static bool configured[64] = {};
   int dev = 0;
   RMN_CUDA_TRY(cudaGetDevice(&dev));
@@ -367,8 +423,10 @@ int launch(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, i
   uint32_t grid = (uint32_t)sms * per_sm;
   if (grid > n_super) grid = n_super;
   kern<<<grid, C::THREADS, C::SMEM, stream>>>((const __nv_bfloat16*)src, (const __nv_bfloat16*)w, nbr, n_dst, K,
-                                               (__nv_bfloat16*)out, n_super, ep_scale, ep_shift, ep_relu);
+                                               (__nv_bfloat16*)out, n_super, ep_scale, ep_shift, ep_relu,
+                                               stats_partial);
   RMN_LAUNCH_CHECK();
+  if (grid_out) *grid_out = grid;
   return RMN_OK;
 }
 
@@ -411,6 +469,29 @@ int tc_conv(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, 
     return transposed_weights                                                                         \
                ? launch_best<R, Cc, true>(src, n_src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream)  \
                : launch_best<R, Cc, false>(src, n_src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream);
+  RMN_TC_CASE(32, 32)
+  RMN_TC_CASE(32, 64)
+  RMN_TC_CASE(64, 32)
+  RMN_TC_CASE(64, 64)
+  RMN_TC_CASE(64, 128)
+  RMN_TC_CASE(128, 64)
+  RMN_TC_CASE(128, 128)
+  RMN_TC_CASE(128, 256)
+  RMN_TC_CASE(256, 128)
+#undef RMN_TC_CASE
+  return RMN_ERR_UNSUPPORTED;
+}
+
+// Forward pass that also leaves per-CTA channel statistics ([*n_partials][2][c_col] floats: sums,
+// sums of squares of the stored values) in stats_partial (room for 2 * SM count partials).
+int tc_conv_stats(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
+                  int c_col, void* out, const float* ep_scale, const float* ep_shift, int ep_relu,
+                  float* stats_partial, uint32_t* n_partials, cudaStream_t stream) {
+  (void)n_src;
+#define RMN_TC_CASE(R, Cc)            \
+  if (c_red == R && c_col == Cc)      \
+    return tc::launch<R, Cc, false, true>(src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream, \
+                                          stats_partial, n_partials);
   RMN_TC_CASE(32, 32)
   RMN_TC_CASE(32, 64)
   RMN_TC_CASE(64, 32)

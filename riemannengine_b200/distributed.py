@@ -77,3 +77,35 @@ def allreduce_gradients(params: Iterable[torch.nn.Parameter], group: Optional[di
         size += nbytes
     flush()
     return calls
+
+
+def merge_batch_stats(stats: torch.Tensor, count: int, group: Optional[dist.ProcessGroup] = None):
+    """Batch-normalisation moments over all ranks from each rank's per-channel sums.
+
+    ``stats`` is float64 [2, C] (sum, sum of squares over this rank's ``count`` rows). One
+    all-reduce of 2C + 1 numbers (no-op without an initialised process group) gives the
+    whole-batch moments, which is what a single-process run over the full batch computes: returns
+    (mean [C], biased variance [C], total row count)."""
+    flat = torch.cat([stats.reshape(-1).to(torch.float64),
+                      torch.tensor([float(count)], dtype=torch.float64, device=stats.device)])
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+    total = float(flat[-1].item())
+    c = stats.size(1)
+    denom = max(total, 1.0)
+    mean = flat[:c] / denom
+    var = (flat[c:2 * c] / denom - mean * mean).clamp_min_(0.0)
+    return mean, var, int(total)
+
+
+def allreduce_sum_(tensors: Sequence[torch.Tensor], group: Optional[dist.ProcessGroup] = None) -> None:
+    """In-place sum over ranks of a few small tensors as ONE flat all-reduce (no-op on one rank)."""
+    if not (dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1):
+        return
+    flat = torch.cat([t.reshape(-1).to(torch.float64) for t in tensors])
+    dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+    pos = 0
+    for t in tensors:
+        n = t.numel()
+        t.copy_(flat[pos:pos + n].reshape(t.shape).to(t.dtype))
+        pos += n

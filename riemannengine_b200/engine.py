@@ -559,19 +559,91 @@ def sparse_convolution(features: torch.Tensor, kernel: torch.Tensor, kmap: Kerne
     return _SparseConvolutionFunction.apply(features, kernel, kmap, bias)
 
 
+class _ConvBNActFunction(torch.autograd.Function):
+    """conv -> batch norm with batch statistics -> optional ReLU (training mode).
+
+    The per-channel sums come out of the convolution's epilogue (ops.conv_forward_stats), the
+    moments are merged over the ranks of ``group`` (whole-batch statistics: the sync batch norm the
+    reference aliases to the plain layer, engine/nn/normalization.hpp:36-37), and normalise + affine
+    + ReLU is one pass (ops.affine_act). The backward pass is the textbook batch-norm gradient
+    followed by the convolution's input and weight gradients."""
+
+    @staticmethod
+    def forward(ctx, features, kernel, bias, gamma, beta, kmap: KernelMap, eps: float, relu: bool, group):
+        from . import distributed as D
+        z, stats = ops.conv_forward_stats(features, kernel, kmap.nbr_out, shift=bias)
+        mean, var, count = D.merge_batch_stats(stats, z.size(0), group)
+        inv = torch.rsqrt(var + eps)
+        g = gamma.detach().double() if gamma is not None else torch.ones_like(inv)
+        b = beta.detach().double() if beta is not None else torch.zeros_like(inv)
+        scale = g * inv
+        y = ops.affine_act(z, scale, b - mean * scale, relu)
+        ctx.save_for_backward(features, kernel, z, y if relu else None, mean, inv, gamma)
+        ctx.kmap, ctx.relu, ctx.count, ctx.group = kmap, relu, count, group
+        ctx.has_bias, ctx.has_beta = bias is not None, beta is not None
+        total = torch.tensor(float(count), dtype=torch.float64, device=y.device)
+        ctx.mark_non_differentiable(mean, var, total)
+        return y, mean, var, total
+
+    @staticmethod
+    def backward(ctx, grad_y, _gm, _gv, _gc):
+        from . import distributed as D
+        features, kernel, z, y, mean, inv, gamma = ctx.saved_tensors
+        dy = grad_y.float()
+        if ctx.relu:
+            dy = dy * (y > 0)
+        zhat = (z.float() - mean.float()) * inv.float()
+        dbeta = dy.sum(0, dtype=torch.float64)
+        dgamma = (dy * zhat).sum(0, dtype=torch.float64)
+        D.allreduce_sum_([dbeta, dgamma], ctx.group)
+        n = float(max(ctx.count, 1))
+        g = gamma.detach().float() if gamma is not None else torch.ones_like(inv, dtype=torch.float32)
+        dz = (g * inv.float()) * (dy - (dbeta / n).float() - zhat * (dgamma / n).float())
+        dz = dz.to(z.dtype)
+        kmap = ctx.kmap
+        g_feat = g_kernel = None
+        if ctx.needs_input_grad[0]:
+            if kmap.self_symmetric:
+                g_feat = ops.conv_backward_input(dz, kernel.flip(0), kmap.nbr_out)
+            else:
+                g_feat = ops.conv_backward_input(dz, kernel, kmap.nbr_in)
+        if ctx.needs_input_grad[1]:
+            g_kernel = ops.conv_backward_weight(features, dz, kmap.nbr_out).to(kernel.dtype)
+        g_bias = dz.sum(0, keepdim=True).to(kernel.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        g_gamma = dgamma.to(gamma.dtype) if gamma is not None and ctx.needs_input_grad[3] else None
+        g_beta = dbeta.to(gamma.dtype if gamma is not None else torch.float32) if ctx.has_beta and ctx.needs_input_grad[4] else None
+        return g_feat, g_kernel, g_bias, g_gamma, g_beta, None, None, None, None
+
+
 def fused_conv_bn_relu(input: "SparseTensor", conv, bn: Optional[torch.nn.BatchNorm1d] = None,
-                       relu: bool = True) -> "SparseTensor":
-    """Inference-only conv -> batch norm (running statistics) -> ReLU as ONE kernel: the norm's
-    affine and the layer's bias are folded into the convolution epilogue. Equals
-    ``relu(bn(conv(input).F))`` with ``bn`` in eval mode (the reference's blocks run these as
-    three passes, engine/nn/residual.cpp:44-52)."""
+                       relu: bool = True, process_group=None) -> "SparseTensor":
+    """conv -> batch norm -> ReLU (the reference's blocks run these as three modules and four passes
+    over the features, engine/nn/residual.cpp:44-52).
+
+    ``bn`` in eval mode: the norm's running statistics and affine and the layer's bias are folded
+    into the convolution epilogue: ONE kernel, inference only.
+    ``bn`` in training mode: batch statistics from the convolution epilogue, merged over
+    ``process_group`` when one is initialised (sync batch norm), then one normalise + ReLU pass;
+    differentiable; running statistics are updated as torch.nn.BatchNorm1d does."""
     base = conv.base if hasattr(conv, "base") else conv
+    if bn is not None and bn.training:
+        out_key, kmap = base._output_key_and_map(input)
+        bias = base.bias.reshape(-1) if base.bias is not None else None
+        y, mean, var, total = _ConvBNActFunction.apply(input.F, base.kernel, bias, bn.weight, bn.bias, kmap, bn.eps,
+                                                       relu, process_group)
+        if bn.track_running_stats and bn.running_mean is not None:
+            with torch.no_grad():
+                bn.num_batches_tracked += 1
+                m = bn.momentum if bn.momentum is not None else 1.0 / float(bn.num_batches_tracked)
+                count = float(total.item())
+                unbiased = var * (count / max(count - 1.0, 1.0))
+                bn.running_mean.mul_(1 - m).add_(mean.to(bn.running_mean.dtype), alpha=m)
+                bn.running_var.mul_(1 - m).add_(unbiased.to(bn.running_var.dtype), alpha=m)
+        return SparseTensor(y, out_key, input.coordinate_manager)
     with torch.no_grad():
         scale = shift = None
         bias = base.bias.reshape(-1).float() if base.bias is not None else None
         if bn is not None:
-            if bn.training:
-                raise RuntimeError("fused_conv_bn_relu folds running statistics: call bn.eval() first")
             inv = torch.rsqrt(bn.running_var.float() + bn.eps)
             scale = inv * (bn.weight.float() if bn.weight is not None else 1.0)
             shift = -bn.running_mean.float() * scale
@@ -584,6 +656,25 @@ def fused_conv_bn_relu(input: "SparseTensor", conv, bn: Optional[torch.nn.BatchN
         out_key, kmap = base._output_key_and_map(input)
         feats = ops.conv_forward(input.F, base.kernel, kmap.nbr_out, scale=scale, shift=shift, relu=relu)
     return SparseTensor(feats, out_key, input.coordinate_manager)
+
+
+class RiemannBatchNorm(torch.nn.Module):
+    """RiemannBatchNormImpl (engine/nn/normalization.hpp:11-34): torch's BatchNorm1d over the feature
+    matrix of a SparseTensor. ``normalization`` is the wrapped module (same attribute name as the
+    reference's registered sub-module); pass it to ``fused_conv_bn_relu`` to fuse it with the
+    preceding convolution."""
+
+    def __init__(self, num_features: int, eps: float = 1e-5, momentum: float = 0.1, affine: bool = True,
+                 track_running_stats: bool = True):
+        super().__init__()
+        self.normalization = torch.nn.BatchNorm1d(num_features, eps=eps, momentum=momentum, affine=affine,
+                                                  track_running_stats=track_running_stats)
+
+    def forward(self, input: "SparseTensor") -> "SparseTensor":
+        return SparseTensor(self.normalization(input.F), input.coordinate_map_key, input.coordinate_manager)
+
+
+RiemannSyncBatchNorm = RiemannBatchNorm  # the reference's alias (engine/nn/normalization.hpp:36-37)
 
 
 class RiemannConvolutionBase(torch.nn.Module):

@@ -335,3 +335,64 @@ def pool_backward(grad_out: torch.Tensor, nbr_in: torch.Tensor, mode: int, aux: 
                                                 int(mode), _ptr(aux), _ptr(grad_in), _dtype_code(grad_out),
                                                 _stream()), "rmn_pool_backward")
     return grad_in
+
+
+def channel_stats(x: torch.Tensor) -> torch.Tensor:
+    """float64 [2, C]: per-channel sum and sum of squares of ``x`` [N, C] (rmn_channel_stats)."""
+    _require_cuda(x, "features")
+    x = x.contiguous()
+    n, c = int(x.size(0)), int(x.size(1))
+    lib = capi.lib()
+    stats = torch.empty((2, c), dtype=torch.float64, device=x.device)
+    wbytes = lib.rmn_channel_stats_workspace_bytes(c)
+    ws = torch.empty(wbytes, dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        capi.check(lib.rmn_channel_stats(_ptr(x), n, c, _dtype_code(x), _ptr(stats), _ptr(ws), wbytes, _stream()),
+                   "rmn_channel_stats")
+    return stats
+
+
+def conv_forward_stats(feats: torch.Tensor, weights: torch.Tensor, nbr: torch.Tensor,
+                       scale: Optional[torch.Tensor] = None, shift: Optional[torch.Tensor] = None,
+                       relu: bool = False):
+    """conv_forward that also returns float64 [2, C_out] channel sums / sums of squares of the output it
+    stores, accumulated in the tensor-core kernel's epilogue (rmn_conv_forward_stats)."""
+    _check_conv(feats, weights, "features")
+    feats, weights = feats.contiguous(), weights.contiguous()
+    K, c_in, c_out = (int(s) for s in weights.shape)
+    if feats.size(1) != c_in or nbr.size(0) != K:
+        raise RuntimeError("Input channel count does not match convolution")
+    n_dst = int(nbr.size(1))
+    out = torch.empty((n_dst, c_out), dtype=feats.dtype, device=feats.device)
+    stats = torch.empty((2, c_out), dtype=torch.float64, device=feats.device)
+
+    def vec(v):
+        return None if v is None else v.detach().reshape(-1).to(device=feats.device, dtype=torch.float32).contiguous()
+
+    sc, sh = vec(scale), vec(shift)
+    lib = capi.lib()
+    wbytes = lib.rmn_channel_stats_workspace_bytes(c_out)
+    ws = torch.empty(wbytes, dtype=torch.uint8, device=feats.device)
+    with torch.cuda.device(feats.device):
+        capi.check(lib.rmn_conv_forward_stats(_ptr(feats), int(feats.size(0)), c_in, _ptr(weights), K, c_out, _ptr(nbr),
+                                              n_dst, _ptr(out), _dtype_code(feats), _ptr(sc), _ptr(sh),
+                                              int(bool(relu)), _ptr(stats), _ptr(ws), wbytes, _stream()),
+                   "rmn_conv_forward_stats")
+    return out, stats
+
+
+def affine_act(x: torch.Tensor, scale: Optional[torch.Tensor], shift: Optional[torch.Tensor], relu: bool = False,
+               inplace: bool = False) -> torch.Tensor:
+    """act(x * scale + shift) per channel in one pass (rmn_affine_act)."""
+    _require_cuda(x, "features")
+    x = x.contiguous()
+    out = x if inplace else torch.empty_like(x)
+
+    def vec(v):
+        return None if v is None else v.detach().reshape(-1).to(device=x.device, dtype=torch.float32).contiguous()
+
+    sc, sh = vec(scale), vec(shift)
+    with torch.cuda.device(x.device):
+        capi.check(capi.lib().rmn_affine_act(_ptr(x), int(x.size(0)), int(x.size(1)), _ptr(sc), _ptr(sh),
+                                             int(bool(relu)), _ptr(out), _dtype_code(x), _stream()), "rmn_affine_act")
+    return out

@@ -178,6 +178,26 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("dilation") = 1, py::arg("bias") = false, py::arg("convolution_mode") = ConvolutionMode::DEFAULT,
            py::arg("dimension") = 3);
 
+  // inference fold of a batch norm given by its tensors (what torch.nn.BatchNorm1d holds in eval mode)
+  m.def(
+      "fused_conv_bn_relu",
+      [](const SparseTensor& input, std::shared_ptr<RiemannConvolutionImpl> conv, at::Tensor running_mean,
+         at::Tensor running_var, at::Tensor weight, at::Tensor bias, double eps, bool relu) {
+        torch::nn::BatchNorm1d bn(torch::nn::BatchNorm1dOptions(running_mean.numel()).eps(eps));
+        bn->to(running_mean.device());
+        {
+          torch::NoGradGuard guard;
+          bn->running_mean.copy_(running_mean);
+          bn->running_var.copy_(running_var);
+          if (weight.defined() && weight.numel()) bn->weight.copy_(weight);
+          if (bias.defined() && bias.numel()) bn->bias.copy_(bias);
+        }
+        bn->eval();
+        return fused_conv_bn_relu(input, *conv->base(), bn, relu);
+      },
+      py::arg("input"), py::arg("conv"), py::arg("running_mean"), py::arg("running_var"), py::arg("weight"),
+      py::arg("bias"), py::arg("eps") = 1e-5, py::arg("relu") = true, py::call_guard<py::gil_scoped_release>());
+
   py::enum_<PoolingMode::Type>(m, "PoolingMode")
       .value("LOCAL_SUM_POOLING", PoolingMode::LOCAL_SUM_POOLING)
       .value("LOCAL_AVG_POOLING", PoolingMode::LOCAL_AVG_POOLING)

@@ -486,7 +486,8 @@ namespace {
 
 // bias (if defined) is folded into the kernel's epilogue as a per-channel shift
 at::Tensor conv_forward(const at::Tensor& feats_in, const at::Tensor& kernel_in, const at::Tensor& nbr,
-                        const at::Tensor& bias = at::Tensor()) {
+                        const at::Tensor& bias = at::Tensor(), const at::Tensor& scale_in = at::Tensor(),
+                        bool relu = false) {
   TORCH_CHECK(feats_in.is_cuda() && kernel_in.is_cuda(), "features and kernel must be CUDA tensors");
   TORCH_CHECK(feats_in.scalar_type() == kernel_in.scalar_type(), "expected features and kernel to have the same dtype");
   auto feats = feats_in.contiguous(), kernel = kernel_in.contiguous();
@@ -499,10 +500,15 @@ at::Tensor conv_forward(const at::Tensor& feats_in, const at::Tensor& kernel_in,
     shift = bias.detach().reshape({-1}).to(at::kFloat).contiguous();
     TORCH_CHECK(shift.numel() == c_out, "bias must have one entry per output channel");
   }
+  at::Tensor scale;
+  if (scale_in.defined() && scale_in.numel() > 0) {
+    scale = scale_in.detach().reshape({-1}).to(at::kFloat).contiguous();
+    TORCH_CHECK(scale.numel() == c_out, "scale must have one entry per output channel");
+  }
   check(rmn_conv_forward_fused(ptr(feats), static_cast<uint32_t>(feats.size(0)), c_in, ptr(kernel), K, c_out,
                                static_cast<const int32_t*>(ptr(nbr)), static_cast<uint32_t>(nbr.size(1)), ptr(out),
-                               dtype_code(feats), nullptr, static_cast<const float*>(ptr(shift)), 0,
-                               current_stream()),
+                               dtype_code(feats), scale.defined() ? static_cast<const float*>(ptr(scale)) : nullptr,
+                               static_cast<const float*>(ptr(shift)), relu ? 1 : 0, current_stream()),
         "rmn_conv_forward_fused");
   return out;
 }
@@ -631,8 +637,62 @@ SparseTensor RiemannConvolutionBaseImpl::forward(const SparseTensor& input) {
   auto kmap = manager->kernel_map(input.coordinate_map_key(), output_key, params.kernel_size, params.kernel_stride,
                                   params.kernel_dilation, params.region_type, params.region_offsets, is_transpose_,
                                   false);
+  if (fold_scale_.defined() || fold_shift_.defined() || fold_relu_) {  // set by fused_conv_bn_relu for one call
+    torch::NoGradGuard guard;
+    auto result = conv_forward(input.F(), kernel_, kmap->nbr_out, fold_shift_, fold_scale_, fold_relu_);
+    return SparseTensor(std::move(result), output_key, std::move(manager));
+  }
   auto result = sparse_convolution(input.F(), kernel_, kmap, bias_);  // the bias add is fused into the epilogue
   return SparseTensor(std::move(result), output_key, std::move(manager));
+}
+
+// conv -> batch norm (running statistics) -> ReLU as ONE kernel (inference): the norm's affine and the
+// layer's bias are folded into the convolution epilogue (engine/nn/residual.cpp:44-52 runs three modules).
+SparseTensor fused_conv_bn_relu(const SparseTensor& input, RiemannConvolutionBaseImpl& conv,
+                                torch::nn::BatchNorm1d bn, bool relu) {
+  torch::NoGradGuard guard;
+  at::Tensor scale, shift;
+  at::Tensor bias = conv.bias_.defined() ? conv.bias_.reshape({-1}).to(at::kFloat) : at::Tensor();
+  if (!bn.is_empty()) {
+    TORCH_CHECK(!bn->is_training(), "fused_conv_bn_relu folds running statistics: call bn->eval() first");
+    TORCH_CHECK(bn->running_var.defined(), "fused_conv_bn_relu needs running statistics");
+    auto inv = torch::rsqrt(bn->running_var.to(at::kFloat) + bn->options.eps());
+    scale = bn->weight.defined() ? inv * bn->weight.to(at::kFloat) : inv;
+    shift = -bn->running_mean.to(at::kFloat) * scale;
+    if (bn->bias.defined()) shift = shift + bn->bias.to(at::kFloat);
+    if (bias.defined()) shift = shift + bias * scale;
+  } else {
+    shift = bias;
+  }
+  conv.fold_scale_ = scale;
+  conv.fold_shift_ = shift;
+  conv.fold_relu_ = relu;
+  try {
+    auto out = conv.forward(input);
+    conv.fold_scale_ = at::Tensor();
+    conv.fold_shift_ = at::Tensor();
+    conv.fold_relu_ = false;
+    return out;
+  } catch (...) {
+    conv.fold_scale_ = at::Tensor();
+    conv.fold_shift_ = at::Tensor();
+    conv.fold_relu_ = false;
+    throw;
+  }
+}
+
+RiemannBatchNormImpl::RiemannBatchNormImpl(int64_t num_features, double eps, double momentum, bool affine,
+                                           bool track_running_stats)
+    : normalization_(register_module(
+          "normalization", torch::nn::BatchNorm1d(torch::nn::BatchNorm1dOptions(num_features)
+                                                      .eps(eps)
+                                                      .momentum(momentum)
+                                                      .affine(affine)
+                                                      .track_running_stats(track_running_stats)))) {}
+
+SparseTensor RiemannBatchNormImpl::forward(const SparseTensor& input) {
+  auto values = normalization_->forward(input.F());
+  return SparseTensor(std::move(values), input.coordinate_map_key(), input.coordinate_manager());
 }
 
 RiemannConvolutionImpl::RiemannConvolutionImpl(int in_channels, int out_channels, int kernel_size, int stride,

@@ -264,7 +264,29 @@ public:
   KernelGenerator kernel_generator_;
   torch::Tensor kernel_{nullptr};
   torch::Tensor bias_{nullptr};
+  // per-call epilogue fold (scale, shift, ReLU) installed by fused_conv_bn_relu; empty otherwise
+  at::Tensor fold_scale_, fold_shift_;
+  bool fold_relu_ = false;
 };
+
+// RiemannBatchNormImpl (engine/nn/normalization.hpp:11-34): torch's BatchNorm1d over the feature matrix.
+class RiemannBatchNormImpl : public torch::nn::Module {
+public:
+  RiemannBatchNormImpl(int64_t num_features, double eps = 1e-5, double momentum = 0.1, bool affine = true,
+                       bool track_running_stats = true);
+  SparseTensor forward(const SparseTensor& input);
+  torch::nn::BatchNorm1d normalization() { return normalization_; }
+
+private:
+  torch::nn::BatchNorm1d normalization_{nullptr};
+};
+TORCH_MODULE(RiemannBatchNorm);
+using RiemannSyncBatchNormImpl = RiemannBatchNormImpl;  // as in the reference (normalization.hpp:36-37)
+using RiemannSyncBatchNorm = RiemannBatchNorm;
+
+// Inference-only conv -> batch norm -> ReLU as one kernel; `bn` may be an empty holder (bias + ReLU only).
+SparseTensor fused_conv_bn_relu(const SparseTensor& input, RiemannConvolutionBaseImpl& conv,
+                                torch::nn::BatchNorm1d bn = nullptr, bool relu = true);
 
 #define RIEMANN_B200_CONV_WRAPPER(Name)                                                                   \
   class Name##Impl : public torch::nn::Cloneable<Name##Impl> {                                            \

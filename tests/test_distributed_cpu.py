@@ -72,3 +72,33 @@ def test_allreduce_is_noop_without_process_group():
     p.grad = torch.ones(3)
     assert D.allreduce_gradients([p]) == 0
     assert torch.equal(p.grad, torch.ones(3))
+
+
+def _stats_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(1000, 6, generator=g, dtype=torch.float64) * 2 + 1   # same full batch on every rank
+    mine = x[:300] if rank == 0 else x[300:]                             # uneven shards
+    stats = torch.stack([mine.sum(0), (mine * mine).sum(0)])
+    mean, var, total = D.merge_batch_stats(stats, mine.size(0))
+    ok = total == 1000 and torch.allclose(mean, x.mean(0)) and torch.allclose(var, x.var(0, unbiased=False))
+    a, b = torch.full((6,), float(rank + 1)), torch.full((2, 3), 10.0 * (rank + 1))
+    D.allreduce_sum_([a, b])
+    ok = ok and torch.equal(a, torch.full((6,), 3.0)) and torch.equal(b, torch.full((2, 3), 30.0))
+    out[rank] = bool(ok)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_batch_stats_merge_two_ranks_gloo():
+    """Whole-batch moments from per-rank sums (the sync batch-norm exchange) equal the single-process moments."""
+    world = 2
+    with mp.Manager() as m:
+        out = m.dict()
+        mp.spawn(_stats_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+        assert all(out[r] for r in range(world))
+    # one rank, no process group: plain moments
+    x = torch.arange(12, dtype=torch.float64).reshape(4, 3)
+    mean, var, total = D.merge_batch_stats(torch.stack([x.sum(0), (x * x).sum(0)]), 4)
+    assert total == 4 and torch.allclose(mean, x.mean(0)) and torch.allclose(var, x.var(0, unbiased=False))

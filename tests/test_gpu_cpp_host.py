@@ -117,3 +117,20 @@ def test_cpp_pooling_matches_reference_golden(C, name):
     ((y.F * y.F).sum() * 0.5).backward()
     parity.check_pool_against_reference(y.C.cpu().numpy(), y.F.detach().cpu().numpy(), f.grad.cpu().numpy(), gold,
                                         tol=1e-4)
+
+
+def test_cpp_fused_conv_bn_relu_inference(C):
+    """One-kernel conv -> batch norm (running statistics) -> ReLU equals the three separate steps."""
+    coords, feats = _inputs(n=1500, c=6, seed=9)
+    x = C.SparseTensor(torch.from_numpy(feats).cuda(), torch.from_numpy(coords).cuda())
+    conv = C.RiemannConvolution(6, 10, kernel_size=3, bias=True, dimension=3)
+    conv.to("cuda")
+    bn = torch.nn.BatchNorm1d(10).cuda().eval()
+    with torch.no_grad():
+        bn.running_mean.uniform_(-0.5, 0.5)
+        bn.running_var.uniform_(0.5, 2.0)
+        bn.weight.uniform_(0.5, 1.5)
+        bn.bias.uniform_(-0.5, 0.5)
+        want = torch.relu(bn(conv(x).F))
+        got = C.fused_conv_bn_relu(x, conv, bn.running_mean, bn.running_var, bn.weight, bn.bias, bn.eps, True).F
+    assert rel_max(got.cpu().numpy(), want.cpu().numpy()) <= 1e-4
