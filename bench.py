@@ -354,6 +354,32 @@ def run_product(args) -> None:
         med = [statistics.median(rep[i].elapsed_time(rep[i + 1]) for rep in marks[2:]) for i in range(len(phase_fns))]
         t_hash, t_kmap, t_pairs, t_fwd, t_kmap_general = med
 
+        # ---- side measurement: the workload's second layer, 2^3 stride-2 64 -> 128 -----------------
+        # hash insert + strided coordinate map + kernel map (general builder, K = 8) + forward on a fresh manager
+        down = E.RiemannConvolution(C_IN, 128, kernel_size=2, stride=2, dimension=3).to(dev).bfloat16()
+        cdown = None
+        if cpp_host is not None:
+            cdown = cpp_host.RiemannConvolution(C_IN, 128, kernel_size=2, stride=2, dimension=3)
+            cdown.to(f"cuda:{local_rank}")
+            cdown.to(torch.bfloat16)
+
+        def down_step():
+            if cdown is not None:
+                return cdown(cpp_host.SparseTensor(feats, coords))
+            return down(E.SparseTensor(feats, coords))
+
+        for _ in range(3):
+            yd = down_step()
+        n_down = len(yd)
+        torch.cuda.synchronize()
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0.record()
+        for _ in range(args.steps):
+            down_step()
+        d1.record()
+        torch.cuda.synchronize()
+        down_ms = d0.elapsed_time(d1) / args.steps
+
         # ---- end to end through the public API with HOST buffers ----------------------------------
         h_coords = torch.from_numpy(coords_np).pin_memory()
         h_feats = torch.from_numpy(feats_np).bfloat16().pin_memory()
@@ -506,6 +532,10 @@ def run_product(args) -> None:
                 "d2h_bytes_per_step": int(h_out.numel() * 2)},
         "gpu_launches": int(launches),
         "clocks": clocks,
+        "strided_layer": {"layer": "2x2x2 stride-2 conv 64->128 on the same batch (hash insert + strided map + "
+                                   "kernel map + forward, fresh manager)", "ms_per_step": down_ms,
+                          "mvoxels_per_s": n_vox / (down_ms / 1e3) / 1e6, "output_voxels_per_gpu": int(n_down),
+                          "note": "this rank only; not part of `value`"},
     }
     print(json.dumps(line))
     if world > 1:

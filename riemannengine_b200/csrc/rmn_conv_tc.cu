@@ -478,6 +478,7 @@ int tc_conv(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, 
   RMN_TC_CASE(128, 128)
   RMN_TC_CASE(128, 256)
   RMN_TC_CASE(256, 128)
+  RMN_TC_CASE(256, 256)
 #undef RMN_TC_CASE
   return RMN_ERR_UNSUPPORTED;
 }
@@ -501,6 +502,7 @@ int tc_conv_stats(const void* src, uint32_t n_src, const void* w, const int32_t*
   RMN_TC_CASE(128, 128)
   RMN_TC_CASE(128, 256)
   RMN_TC_CASE(256, 128)
+  RMN_TC_CASE(256, 256)
 #undef RMN_TC_CASE
   return RMN_ERR_UNSUPPORTED;
 }

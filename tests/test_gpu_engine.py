@@ -182,6 +182,9 @@ def test_fused_conv_bn_relu_matches_unfused(dtype, c_in, c_out, tol):
         # bias-only epilogue is what the layer's own forward uses
         y = conv(x).F.float()
         assert float((y - acc).norm() / acc.norm()) <= tol
+    # training mode takes the batch-statistics path (checked against torch's BatchNorm1d in
+    # tests/test_gpu_norm.py): it runs, and it moves the running statistics
     bn.train()
-    with pytest.raises(RuntimeError, match="eval"):
-        E.fused_conv_bn_relu(x, conv, bn)
+    before = bn.running_mean.clone()
+    out = E.fused_conv_bn_relu(x, conv, bn)
+    assert torch.isfinite(out.F.float()).all() and not torch.equal(before, bn.running_mean)

@@ -183,7 +183,8 @@ def test_sphere_shell_strided_and_transposed(gpu):
         assert rel_max(r1[key], r0[key]) <= FP32_TOL, key
 
 
-@pytest.mark.parametrize("c_in,c_out", [(64, 64), (32, 64), (4, 32), (64, 128), (16, 16), (128, 64)])
+@pytest.mark.parametrize("c_in,c_out", [(64, 64), (32, 64), (4, 32), (64, 128), (16, 16), (128, 64), (128, 256),
+                                         (256, 256)])
 def test_bf16_conv_against_fp64_oracle(gpu, c_in, c_out):
     from riemannengine_b200 import synthetic
     O, G = OracleBackend(f64=True), gpu(torch.bfloat16)
