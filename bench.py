@@ -58,6 +58,23 @@ def captured_traffic(*names: str):
         return None
 
 
+class stdout_to_stderr:
+    """Point file descriptor 1 at stderr for the duration of the block (native libraries write
+    banners to stdout behind Python's back)."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self._saved = os.dup(1)
+        os.dup2(2, 1)
+        return self
+
+    def __exit__(self, *exc):
+        sys.stdout.flush()
+        os.dup2(self._saved, 1)
+        os.close(self._saved)
+        return False
+
+
 def load_peaks() -> dict:
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -235,9 +252,9 @@ def run_product(args) -> None:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        # NCCL writes its version banner to stdout when NCCL_DEBUG is set; stdout carries the JSON line only
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        dist.init_process_group("nccl", device_id=dev)
+        with stdout_to_stderr():  # NCCL's version banner goes to stdout; stdout carries the JSON line only
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
     lib = capi.lib()
 
     coords_np, feats_np, weights_np = make_batch(rank)
@@ -558,9 +575,9 @@ def run_train(args) -> None:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        # NCCL writes its version banner to stdout when NCCL_DEBUG is set; stdout carries the JSON line only
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        dist.init_process_group("nccl", device_id=dev)
+        with stdout_to_stderr():  # NCCL's version banner goes to stdout; stdout carries the JSON line only
+            dist.init_process_group("nccl", device_id=dev)
+            dist.barrier()
     lib = capi.lib()
     coords_np, feats_np, weights_np = make_batch(rank)
     coords = torch.from_numpy(coords_np).to(dev)

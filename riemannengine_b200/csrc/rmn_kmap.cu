@@ -223,8 +223,8 @@ __global__ void __launch_bounds__(1024) k_kmap_scan_blocks(uint32_t* __restrict_
 // one thread: offset_ptr[0..K] = exclusive scan of totals (K is small)
 // mirror_half > 0 (self map): offsets K-1-k and k hold the same number of pairs, so the totals of
 // the mirrored half are copied from the probed half, and *mirror_flag records the half: the pair
-// lists of the mirrored offsets are then the swapped lists of their mirror offsets (k_kmap_pairs_mirror)
-// and need no per-block counts.
+// lists of the mirrored offsets are then the exchanged lists of their mirror offsets (written by
+// k_kmap_pairs together with the originals) and need no per-block counts.
 __global__ void k_kmap_offset_ptr(uint32_t* __restrict__ totals, int K, int64_t* __restrict__ offset_ptr,
                                   int mirror_half, uint32_t* mirror_flag) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
@@ -248,10 +248,17 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_pairs(
     unsigned long long capacity, uint32_t* __restrict__ overflow) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t row0 = blockIdx.x * kKmapBlock;
-  K -= (int)overflow[1];  // self map: the mirrored offsets are filled by k_kmap_pairs_mirror
+  // Self map (flag word after the overflow word = K / 2): only the offsets up to the centre are walked;
+  // a pair (a, q) of offset k < K / 2 is also stored, exchanged, at the same rank of offset K-1-k, whose
+  // list therefore comes out sorted by table row.
+  const int mirror_half = (int)overflow[1];
+  const int K_full = K;
+  K -= mirror_half;
   for (int k = warp; k < K; k += kKmapBlock / 32) {
-    unsigned long long pos =
-        (unsigned long long)offset_ptr[k] + block_prefix[(size_t)k * n_blocks + blockIdx.x];
+    const unsigned long long base = (unsigned long long)offset_ptr[k];
+    unsigned long long pos = base + block_prefix[(size_t)k * n_blocks + blockIdx.x];
+    const bool mirror = k < mirror_half;
+    const unsigned long long mbase = mirror ? (unsigned long long)offset_ptr[K_full - 1 - k] : 0ull;
     // all eight row groups are loaded before the first ballot (eight independent 128-byte reads in flight)
     int32_t av[kKmapBlock / 32];
 #pragma unroll
@@ -271,6 +278,15 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_pairs(
           __stcs(q_idx + p, (int32_t)q);
         } else {
           *overflow = 1;
+        }
+        if (mirror) {
+          const unsigned long long d = mbase + (p - base);
+          if (d < capacity) {
+            __stcs(a_idx + d, (int32_t)q);
+            __stcs(q_idx + d, a);
+          } else {
+            *overflow = 1;
+          }
         }
       }
       pos += __popc(hits);
@@ -347,26 +363,6 @@ extern "C" int rmn_region_offsets(int region_type, int D, const int32_t* kernel_
     }
   }
   return K;
-}
-
-// Self map: the pairs of offset K-1-k are the pairs of offset k with input and output row
-// exchanged (grid.y = offset k < half). They come out sorted by input row.
-__global__ void __launch_bounds__(256) k_kmap_pairs_mirror(const int64_t* __restrict__ offset_ptr, int K,
-                                                           const uint32_t* __restrict__ mirror_flag,
-                                                           int32_t* __restrict__ a_idx, int32_t* __restrict__ q_idx,
-                                                           unsigned long long capacity) {
-  const int half = (int)*mirror_flag, k = blockIdx.y;
-  if (k >= half) return;
-  const unsigned long long begin = (unsigned long long)offset_ptr[k], end = (unsigned long long)offset_ptr[k + 1];
-  const unsigned long long dst0 = (unsigned long long)offset_ptr[K - 1 - k];
-  for (unsigned long long p = begin + blockIdx.x * blockDim.x + threadIdx.x; p < end;
-       p += (unsigned long long)gridDim.x * blockDim.x) {
-    const unsigned long long d = dst0 + (p - begin);
-    if (p < capacity && d < capacity) {
-      a_idx[d] = q_idx[p];
-      q_idx[d] = a_idx[p];
-    }
-  }
 }
 
 extern "C" size_t rmn_kmap_workspace_bytes(uint32_t n_query, int K) {
@@ -456,12 +452,6 @@ extern "C" int rmn_kmap_pairs(const int32_t* d_nbr, uint32_t n_query, int K,
   k_kmap_pairs<<<nb, kKmapBlock, 0, stream>>>(d_nbr, n_query, K, d_offset_ptr, block_prefix, nb,
                                               d_a_idx, d_q_idx, capacity, overflow);
   RMN_LAUNCH_CHECK();
-  if (K >= 3 && (K & 1)) {  // possibly a self map (odd K): returns at once unless its flag is set
-    const uint32_t per_offset = (n_query + 255u) / 256u < 64u ? (n_query + 255u) / 256u : 64u;
-    k_kmap_pairs_mirror<<<dim3(per_offset ? per_offset : 1u, (unsigned)(K / 2)), 256, 0, stream>>>(
-        d_offset_ptr, K, overflow + 1, d_a_idx, d_q_idx, capacity);
-    RMN_LAUNCH_CHECK();
-  }
   return RMN_OK;
 }
 
