@@ -849,3 +849,16 @@ class RiemannSumPooling(RiemannPoolingBase):
 class RiemannMaxPooling(RiemannPoolingBase):
     def __init__(self, kernel_size: int, stride: int = 1, dilation: int = 1, dimension: int = 3):
         super().__init__(kernel_size, stride, dilation, PoolingMode.LOCAL_MAX_POOLING, dimension)
+
+
+def cat(tensors: Sequence[SparseTensor]) -> SparseTensor:
+    """Channel concatenation of tensors that share one coordinate map (riemann::cat,
+    engine/nn/operations.cpp:56-64): the skip connections of encoder/decoder networks."""
+    tensors = list(tensors)
+    if not tensors:
+        raise RuntimeError("cat needs at least one tensor")
+    first = tensors[0]
+    for t in tensors[1:]:
+        if t.coordinate_manager is not first.coordinate_manager or t.coordinate_map_key != first.coordinate_map_key:
+            raise RuntimeError("Sparse tensors must share the same coordinate map")
+    return SparseTensor(torch.cat([t.F for t in tensors], 1), first.coordinate_map_key, first.coordinate_manager)
