@@ -154,6 +154,18 @@ int rmn_table_find(const void *d_table, const int32_t *d_query, uint32_t n_query
 int rmn_coords_stride(const int32_t *d_coords, uint32_t n_rows, int W,
                       const int32_t *out_tensor_stride, int32_t *d_out, void *stream);
 
+/*
+ * Region expansion: d_out[(row * K + k)] = d_coords[row] + d_offsets[k] on the spatial columns (batch
+ * column copied), d_out int32 [n_rows * K, W]; d_offsets device int32 [K, W-1]. Deduplicating the result
+ * with rmn_table_build gives the coordinate map that
+ * Replaces: CoordinateMapCPU::stride_region for transposed regions (engine/grid/lattice_cpu.hpp:499-534;
+ *   GPU: engine/grid/lattice_gpu.cu:434-601), the coordinate generation of pooling-transpose and generative
+ *   transposed layers. (Rows come out numbered by first occurrence over (row, k); the reference numbers
+ *   them in hash-iteration order.)
+ */
+int rmn_coords_expand(const int32_t *d_coords, uint32_t n_rows, int W, const int32_t *d_offsets, int K,
+                      int32_t *d_out, void *stream);
+
 /* =======================================================================
  * Kernel regions and kernel maps
  * ===================================================================== */

@@ -24,10 +24,11 @@
 //     convolution with the same kernel_size/stride using `weights2`
 //     [K, Cout, C2] back onto the input coordinates.
 //   weights2 f32 (only when chain = 1)
-//   pool    i32 [3] = {mode (1 sum, 2 average, 3 maximum), kernel_size, stride}  (optional):
+//   pool    i32 [3 or 4] = {mode (1 sum, 2 average, 3 maximum), kernel_size, stride[, transpose]}  (optional):
 //     also run the reference's local pooling layer on the input tensor
 //     (engine/nn/pooling.cpp:17-144) and write pool_coords, pool_feats and
-//     pool_grad_feats (gradient of 0.5 * sum(pool_feats^2) w.r.t. the input features).
+//     pool_grad_feats (gradient of 0.5 * sum(pool_feats^2) w.r.t. the input features). With transpose = 1 the
+//     pooling-transpose layer (sum; engine/nn/pooling.cpp:197-229) is applied to the convolution's output instead.
 // Output arrays: mapping, inverse, in_coords, out_coords, out_feats,
 //   kmap_ptr / kmap_in / kmap_out, grad_feats, grad_weights, and for chain = 1
 //   up_coords, up_feats, kmap2_ptr / kmap2_in / kmap2_out, grad_weights2;
@@ -276,13 +277,25 @@ int main(int argc, char** argv) {
       const auto mode = pmode == 1   ? riemann::PoolingMode::LOCAL_SUM_POOLING
                         : pmode == 2 ? riemann::PoolingMode::LOCAL_AVG_POOLING
                                      : riemann::PoolingMode::LOCAL_MAX_POOLING;
-      riemann::RiemannPoolingBaseImpl pooling(pk, ps, 1, mode, D);
+      const bool pool_transpose = pool.numel() > 3 && pool[3].item<int>() != 0;
       auto fp = feats.clone().requires_grad_(true);
       riemann::SparseTensor xp(fp, coords);
-      auto yp = pooling.forward(xp);
-      write_array(out, "pool_coords", yp.C());
-      write_array(out, "pool_feats", yp.F());
-      (yp.F() * yp.F()).sum().mul(0.5).backward();
+      if (!pool_transpose) {
+        riemann::RiemannPoolingBaseImpl pooling(pk, ps, 1, mode, D);
+        auto yp = pooling.forward(xp);
+        write_array(out, "pool_coords", yp.C());
+        write_array(out, "pool_feats", yp.F());
+        (yp.F() * yp.F()).sum().mul(0.5).backward();
+      } else {
+        // pooling-transpose (sum) of the convolution's output: un-pooling onto generated coordinates
+        conv->zero_grad();
+        auto yc = conv->forward(xp);
+        riemann::RiemannPoolingTranspose unpool(pk, ps, 1, false, D);
+        auto yp = unpool->forward(yc);
+        write_array(out, "pool_coords", yp.C());
+        write_array(out, "pool_feats", yp.F());
+        (yp.F() * yp.F()).sum().mul(0.5).backward();
+      }
       write_array(out, "pool_grad_feats", fp.grad());
     }
     return 0;

@@ -52,6 +52,7 @@ SIGNATURES = {
     "rmn_conv_backward_weight_workspace_bytes": (c_size_t, [c_uint32, c_int, c_int, c_int, c_int]),
     "rmn_conv_backward_weight": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_uint32, c_int, c_void_p, c_int,
                                          c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
+    "rmn_coords_expand": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_void_p, c_void_p]),
     "rmn_channel_stats_workspace_bytes": (c_size_t, [c_int]),
     "rmn_channel_stats": (c_int, [c_void_p, c_uint32, c_int, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
     "rmn_conv_forward_stats": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_int, c_void_p, c_uint32,

@@ -317,9 +317,36 @@ __global__ void __launch_bounds__(256) k_stride(const int32_t* __restrict__ coor
   out[i] = c;
 }
 
+// out[(row * K + k)] = coords[row] + offsets[k] on the spatial columns (batch column copied)
+__global__ void __launch_bounds__(256) k_expand(const int32_t* __restrict__ coords, uint64_t total, int W, int K,
+                                                const int32_t* __restrict__ offsets, int32_t* __restrict__ out) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int col = (int)(i % (uint64_t)W);
+  const uint64_t rk = i / (uint64_t)W;
+  const int k = (int)(rk % (uint64_t)K);
+  const uint64_t row = rk / (uint64_t)K;
+  int32_t c = __ldg(coords + row * W + col);
+  if (col > 0) c += __ldg(offsets + (size_t)k * (W - 1) + (col - 1));
+  out[i] = c;
+}
+
 }  // namespace rmn
 
 using namespace rmn;
+
+extern "C" int rmn_coords_expand(const int32_t* d_coords, uint32_t n_rows, int W, const int32_t* d_offsets, int K,
+                                 int32_t* d_out, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (W < 2 || W > RMN_MAX_W || K < 1) return RMN_ERR_BAD_ARG;
+  if (n_rows == 0) return RMN_OK;
+  if (!d_coords || !d_offsets || !d_out) return RMN_ERR_BAD_ARG;
+  const uint64_t total = (uint64_t)n_rows * (uint64_t)K * (uint64_t)W;
+  if ((uint64_t)n_rows * (uint64_t)K >= 0x7FFFFFFFull) return RMN_ERR_TOO_LARGE;
+  k_expand<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(d_coords, total, W, K, d_offsets, d_out);
+  RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}
 
 extern "C" size_t rmn_table_bytes(uint32_t n_rows) {
   return sizeof(TableHeader) + sizeof(Slot) * (size_t)table_capacity(n_rows);

@@ -253,6 +253,25 @@ class CoordinateManager:
             self._maps[out_key] = _CoordinateMap(ops.table_build(aligned), out_stride)
         return CoordinateMapKey(*out_key)
 
+    def stride_region(self, in_key: CoordinateMapKey, kernel_size: Sequence[int], kernel_dilation: Sequence[int],
+                      out_tensor_stride: Sequence[int], region_type: int = RegionType.HYPER_CUBE,
+                      offsets: Optional[torch.Tensor] = None, string_id: str = "") -> CoordinateMapKey:
+        """New coordinate map holding every ``in + offset`` of a transposed region on ``out_tensor_stride``
+        (engine/grid/lattice_cpu.hpp:499-534 through space_impl.hpp:359-381): the coordinate generation of
+        pooling-transpose. Rows are numbered by first occurrence over (input row, offset); the reference's
+        numbering follows its hash iteration order, so results are compared by coordinate. A key that already
+        exists gets a random suffix, as insert_and_map does."""
+        in_map = self._map(in_key)
+        custom = None
+        if region_type == RegionType.CUSTOM:
+            if offsets is None:
+                raise RuntimeError("CUSTOM region needs offsets")
+            custom = np.ascontiguousarray(offsets.detach().cpu().numpy(), np.int32).reshape(-1, len(kernel_size))
+        off = ops.region_offsets(region_type, list(kernel_size), list(kernel_dilation), list(out_tensor_stride), custom)
+        generated = ops.coords_expand(in_map.coords, off)
+        key, _ = self.insert_and_map(generated, list(out_tensor_stride), string_id)
+        return key
+
     def stride_map(self, in_key: CoordinateMapKey, out_key: CoordinateMapKey) -> torch.Tensor:
         """Row of ``out_key`` that every row of ``in_key`` floor-aligns to
         (engine/grid/lattice_cpu.hpp:679-710)."""
@@ -862,3 +881,43 @@ def cat(tensors: Sequence[SparseTensor]) -> SparseTensor:
         if t.coordinate_manager is not first.coordinate_manager or t.coordinate_map_key != first.coordinate_map_key:
             raise RuntimeError("Sparse tensors must share the same coordinate map")
     return SparseTensor(torch.cat([t.F for t in tensors], 1), first.coordinate_map_key, first.coordinate_manager)
+
+
+class RiemannPoolingTranspose(torch.nn.Module):
+    """RiemannPoolingTransposeImpl (engine/nn/pooling.cpp:197-229, maps: pooling.cpp:49-70): un-pooling
+    onto GENERATED coordinates. The output map holds every input coordinate expanded through the
+    kernel region on the finer tensor stride (stride_region); every output row then reduces (sum by
+    default) the input rows whose region reaches it."""
+
+    def __init__(self, kernel_size=2, stride=2, dilation=1, expand_coordinates: bool = False, dimension: int = 3,
+                 kernel_generator: Optional["KernelGenerator"] = None, mode: int = PoolingMode.LOCAL_SUM_POOLING):
+        super().__init__()
+        if mode not in _LOCAL_POOL_MODES:
+            raise RuntimeError("Transpose pooling requires a local pooling mode")
+        self.kernel_generator = kernel_generator if kernel_generator is not None else KernelGenerator(
+            kernel_size, stride, dilation, True, RegionType.HYPER_CUBE, None, expand_coordinates, dimension=dimension)
+        self.mode = mode
+        self.dimension = dimension
+
+    def forward(self, input: SparseTensor) -> SparseTensor:
+        if input.dimension != self.dimension:
+            raise RuntimeError("Input dimension mismatch")
+        params = self.kernel_generator.get_kernel(input.tensor_stride, True)
+        in_stride = input.tensor_stride
+        out_stride = []
+        for s, step in zip(in_stride, params.kernel_stride):
+            if step == 0 or s % step != 0:
+                raise RuntimeError("Transpose stride must divide tensor stride")
+            out_stride.append(s // step)
+        manager = input.coordinate_manager
+        if list(out_stride) == list(in_stride) and not params.expand_coordinates:
+            # a map of the output stride exists (the input's own): it is reused, not regenerated
+            # (engine/grid/space_impl.hpp:366-380 inside the layer's private manager)
+            out_key = input.coordinate_map_key
+        else:
+            out_key = manager.stride_region(input.coordinate_map_key, params.kernel_size, params.kernel_dilation,
+                                            out_stride, params.region_type, params.region_offsets)
+        kmap = manager.kernel_map(input.coordinate_map_key, out_key, params.kernel_size, params.kernel_stride,
+                                  params.kernel_dilation, params.region_type, params.region_offsets, True, True)
+        result = _SparsePoolingFunction.apply(input.F, kmap, _LOCAL_POOL_MODES[self.mode])
+        return SparseTensor(result, out_key, manager)

@@ -396,3 +396,19 @@ def affine_act(x: torch.Tensor, scale: Optional[torch.Tensor], shift: Optional[t
         capi.check(capi.lib().rmn_affine_act(_ptr(x), int(x.size(0)), int(x.size(1)), _ptr(sc), _ptr(sh),
                                              int(bool(relu)), _ptr(out), _dtype_code(x), _stream()), "rmn_affine_act")
     return out
+
+
+def coords_expand(coords: torch.Tensor, offsets: np.ndarray) -> torch.Tensor:
+    """[N * K, W] coordinates ``coords[row] + offsets[k]`` (rmn_coords_expand), row-major over (row, k)."""
+    _check_coords(coords)
+    off = np.ascontiguousarray(offsets, dtype=np.int32)
+    K = int(off.shape[0])
+    n, w = int(coords.size(0)), int(coords.size(1))
+    if off.ndim != 2 or off.shape[1] != w - 1:
+        raise RuntimeError("kernel size mismatch")
+    out = torch.empty((n * K, w), dtype=torch.int32, device=coords.device)
+    with torch.cuda.device(coords.device):
+        d_off = _device_offsets(off, coords.device)
+        capi.check(capi.lib().rmn_coords_expand(_ptr(coords), n, w, _ptr(d_off), K, _ptr(out), _stream()),
+                   "rmn_coords_expand")
+    return out

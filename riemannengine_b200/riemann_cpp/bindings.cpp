@@ -202,6 +202,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .value("LOCAL_SUM_POOLING", PoolingMode::LOCAL_SUM_POOLING)
       .value("LOCAL_AVG_POOLING", PoolingMode::LOCAL_AVG_POOLING)
       .value("LOCAL_MAX_POOLING", PoolingMode::LOCAL_MAX_POOLING);
+  py::class_<RiemannPoolingTransposeImpl, std::shared_ptr<RiemannPoolingTransposeImpl>>(m, "RiemannPoolingTranspose")
+      .def(py::init([](int kernel_size, int stride, int dilation, bool expand_coordinates, int dimension) {
+             return std::make_shared<RiemannPoolingTransposeImpl>(kernel_size, stride, dilation, expand_coordinates,
+                                                                  dimension);
+           }),
+           py::arg("kernel_size"), py::arg("stride"), py::arg("dilation") = 1, py::arg("expand_coordinates") = false,
+           py::arg("dimension") = 3)
+      .def("forward", [](RiemannPoolingTransposeImpl& self, const SparseTensor& input) { return self.forward(input); },
+           py::arg("input"), py::call_guard<py::gil_scoped_release>())
+      .def("__call__", [](RiemannPoolingTransposeImpl& self, const SparseTensor& input) { return self.forward(input); },
+           py::arg("input"), py::call_guard<py::gil_scoped_release>());
   bind_pool<RiemannAvgPoolingImpl>(m, "RiemannAvgPooling");
   bind_pool<RiemannSumPoolingImpl>(m, "RiemannSumPooling");
   bind_pool<RiemannMaxPoolingImpl>(m, "RiemannMaxPooling");

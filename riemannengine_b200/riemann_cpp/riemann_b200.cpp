@@ -246,6 +246,39 @@ CoordinateMapKey CoordinateManager::stride(const CoordinateMapKey& in_key, const
   return CoordinateMapKey(in_key.get_coordinate_size(), out_key);
 }
 
+CoordinateMapKey CoordinateManager::stride_region(const CoordinateMapKey& in_key, const stride_type& kernel_size,
+                                                  const stride_type& kernel_dilation,
+                                                  const stride_type& out_tensor_stride, RegionType::Type region_type,
+                                                  const at::Tensor& offsets) {
+  auto const& in_map = find(in_key, "in_map");
+  const int D = static_cast<int>(kernel_size.size());
+  if (kernel_dilation.size() != kernel_size.size() || out_tensor_stride.size() != kernel_size.size() ||
+      static_cast<int64_t>(D) + 1 != in_map.coords.size(1))
+    throw std::runtime_error("kernel size mismatch");
+  std::vector<int32_t> custom;
+  if (region_type == RegionType::CUSTOM) {
+    TORCH_CHECK(offsets.defined(), "CUSTOM region needs offsets");
+    auto host = offsets.to(at::kCPU, at::kInt).contiguous();
+    custom.assign(host.data_ptr<int32_t>(), host.data_ptr<int32_t>() + host.numel());
+  }
+  auto ks = to_i32(kernel_size), kd = to_i32(kernel_dilation), ts = to_i32(out_tensor_stride);
+  const int n_custom = D ? static_cast<int>(custom.size()) / D : 0;
+  const int K = rmn_region_volume(int(region_type), D, ks.data(), n_custom);
+  if (K < 0) check(-K, "rmn_region_volume");
+  std::vector<int32_t> off(static_cast<size_t>(K) * D);
+  const int K2 = rmn_region_offsets(int(region_type), D, ks.data(), kd.data(), ts.data(),
+                                    custom.empty() ? nullptr : custom.data(), n_custom, off.data());
+  if (K2 < 0) check(-K2, "rmn_region_offsets");
+  c10::cuda::CUDAGuard guard(in_map.coords.device());
+  auto d_off = at::from_blob(off.data(), {static_cast<int64_t>(off.size())}, at::kInt).to(in_map.coords.device());
+  auto generated = at::empty({static_cast<int64_t>(in_map.size) * K, in_map.coords.size(1)}, in_map.coords.options());
+  check(rmn_coords_expand(static_cast<const int32_t*>(ptr(in_map.coords)), in_map.size,
+                          static_cast<int>(in_map.coords.size(1)), static_cast<const int32_t*>(ptr(d_off)), K,
+                          static_cast<int32_t*>(ptr(generated)), current_stream()),
+        "rmn_coords_expand");
+  return insert_and_map(generated, out_tensor_stride, "").first;
+}
+
 std::shared_ptr<KernelMap> CoordinateManager::kernel_map(const CoordinateMapKey& in_key,
                                                          const CoordinateMapKey& out_key,
                                                          const stride_type& kernel_size,
@@ -851,6 +884,41 @@ RiemannPoolingBaseImpl::RiemannPoolingBaseImpl(int kernel_size, int stride, int 
 RiemannPoolingBaseImpl::RiemannPoolingBaseImpl(KernelGenerator kernel_generator, PoolingMode::Type mode, int dimension)
     : kernel_generator_(std::move(kernel_generator)), mode_(mode), dimension_(dimension) {
   pool_code(mode);
+}
+
+RiemannPoolingTransposeImpl::RiemannPoolingTransposeImpl(int kernel_size, int stride, int dilation,
+                                                         bool expand_coordinates, int dimension)
+    : kernel_generator_({kernel_size}, {stride}, {dilation}, true, RegionType::HYPER_CUBE, {}, expand_coordinates, {},
+                        dimension),
+      dimension_(dimension) {}
+
+RiemannPoolingTransposeImpl::RiemannPoolingTransposeImpl(KernelGenerator kernel_generator, int dimension,
+                                                         PoolingMode::Type mode)
+    : kernel_generator_(std::move(kernel_generator)), dimension_(dimension), mode_(mode) {
+  pool_code(mode);
+}
+
+SparseTensor RiemannPoolingTransposeImpl::forward(const SparseTensor& input) {
+  TORCH_CHECK(input.dimension() == dimension_, "Input dimension mismatch");
+  const auto params = kernel_generator_.get_kernel(input.tensor_stride(), true);
+  const auto in_stride = input.tensor_stride();
+  stride_type out_stride(in_stride);
+  for (size_t axis = 0; axis < out_stride.size(); ++axis) {
+    const auto step = params.kernel_stride[axis];
+    TORCH_CHECK(step != 0 && out_stride[axis] % step == 0, "Transpose stride must divide tensor stride");
+    out_stride[axis] /= step;
+  }
+  auto manager = input.coordinate_manager();
+  // a map of the output stride that exists already (the input's own) is reused unless coordinates are expanded
+  CoordinateMapKey output_key =
+      (out_stride == in_stride && !kernel_generator_.expand_coordinates())
+          ? input.coordinate_map_key()
+          : manager->stride_region(input.coordinate_map_key(), params.kernel_size, params.kernel_dilation, out_stride,
+                                   params.region_type, params.region_offsets);
+  auto kmap = manager->kernel_map(input.coordinate_map_key(), output_key, params.kernel_size, params.kernel_stride,
+                                  params.kernel_dilation, params.region_type, params.region_offsets, true, true);
+  auto result = sparse_pooling(input.F(), kmap, mode_);
+  return SparseTensor(std::move(result), output_key, std::move(manager));
 }
 
 SparseTensor RiemannPoolingBaseImpl::forward(const SparseTensor& input) {

@@ -129,6 +129,12 @@ public:
 
   CoordinateMapKey stride(const CoordinateMapKey& in_key, const stride_type& kernel_stride,
                           std::string string_id = "");
+  // New map holding every `in + offset` of a transposed region on out_tensor_stride
+  // (engine/grid/lattice_cpu.hpp:499-534 through space_impl.hpp:359-381): pooling-transpose's coordinates.
+  CoordinateMapKey stride_region(const CoordinateMapKey& in_key, const stride_type& kernel_size,
+                                 const stride_type& kernel_dilation, const stride_type& out_tensor_stride,
+                                 RegionType::Type region_type = RegionType::HYPER_CUBE,
+                                 const at::Tensor& offsets = at::Tensor());
 
   at::Tensor get_coordinates(const CoordinateMapKey& key) const;
   uint32_t size(const CoordinateMapKey& key) const;
@@ -352,6 +358,22 @@ private:
     RiemannPoolingBaseImpl pooling_;                                                           \
   };                                                                                           \
   TORCH_MODULE(Name)
+
+// RiemannPoolingTransposeImpl (engine/nn/pooling.hpp:79-93): un-pooling onto generated coordinates.
+class RiemannPoolingTransposeImpl : public torch::nn::Module {
+public:
+  RiemannPoolingTransposeImpl(int kernel_size, int stride, int dilation = 1, bool expand_coordinates = false,
+                              int dimension = 3);
+  RiemannPoolingTransposeImpl(KernelGenerator kernel_generator, int dimension,
+                              PoolingMode::Type mode = PoolingMode::LOCAL_SUM_POOLING);
+  SparseTensor forward(const SparseTensor& input);
+
+private:
+  KernelGenerator kernel_generator_;
+  int dimension_;
+  PoolingMode::Type mode_ = PoolingMode::LOCAL_SUM_POOLING;
+};
+TORCH_MODULE(RiemannPoolingTranspose);
 
 RIEMANN_B200_POOL_WRAPPER(RiemannAvgPooling, PoolingMode::LOCAL_AVG_POOLING);
 RIEMANN_B200_POOL_WRAPPER(RiemannSumPooling, PoolingMode::LOCAL_SUM_POOLING);

@@ -5,7 +5,7 @@ Runs the unmodified reference CPU path (``oracle/_ref/ref_driver``, built by
 stores inputs + reference outputs as ``<case>.npz``. The parity tests load the
 fixtures only; they never need the reference at run time.
 
-    python tests/golden/make_golden.py [--pool-only]
+    python tests/golden/make_golden.py [--pool-only | --unpool-only]
 """
 from __future__ import annotations
 
@@ -41,6 +41,11 @@ POOL_CASES = {
     "pool_d2_sum_k3_s1": (26, 2, 300, 2, -9, 9, 3, 1, 3, 1),
 }
 
+UNPOOL_CASES = {
+    "unpool_d3_k3_s2": (31, 3, 500, 2, -7, 7, 4, 6, 3, 2),
+    "unpool_d2_k2_s1": (32, 2, 300, 2, -12, 12, 3, 5, 2, 1),
+}
+
 
 def make_inputs(seed, D, n, batches, lo, hi, c_in, c_out, kernel, stride, dilation, c2):
     rng = np.random.default_rng(seed)
@@ -62,7 +67,7 @@ def make_inputs(seed, D, n, batches, lo, hi, c_in, c_out, kernel, stride, dilati
 
 
 def main() -> None:
-    only_pool = "--pool-only" in sys.argv
+    only_pool = "--pool-only" in sys.argv or "--unpool-only" in sys.argv
     for name, spec in ({} if only_pool else CASES).items():
         coords, feats, weights, weights2 = make_inputs(*spec)
         _, D, _, _, _, _, _, _, kernel, stride, dilation, _ = spec
@@ -78,6 +83,22 @@ def main() -> None:
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, **arrays)
         print(name, {k: v.shape for k, v in ref.items()}, os.path.getsize(path), "bytes")
+    # pooling-transpose after a (strided) convolution with the same kernel size and stride:
+    # name: (seed, D, n_rows, batches, lo, hi, c_in, c_out, kernel, stride). The reference's layer fails an
+    # assertion of its own when kernel == stride > 1 (its pooling kernel map takes the stride_map shortcut,
+    # engine/grid/lattice_cpu.hpp:679-710), so the fixtures use kernel != stride.
+    for name, (seed, D, n, batches, lo, hi, c_in, c_out, ks, st) in UNPOOL_CASES.items():
+        coords, feats, weights, _ = make_inputs(seed, D, n, batches, lo, hi, c_in, c_out, ks, st, 1, None)
+        ref = refrun.run(coords, feats, weights, ks, st, 1, threads=1, pool=(1, ks, st, 1))
+        arrays = {"in_coords_raw": coords, "in_feats_raw": feats, "weights": weights,
+                  "spec": np.array([D, ks, st, 1], np.int32)}
+        for k in ("mapping", "in_coords", "out_coords", "pool_coords", "pool_feats", "pool_grad_feats"):
+            arrays["ref_" + k] = ref[k]
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **arrays)
+        print(name, {k: v.shape for k, v in arrays.items() if k.startswith("ref_")}, os.path.getsize(path), "bytes")
+    if "--unpool-only" in sys.argv:
+        return
     for name, (seed, D, n, batches, lo, hi, C, mode, kernel, stride) in POOL_CASES.items():
         coords, feats, _, _ = make_inputs(seed, D, n, batches, lo, hi, C, 1, 1, 1, 1, None)
         ident = np.ones((1, C, 1), np.float32)  # the driver always runs a convolution first: 1^D kernel, unused here

@@ -199,3 +199,38 @@ def check_pool_against_reference(out_coords, out_feats, grad_raw, gold, tol: flo
     gscale = max(float(np.abs(ref_g).max()), 1e-30)
     gerr = float(np.abs(np.asarray(grad_raw, np.float64) - ref_g).max()) / gscale
     assert gerr <= tol, f"pooling gradient differs: {gerr}"
+
+
+UNPOOL_GOLDEN_CASES = ["unpool_d3_k3_s2", "unpool_d2_k2_s1"]
+
+
+def oracle_unpool_case(gold: Dict[str, np.ndarray]):
+    """Oracle result of a (strided) convolution followed by the pooling-transpose layer (sum) with the same
+    kernel size and stride (reference engine/nn/pooling.cpp:49-70, 197-229; coordinate generation
+    engine/grid/lattice_cpu.hpp:499-534): (out_coords, out_feats, grad w.r.t. the raw features) for the loss
+    0.5 * sum(out^2)."""
+    from oracle import oracle as O
+
+    D, kernel, stride, _ = (int(v) for v in gold["spec"])
+    coords, feats, weights = gold["in_coords_raw"], gold["in_feats_raw"], gold["weights"]
+    mapping, _ = O.insert_and_map(coords)
+    fine, f_in = coords[mapping], feats[mapping]
+    coarse = O.stride_map(fine, [stride] * D)[0] if stride > 1 else fine
+    kc = O.conv_kernel_map(fine, coarse, O.region_offsets(O.HYPER_CUBE, [kernel] * D, [1] * D, [1] * D))
+    y = O.conv_forward(f_in, weights, *kc, len(coarse), f64=True)
+    # un-pooling region on the output (finer) tensor stride: out = in + off
+    off = O.region_offsets(O.HYPER_CUBE, [kernel] * D, [1] * D, [1] * D)
+    if stride > 1:
+        expanded = (coarse[:, None, :].astype(np.int64)
+                    + np.concatenate([np.zeros((len(off), 1), np.int64), off.astype(np.int64)], 1)[None]).reshape(
+                        -1, coords.shape[1]).astype(np.int32)
+        generated = expanded[O.insert_and_map(expanded)[0]]
+    else:
+        generated = coarse  # a map of the output stride exists already and is reused
+    ku = O.conv_kernel_map(coarse, generated, off, transposed=True)
+    out = O.pool_forward(y, ku[1], ku[2], len(generated), O.POOL_SUM)
+    g_y = O.pool_backward(y, out, ku[1], ku[2], O.POOL_SUM)
+    g_in, _ = O.conv_backward(f_in, g_y.astype(np.float32), weights, *kc, f64=True)
+    g_raw = np.zeros(feats.shape, np.float64)
+    g_raw[mapping] = g_in
+    return generated, out, g_raw

@@ -134,3 +134,20 @@ def test_cpp_fused_conv_bn_relu_inference(C):
         want = torch.relu(bn(conv(x).F))
         got = C.fused_conv_bn_relu(x, conv, bn.running_mean, bn.running_var, bn.weight, bn.bias, bn.eps, True).F
     assert rel_max(got.cpu().numpy(), want.cpu().numpy()) <= 1e-4
+
+
+@pytest.mark.parametrize("name", parity.UNPOOL_GOLDEN_CASES)
+def test_cpp_pooling_transpose_matches_reference_golden(C, name):
+    gold = parity.load_golden(name)
+    D, kernel, stride, _ = (int(v) for v in gold["spec"])
+    w = torch.from_numpy(gold["weights"]).cuda()
+    conv = C.RiemannConvolution(w.size(1), w.size(2), kernel_size=kernel, stride=stride, dimension=D)
+    conv.to("cuda")
+    with torch.no_grad():
+        conv.kernel.copy_(w)
+    f = torch.from_numpy(gold["in_feats_raw"]).cuda().requires_grad_(True)
+    x = C.SparseTensor(f, torch.from_numpy(gold["in_coords_raw"]).cuda())
+    y = C.RiemannPoolingTranspose(kernel, stride, 1, False, D)(conv(x))
+    ((y.F * y.F).sum() * 0.5).backward()
+    parity.check_pool_against_reference(y.C.cpu().numpy(), y.F.detach().cpu().numpy(), f.grad.cpu().numpy(), gold,
+                                        tol=1e-4)

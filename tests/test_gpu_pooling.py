@@ -80,3 +80,23 @@ def test_pooling_properties_at_benchmark_size():
     assert (m.F >= a.F - 1e-5).all()
     s.F.sum().backward()
     assert torch.equal(feats.grad, count.expand(-1, C))  # symmetric region: in-degree == out-degree
+
+
+@pytest.mark.parametrize("name", parity.UNPOOL_GOLDEN_CASES)
+def test_pooling_transpose_matches_reference_golden_fp32(name):
+    """(strided) convolution -> RiemannPoolingTranspose: generated coordinates, values and the gradient back to
+    the raw features equal the reference's (fixtures from engine/nn/pooling.cpp:197-229); fp32 bar 1e-4."""
+    from riemannengine_b200 import engine as E
+    gold = parity.load_golden(name)
+    D, kernel, stride, _ = (int(v) for v in gold["spec"])
+    w = torch.from_numpy(gold["weights"]).cuda()
+    conv = E.RiemannConvolution(w.size(1), w.size(2), kernel_size=kernel, stride=stride, dimension=D).cuda()
+    with torch.no_grad():
+        conv.kernel.copy_(w)
+    feats = torch.from_numpy(gold["in_feats_raw"]).cuda().requires_grad_(True)
+    x = E.SparseTensor(feats, torch.from_numpy(gold["in_coords_raw"]).cuda())
+    y = E.RiemannPoolingTranspose(kernel, stride, 1, False, dimension=D)(conv(x))
+    assert y.tensor_stride == [1] * D
+    (y.F * y.F).sum().mul(0.5).backward()
+    parity.check_pool_against_reference(y.C.cpu().numpy(), y.F.detach().cpu().numpy(), feats.grad.cpu().numpy(), gold,
+                                        tol=1e-4)

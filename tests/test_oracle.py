@@ -98,3 +98,10 @@ def test_oracle_pooling_matches_reference_golden(name):
     gold = parity.load_golden(name)
     out_coords, out, g_raw = parity.oracle_pool_case(gold)
     parity.check_pool_against_reference(out_coords, out, g_raw, gold, tol=1e-5)
+
+
+@pytest.mark.parametrize("name", parity.UNPOOL_GOLDEN_CASES)
+def test_oracle_pooling_transpose_matches_reference_golden(name):
+    gold = parity.load_golden(name)
+    out_coords, out, g_raw = parity.oracle_unpool_case(gold)
+    parity.check_pool_against_reference(out_coords, out, g_raw, gold, tol=1e-5)
