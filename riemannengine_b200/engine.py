@@ -272,6 +272,26 @@ class CoordinateManager:
         key, _ = self.insert_and_map(generated, list(out_tensor_stride), string_id)
         return key
 
+    def union_map(self, in_keys: Sequence[CoordinateMapKey]):
+        """Union of several maps of one tensor stride (engine/grid/space_impl.hpp:896-914,
+        lattice_cpu.hpp:801-833): returns (key of the merged map, one int64 [2, N_i] tensor per input
+        map: row in that map, row in the merged map). Merged rows are numbered by first occurrence over
+        the concatenated inputs."""
+        if not in_keys:
+            raise RuntimeError("union_map needs at least one map")
+        maps = [self._map(k) for k in in_keys]
+        stride = maps[0].tensor_stride
+        if any(m.tensor_stride != stride for m in maps):
+            raise RuntimeError("all maps of a union must share one tensor stride")
+        merged = torch.cat([m.coords for m in maps], 0)
+        key, _ = self.insert_and_map(merged, list(stride), "")
+        table = self._map(key).table
+        out = []
+        for m in maps:
+            rows = ops.table_find(table, m.coords).to(torch.int64)
+            out.append(torch.stack([torch.arange(m.size, dtype=torch.int64, device=rows.device), rows]))
+        return key, out
+
     def stride_map(self, in_key: CoordinateMapKey, out_key: CoordinateMapKey) -> torch.Tensor:
         """Row of ``out_key`` that every row of ``in_key`` floor-aligns to
         (engine/grid/lattice_cpu.hpp:679-710)."""

@@ -100,6 +100,22 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("string_id") = "")
       .def("stride", &CoordinateManager::stride, py::arg("in_key"), py::arg("kernel_stride"),
            py::arg("string_id") = "")
+      .def("union_map",
+           [](CoordinateManager& self, const std::vector<CoordinateMapKey>& in_keys) {
+             CoordinateMapKey out_key(in_keys.empty() ? 0 : in_keys.front().get_coordinate_size());
+             auto maps = self.union_map(in_keys, out_key);
+             return py::make_tuple(out_key, maps);
+           },
+           py::arg("in_keys"))
+      .def("stride_region",
+           [](CoordinateManager& self, const CoordinateMapKey& in_key, stride_type kernel_size,
+              stride_type kernel_dilation, stride_type out_tensor_stride, RegionType::Type region_type,
+              std::optional<at::Tensor> offsets) {
+             return self.stride_region(in_key, kernel_size, kernel_dilation, out_tensor_stride, region_type,
+                                       offsets.value_or(at::Tensor()));
+           },
+           py::arg("in_key"), py::arg("kernel_size"), py::arg("kernel_dilation"), py::arg("out_tensor_stride"),
+           py::arg("region_type") = RegionType::HYPER_CUBE, py::arg("offsets") = py::none())
       .def("kernel_map_pairs",
            [](CoordinateManager& self, const CoordinateMapKey& in_key, const CoordinateMapKey& out_key,
               stride_type kernel_size, stride_type kernel_stride, stride_type kernel_dilation,

@@ -246,6 +246,32 @@ CoordinateMapKey CoordinateManager::stride(const CoordinateMapKey& in_key, const
   return CoordinateMapKey(in_key.get_coordinate_size(), out_key);
 }
 
+std::vector<at::Tensor> CoordinateManager::union_map(const std::vector<CoordinateMapKey>& in_keys,
+                                                     CoordinateMapKey& out_key) {
+  if (in_keys.empty()) throw std::runtime_error("union_map needs at least one map");
+  std::vector<at::Tensor> coords;
+  auto const& first = find(in_keys.front());
+  for (auto const& key : in_keys) {
+    auto const& m = find(key);
+    if (m.tensor_stride != first.tensor_stride)
+      throw std::runtime_error("all maps of a union must share one tensor stride");
+    coords.push_back(m.coords);
+  }
+  auto inserted = insert_and_map(at::cat(coords, 0), first.tensor_stride, "");
+  out_key = inserted.first;
+  auto const& merged = find(out_key);
+  std::vector<at::Tensor> out;
+  for (auto const& c : coords) {
+    c10::cuda::CUDAGuard guard(c.device());
+    auto rows = at::empty({c.size(0)}, c.options());
+    check(rmn_table_find(ptr(merged.table), static_cast<const int32_t*>(ptr(c)), static_cast<uint32_t>(c.size(0)),
+                         static_cast<int>(c.size(1)), static_cast<int32_t*>(ptr(rows)), current_stream()),
+          "rmn_table_find");
+    out.push_back(at::stack({at::arange(c.size(0), rows.options().dtype(at::kLong)), rows.to(at::kLong)}));
+  }
+  return out;
+}
+
 CoordinateMapKey CoordinateManager::stride_region(const CoordinateMapKey& in_key, const stride_type& kernel_size,
                                                   const stride_type& kernel_dilation,
                                                   const stride_type& out_tensor_stride, RegionType::Type region_type,

@@ -129,6 +129,9 @@ public:
 
   CoordinateMapKey stride(const CoordinateMapKey& in_key, const stride_type& kernel_stride,
                           std::string string_id = "");
+  // Union of maps of one tensor stride (engine/grid/space.hpp:862-863, space_impl.hpp:896-914): sets out_key to the
+  // merged map and returns one int64 [2, N_i] tensor per input map (row in that map, row in the merged map).
+  std::vector<at::Tensor> union_map(const std::vector<CoordinateMapKey>& in_keys, CoordinateMapKey& out_key);
   // New map holding every `in + offset` of a transposed region on out_tensor_stride
   // (engine/grid/lattice_cpu.hpp:499-534 through space_impl.hpp:359-381): pooling-transpose's coordinates.
   CoordinateMapKey stride_region(const CoordinateMapKey& in_key, const stride_type& kernel_size,

@@ -188,3 +188,34 @@ def test_fused_conv_bn_relu_matches_unfused(dtype, c_in, c_out, tol):
     before = bn.running_mean.clone()
     out = E.fused_conv_bn_relu(x, conv, bn)
     assert torch.isfinite(out.F.float()).all() and not torch.equal(before, bn.running_mean)
+
+
+def test_union_map_and_stride_region():
+    """union_map (engine/grid/space_impl.hpp:896-914): merged map == set union, per-map rows point at equal
+    coordinates; stride_region: generated map == set of in + offset. Checked on both host layers."""
+    from riemannengine_b200 import cpp, engine as E
+    rng = np.random.default_rng(17)
+
+    def cloud(n):
+        c = np.concatenate([rng.integers(0, 2, (n, 1)), rng.integers(-5, 6, (n, 3))], 1).astype(np.int32)
+        return np.unique(c, axis=0)[rng.permutation(len(np.unique(c, axis=0)))]
+
+    a, b = cloud(700), cloud(900)
+    want = {tuple(r) for r in np.concatenate([a, b]).tolist()}
+    off = np.array([[dx, dy, dz] for dz in (0, 1) for dy in (0, 1) for dx in (0, 1)], np.int32)
+    want_region = {tuple(r) for r in (a[:, None, :] + np.concatenate([np.zeros((8, 1), np.int32), off], 1)[None])
+                   .reshape(-1, 4).tolist()}
+    for host in (E, cpp.load()):
+        m = host.CoordinateManager(3)
+        ka, _ = m.insert_and_map(torch.from_numpy(a).cuda(), [1, 1, 1], "a")
+        kb, _ = m.insert_and_map(torch.from_numpy(b).cuda(), [1, 1, 1], "b")
+        ku, maps = m.union_map([ka, kb])
+        cu = m.get_coordinates(ku).cpu().numpy()
+        assert len(cu) == len(want) and {tuple(r) for r in cu.tolist()} == want
+        for src, mp in zip((a, b), maps):
+            mp = mp.cpu().numpy()
+            assert mp.shape == (2, len(src)) and (mp[0] == np.arange(len(src))).all()
+            assert (cu[mp[1]] == src).all()
+        kr = m.stride_region(ka, [2, 2, 2], [1, 1, 1], [1, 1, 1])
+        cr = m.get_coordinates(kr).cpu().numpy()
+        assert len(cr) == len(want_region) and {tuple(r) for r in cr.tolist()} == want_region
