@@ -8,8 +8,10 @@
 //
 // Grid = (row chunks, offset sets). A CTA keeps the accumulators of its offset
 // set resident in TMEM (groups * C_out <= 512 columns) while it walks its row
-// chunk in blocks of 64 rows; one pipeline stage = (row block, offset group):
-// 64 x G gathered rows (16 KB) + the 64 dY rows. At the end the four producer
+// chunk in blocks of 64 rows; one pipeline stage = (row block, GP offset groups):
+// GP x 64 x G gathered rows (GP x 16 KB) + the 64 dY rows, which the GP groups
+// share (copied once, and read from shared memory once per K slice: the second
+// group's MMA reuses the collector buffer). At the end the four producer
 // warps read the accumulators back and write an fp32 partial
 // [chunk][K][C_in][C_out]; a second kernel adds the chunks in a fixed order, so
 // the result is bit-reproducible (no atomics).
@@ -25,7 +27,7 @@ namespace tc {
 constexpr int kRowsPerStage = 64;
 constexpr int kWgProducerWarps = 16;  // gather warps (the first four also run the epilogue)
 constexpr int kWgProducers = kWgProducerWarps * 32;
-constexpr int kWgIdxPerThread = 32 / kWgProducerWarps * 4 / 4;  // A' lines per thread and stage
+constexpr int kWgLinesPerGroup = kRowsPerStage * 2 * 8 / kWgProducers;  // A' lines per thread, stage and group
 constexpr int kWgradThreads = kWgProducers + 32;
 
 constexpr uint32_t instr_desc_mn(int m, int n) {
@@ -38,16 +40,20 @@ template <int CIN, int COUT>
 struct WgradCfg {
   static constexpr int G = 128 / CIN;                     // offsets stacked along M
   static constexpr int MAX_GROUPS = 512 / COUT;           // accumulators resident in TMEM
-  static constexpr uint32_t A_BYTES = kRowsPerStage * 128 * 2;
+  static constexpr uint32_t A_GROUP = kRowsPerStage * 128 * 2;   // gathered rows of one offset group
   static constexpr uint32_t B_BYTES = kRowsPerStage * COUT * 2;
+  // two offset groups per stage (sharing the dY rows) where at least three such stages fit
+  static constexpr int GP = (MAX_GROUPS >= 2 && (2 * A_GROUP + B_BYTES) * 3 <= 200 * 1024) ? 2 : 1;
+  static constexpr uint32_t A_BYTES = GP * A_GROUP;
   static constexpr uint32_t STAGE = A_BYTES + B_BYTES;
-  // six stages where they fit: deeper prefetch, and > 114 KB keeps one CTA (one TMEM owner) per SM
-  static constexpr int STAGES = STAGE * 6 <= 200 * 1024 ? 6 : 4;
+  static constexpr int IDX_PER_THREAD = GP * kWgLinesPerGroup;
+  // as many stages (up to six) as 227 KB of shared memory hold beside the barriers;
+  // more than 114 KB in total also keeps one CTA (one TMEM owner) per SM
+  static constexpr uint32_t STAGE_BUDGET = 227 * 1024 - 256;
+  static constexpr int STAGES = STAGE * 6 <= STAGE_BUDGET ? 6 : (STAGE * 5 <= STAGE_BUDGET ? 5 : (STAGE * 4 <= STAGE_BUDGET ? 4 : 3));
+  static_assert(STAGE * STAGES <= STAGE_BUDGET, "stages do not fit in shared memory");
   static constexpr uint32_t BAR_OFFSET = STAGES * STAGE;
-  static constexpr int IDX_AHEAD = 3;   // stages of lead of the neighbour-index prefetch
-  static constexpr int IDX_SLOTS = 4;   // ring slots (> IDX_AHEAD)
-  static constexpr uint32_t IDX_OFFSET = BAR_OFFSET + 256;
-  static constexpr uint32_t SMEM = IDX_OFFSET + IDX_SLOTS * kWgProducers * kWgIdxPerThread * 4;
+  static constexpr uint32_t SMEM = BAR_OFFSET + 256;
 };
 
 template <int CIN, int COUT>
@@ -56,7 +62,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
     const int32_t* __restrict__ nbr, uint32_t n_dst, int K, uint32_t chunk_rows, int groups_per_set,
     uint32_t tmem_cols, float* __restrict__ partial) {
   using C = WgradCfg<CIN, COUT>;
-  constexpr int STAGES = C::STAGES, G = C::G;
+  constexpr int STAGES = C::STAGES, G = C::G, GP = C::GP, kWgIdxPerThread = C::IDX_PER_THREAD;
   constexpr int SWB = (COUT < 64 ? COUT : 64) * 2;     // bytes per dY line
   constexpr int B_CPL = SWB / 16;                      // chunks per dY line
   constexpr uint32_t A_ATOM = kRowsPerStage * 128;     // bytes of one 64-channel atom of A' (all stage rows)
@@ -73,11 +79,12 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_groups_total = (K + G - 1) / G;
   const int group0 = blockIdx.y * groups_per_set;
-  const int n_groups = min(groups_per_set, n_groups_total - group0);
+  const int n_groups = min(groups_per_set, n_groups_total - group0);  // offset groups of this CTA
+  const int n_sg = (n_groups + GP - 1) / GP;                          // stages per row block
   const uint32_t j_begin = blockIdx.x * chunk_rows;
   const uint32_t j_end = min(n_dst, j_begin + chunk_rows);
   const uint32_t n_blocks = j_end > j_begin ? (j_end - j_begin + kRowsPerStage - 1) / kRowsPerStage : 0;
-  const uint32_t n_stage = n_blocks * (uint32_t)n_groups;
+  const uint32_t n_stage = n_blocks * (uint32_t)n_sg;
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -105,52 +112,57 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
     // ------------------------------ producers ------------------------------------------
     // A' image: one 128-byte swizzled line per (stage row, 64-channel atom of the stacked M axis);
     // eight consecutive lanes copy one line, i.e. one (CIN >= 64) or two (CIN = 32) gathered rows.
-    // The neighbour indices a thread needs for a stage are copied (4-byte cp.async) into a private
-    // slot of a small shared-memory ring kIdxAhead stages before that stage is issued: the table
-    // read is a streaming DRAM access and must not sit on the critical path of the gathers.
+    // Neighbour indices: warp w copies rows [4w, 4w + 4) of every stage, for all G * GP offsets of the
+    // stage, i.e. 4 * G * GP <= 32 table entries: lane l < 4 * G * GP loads entry (offset l / 4, row l % 4)
+    // with ONE coalesced load per warp and stage, three stages before use (a rotating window of
+    // named registers); the lanes of a line fetch theirs with a shuffle when the stage is issued.
     uint32_t it = 0;
-    int32_t* idx_ring = reinterpret_cast<int32_t*>(smem + C::IDX_OFFSET);
-    auto issue_indices = [&](uint32_t v) {
-      const uint32_t blk_ = v / (uint32_t)n_groups;
-      const int g_ = (int)(v - blk_ * (uint32_t)n_groups);
-      int32_t* slot = idx_ring + (v % C::IDX_SLOTS) * (kWgProducers * kWgIdxPerThread) + tid * kWgIdxPerThread;
-#pragma unroll
-      for (int i = 0; i < kWgIdxPerThread; ++i) {
-        const int unit = (i * kWgProducerWarps + warp) * 4 + (lane >> 3);
-        const int r = unit & (kRowsPerStage - 1), atom = unit / kRowsPerStage;
-        const int gg = (atom * 8 + (lane & 7)) / (CIN / 8);
-        const uint32_t j = j_begin + blk_ * kRowsPerStage + r;
-        const int k = (group0 + g_) * G + gg;
-        if (blk_ < n_blocks && j < j_end && k < K)
-          cp_async4(smem_u32(slot + i), nbr + (size_t)k * n_dst + j);
-        else
-          slot[i] = -1;
+    constexpr int NIDX = 4 * G * GP;
+    uint32_t pf_blk = 0;
+    int pf_sg = 0;
+    auto load_indices = [&]() -> int32_t {
+      int32_t v = -1;
+      if (lane < NIDX) {
+        const int combo = lane >> 2, gp = combo / G, gg = combo % G;
+        const uint32_t j = j_begin + pf_blk * kRowsPerStage + warp * 4 + (lane & 3);
+        const int k = (group0 + pf_sg * GP + gp) * G + gg;
+        if (pf_blk < n_blocks && j < j_end && k < K && pf_sg * GP + gp < n_groups) v = __ldg(nbr + (size_t)k * n_dst + j);
       }
-      cp_async_commit();
+      if (++pf_sg == n_sg) { pf_sg = 0; ++pf_blk; }
+      return v;
     };
-    for (uint32_t v = 0; v < (uint32_t)C::IDX_AHEAD; ++v) issue_indices(v);
+#ifdef RMN_PROF
+    long long prof_wait = 0; const long long prof_start = clock64();
+#endif
+    int32_t idx_w0 = load_indices(), idx_w1 = load_indices(), idx_w2 = load_indices();
     for (uint32_t blk = 0; blk < n_blocks && !timed_out; ++blk) {
       const uint32_t j0 = j_begin + blk * kRowsPerStage;
 #pragma unroll 1
-      for (int g = 0; g < n_groups; ++g, ++it) {
-        issue_indices(it + C::IDX_AHEAD);
-        cp_async_wait<C::IDX_AHEAD>();  // the indices of stage `it` (and all older copies) have landed
+      for (int sg = 0; sg < n_sg; ++sg, ++it) {
+        const int32_t mine = idx_w0;
+        idx_w0 = idx_w1; idx_w1 = idx_w2;
+        idx_w2 = load_indices();
         int32_t idx[kWgIdxPerThread];
-        {
-          const int32_t* slot =
-              idx_ring + (it % C::IDX_SLOTS) * (kWgProducers * kWgIdxPerThread) + tid * kWgIdxPerThread;
 #pragma unroll
-          for (int i = 0; i < kWgIdxPerThread; ++i) idx[i] = slot[i];
+        for (int i = 0; i < kWgIdxPerThread; ++i) {
+          const int gp = i / kWgLinesPerGroup, atom = i % kWgLinesPerGroup;
+          const int gg = (atom * 8 + (lane & 7)) / (CIN / 8);
+          idx[i] = __shfl_sync(0xFFFFFFFFu, mine, (gp * G + gg) * 4 + (lane >> 3));
         }
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-        if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
+        {
+          PROF_T0();
+          if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
+          PROF_ADD(prof_wait);
+        }
         const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
 #pragma unroll
         for (int i = 0; i < kWgIdxPerThread; ++i) {
-          const int unit = (i * kWgProducerWarps + warp) * 4 + (lane >> 3);
+          const int gp = i / kWgLinesPerGroup;
+          const int unit = ((i % kWgLinesPerGroup) * kWgProducerWarps + warp) * 4 + (lane >> 3);
           const uint32_t r = unit & (kRowsPerStage - 1), atom = unit / kRowsPerStage, c = lane & 7;
           const int cch = (atom * 8 + c) % (CIN / 8);
-          cp_async16(a_s + atom * A_ATOM + r * 128 + (swz<128>(r, c) << 4),
+          cp_async16(a_s + gp * C::A_GROUP + atom * A_ATOM + r * 128 + (swz<128>(r, c) << 4),
                      feats + (size_t)(idx[i] < 0 ? 0 : idx[i]) * CIN + cch * 8, idx[i] < 0 ? 0u : 16u);
         }
         // B': the 64 dY rows of this block, one swizzled line per (row, 64-column atom)
@@ -166,6 +178,9 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
         cp_async_arrive_noinc(&full[s]);  // fires when this thread's copies have landed
       }
     }
+#ifdef RMN_PROF
+    if (tid == 0) { atomicAdd(&g_prof[8], (unsigned long long)prof_wait); atomicAdd(&g_prof[10], (unsigned long long)(clock64() - prof_start)); }
+#endif
     cp_async_wait<0>();
     // ------------------------------ epilogue (first four producer warps) ----------------
     if (warp < 4) {
@@ -203,10 +218,17 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
     constexpr uint64_t B_DESC0 = smem_desc_sw_const(B_ATOM, 8 * SWB, LT_B);
     constexpr uint32_t A_DESC_HI = (uint32_t)(A_DESC0 >> 32), B_DESC_HI = (uint32_t)(B_DESC0 >> 32);
     uint32_t it = 0;
+#ifdef RMN_PROF
+    long long prof_wait = 0; const long long prof_start = clock64();
+#endif
     for (uint32_t blk = 0; blk < n_blocks && !timed_out; ++blk) {
-      for (int g = 0; g < n_groups; ++g, ++it) {
+      for (int sg = 0; sg < n_sg; ++sg, ++it) {
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-        if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
+        {
+          PROF_T0();
+          if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
+          PROF_ADD(prof_wait);
+        }
         fence_proxy_async();  // cp.async wrote through the generic proxy; the MMA reads through the async proxy
         tc_fence_after();
         {
@@ -215,17 +237,33 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
           const uint32_t a_s = smem_base + s * C::STAGE;
           const uint32_t a_lo = (a_s >> 4) + (uint32_t)(A_DESC0 & 0xFFFFFFFFu);
           const uint32_t b_lo = ((a_s + C::A_BYTES) >> 4) + (uint32_t)(B_DESC0 & 0xFFFFFFFFu);
-#pragma unroll
-          for (int jj = 0; jj < kRowsPerStage / 16; ++jj) {
+          const uint32_t d0 = tmem_base + (uint32_t)(sg * GP) * COUT;
+          static_for<kRowsPerStage / 16>([&](auto jc) {
+            constexpr int jj = decltype(jc)::value;
             // MN-major swizzled operands: 8-row K groups 8 lines apart (SBO), 64-channel atoms one ATOM apart (LBO)
             const uint64_t a_desc = ((uint64_t)A_DESC_HI << 32) | (a_lo + (uint32_t)((jj * 16 * 128) >> 4));
             const uint64_t b_desc = ((uint64_t)B_DESC_HI << 32) | (b_lo + (uint32_t)((jj * 16 * SWB) >> 4));
-            tc_mma_bf16_elect(tmem_base + g * COUT, a_desc, b_desc, IDESC, (blk | (uint32_t)jj) != 0 ? 1u : 0u);
-          }
+            const uint32_t accumulate = (blk | (uint32_t)jj) != 0 ? 1u : 0u;
+            if constexpr (GP == 2) {
+              const uint64_t a2_desc = a_desc + (C::A_GROUP >> 4);
+              if constexpr (COUT == 64 || COUT == 128 || COUT == 256) {  // .ws shapes: dY slice read once
+                tc_mma_bf16_ws_elect<jj & 3, 0>(d0, a_desc, b_desc, IDESC, accumulate);
+                tc_mma_bf16_ws_elect<jj & 3, 2>(d0 + COUT, a2_desc, b_desc, IDESC, accumulate);
+              } else {
+                tc_mma_bf16_elect(d0, a_desc, b_desc, IDESC, accumulate);
+                tc_mma_bf16_elect(d0 + COUT, a2_desc, b_desc, IDESC, accumulate);
+              }
+            } else {
+              tc_mma_bf16_elect(d0, a_desc, b_desc, IDESC, accumulate);
+            }
+          });
           tc_commit_elect(&empty[s]);
         }
       }
     }
+#ifdef RMN_PROF
+    if (lane == 0) { atomicAdd(&g_prof[11], (unsigned long long)prof_wait); atomicAdd(&g_prof[12], (unsigned long long)(clock64() - prof_start)); }
+#endif
     if (!timed_out) tc_commit_elect(done);
   }
 
@@ -261,7 +299,8 @@ WgradPlan plan(uint32_t n_dst, int K, int sms) {
   const int groups = (K + C::G - 1) / C::G;
   p.sets = (groups + C::MAX_GROUPS - 1) / C::MAX_GROUPS;
   p.groups_per_set = (groups + p.sets - 1) / p.sets;
-  p.tmem_cols = pow2_at_least((uint32_t)p.groups_per_set * COUT);
+  // (a stage always carries GP groups: an odd set is padded with an all-zero group)
+  p.tmem_cols = pow2_at_least((uint32_t)((p.groups_per_set + C::GP - 1) / C::GP * C::GP) * COUT);
   uint32_t want = (uint32_t)(sms / p.sets);
   if (want < 1) want = 1;
   uint32_t rows = (n_dst + want - 1) / want;
