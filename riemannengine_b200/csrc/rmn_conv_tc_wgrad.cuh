@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
     // eight consecutive lanes copy one line, i.e. one (CIN >= 64) or two (CIN = 32) gathered rows.
     // Neighbour indices: warp w copies rows [4w, 4w + 4) of every stage, for all G * GP offsets of the
     // stage, i.e. 4 * G * GP <= 32 table entries: lane l < 4 * G * GP loads entry (offset l / 4, row l % 4)
-    // with ONE coalesced load per warp and stage, three stages before use (a rotating window of
+    // with ONE coalesced load per warp and stage, six stages before use (the table is streamed from DRAM) (a rotating window of
     // named registers); the lanes of a line fetch theirs with a shuffle when the stage is issued.
     uint32_t it = 0;
     constexpr int NIDX = 4 * G * GP;
@@ -134,14 +134,15 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
 #ifdef RMN_PROF
     long long prof_wait = 0; const long long prof_start = clock64();
 #endif
-    int32_t idx_w0 = load_indices(), idx_w1 = load_indices(), idx_w2 = load_indices();
+    int32_t idx_w0 = load_indices(), idx_w1 = load_indices(), idx_w2 = load_indices(), idx_w3 = load_indices(),
+            idx_w4 = load_indices(), idx_w5 = load_indices();
     for (uint32_t blk = 0; blk < n_blocks && !timed_out; ++blk) {
       const uint32_t j0 = j_begin + blk * kRowsPerStage;
 #pragma unroll 1
       for (int sg = 0; sg < n_sg; ++sg, ++it) {
         const int32_t mine = idx_w0;
-        idx_w0 = idx_w1; idx_w1 = idx_w2;
-        idx_w2 = load_indices();
+        idx_w0 = idx_w1; idx_w1 = idx_w2; idx_w2 = idx_w3; idx_w3 = idx_w4; idx_w4 = idx_w5;
+        idx_w5 = load_indices();
         int32_t idx[kWgIdxPerThread];
 #pragma unroll
         for (int i = 0; i < kWgIdxPerThread; ++i) {

@@ -100,3 +100,27 @@ def test_pooling_transpose_matches_reference_golden_fp32(name):
     (y.F * y.F).sum().mul(0.5).backward()
     parity.check_pool_against_reference(y.C.cpu().numpy(), y.F.detach().cpu().numpy(), feats.grad.cpu().numpy(), gold,
                                         tol=1e-4)
+
+
+def test_empty_inputs_through_pooling_and_statistics():
+    """Zero voxels: every layer returns an empty tensor of the right width, nothing is launched on no data."""
+    from riemannengine_b200 import engine as E, ops
+    coords = torch.zeros((0, 4), dtype=torch.int32, device="cuda")
+    feats = torch.zeros((0, 6), device="cuda")
+    x = E.SparseTensor(feats, coords)
+    assert len(x) == 0
+    for layer in (E.RiemannSumPooling(2, 2, 1, dimension=3), E.RiemannMaxPooling(3, 1, 1, dimension=3)):
+        y = layer(x)
+        assert tuple(y.F.shape) == (0, 6) and len(y) == 0
+    y = E.RiemannConvolution(6, 5, kernel_size=3, dimension=3).cuda()(x)
+    assert tuple(y.F.shape) == (0, 5)
+    assert torch.equal(ops.channel_stats(feats), torch.zeros(2, 6, dtype=torch.float64, device="cuda"))
+    assert ops.affine_act(feats, None, None, relu=True).shape == (0, 6)
+    # an output row without any neighbour pools to zero (isolated voxel, region that misses the centre)
+    c1 = torch.tensor([[0, 0, 0, 0], [0, 10, 10, 10]], dtype=torch.int32, device="cuda")
+    f1 = torch.tensor([[1.0, -2.0], [3.0, 4.0]], device="cuda")
+    t = ops.table_build(c1)
+    res = ops.kmap_build(t, t.coords, np.array([[1, 0, 0], [0, 1, 0]], np.int32))
+    for mode in (ops.POOL_SUM, ops.POOL_AVG, ops.POOL_MAX):
+        out, _ = ops.pool_forward(f1, res.nbr, mode)
+        assert torch.equal(out, torch.zeros_like(f1))
