@@ -155,6 +155,41 @@ int rmn_coords_stride(const int32_t *d_coords, uint32_t n_rows, int W,
                       const int32_t *out_tensor_stride, int32_t *d_out, void *stream);
 
 /*
+ * Continuous (field) coordinates -> integer voxel coordinates at a tensor stride, in float32 as the
+ * reference computes it: batch column lroundf(v); spatial column j
+ * tensor_stride[j] * (int)floor(v / tensor_stride[j]). d_field float32 [n_rows, W] (device),
+ * tensor_stride int32 [W-1] (host), d_out int32 [n_rows, W] (device). Feeding d_out to rmn_table_build gives
+ * the sparse map of a field and its d_inverse is the field-to-sparse map.
+ * Replaces: CoordinateFieldMapCPU::quantize_coordinates (engine/grid/lattice_cpu.hpp:944-984),
+ *   quantize_coordinates_kernel (engine/grid/lattice_gpu.cu:78-151), as called by
+ *   field_to_sparse_insert_and_map_cpp (engine/grid/space_impl.hpp:103-166) under TensorField::sparse
+ *   (engine/tensor/field.cpp:41-59).
+ */
+int rmn_field_quantize(const float *d_field, uint32_t n_rows, int W, const int32_t *tensor_stride,
+                       int32_t *d_out, void *stream);
+
+/*
+ * d_out[i] = (int32)floor((double)d_in[i] / quantization_size) over ALL n_elems elements (every column,
+ * the batch column included, as the reference does); quantization_size <= 0 means floor only.
+ * in_type: 0 float32, 1 float64, 2 int32.
+ * Replaces: the discretisation of sparse_quantize (engine/helpers/discretization.cpp:97-102), which the
+ *   reference runs as torch ops in float64.
+ */
+int rmn_coords_discretize(const void *d_in, int in_type, uint64_t n_elems, double quantization_size,
+                          int32_t *d_out, void *stream);
+
+/*
+ * Multilinear splat of a field onto the 2^D lattice corners around every point: output row
+ * corner * n_rows + point has coordinates floor(v) (+1 on spatial axis a when bit a of `corner` is set; batch
+ * column floor(v)) and features feats[point] * prod_a (bit ? frac_a : 1 - frac_a). d_out_coords int32
+ * [n_rows << (W-1), W], d_out_feats [n_rows << (W-1), C] in `dtype` (RMN_F32 / RMN_BF16). Deduplicating
+ * d_out_coords with rmn_table_build and summing the features of equal rows gives the splatted tensor.
+ * Replaces: TensorField::splat (engine/tensor/field.cpp:61-94), a per-corner loop of torch ops there.
+ */
+int rmn_field_splat(const float *d_field, const void *d_feats, int dtype, uint32_t n_rows, int W, int C,
+                    int32_t *d_out_coords, void *d_out_feats, void *stream);
+
+/*
  * Region expansion: d_out[(row * K + k)] = d_coords[row] + d_offsets[k] on the spatial columns (batch
  * column copied), d_out int32 [n_rows * K, W]; d_offsets device int32 [K, W-1]. Deduplicating the result
  * with rmn_table_build gives the coordinate map that

@@ -227,3 +227,82 @@ def pool_backward(feats, grad_out, in_idx, out_idx, mode: int) -> np.ndarray:
         mx = pool_forward(f, in_idx, out_idx, n_out, POOL_MAX)
         np.add.at(gi, ii, g[oi] * (f[ii] == mx[oi]))
     return gi
+
+
+# --- input step: field quantisation, sparse_quantize, splat (numpy restatements) ---------------------------
+def field_quantize(field: np.ndarray, tensor_stride: Sequence[int]) -> np.ndarray:
+    """int32 voxel coordinates of float32 field rows, computed in float32: batch column lroundf, spatial
+    column j ``stride_j * (int)floor(v / stride_j)`` (engine/grid/lattice_cpu.hpp:944-984)."""
+    f = np.ascontiguousarray(field, dtype=np.float32)
+    out = np.empty(f.shape, np.int32)
+    b = f[:, 0]
+    out[:, 0] = (np.sign(b) * np.floor(np.abs(b) + np.float32(0.5))).astype(np.int32)  # half away from zero
+    for j, s in enumerate(tensor_stride):
+        col = f[:, j + 1]
+        if int(s) == 1:
+            out[:, j + 1] = np.floor(col).astype(np.int32)
+        else:
+            out[:, j + 1] = np.int32(s) * np.floor(col / np.float32(s)).astype(np.int32)
+    return out
+
+
+def quantize_features(feats: np.ndarray, mapping: np.ndarray, inverse: np.ndarray, mode: int) -> np.ndarray:
+    """engine/tensor/field.cpp:109-140 (same rule as engine/tensor/sparse_tensor.cpp:447-481); mode 0 first row,
+    1 average, 2 sum, 3 maximum, 4 none. Sums run in float64 here."""
+    f = np.asarray(feats, np.float64)
+    nu = len(mapping)
+    if mode == 0:
+        return f[mapping]
+    if mode == 4:
+        return f
+    if mode in (1, 2):
+        acc = np.zeros((nu, f.shape[1]))
+        np.add.at(acc, inverse, f)
+        if mode == 2:
+            return acc
+        cnt = np.bincount(inverse, minlength=nu).astype(np.float64)
+        return acc / np.maximum(cnt, 1)[:, None]
+    if mode == 3:
+        acc = np.full((nu, f.shape[1]), -np.inf)
+        np.maximum.at(acc, inverse, f)
+        return acc
+    raise ValueError("Unknown quantization mode")
+
+
+def field_sparse(field: np.ndarray, feats: np.ndarray, tensor_stride: Sequence[int], mode: int):
+    """TensorField::sparse (engine/tensor/field.cpp:41-59): (voxel coords, features, field row -> voxel row)."""
+    q = field_quantize(field, tensor_stride)
+    mapping, inverse = insert_and_map(q)
+    return q[mapping], quantize_features(feats, mapping, inverse, mode), inverse
+
+
+def sparse_quantize(coords: np.ndarray, feats: Optional[np.ndarray], quantization_size: Optional[float] = None):
+    """engine/helpers/discretization.cpp:78-125 without labels: float64 floor-divide on every column, first
+    point per voxel. Returns (coords, features, unique_index, inverse)."""
+    d = np.asarray(coords, np.float64)
+    if quantization_size:
+        d = d / float(quantization_size)
+    d = np.floor(d).astype(np.int32)
+    mapping, inverse = insert_and_map(d)
+    return d[mapping], (None if feats is None else np.asarray(feats)[mapping]), mapping, inverse
+
+
+def field_splat(field: np.ndarray, feats: np.ndarray):
+    """TensorField::splat (engine/tensor/field.cpp:61-94): corner-major lattice points and weighted features
+    (before the summing SparseTensor constructor)."""
+    f = np.ascontiguousarray(field, dtype=np.float32)
+    D = f.shape[1] - 1
+    fl = np.floor(f)
+    frac = f - fl
+    base = fl.astype(np.int32)
+    pts, fs = [], []
+    for corner in range(1 << D):
+        off = np.zeros(D + 1, np.int32)
+        w = np.ones(len(f), np.float32)
+        for a in range(D):
+            up = (corner >> a) & 1
+            off[a + 1] = up
+            w = w * (frac[:, a + 1] if up else np.float32(1) - frac[:, a + 1])
+        pts.append(base + off)
+        fs.append(np.asarray(feats, np.float32) * w[:, None])
+    return np.concatenate(pts, 0), np.concatenate(fs, 0)

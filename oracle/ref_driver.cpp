@@ -29,6 +29,12 @@
 //     (engine/nn/pooling.cpp:17-144) and write pool_coords, pool_feats and
 //     pool_grad_feats (gradient of 0.5 * sum(pool_feats^2) w.r.t. the input features). With transpose = 1 the
 //     pooling-transpose layer (sum; engine/nn/pooling.cpp:197-229) is applied to the convolution's output instead.
+//   field   f32 [N, W] + field_params f64 [2 + D] = {quantisation mode, quantisation size, tensor stride...}
+//     (optional; when present ONLY the input step is run and the arrays above other than feats are ignored):
+//     riemann::TensorField(feats, field).sparse(stride, mode) (engine/tensor/field.cpp:41-59) -> field_coords,
+//     field_feats, field_inverse; TensorField::splat (field.cpp:61-94) -> splat_coords, splat_feats;
+//     riemann::sparse_quantize(field, feats, quantization_size) (engine/helpers/discretization.cpp:78-125) ->
+//     sq_coords, sq_feats, sq_unique_index, sq_inverse.
 // Output arrays: mapping, inverse, in_coords, out_coords, out_feats,
 //   kmap_ptr / kmap_in / kmap_out, grad_feats, grad_weights, and for chain = 1
 //   up_coords, up_feats, kmap2_ptr / kmap2_in / kmap2_out, grad_weights2;
@@ -38,7 +44,9 @@
 //   info i32 [2] = {hardware_concurrency, torch threads}.
 #include "engine/nn/conv.hpp"
 #include "engine/nn/pooling.hpp"
+#include "engine/tensor/field.hpp"
 #include "engine/tensor/sparse_tensor.hpp"
+#include "helpers/discretization.hpp"
 
 #include <torch/torch.h>
 
@@ -152,6 +160,34 @@ int main(int argc, char** argv) {
   }
   try {
     auto arrays = read_arrays(argv[1]);
+    if (arrays.count("field")) {
+      torch::set_num_threads(1);
+      auto field = to_tensor(arrays.at("field"));
+      auto ffeats = to_tensor(arrays.at("feats"));
+      auto fp = to_tensor(arrays.at("field_params"));
+      const int D = static_cast<int>(field.size(1)) - 1;
+      const auto mode = static_cast<riemann::SparseTensorQuantizationMode::Type>(fp[0].item<double>());
+      const double qsize = fp[1].item<double>();
+      riemann::stride_type stride;
+      for (int a = 0; a < D; ++a) stride.push_back(static_cast<uint32_t>(fp[2 + a].item<double>()));
+      std::ofstream out(argv[2], std::ios::binary);
+      riemann::TensorField tf(ffeats, field);
+      auto sp = tf.sparse(stride, c10::nullopt, mode);
+      write_array(out, "field_coords", sp.C());
+      write_array(out, "field_feats", sp.F());
+      write_array(out, "field_inverse", tf.inverse_mapping(sp.coordinate_map_key()));
+      riemann::TensorField tf2(ffeats, field);
+      auto spl = tf2.splat();
+      write_array(out, "splat_coords", spl.C());
+      write_array(out, "splat_feats", spl.F());
+      auto sq = riemann::sparse_quantize(field, ffeats, c10::nullopt, -100,
+                                         qsize > 0 ? c10::optional<double>(qsize) : c10::nullopt);
+      write_array(out, "sq_coords", sq.coordinates);
+      write_array(out, "sq_feats", sq.features.value());
+      write_array(out, "sq_unique_index", sq.unique_index);
+      write_array(out, "sq_inverse", sq.inverse_mapping);
+      return 0;
+    }
     auto coords = to_tensor(arrays.at("coords"));
     auto feats = to_tensor(arrays.at("feats"));
     auto weights = to_tensor(arrays.at("weights"));

@@ -84,3 +84,22 @@ def run(coords: np.ndarray, feats: np.ndarray, weights: np.ndarray, kernel_size:
         write_arrays(fin, arrays)
         subprocess.run([DRIVER, fin, fout], check=True, timeout=timeout)
         return read_arrays(fout)
+
+
+def run_field(field: np.ndarray, feats: np.ndarray, tensor_stride, mode: int, quantization_size: float = 0.0,
+              timeout: Optional[float] = None) -> Dict[str, np.ndarray]:
+    """The reference's input step on continuous coordinates ``field`` f32 [N, 1+D]: ``TensorField.sparse``
+    (outputs ``field_*``), ``TensorField.splat`` (``splat_*``) and ``sparse_quantize`` (``sq_*``;
+    ``quantization_size`` 0 = none). ``mode`` is the reference's SparseTensorQuantizationMode value."""
+    if not available():
+        raise RuntimeError("reference driver not built: make -C oracle ref")
+    arrays = {
+        "field": np.ascontiguousarray(field, np.float32),
+        "feats": np.ascontiguousarray(feats, np.float32),
+        "field_params": np.array([mode, quantization_size, *tensor_stride], np.float64),
+    }
+    with tempfile.TemporaryDirectory() as d:
+        fin, fout = os.path.join(d, "in.rmna"), os.path.join(d, "out.rmna")
+        write_arrays(fin, arrays)
+        subprocess.run([DRIVER, fin, fout], check=True, timeout=timeout)
+        return read_arrays(fout)

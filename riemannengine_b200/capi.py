@@ -53,6 +53,9 @@ SIGNATURES = {
     "rmn_conv_backward_weight": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_uint32, c_int, c_void_p, c_int,
                                          c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
     "rmn_coords_expand": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_void_p, c_void_p]),
+    "rmn_field_quantize": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_void_p, c_void_p]),
+    "rmn_coords_discretize": (c_int, [c_void_p, c_int, c_uint64, ctypes.c_double, c_void_p, c_void_p]),
+    "rmn_field_splat": (c_int, [c_void_p, c_void_p, c_int, c_uint32, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "rmn_channel_stats_workspace_bytes": (c_size_t, [c_int]),
     "rmn_channel_stats": (c_int, [c_void_p, c_uint32, c_int, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
     "rmn_conv_forward_stats": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_int, c_void_p, c_uint32,

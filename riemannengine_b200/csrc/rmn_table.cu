@@ -14,6 +14,8 @@
 // (engine/grid/lattice_gpu.cu:30-51).
 #include "rmn_common.cuh"
 
+#include <cuda_bf16.h>
+
 #include <limits.h>
 
 #include <mutex>
@@ -317,6 +319,69 @@ __global__ void __launch_bounds__(256) k_stride(const int32_t* __restrict__ coor
   out[i] = c;
 }
 
+// Continuous (field) coordinates -> integer voxel coordinates, the reference's rule in float32:
+// batch column lroundf(v), spatial column j: stride_j * (int)floor(v / stride_j)
+// (engine/grid/lattice_cpu.hpp:944-984, engine/grid/lattice_gpu.cu:78-151). One thread per element, streaming.
+__global__ void __launch_bounds__(256) k_field_quantize(const float* __restrict__ field, uint64_t total, int W,
+                                                        StrideArg st, int32_t* __restrict__ out) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int col = (int)(i % (uint64_t)W);
+  const float v = field[i];
+  int32_t c;
+  if (col == 0) {
+    c = (int32_t)lroundf(v);
+  } else {
+    const int32_t s = st.s[col - 1];
+    c = s == 1 ? (int32_t)floorf(v) : s * (int32_t)floorf(__fdiv_rn(v, (float)s));
+  }
+  out[i] = c;
+}
+
+// out = (int32)floor((double)v / q) on EVERY column (q <= 0: floor only): the discretisation step of
+// sparse_quantize (engine/helpers/discretization.cpp:97-102), computed in float64 as there.
+template <typename T>
+__global__ void __launch_bounds__(256) k_discretize(const T* __restrict__ in, uint64_t total, double q,
+                                                    int32_t* __restrict__ out) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  double v = (double)in[i];
+  if (q > 0.0) v = __ddiv_rn(v, q);
+  out[i] = (int32_t)floor(v);
+}
+
+// Multilinear splat of a field onto the 2^D lattice corners around every point
+// (engine/tensor/field.cpp:61-94): corner-major rows (row = corner * n + point), coordinates
+// floor(v) + corner bit per spatial axis (batch column floor(v)), features scaled by
+// prod_axis (bit ? frac : 1 - frac). One thread per (output row, 4-channel group).
+template <typename T>
+__global__ void __launch_bounds__(256) k_field_splat(const float* __restrict__ field, const T* __restrict__ feats,
+                                                     uint32_t n, int W, int C, int32_t* __restrict__ out_coords,
+                                                     T* __restrict__ out_feats) {
+  const int groups = (C + 3) / 4;
+  const uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const uint64_t rows = (uint64_t)n << (W - 1);
+  if (t >= rows * groups) return;
+  const uint64_t row = t / groups;
+  const int g = (int)(t % groups);
+  const uint32_t corner = (uint32_t)(row / n), point = (uint32_t)(row % n);
+  float w = 1.0f;
+  for (int a = 0; a < W; ++a) {
+    const float v = field[(size_t)point * W + a];
+    const float fl = floorf(v);
+    int32_t c = (int32_t)fl;
+    if (a > 0) {
+      const float frac = v - fl;
+      const bool upper = (corner >> (a - 1)) & 1u;
+      w *= upper ? frac : 1.0f - frac;
+      c += upper ? 1 : 0;
+    }
+    if (g == 0) out_coords[row * W + a] = c;
+  }
+  for (int ch = g * 4; ch < min(C, g * 4 + 4); ++ch)
+    out_feats[row * C + ch] = (T)((float)feats[(size_t)point * C + ch] * w);
+}
+
 // out[(row * K + k)] = coords[row] + offsets[k] on the spatial columns (batch column copied)
 __global__ void __launch_bounds__(256) k_expand(const int32_t* __restrict__ coords, uint64_t total, int W, int K,
                                                 const int32_t* __restrict__ offsets, int32_t* __restrict__ out) {
@@ -344,6 +409,63 @@ extern "C" int rmn_coords_expand(const int32_t* d_coords, uint32_t n_rows, int W
   const uint64_t total = (uint64_t)n_rows * (uint64_t)K * (uint64_t)W;
   if ((uint64_t)n_rows * (uint64_t)K >= 0x7FFFFFFFull) return RMN_ERR_TOO_LARGE;
   k_expand<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(d_coords, total, W, K, d_offsets, d_out);
+  RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}
+
+extern "C" int rmn_field_quantize(const float* d_field, uint32_t n_rows, int W, const int32_t* tensor_stride,
+                                  int32_t* d_out, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (W < 2 || W > RMN_MAX_W || !tensor_stride) return RMN_ERR_BAD_ARG;
+  if (n_rows == 0) return RMN_OK;
+  if (!d_field || !d_out) return RMN_ERR_BAD_ARG;
+  StrideArg st;
+  for (int a = 0; a < RMN_MAX_W; ++a) st.s[a] = 1;
+  for (int a = 0; a < W - 1; ++a) {
+    if (tensor_stride[a] <= 0) return RMN_ERR_BAD_ARG;
+    st.s[a] = tensor_stride[a];
+  }
+  const uint64_t total = (uint64_t)n_rows * W;
+  k_field_quantize<<<(uint32_t)((total + 255) / 256), 256, 0, stream>>>(d_field, total, W, st, d_out);
+  RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}
+
+extern "C" int rmn_coords_discretize(const void* d_in, int in_type, uint64_t n_elems, double quantization_size,
+                                     int32_t* d_out, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (n_elems == 0) return RMN_OK;
+  if (!d_in || !d_out || n_elems >= ((uint64_t)1 << 39)) return RMN_ERR_BAD_ARG;
+  if (quantization_size != quantization_size) return RMN_ERR_BAD_ARG;  // NaN
+  const uint32_t nb = (uint32_t)((n_elems + 255) / 256);
+  switch (in_type) {
+    case 0: k_discretize<float><<<nb, 256, 0, stream>>>((const float*)d_in, n_elems, quantization_size, d_out); break;
+    case 1: k_discretize<double><<<nb, 256, 0, stream>>>((const double*)d_in, n_elems, quantization_size, d_out); break;
+    case 2: k_discretize<int32_t><<<nb, 256, 0, stream>>>((const int32_t*)d_in, n_elems, quantization_size, d_out); break;
+    default: return RMN_ERR_UNSUPPORTED;
+  }
+  RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}
+
+extern "C" int rmn_field_splat(const float* d_field, const void* d_feats, int dtype, uint32_t n_rows, int W, int C,
+                               int32_t* d_out_coords, void* d_out_feats, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (W < 2 || W > RMN_MAX_W || C < 1) return RMN_ERR_BAD_ARG;
+  if (n_rows == 0) return RMN_OK;
+  if (!d_field || !d_feats || !d_out_coords || !d_out_feats) return RMN_ERR_BAD_ARG;
+  const uint64_t rows = (uint64_t)n_rows << (W - 1);
+  if (rows >= 0x7FFFFFFFull) return RMN_ERR_TOO_LARGE;
+  const uint64_t threads = rows * (uint64_t)((C + 3) / 4);
+  const uint32_t nb = (uint32_t)((threads + 255) / 256);
+  if (dtype == RMN_F32)
+    k_field_splat<float><<<nb, 256, 0, stream>>>(d_field, (const float*)d_feats, n_rows, W, C, d_out_coords,
+                                                 (float*)d_out_feats);
+  else if (dtype == RMN_BF16)
+    k_field_splat<__nv_bfloat16><<<nb, 256, 0, stream>>>(d_field, (const __nv_bfloat16*)d_feats, n_rows, W, C,
+                                                         d_out_coords, (__nv_bfloat16*)d_out_feats);
+  else
+    return RMN_ERR_UNSUPPORTED;
   RMN_LAUNCH_CHECK();
   return RMN_OK;
 }

@@ -189,6 +189,8 @@ class CoordinateManager:
         self._backend = backend
         self._maps: Dict[Tuple[Tuple[int, ...], str], _CoordinateMap] = {}
         self._kernel_maps: Dict[tuple, KernelMap] = {}
+        self._fields: Dict[Tuple[Tuple[int, ...], str], torch.Tensor] = {}
+        self._field_to_sparse: Dict[tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
 
     # -- introspection -------------------------------------------------------------------
     @property
@@ -238,6 +240,46 @@ class CoordinateManager:
         table = ops.table_build(coordinates)
         self._maps[(stride, string_id)] = _CoordinateMap(table, stride)
         return CoordinateMapKey(stride, string_id), (table.mapping, table.inverse)
+
+    def insert_field(self, coordinates: torch.Tensor, tensor_stride: Sequence[int],
+                     string_id: str = "") -> CoordinateMapKey:
+        """Registers continuous coordinates (float32 [N, 1 + D]) under a field key
+        (engine/grid/space_impl.hpp:36-80)."""
+        ops._check_field(coordinates)
+        stride = tuple(int(s) for s in tensor_stride)
+        if coordinates.size(1) - 1 != len(stride):
+            raise RuntimeError(f"The coordinate dimension (coordinate_size - 1): {coordinates.size(1) - 1} "
+                               f"must match the size of tensor stride: {list(stride)}")
+        while (stride, string_id) in self._fields:
+            string_id = string_id + "-" + "".join(random.choice(string.ascii_lowercase) for _ in range(8))
+        self._fields[(stride, string_id)] = coordinates
+        return CoordinateMapKey(stride, string_id)
+
+    def get_field_coordinates(self, field_key: CoordinateMapKey) -> torch.Tensor:
+        f = self._fields.get(field_key.get_key())
+        if f is None:
+            raise RuntimeError(ERROR_MAP_NOT_FOUND)
+        return f
+
+    def field_to_sparse_insert_and_map(self, field_key: CoordinateMapKey, sparse_tensor_stride: Sequence[int],
+                                       sparse_tensor_string_id: str = ""):
+        """Quantises a field at ``sparse_tensor_stride`` and inserts the voxels as a new sparse map; returns
+        (sparse key, (first rows, field-row -> sparse-row)) (engine/grid/space_impl.hpp:103-166)."""
+        field = self.get_field_coordinates(field_key)
+        stride = [int(s) for s in sparse_tensor_stride]
+        if field.size(1) - 1 != len(stride):
+            raise RuntimeError(f"The coordinate dimension (coordinate_size - 1): {field.size(1) - 1} "
+                               f"must match the size of tensor stride: {stride}")
+        voxels = ops.field_quantize(field, stride)
+        key, maps = self.insert_and_map(voxels, stride, sparse_tensor_string_id)
+        self._field_to_sparse[(field_key.get_key(), key.get_key())] = maps
+        return key, maps
+
+    def get_field_to_sparse_map(self, field_key: CoordinateMapKey, sparse_key: CoordinateMapKey):
+        maps = self._field_to_sparse.get((field_key.get_key(), sparse_key.get_key()))
+        if maps is None:
+            raise RuntimeError("Field To Sparse Map doesn't exist")
+        return maps
 
     def stride(self, in_key: CoordinateMapKey, kernel_stride: Sequence[int], string_id: str = "") -> CoordinateMapKey:
         """Strided-down map, created if absent (engine/grid/space_impl.hpp:331-350). Coarse rows
@@ -489,6 +531,148 @@ class SparseTensor:
     def __repr__(self) -> str:
         return (f"SparseTensor(N={self._features.size(0)}, C={self._features.size(1)}, D={self._dimension}, "
                 f"device={self._features.device})")
+
+
+class TensorField:
+    """Features on continuous coordinates; ``sparse()`` voxelises them (engine/tensor/field.hpp:10-53,
+    engine/tensor/field.cpp:9-142)."""
+
+    def __init__(self, features: torch.Tensor, coordinates: torch.Tensor,
+                 coordinate_manager: Optional[CoordinateManager] = None,
+                 quantization_mode: int = SparseTensorQuantizationMode.UNWEIGHTED_AVERAGE):
+        if features.dim() != 2:
+            raise RuntimeError("Features must be a 2D tensor")
+        if coordinates.dim() != 2:
+            raise RuntimeError("Coordinates must be a 2D tensor")
+        if features.size(0) != coordinates.size(0):
+            raise RuntimeError("Features and coordinates must have same number of rows")
+        if coordinates.dtype not in (torch.float32, torch.float64):
+            raise RuntimeError("TensorField coordinates must be float or double")
+        if coordinates.size(1) < 2:
+            raise RuntimeError("Coordinates must contain a batch column and spatial columns")
+        self._dimension = int(coordinates.size(1)) - 1
+        if coordinate_manager is None:
+            coordinate_manager = CoordinateManager(self._dimension, CoordinateMapBackend.CUDA)
+        if coordinate_manager.D() != self._dimension:
+            raise RuntimeError("Coordinate manager dimension does not match coordinates")
+        self._manager = coordinate_manager
+        self._features = features
+        # the reference's manager takes float32 fields only (engine/grid/space_impl.hpp:47)
+        self._coordinates = coordinates.contiguous()
+        self._field_key = coordinate_manager.insert_field(self._coordinates, [1] * self._dimension)
+        self._inverse_mappings: Dict[tuple, torch.Tensor] = {}
+
+    def sparse(self, tensor_stride: Optional[Sequence[int]] = None,
+               coordinate_map_key: Optional[CoordinateMapKey] = None,
+               quantization_mode: int = SparseTensorQuantizationMode.UNWEIGHTED_AVERAGE) -> "SparseTensor":
+        stride = _stride_list(tensor_stride if tensor_stride else 1, self._dimension)
+        key, (first_rows, row_to_unique) = self._manager.field_to_sparse_insert_and_map(self._field_key, stride)
+        feats = SparseTensor._quantize(self._features, first_rows, row_to_unique, self._manager.size(key),
+                                       quantization_mode)
+        self._inverse_mappings[key.get_key()] = row_to_unique
+        return SparseTensor(feats, coordinate_map_key=key, coordinate_manager=self._manager)
+
+    def splat(self) -> "SparseTensor":
+        coords, feats = ops.field_splat(self._coordinates, self._features)
+        return SparseTensor(feats, coords, self._manager, SparseTensorQuantizationMode.UNWEIGHTED_SUM)
+
+    def inverse_mapping(self, sparse_key: CoordinateMapKey) -> torch.Tensor:
+        found = self._inverse_mappings.get(sparse_key.get_key())
+        if found is None:
+            _, (_, found) = self._manager.field_to_sparse_insert_and_map(self._field_key,
+                                                                         sparse_key.get_tensor_stride())
+            self._inverse_mappings[sparse_key.get_key()] = found
+        return found
+
+    def slice(self, sparse: "SparseTensor") -> torch.Tensor:
+        """Features of ``sparse`` read back at the field's points (rows of the sparse tensor gathered
+        through the field-to-sparse map)."""
+        return sparse.F.index_select(0, self.inverse_mapping(sparse.coordinate_map_key))
+
+    @property
+    def F(self) -> torch.Tensor:
+        return self._features
+
+    @property
+    def C(self) -> torch.Tensor:
+        return self._coordinates
+
+    @property
+    def coordinate_field_map_key(self) -> CoordinateMapKey:
+        return self._field_key
+
+    @property
+    def coordinate_manager(self) -> CoordinateManager:
+        return self._manager
+
+    @property
+    def dimension(self) -> int:
+        return self._dimension
+
+    @property
+    def device(self):
+        return self._features.device
+
+    @property
+    def dtype(self):
+        return self._features.dtype
+
+
+class SparseQuantizeResult:
+    """Fields of the reference's struct (helpers/discretization.hpp:15-21)."""
+
+    def __init__(self, coordinates, features, labels, unique_index, inverse_mapping):
+        self.coordinates = coordinates
+        self.features = features
+        self.labels = labels
+        self.unique_index = unique_index
+        self.inverse_mapping = inverse_mapping
+
+
+def unique_coordinate_map(coordinates: torch.Tensor, tensor_stride: Optional[Sequence[int]] = None):
+    """(first rows, row -> unique row) of int32 coordinates (engine/helpers/discretization.cpp:127-141)."""
+    if coordinates.dim() != 2 or coordinates.size(1) < 2:
+        raise RuntimeError("Coordinates must include a batch column and spatial dimensions")
+    dimension = int(coordinates.size(1)) - 1
+    stride = list(tensor_stride) if tensor_stride else [1] * dimension
+    if len(stride) != dimension:
+        raise RuntimeError("Tensor stride dimension must match coordinates")
+    manager = CoordinateManager(dimension, CoordinateMapBackend.CUDA)
+    return manager.insert_and_map(coordinates.contiguous(), stride)[1]
+
+
+def quantize_th(coordinates: torch.Tensor):
+    """[first rows, inverse] (engine/helpers/discretization.cpp:24-29)."""
+    if coordinates.dtype != torch.int32:
+        raise RuntimeError("Coordinates must have int32 dtype")
+    unique, inverse = unique_coordinate_map(coordinates)
+    return [unique, inverse]
+
+
+def sparse_quantize(coordinates: torch.Tensor, features: Optional[torch.Tensor] = None,
+                    labels: Optional[torch.Tensor] = None, ignore_label: int = -100,
+                    quantization_size: Optional[float] = None, device=None) -> SparseQuantizeResult:
+    """Voxelise points: ``floor(coordinates / quantization_size)`` on every column, deduplicate, keep the
+    first point of every voxel (engine/helpers/discretization.cpp:78-125). The label-coalescing branch is a
+    CPU-only loop in the reference (discretization.cpp:31-76) and has no device path here."""
+    if coordinates.dim() != 2:
+        raise RuntimeError("Coordinates must be a 2D matrix")
+    if features is not None and (features.dim() != 2 or features.size(0) != coordinates.size(0)):
+        raise RuntimeError("Feature rows must match coordinate rows")
+    if labels is not None:
+        raise RuntimeError("Label quantization currently requires CPU tensors")
+    if quantization_size is not None and not (quantization_size > 0.0 and math.isfinite(quantization_size)):
+        raise RuntimeError("Quantization size must be positive and finite")
+    if device is not None:
+        coordinates = coordinates.to(device)
+    discrete = ops.coords_discretize(coordinates, quantization_size)
+    if discrete.size(1) < 2:
+        raise RuntimeError("Coordinates must include a batch column and spatial dimensions")
+    unique, inverse = unique_coordinate_map(discrete)
+    out_feats = None
+    if features is not None:
+        out_feats = features.to(discrete.device).index_select(0, unique)
+    return SparseQuantizeResult(discrete.index_select(0, unique), out_feats, None, unique, inverse)
 
 
 class KernelGenerator:

@@ -412,3 +412,57 @@ def coords_expand(coords: torch.Tensor, offsets: np.ndarray) -> torch.Tensor:
         capi.check(capi.lib().rmn_coords_expand(_ptr(coords), n, w, _ptr(d_off), K, _ptr(out), _stream()),
                    "rmn_coords_expand")
     return out
+
+
+def _check_field(field: torch.Tensor) -> None:
+    _require_cuda(field, "coordinates")
+    if field.dim() != 2 or field.dtype != torch.float32 or not field.is_contiguous():
+        raise RuntimeError("field coordinates must be a contiguous 2D float32 tensor")
+    if not 2 <= field.size(1) <= capi.MAX_W:
+        raise RuntimeError("Coordinates must contain a batch column and spatial columns")
+
+
+def field_quantize(field: torch.Tensor, tensor_stride: Sequence[int]) -> torch.Tensor:
+    """int32 voxel coordinates of continuous ``field`` rows at ``tensor_stride`` (rmn_field_quantize)."""
+    _check_field(field)
+    st = np.ascontiguousarray(tensor_stride, dtype=np.int32)
+    if st.size != field.size(1) - 1 or (st <= 0).any():
+        raise RuntimeError("Invalid stride")
+    out = torch.empty(field.shape, dtype=torch.int32, device=field.device)
+    with torch.cuda.device(field.device):
+        capi.check(capi.lib().rmn_field_quantize(_ptr(field), int(field.size(0)), int(field.size(1)),
+                                                 st.ctypes.data_as(ctypes.c_void_p), _ptr(out), _stream()),
+                   "rmn_field_quantize")
+    return out
+
+
+def coords_discretize(coords: torch.Tensor, quantization_size: Optional[float] = None) -> torch.Tensor:
+    """``floor(float64(coords) / quantization_size)`` as int32 on every column (rmn_coords_discretize)."""
+    _require_cuda(coords, "coordinates")
+    codes = {torch.float32: 0, torch.float64: 1, torch.int32: 2}
+    if coords.dtype not in codes:
+        coords = coords.to(torch.float64)
+    coords = coords.contiguous()
+    out = torch.empty(coords.shape, dtype=torch.int32, device=coords.device)
+    q = 0.0 if quantization_size is None else float(quantization_size)
+    with torch.cuda.device(coords.device):
+        capi.check(capi.lib().rmn_coords_discretize(_ptr(coords), codes[coords.dtype], coords.numel(), q, _ptr(out),
+                                                    _stream()), "rmn_coords_discretize")
+    return out
+
+
+def field_splat(field: torch.Tensor, feats: torch.Tensor):
+    """Corner-major lattice coordinates [N * 2^D, W] and weighted features [N * 2^D, C] (rmn_field_splat)."""
+    _check_field(field)
+    _require_cuda(feats, "features")
+    if feats.dim() != 2 or feats.size(0) != field.size(0):
+        raise RuntimeError("Features and coordinates must have same number of rows")
+    feats = feats.contiguous()
+    n, w, c = int(field.size(0)), int(field.size(1)), int(feats.size(1))
+    rows = n << (w - 1)
+    out_c = torch.empty((rows, w), dtype=torch.int32, device=field.device)
+    out_f = torch.empty((rows, c), dtype=feats.dtype, device=field.device)
+    with torch.cuda.device(field.device):
+        capi.check(capi.lib().rmn_field_splat(_ptr(field), _ptr(feats), _dtype_code(feats), n, w, c, _ptr(out_c),
+                                              _ptr(out_f), _stream()), "rmn_field_splat")
+    return out_c, out_f

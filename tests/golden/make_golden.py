@@ -5,7 +5,7 @@ Runs the unmodified reference CPU path (``oracle/_ref/ref_driver``, built by
 stores inputs + reference outputs as ``<case>.npz``. The parity tests load the
 fixtures only; they never need the reference at run time.
 
-    python tests/golden/make_golden.py [--pool-only | --unpool-only]
+    python tests/golden/make_golden.py [--pool-only | --unpool-only | --field-only]
 """
 from __future__ import annotations
 
@@ -47,6 +47,29 @@ UNPOOL_CASES = {
 }
 
 
+# input step on continuous coordinates (reference engine/tensor/field.cpp, engine/helpers/discretization.cpp):
+# name: (seed, D, n_rows, batches, extent, channels, tensor stride, quantisation mode, quantisation size)
+# mode: 0 first point, 1 average, 2 sum, 3 maximum (engine/foundation/types.hpp:88-93)
+FIELD_CASES = {
+    "field_d3_s1_avg": (41, 3, 400, 2, 4.0, 5, [1, 1, 1], 1, 0.5),
+    "field_d3_s2_sum": (42, 3, 400, 3, 6.0, 4, [2, 2, 2], 2, 0.0),
+    "field_d2_s42_max": (43, 2, 300, 2, 9.0, 3, [4, 2], 3, 0.25),
+    "field_d3_s123_first": (44, 3, 350, 1, 5.0, 6, [1, 2, 3], 0, 1.5),
+    "field_d4_s1_avg": (45, 4, 250, 2, 2.0, 3, [1, 1, 1, 1], 1, 0.0),
+}
+
+
+def make_field_inputs(seed, D, n, batches, extent, channels):
+    rng = np.random.default_rng(seed)
+    field = np.concatenate([rng.integers(0, batches, (n, 1)).astype(np.float32),
+                            rng.uniform(-extent, extent, (n, D)).astype(np.float32)], axis=1)
+    field[::7, 1:] = np.round(field[::7, 1:])           # points exactly on voxel boundaries
+    k = len(field[1::9])
+    field[1::9] = field[2::9][:k]                        # exact duplicate points
+    feats = rng.standard_normal((n, channels)).astype(np.float32)
+    return field, feats
+
+
 def make_inputs(seed, D, n, batches, lo, hi, c_in, c_out, kernel, stride, dilation, c2):
     rng = np.random.default_rng(seed)
     spatial = rng.integers(lo, hi + 1, size=(n, D), dtype=np.int32)
@@ -66,7 +89,22 @@ def make_inputs(seed, D, n, batches, lo, hi, c_in, c_out, kernel, stride, dilati
     return coords, feats, weights, weights2
 
 
+def main_field() -> None:
+    for name, (seed, D, n, batches, extent, channels, stride, mode, qsize) in FIELD_CASES.items():
+        field, feats = make_field_inputs(seed, D, n, batches, extent, channels)
+        ref = refrun.run_field(field, feats, stride, mode, qsize)
+        arrays = {"field": field, "feats": feats, "stride": np.array(stride, np.int32),
+                  "spec": np.array([D, mode], np.int32), "qsize": np.array([qsize], np.float64)}
+        for k, v in ref.items():
+            arrays["ref_" + k] = v
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **arrays)
+        print(name, {k: v.shape for k, v in ref.items()}, os.path.getsize(path), "bytes")
+
+
 def main() -> None:
+    if "--field-only" in sys.argv:
+        return main_field()
     only_pool = "--pool-only" in sys.argv or "--unpool-only" in sys.argv
     for name, spec in ({} if only_pool else CASES).items():
         coords, feats, weights, weights2 = make_inputs(*spec)
@@ -99,6 +137,8 @@ def main() -> None:
         print(name, {k: v.shape for k, v in arrays.items() if k.startswith("ref_")}, os.path.getsize(path), "bytes")
     if "--unpool-only" in sys.argv:
         return
+    if not only_pool:
+        main_field()
     for name, (seed, D, n, batches, lo, hi, C, mode, kernel, stride) in POOL_CASES.items():
         coords, feats, _, _ = make_inputs(seed, D, n, batches, lo, hi, C, 1, 1, 1, 1, None)
         ident = np.ones((1, C, 1), np.float32)  # the driver always runs a convolution first: 1^D kernel, unused here

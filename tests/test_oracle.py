@@ -105,3 +105,25 @@ def test_oracle_pooling_transpose_matches_reference_golden(name):
     gold = parity.load_golden(name)
     out_coords, out, g_raw = parity.oracle_unpool_case(gold)
     parity.check_pool_against_reference(out_coords, out, g_raw, gold, tol=1e-5)
+
+
+FIELD_CASES = ["field_d3_s1_avg", "field_d3_s2_sum", "field_d2_s42_max", "field_d3_s123_first", "field_d4_s1_avg"]
+
+
+@pytest.mark.parametrize("name", FIELD_CASES)
+def test_field_oracle_matches_reference_fixture(name):
+    """Input step (TensorField.sparse / splat, sparse_quantize) against fixtures the reference produced."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", name + ".npz"))
+    field, feats, stride = g["field"], g["feats"], g["stride"].tolist()
+    mode, q = int(g["spec"][1]), float(g["qsize"][0])
+    c, f, inv = O.field_sparse(field, feats, stride, mode)
+    assert np.array_equal(c, g["ref_field_coords"]) and np.array_equal(inv, g["ref_field_inverse"])
+    assert np.abs(f - g["ref_field_feats"]).max() <= 1e-5 * max(1.0, np.abs(f).max())
+    sc, sf = O.field_splat(field, feats)
+    m, i = O.insert_and_map(sc)
+    assert np.array_equal(sc[m], g["ref_splat_coords"])
+    assert np.abs(O.quantize_features(sf, m, i, 2) - g["ref_splat_feats"]).max() <= 1e-5
+    qc, qf, qu, qi = O.sparse_quantize(field, feats, q if q > 0 else None)
+    assert np.array_equal(qc, g["ref_sq_coords"]) and np.array_equal(qf, g["ref_sq_feats"])
+    assert np.array_equal(qu, g["ref_sq_unique_index"]) and np.array_equal(qi, g["ref_sq_inverse"])
