@@ -165,6 +165,38 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("__len__", [](const SparseTensor& self) { return self.F().size(0); })
       .def("detach", &SparseTensor::detach);
 
+  // python/src/sparse_bindings.cpp:204-233
+  py::class_<TensorField>(m, "TensorField")
+      .def(py::init<at::Tensor, at::Tensor, std::shared_ptr<CoordinateManager>, SparseTensorQuantizationMode::Type>(),
+           py::arg("features"), py::arg("coordinates"),
+           py::arg("coordinate_manager") = std::shared_ptr<CoordinateManager>(),
+           py::arg("quantization_mode") = SparseTensorQuantizationMode::UNWEIGHTED_AVERAGE)
+      .def("sparse",
+           [](const TensorField& self, stride_type tensor_stride, c10::optional<CoordinateMapKey> key,
+              SparseTensorQuantizationMode::Type mode) { return self.sparse(std::move(tensor_stride), key, mode); },
+           py::arg("tensor_stride") = stride_type{}, py::arg("coordinate_map_key") = py::none(),
+           py::arg("quantization_mode") = SparseTensorQuantizationMode::UNWEIGHTED_AVERAGE)
+      .def("splat", &TensorField::splat)
+      .def("inverse_mapping", &TensorField::inverse_mapping, py::arg("sparse_coordinate_map_key"))
+      .def_property_readonly("F", &TensorField::F)
+      .def_property_readonly("C", &TensorField::C)
+      .def_property_readonly("features", &TensorField::F)
+      .def_property_readonly("coordinates", &TensorField::C)
+      .def_property_readonly("coordinate_field_map_key", &TensorField::coordinate_field_map_key)
+      .def_property_readonly("coordinate_manager", &TensorField::coordinate_manager)
+      .def_property_readonly("dimension", &TensorField::dimension)
+      .def("__len__", [](const TensorField& self) { return self.F().size(0); });
+
+  m.def(
+      "sparse_quantize",
+      [](at::Tensor coordinates, c10::optional<at::Tensor> features, c10::optional<double> quantization_size) {
+        auto r = sparse_quantize(std::move(coordinates), std::move(features), c10::nullopt, -100, quantization_size);
+        return py::make_tuple(r.coordinates, r.features.has_value() ? py::cast(*r.features) : py::none(),
+                              r.unique_index, r.inverse_mapping);
+      },
+      py::arg("coordinates"), py::arg("features") = py::none(), py::arg("quantization_size") = py::none(),
+      "(coordinates, features, unique_index, inverse_mapping) of the voxelised points");
+
   bind_conv<RiemannConvolutionImpl>(m, "RiemannConvolution")
       .def(py::init([](int in_channels, int out_channels, int kernel_size, int stride, int dilation, bool bias,
                        bool expand_coordinates, ConvolutionMode::Type convolution_mode, int dimension) {

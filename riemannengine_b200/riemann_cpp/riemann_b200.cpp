@@ -226,6 +226,50 @@ CoordinateManager::insert_and_map(const at::Tensor& coordinates, stride_type ten
   return {CoordinateMapKey(coordinate_size, map_key), {mapping, inverse}};
 }
 
+CoordinateMapKey CoordinateManager::insert_field(const at::Tensor& coordinates, stride_type tensor_stride,
+                                                 std::string string_id) {
+  TORCH_CHECK(coordinates.is_cuda(), "coordinates must be a CUDA tensor: this library has no CPU path");
+  TORCH_CHECK(coordinates.dim() == 2 && coordinates.is_contiguous() && coordinates.scalar_type() == at::kFloat,
+              "field coordinates must be a contiguous 2D float32 tensor");
+  const auto coordinate_size = static_cast<size_type>(coordinates.size(1));
+  if (coordinate_size - 1 != tensor_stride.size())
+    throw std::runtime_error("The coordinate dimension (coordinate_size - 1): " +
+                             std::to_string(coordinate_size - 1) +
+                             " must match the size of tensor stride: " + stride_string(tensor_stride));
+  coordinate_map_key_type map_key(tensor_stride, string_id);
+  while (fields_.count(map_key)) {
+    std::string suffix = "-";
+    for (int i = 0; i < 8; ++i) suffix.push_back(static_cast<char>('a' + std::rand() % 26));
+    map_key.second = string_id + suffix;
+  }
+  fields_[map_key] = coordinates;
+  return CoordinateMapKey(coordinate_size, map_key);
+}
+
+at::Tensor CoordinateManager::get_field_coordinates(const CoordinateMapKey& field_key) const {
+  auto it = fields_.find(field_key.get_key());
+  if (it == fields_.end()) throw std::runtime_error(ERROR_MAP_NOT_FOUND);
+  return it->second;
+}
+
+std::pair<CoordinateMapKey, std::pair<at::Tensor, at::Tensor>>
+CoordinateManager::field_to_sparse_insert_and_map(const CoordinateMapKey& field_key, stride_type sparse_tensor_stride,
+                                                  std::string sparse_tensor_string_id) {
+  auto field = get_field_coordinates(field_key);
+  if (static_cast<size_t>(field.size(1)) - 1 != sparse_tensor_stride.size())
+    throw std::runtime_error("The coordinate dimension (coordinate_size - 1): " +
+                             std::to_string(field.size(1) - 1) +
+                             " must match the size of tensor stride: " + stride_string(sparse_tensor_stride));
+  c10::cuda::CUDAGuard guard(field.device());
+  auto voxels = at::empty(field.sizes(), field.options().dtype(at::kInt));
+  auto st = to_i32(sparse_tensor_stride);
+  check(rmn_field_quantize(static_cast<const float*>(ptr(field)), static_cast<uint32_t>(field.size(0)),
+                           static_cast<int>(field.size(1)), st.data(), static_cast<int32_t*>(ptr(voxels)),
+                           current_stream()),
+        "rmn_field_quantize");
+  return insert_and_map(voxels, sparse_tensor_stride, sparse_tensor_string_id);
+}
+
 CoordinateMapKey CoordinateManager::stride(const CoordinateMapKey& in_key, const stride_type& kernel_stride,
                                            std::string string_id) {
   auto const& in_map = find(in_key);
@@ -477,6 +521,104 @@ SparseTensor::SparseTensor(at::Tensor features, CoordinateMapKey coordinate_map_
 at::Tensor SparseTensor::C() const {
   if (!coordinates_.has_value()) coordinates_ = manager_->get_coordinates(key_);
   return coordinates_.value();
+}
+
+// ---------------------------------------------------------------------------------------------
+// TensorField (engine/tensor/field.cpp:9-142) and the discretisation helpers
+// (engine/helpers/discretization.cpp:78-141)
+// ---------------------------------------------------------------------------------------------
+TensorField::TensorField(at::Tensor features, at::Tensor coordinates, std::shared_ptr<CoordinateManager> manager,
+                         SparseTensorQuantizationMode::Type)
+    : features_(std::move(features)), field_key_(static_cast<size_type>(coordinates.dim() == 2 ? coordinates.size(1) : 0)),
+      dimension_(0) {
+  TORCH_CHECK(features_.dim() == 2, "Features must be a 2D tensor");
+  TORCH_CHECK(coordinates.dim() == 2, "Coordinates must be a 2D tensor");
+  TORCH_CHECK(features_.size(0) == coordinates.size(0), "Features and coordinates must have same number of rows");
+  TORCH_CHECK(coordinates.scalar_type() == at::kFloat || coordinates.scalar_type() == at::kDouble,
+              "TensorField coordinates must be float or double");
+  TORCH_CHECK(coordinates.size(1) >= 2, "Coordinates must contain a batch column and spatial columns");
+  dimension_ = static_cast<int>(coordinates.size(1) - 1);
+  if (!manager) manager = std::make_shared<CoordinateManager>(dimension_, CoordinateMapBackend::CUDA);
+  TORCH_CHECK(manager->D() == dimension_, "Coordinate manager dimension does not match coordinates");
+  manager_ = std::move(manager);
+  coordinates_ = coordinates.contiguous();
+  field_key_ = manager_->insert_field(coordinates_, stride_type(static_cast<size_t>(dimension_), 1));
+}
+
+SparseTensor TensorField::sparse(stride_type tensor_stride, c10::optional<CoordinateMapKey>,
+                                 SparseTensorQuantizationMode::Type quantization_mode) const {
+  if (tensor_stride.empty()) tensor_stride.assign(static_cast<size_t>(dimension_), 1);
+  auto inserted = manager_->field_to_sparse_insert_and_map(field_key_, tensor_stride);
+  auto const& sparse_key = inserted.first;
+  auto quantized = quantize_features(features_, inserted.second.first, inserted.second.second,
+                                     manager_->size(sparse_key), quantization_mode);
+  inverse_mappings_[sparse_key.get_key()] = inserted.second.second;
+  return SparseTensor(std::move(quantized), sparse_key, manager_);
+}
+
+SparseTensor TensorField::splat() const {
+  c10::cuda::CUDAGuard guard(coordinates_.device());
+  TORCH_CHECK(coordinates_.scalar_type() == at::kFloat, "field coordinates must be float32");
+  auto feats = features_.contiguous();
+  const int64_t n = coordinates_.size(0), W = coordinates_.size(1), C = feats.size(1);
+  const int64_t rows = n << (W - 1);
+  auto out_c = at::empty({rows, W}, coordinates_.options().dtype(at::kInt));
+  auto out_f = at::empty({rows, C}, feats.options());
+  check(rmn_field_splat(static_cast<const float*>(ptr(coordinates_)), ptr(feats), dtype_code(feats),
+                        static_cast<uint32_t>(n), static_cast<int>(W), static_cast<int>(C),
+                        static_cast<int32_t*>(ptr(out_c)), ptr(out_f), current_stream()),
+        "rmn_field_splat");
+  return SparseTensor(std::move(out_f), std::move(out_c), manager_, SparseTensorQuantizationMode::UNWEIGHTED_SUM);
+}
+
+at::Tensor TensorField::inverse_mapping(const CoordinateMapKey& sparse_key) const {
+  auto it = inverse_mappings_.find(sparse_key.get_key());
+  if (it != inverse_mappings_.end()) return it->second;
+  auto inserted = manager_->field_to_sparse_insert_and_map(field_key_, sparse_key.get_tensor_stride());
+  inverse_mappings_[sparse_key.get_key()] = inserted.second.second;
+  return inserted.second.second;
+}
+
+std::pair<at::Tensor, at::Tensor> unique_coordinate_map(at::Tensor coordinates, stride_type tensor_stride) {
+  TORCH_CHECK(coordinates.dim() == 2 && coordinates.size(1) >= 2,
+              "Coordinates must include a batch column and spatial dimensions");
+  const auto dimension = static_cast<size_t>(coordinates.size(1) - 1);
+  if (tensor_stride.empty()) tensor_stride.assign(dimension, 1);
+  TORCH_CHECK(tensor_stride.size() == dimension, "Tensor stride dimension must match coordinates");
+  auto manager = std::make_shared<CoordinateManager>(static_cast<int>(dimension), CoordinateMapBackend::CUDA);
+  return manager->insert_and_map(coordinates.contiguous(), tensor_stride).second;
+}
+
+SparseQuantizeResult sparse_quantize(at::Tensor coordinates, c10::optional<at::Tensor> features,
+                                     c10::optional<at::Tensor> labels, int, c10::optional<double> quantization_size) {
+  TORCH_CHECK(coordinates.dim() == 2, "Coordinates must be a 2D matrix");
+  TORCH_CHECK(!features.has_value() || (features->dim() == 2 && features->size(0) == coordinates.size(0)),
+              "Feature rows must match coordinate rows");
+  // the reference coalesces labels in a CPU-only loop (engine/helpers/discretization.cpp:31-76)
+  TORCH_CHECK(!labels.has_value(), "Label quantization currently requires CPU tensors");
+  if (quantization_size.has_value())
+    TORCH_CHECK(*quantization_size > 0.0 && std::isfinite(*quantization_size),
+                "Quantization size must be positive and finite");
+  TORCH_CHECK(coordinates.is_cuda(), "coordinates must be a CUDA tensor: this library has no CPU path");
+  int in_type = coordinates.scalar_type() == at::kFloat ? 0 : coordinates.scalar_type() == at::kDouble ? 1
+                : coordinates.scalar_type() == at::kInt ? 2 : -1;
+  if (in_type < 0) {
+    coordinates = coordinates.to(at::kDouble);
+    in_type = 1;
+  }
+  coordinates = coordinates.contiguous();
+  c10::cuda::CUDAGuard guard(coordinates.device());
+  auto discrete = at::empty(coordinates.sizes(), coordinates.options().dtype(at::kInt));
+  check(rmn_coords_discretize(ptr(coordinates), in_type, static_cast<uint64_t>(coordinates.numel()),
+                              quantization_size.value_or(0.0), static_cast<int32_t*>(ptr(discrete)), current_stream()),
+        "rmn_coords_discretize");
+  auto maps = unique_coordinate_map(discrete);
+  SparseQuantizeResult result;
+  result.unique_index = maps.first;
+  result.inverse_mapping = maps.second;
+  result.coordinates = discrete.index_select(0, maps.first);
+  if (features.has_value()) result.features = features->to(discrete.device()).index_select(0, maps.first);
+  return result;
 }
 
 SparseTensor SparseTensor::to(c10::ScalarType dtype) const { return SparseTensor(features_.to(dtype), key_, manager_); }

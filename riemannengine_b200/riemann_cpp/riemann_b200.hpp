@@ -139,6 +139,15 @@ public:
                                  RegionType::Type region_type = RegionType::HYPER_CUBE,
                                  const at::Tensor& offsets = at::Tensor());
 
+  // Continuous coordinates (float32 [N, 1 + D]) under a field key (engine/grid/space_impl.hpp:36-80), and their
+  // voxelisation at a tensor stride into a new sparse map: (sparse key, (first rows, field row -> sparse row))
+  // (engine/grid/space_impl.hpp:103-166).
+  CoordinateMapKey insert_field(const at::Tensor& coordinates, stride_type tensor_stride, std::string string_id = "");
+  std::pair<CoordinateMapKey, std::pair<at::Tensor, at::Tensor>>
+  field_to_sparse_insert_and_map(const CoordinateMapKey& field_key, stride_type sparse_tensor_stride,
+                                 std::string sparse_tensor_string_id = "");
+  at::Tensor get_field_coordinates(const CoordinateMapKey& field_key) const;
+
   at::Tensor get_coordinates(const CoordinateMapKey& key) const;
   uint32_t size(const CoordinateMapKey& key) const;
   bool exists(const CoordinateMapKey& key) const;
@@ -171,6 +180,7 @@ private:
   CoordinateMapBackend::Type map_type_;
   std::map<coordinate_map_key_type, Map> maps_;
   std::map<std::string, std::shared_ptr<KernelMap>> kernel_maps_;
+  std::map<coordinate_map_key_type, at::Tensor> fields_;
 };
 
 class SparseTensor {
@@ -200,6 +210,46 @@ private:
   std::shared_ptr<CoordinateManager> manager_;
   int dimension_;
 };
+
+// Features on continuous coordinates (engine/tensor/field.hpp:10-53).
+class TensorField {
+public:
+  TensorField(at::Tensor features, at::Tensor coordinates, std::shared_ptr<CoordinateManager> manager = nullptr,
+              SparseTensorQuantizationMode::Type quantization_mode = SparseTensorQuantizationMode::UNWEIGHTED_AVERAGE);
+  SparseTensor sparse(stride_type tensor_stride = {}, c10::optional<CoordinateMapKey> coordinate_map_key = c10::nullopt,
+                      SparseTensorQuantizationMode::Type quantization_mode =
+                          SparseTensorQuantizationMode::UNWEIGHTED_AVERAGE) const;
+  SparseTensor splat() const;
+  at::Tensor inverse_mapping(const CoordinateMapKey& sparse_key) const;
+
+  const at::Tensor& F() const noexcept { return features_; }
+  at::Tensor C() const { return coordinates_; }
+  const CoordinateMapKey& coordinate_field_map_key() const noexcept { return field_key_; }
+  std::shared_ptr<CoordinateManager> coordinate_manager() const noexcept { return manager_; }
+  int dimension() const noexcept { return dimension_; }
+  torch::Device device() const { return features_.device(); }
+  c10::ScalarType dtype() const { return features_.scalar_type(); }
+
+private:
+  at::Tensor features_, coordinates_;
+  CoordinateMapKey field_key_;
+  std::shared_ptr<CoordinateManager> manager_;
+  int dimension_;
+  mutable std::map<coordinate_map_key_type, at::Tensor> inverse_mappings_;
+};
+
+// helpers/discretization.hpp:15-34
+struct SparseQuantizeResult {
+  at::Tensor coordinates;
+  c10::optional<at::Tensor> features;
+  c10::optional<at::Tensor> labels;
+  at::Tensor unique_index;
+  at::Tensor inverse_mapping;
+};
+SparseQuantizeResult sparse_quantize(at::Tensor coordinates, c10::optional<at::Tensor> features = c10::nullopt,
+                                     c10::optional<at::Tensor> labels = c10::nullopt, int ignore_label = -100,
+                                     c10::optional<double> quantization_size = c10::nullopt);
+std::pair<at::Tensor, at::Tensor> unique_coordinate_map(at::Tensor coordinates, stride_type tensor_stride = {});
 
 class KernelGenerator {
 public:

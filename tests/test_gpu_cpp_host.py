@@ -151,3 +151,29 @@ def test_cpp_pooling_transpose_matches_reference_golden(C, name):
     ((y.F * y.F).sum() * 0.5).backward()
     parity.check_pool_against_reference(y.C.cpu().numpy(), y.F.detach().cpu().numpy(), f.grad.cpu().numpy(), gold,
                                         tol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["field_d3_s1_avg", "field_d3_s2_sum", "field_d2_s42_max", "field_d3_s123_first",
+                                  "field_d4_s1_avg"])
+def test_cpp_tensor_field_matches_reference_fixture(C, name):
+    """TensorField.sparse / splat / inverse_mapping and sparse_quantize of the C++ host against fixtures the
+    reference produced (engine/tensor/field.cpp, engine/helpers/discretization.cpp)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", name + ".npz"))
+    stride, mode, q = g["stride"].tolist(), int(g["spec"][1]), float(g["qsize"][0])
+    field = torch.from_numpy(g["field"]).cuda()
+    feats = torch.from_numpy(g["feats"]).cuda()
+    tf = C.TensorField(feats, field)
+    sp = tf.sparse(stride, None, C.SparseTensorQuantizationMode(mode))
+    assert list(sp.tensor_stride) == stride
+    assert np.array_equal(sp.C.cpu().numpy(), g["ref_field_coords"])
+    assert np.array_equal(tf.inverse_mapping(sp.coordinate_map_key).cpu().numpy(), g["ref_field_inverse"])
+    assert np.abs(sp.F.cpu().numpy() - g["ref_field_feats"]).max() <= 1e-5 * max(1.0, np.abs(g["ref_field_feats"]).max())
+    spl = C.TensorField(feats, field).splat()
+    assert np.array_equal(spl.C.cpu().numpy(), g["ref_splat_coords"])
+    assert np.abs(spl.F.cpu().numpy() - g["ref_splat_feats"]).max() <= 1e-5
+    coords, fq, unique, inverse = C.sparse_quantize(field, feats, q if q > 0 else None)
+    assert np.array_equal(coords.cpu().numpy(), g["ref_sq_coords"])
+    assert np.array_equal(fq.cpu().numpy(), g["ref_sq_feats"])
+    assert np.array_equal(unique.cpu().numpy(), g["ref_sq_unique_index"])
+    assert np.array_equal(inverse.cpu().numpy(), g["ref_sq_inverse"])
