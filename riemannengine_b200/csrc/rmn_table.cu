@@ -588,9 +588,23 @@ extern "C" int rmn_table_build_static(const int32_t* d_coords, uint32_t n_rows, 
 extern "C" int rmn_table_info(const void* d_table, uint32_t info[4], void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (!d_table || !info) return RMN_ERR_BAD_ARG;
-  TableHeader h;
-  RMN_CUDA_TRY(cudaMemcpyAsync(&h, d_table, sizeof(TableHeader), cudaMemcpyDeviceToHost, stream));
+  // The header is read back through a page-locked staging block owned by the calling thread: a copy into
+  // pageable memory is staged by the driver and costs several microseconds more, and this read-back is the
+  // one host synchronisation of a table build.
+  thread_local TableHeader* staging = nullptr;
+  if (!staging) {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, sizeof(TableHeader), cudaHostAllocPortable) != cudaSuccess) {
+      cudaGetLastError();
+      p = nullptr;
+    }
+    staging = static_cast<TableHeader*>(p);
+  }
+  TableHeader pageable;
+  TableHeader* dst = staging ? staging : &pageable;
+  RMN_CUDA_TRY(cudaMemcpyAsync(dst, d_table, sizeof(TableHeader), cudaMemcpyDeviceToHost, stream));
   RMN_CUDA_TRY(cudaStreamSynchronize(stream));
+  const TableHeader h = *dst;
   if (h.magic != kTableMagic) return RMN_ERR_BAD_ARG;
   info[0] = h.n_unique;
   info[1] = h.status;

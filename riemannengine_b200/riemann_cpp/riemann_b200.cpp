@@ -7,6 +7,9 @@
 
 #include <cmath>
 #include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
 #include <stdexcept>
 
 #include "rmn_b200.h"
@@ -160,6 +163,26 @@ std::shared_ptr<KernelMap> KernelMap::swapped(std::shared_ptr<KernelMap> const& 
 // ---------------------------------------------------------------------------------------------
 // CoordinateManager
 // ---------------------------------------------------------------------------------------------
+namespace {
+// Device copy of a region's offsets, cached per device: networks build a fresh manager per forward pass
+// and ask for the same few regions every time, and a copy from pageable host memory blocks the host while
+// the GPU waits for its next launch.
+at::Tensor device_offsets(const std::vector<int32_t>& off, const c10::Device& device) {
+  static std::mutex lock;
+  static std::map<std::pair<int, std::vector<int32_t>>, at::Tensor> cache;
+  std::lock_guard<std::mutex> guard(lock);
+  auto key = std::make_pair(static_cast<int>(device.index()), off);
+  auto it = cache.find(key);
+  if (it != cache.end()) return it->second;
+  if (cache.size() > 256) cache.clear();
+  auto host = at::empty({static_cast<int64_t>(off.size())}, at::TensorOptions().dtype(at::kInt));
+  if (!off.empty()) std::memcpy(host.data_ptr(), off.data(), off.size() * sizeof(int32_t));
+  auto dev = host.to(device);
+  cache[key] = dev;
+  return dev;
+}
+}  // namespace
+
 CoordinateManager::CoordinateManager(int D, CoordinateMapBackend::Type map_type, GPUMemoryAllocatorBackend::Type,
                                      RiemannAlgorithm::Mode)
     : D_(D), map_type_(map_type) {
@@ -340,7 +363,7 @@ CoordinateMapKey CoordinateManager::stride_region(const CoordinateMapKey& in_key
                                     custom.empty() ? nullptr : custom.data(), n_custom, off.data());
   if (K2 < 0) check(-K2, "rmn_region_offsets");
   c10::cuda::CUDAGuard guard(in_map.coords.device());
-  auto d_off = at::from_blob(off.data(), {static_cast<int64_t>(off.size())}, at::kInt).to(in_map.coords.device());
+  auto d_off = device_offsets(off, in_map.coords.device());
   auto generated = at::empty({static_cast<int64_t>(in_map.size) * K, in_map.coords.size(1)}, in_map.coords.options());
   check(rmn_coords_expand(static_cast<const int32_t*>(ptr(in_map.coords)), in_map.size,
                           static_cast<int>(in_map.coords.size(1)), static_cast<const int32_t*>(ptr(d_off)), K,
@@ -409,7 +432,7 @@ std::shared_ptr<KernelMap> CoordinateManager::kernel_map(const CoordinateMapKey&
 
     c10::cuda::CUDAGuard guard(in_map.coords.device());
     auto ints = in_map.coords.options();
-    auto d_off = at::from_blob(off.data(), {static_cast<int64_t>(off.size())}, at::kInt).to(in_map.coords.device());
+    auto d_off = device_offsets(off, in_map.coords.device());
     result = std::make_shared<KernelMap>();
     result->n_in = in_map.size;
     result->n_out = out_map.size;
