@@ -9,6 +9,7 @@ Every coordinate and convolution operation runs in the CUDA library through
 """
 from __future__ import annotations
 
+import builtins
 import math
 import random
 import string
@@ -528,6 +529,54 @@ class SparseTensor:
     def detach(self) -> "SparseTensor":
         return SparseTensor(self._features.detach(), self._key, self._manager)
 
+    # -- arithmetic (engine/tensor/sparse_tensor.cpp:31-58, 345-395) ---------------------------
+    def _binary(self, other: "SparseTensor", what: str, op) -> "SparseTensor":
+        """Element-wise ``op`` on the union of the two coordinate sets (rows a side lacks count as zero).
+        Tensors on one coordinate map are combined row by row and keep manager and key; otherwise the
+        result lives on a new manager, as in the reference."""
+        if self._dimension != other._dimension:
+            raise RuntimeError(f"Cannot {what} tensors with different dimensions")
+        if self.F.size(1) != other.F.size(1):
+            raise RuntimeError(f"Cannot {what} tensors with different feature channel counts")
+        if self.F.device != other.F.device:
+            raise RuntimeError(f"Cannot {what} tensors on different devices")
+        if self._manager is other._manager and self._key == other._key:
+            return SparseTensor(op(self.F, other.F), coordinate_map_key=self._key, coordinate_manager=self._manager)
+        stride = [min(a, b) for a, b in zip(self.tensor_stride, other.tensor_stride)]
+        manager = CoordinateManager(self._dimension, CoordinateMapBackend.CUDA)
+        key, (_, row_to_union) = manager.insert_and_map(torch.cat([self.C, other.C], 0).contiguous(), stride)
+        size, n_l = manager.size(key), self.F.size(0)
+
+        def align(feats, rows):
+            return torch.zeros((size, feats.size(1)), dtype=feats.dtype, device=feats.device).index_copy(0, rows, feats)
+
+        return SparseTensor(op(align(self.F, row_to_union[:n_l]), align(other.F, row_to_union[n_l:])),
+                            coordinate_map_key=key, coordinate_manager=manager)
+
+    def __add__(self, other):
+        if isinstance(other, SparseTensor):
+            return self._binary(other, "add", torch.add)
+        return SparseTensor(self.F + other, coordinate_map_key=self._key, coordinate_manager=self._manager)
+
+    def __sub__(self, other: "SparseTensor"):
+        return self._binary(other, "subtract", torch.sub)
+
+    def __mul__(self, other):
+        if isinstance(other, SparseTensor):
+            return self._binary(other, "multiply", torch.mul)
+        return SparseTensor(self.F * other, coordinate_map_key=self._key, coordinate_manager=self._manager)
+
+    def __truediv__(self, other: "SparseTensor"):
+        return self._binary(other, "divide", torch.div)
+
+    def __iadd__(self, other: "SparseTensor"):
+        if self._manager is not other._manager:
+            raise RuntimeError("Cannot add tensors from different managers")
+        if self._key != other._key:
+            raise RuntimeError("In-place addition requires same key")
+        self._features += other.F
+        return self
+
     def __repr__(self) -> str:
         return (f"SparseTensor(N={self._features.size(0)}, C={self._features.size(1)}, D={self._dimension}, "
                 f"device={self._features.device})")
@@ -710,7 +759,7 @@ class KernelGenerator:
         if region_type == RegionType.HYPER_CUBE:
             self._volume = int(np.prod(self._ks))
         elif region_type == RegionType.HYPER_CROSS:
-            self._volume = 1 + sum(k - 1 for k in self._ks)
+            self._volume = 1 + builtins.sum(k - 1 for k in self._ks)
         else:
             self._volume = int(self._offsets.size(0))
 
@@ -1085,6 +1134,35 @@ def cat(tensors: Sequence[SparseTensor]) -> SparseTensor:
         if t.coordinate_manager is not first.coordinate_manager or t.coordinate_map_key != first.coordinate_map_key:
             raise RuntimeError("Sparse tensors must share the same coordinate map")
     return SparseTensor(torch.cat([t.F for t in tensors], 1), first.coordinate_map_key, first.coordinate_manager)
+
+
+def sum(tensors: Sequence[SparseTensor]) -> SparseTensor:  # noqa: A001 - the reference's name
+    """Feature sum of tensors on one coordinate map (engine/nn/operations.cpp:66-73)."""
+    out = cat(tensors)
+    first = tensors[0]
+    if any(t.F.size(1) != first.F.size(1) for t in tensors):
+        raise RuntimeError("Sparse tensor feature widths must match")
+    total = first.F
+    for t in tensors[1:]:
+        total = total + t.F
+    return SparseTensor(total, out.coordinate_map_key, out.coordinate_manager)
+
+
+def mean(tensors: Sequence[SparseTensor]) -> SparseTensor:
+    """engine/nn/operations.cpp:75-77"""
+    return sum(tensors) * (1.0 / len(tensors))
+
+
+class RiemannReLU(torch.nn.Module):
+    """ReLU on the features; the coordinate map is shared (engine/nn/activation.hpp:11-29)."""
+
+    def __init__(self, inplace: bool = False):
+        super().__init__()
+        self.inplace = inplace
+
+    def forward(self, input: SparseTensor) -> SparseTensor:
+        out = torch.relu_(input.F) if self.inplace else torch.relu(input.F)
+        return SparseTensor(out, input.coordinate_map_key, input.coordinate_manager)
 
 
 class RiemannPoolingTranspose(torch.nn.Module):

@@ -163,7 +163,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_property_readonly("shape",
                              [](const SparseTensor& self) { return py::make_tuple(self.F().size(0), self.F().size(1)); })
       .def("__len__", [](const SparseTensor& self) { return self.F().size(0); })
-      .def("detach", &SparseTensor::detach);
+      .def("detach", &SparseTensor::detach)
+      .def("__add__", [](const SparseTensor& a, const SparseTensor& b) { return a + b; })
+      .def("__sub__", [](const SparseTensor& a, const SparseTensor& b) { return a - b; })
+      .def("__mul__", [](const SparseTensor& a, const SparseTensor& b) { return a * b; })
+      .def("__truediv__", [](const SparseTensor& a, const SparseTensor& b) { return a / b; })
+      .def("__add__", [](const SparseTensor& a, double s) { return a + at::Scalar(s); })
+      .def("__mul__", [](const SparseTensor& a, double s) { return a * at::Scalar(s); });
+  m.def("cat", &cat, py::arg("tensors"));
+  m.def("sum", &sum, py::arg("tensors"));
+  m.def("mean", &mean, py::arg("tensors"));
+  py::class_<RiemannReLUImpl, std::shared_ptr<RiemannReLUImpl>>(m, "RiemannReLU")
+      .def(py::init<bool>(), py::arg("inplace") = false)
+      .def("forward", &RiemannReLUImpl::forward, py::arg("input"))
+      .def("__call__", &RiemannReLUImpl::forward, py::arg("input"));
 
   // python/src/sparse_bindings.cpp:204-233
   py::class_<TensorField>(m, "TensorField")

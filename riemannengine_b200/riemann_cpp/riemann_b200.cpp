@@ -5,6 +5,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -642,6 +643,101 @@ SparseQuantizeResult sparse_quantize(at::Tensor coordinates, c10::optional<at::T
   result.coordinates = discrete.index_select(0, maps.first);
   if (features.has_value()) result.features = features->to(discrete.device()).index_select(0, maps.first);
   return result;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Arithmetic between sparse tensors and the same-map helpers
+// ---------------------------------------------------------------------------------------------
+namespace {
+template <typename Operation>
+SparseTensor union_binary_operation(const SparseTensor& lhs, const SparseTensor& rhs, const char* what,
+                                    Operation operation) {
+  TORCH_CHECK(lhs.dimension() == rhs.dimension(), "Cannot ", what, " tensors with different dimensions");
+  TORCH_CHECK(lhs.F().size(1) == rhs.F().size(1), "Cannot ", what,
+              " tensors with different feature channel counts");
+  TORCH_CHECK(lhs.F().device() == rhs.F().device(), "Cannot ", what, " tensors on different devices");
+  if (lhs.coordinate_manager() == rhs.coordinate_manager() && lhs.coordinate_map_key() == rhs.coordinate_map_key())
+    return SparseTensor(operation(lhs.F(), rhs.F()), lhs.coordinate_map_key(), lhs.coordinate_manager());
+  auto output_stride = lhs.tensor_stride();
+  const auto other_stride = rhs.tensor_stride();
+  for (size_t axis = 0; axis < output_stride.size(); ++axis)
+    output_stride[axis] = std::min(output_stride[axis], other_stride[axis]);
+  auto manager = std::make_shared<CoordinateManager>(lhs.dimension(), CoordinateMapBackend::CUDA);
+  auto inserted = manager->insert_and_map(at::cat({lhs.C(), rhs.C()}, 0).contiguous(), std::move(output_stride));
+  const int64_t union_size = manager->size(inserted.first);
+  auto const& row_to_union = inserted.second.second;
+  const int64_t lhs_rows = lhs.F().size(0), rhs_rows = rhs.F().size(0);
+  auto align = [&](const at::Tensor& features, const at::Tensor& rows) {
+    auto result = torch::zeros({union_size, features.size(1)}, features.options());
+    return result.index_copy(0, rows, features);
+  };
+  return SparseTensor(operation(align(lhs.F(), row_to_union.slice(0, 0, lhs_rows)),
+                                align(rhs.F(), row_to_union.slice(0, lhs_rows, lhs_rows + rhs_rows))),
+                      inserted.first, std::move(manager));
+}
+
+void validate_same_map(const std::vector<SparseTensor>& tensors, bool same_channels) {
+  TORCH_CHECK(tensors.size() > 1, "At least two sparse tensors are required");
+  for (size_t i = 1; i < tensors.size(); ++i) {
+    TORCH_CHECK(tensors.front().coordinate_manager() == tensors[i].coordinate_manager(),
+                "Sparse tensors must share a coordinate manager");
+    TORCH_CHECK(tensors.front().coordinate_map_key() == tensors[i].coordinate_map_key(),
+                "Sparse tensors must share a coordinate map key");
+    TORCH_CHECK(!same_channels || tensors[i].F().size(1) == tensors.front().F().size(1),
+                "Sparse tensor feature widths must match");
+  }
+}
+}  // namespace
+
+SparseTensor SparseTensor::operator+(const SparseTensor& other) const {
+  return union_binary_operation(*this, other, "add", [](const at::Tensor& a, const at::Tensor& b) { return a + b; });
+}
+SparseTensor SparseTensor::operator-(const SparseTensor& other) const {
+  return union_binary_operation(*this, other, "subtract",
+                                [](const at::Tensor& a, const at::Tensor& b) { return a - b; });
+}
+SparseTensor SparseTensor::operator*(const SparseTensor& other) const {
+  return union_binary_operation(*this, other, "multiply",
+                                [](const at::Tensor& a, const at::Tensor& b) { return a * b; });
+}
+SparseTensor SparseTensor::operator/(const SparseTensor& other) const {
+  return union_binary_operation(*this, other, "divide", [](const at::Tensor& a, const at::Tensor& b) { return a / b; });
+}
+SparseTensor& SparseTensor::operator+=(const SparseTensor& other) {
+  TORCH_CHECK(manager_ == other.manager_, "Cannot add tensors from different managers");
+  TORCH_CHECK(key_ == other.key_, "In-place addition requires same key");
+  features_ += other.features_;
+  return *this;
+}
+SparseTensor SparseTensor::operator+(at::Scalar scalar) const { return SparseTensor(features_ + scalar, key_, manager_); }
+SparseTensor SparseTensor::operator*(at::Scalar scalar) const { return SparseTensor(features_ * scalar, key_, manager_); }
+
+SparseTensor cat(const std::vector<SparseTensor>& tensors) {
+  validate_same_map(tensors, false);
+  std::vector<at::Tensor> features;
+  for (auto const& t : tensors) features.push_back(t.F());
+  return SparseTensor(torch::cat(features, 1), tensors.front().coordinate_map_key(),
+                      tensors.front().coordinate_manager());
+}
+
+SparseTensor sum(const std::vector<SparseTensor>& tensors) {
+  validate_same_map(tensors, true);
+  auto output = tensors.front().F();
+  for (size_t i = 1; i < tensors.size(); ++i) output = output + tensors[i].F();
+  return SparseTensor(std::move(output), tensors.front().coordinate_map_key(), tensors.front().coordinate_manager());
+}
+
+SparseTensor mean(const std::vector<SparseTensor>& tensors) {
+  return sum(tensors) * (1.0 / static_cast<double>(tensors.size()));
+}
+
+SparseTensor RiemannReLUImpl::forward(const SparseTensor& input) {
+  auto output = input.F();
+  if (inplace_)
+    at::relu_(output);
+  else
+    output = at::relu(output);
+  return SparseTensor(std::move(output), input.coordinate_map_key(), input.coordinate_manager());
 }
 
 SparseTensor SparseTensor::to(c10::ScalarType dtype) const { return SparseTensor(features_.to(dtype), key_, manager_); }

@@ -203,6 +203,18 @@ public:
   SparseTensor to(c10::ScalarType dtype) const;
   SparseTensor detach() const;
 
+  // Element-wise arithmetic on the union of the two coordinate sets, rows a side lacks counting as zero
+  // (engine/tensor/sparse_tensor.cpp:31-58, 345-395). Tensors that share manager and key (residual
+  // connections) are combined row by row on that map and keep it, so cached kernel maps stay usable;
+  // otherwise the result lives on a new manager, as in the reference.
+  SparseTensor operator+(const SparseTensor& other) const;
+  SparseTensor operator-(const SparseTensor& other) const;
+  SparseTensor operator*(const SparseTensor& other) const;
+  SparseTensor operator/(const SparseTensor& other) const;
+  SparseTensor& operator+=(const SparseTensor& other);
+  SparseTensor operator+(at::Scalar scalar) const;
+  SparseTensor operator*(at::Scalar scalar) const;
+
 private:
   at::Tensor features_;
   mutable c10::optional<at::Tensor> coordinates_;
@@ -250,6 +262,23 @@ SparseQuantizeResult sparse_quantize(at::Tensor coordinates, c10::optional<at::T
                                      c10::optional<at::Tensor> labels = c10::nullopt, int ignore_label = -100,
                                      c10::optional<double> quantization_size = c10::nullopt);
 std::pair<at::Tensor, at::Tensor> unique_coordinate_map(at::Tensor coordinates, stride_type tensor_stride = {});
+
+// engine/nn/operations.hpp:10-12: tensors of one coordinate map, concatenated along channels / summed / averaged
+SparseTensor cat(const std::vector<SparseTensor>& tensors);
+SparseTensor sum(const std::vector<SparseTensor>& tensors);
+SparseTensor mean(const std::vector<SparseTensor>& tensors);
+
+// engine/nn/activation.hpp:11-29
+class RiemannReLUImpl : public torch::nn::Module {
+public:
+  explicit RiemannReLUImpl(bool inplace = false) : inplace_(inplace) {}
+  explicit RiemannReLUImpl(torch::nn::ReLUOptions options) : inplace_(options.inplace()) {}
+  SparseTensor forward(const SparseTensor& input);
+
+private:
+  bool inplace_;
+};
+TORCH_MODULE(RiemannReLU);
 
 class KernelGenerator {
 public:

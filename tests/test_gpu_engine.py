@@ -219,3 +219,51 @@ def test_union_map_and_stride_region():
         kr = m.stride_region(ka, [2, 2, 2], [1, 1, 1], [1, 1, 1])
         cr = m.get_coordinates(kr).cpu().numpy()
         assert len(cr) == len(want_region) and {tuple(r) for r in cr.tolist()} == want_region
+
+
+def _two_clouds(seed=5, n=600, c=4):
+    rng = np.random.default_rng(seed)
+    a = np.concatenate([rng.integers(0, 2, (n, 1)), rng.integers(-5, 6, (n, 3))], 1).astype(np.int32)
+    b = np.concatenate([rng.integers(0, 2, (n, 1)), rng.integers(-5, 6, (n, 3))], 1).astype(np.int32)
+    return a, b, rng.standard_normal((n, c)).astype(np.float32), rng.standard_normal((n, c)).astype(np.float32)
+
+
+@pytest.mark.parametrize("host", ["py", "cpp"])
+def test_sparse_tensor_arithmetic_on_the_union(host):
+    """x + y, x - y, x * y on different coordinate sets: coordinates are the first occurrences of
+    cat(x.C, y.C), rows a side lacks count as zero (engine/tensor/sparse_tensor.cpp:31-58, 345-379)."""
+    from oracle import oracle as O
+    if host == "py":
+        from riemannengine_b200 import engine as H
+    else:
+        from riemannengine_b200 import cpp
+        H = cpp.load()
+    ca, cb, fa, fb = _two_clouds()
+    x = H.SparseTensor(torch.from_numpy(fa).cuda(), torch.from_numpy(ca).cuda())
+    y = H.SparseTensor(torch.from_numpy(fb).cuda(), torch.from_numpy(cb).cuda())
+    ma, _ = O.insert_and_map(ca)
+    mb, _ = O.insert_and_map(cb)
+    ua, ub = ca[ma], cb[mb]
+    mu, inv = O.insert_and_map(np.concatenate([ua, ub], 0))
+    want_c = np.concatenate([ua, ub], 0)[mu]
+    la = np.zeros((len(mu), fa.shape[1]), np.float32)
+    lb = np.zeros_like(la)
+    la[inv[:len(ua)]] = fa[ma]
+    lb[inv[len(ua):]] = fb[mb]
+    for got, want in ((x + y, la + lb), (x - y, la - lb), (x * y, la * lb)):
+        assert np.array_equal(got.C.cpu().numpy(), want_c)
+        assert np.allclose(got.F.cpu().numpy(), want, rtol=0, atol=1e-6)
+    # same map: row by row on that map, manager and key kept (residual connection)
+    z = x + x
+    assert z.coordinate_map_key == x.coordinate_map_key
+    assert np.allclose(z.F.cpu().numpy(), 2 * fa[ma])
+    s = x * 0.5
+    assert np.allclose(s.F.cpu().numpy(), 0.5 * fa[ma])
+    relu = H.RiemannReLU()
+    assert np.array_equal(relu(x).F.cpu().numpy(), np.maximum(fa[ma], 0))
+    both = H.cat([x, z])
+    assert both.F.shape[1] == 2 * fa.shape[1] and both.coordinate_map_key == x.coordinate_map_key
+    assert np.allclose(H.sum([x, z]).F.cpu().numpy(), 3 * fa[ma])
+    assert np.allclose(H.mean([x, z]).F.cpu().numpy(), 1.5 * fa[ma])
+    with pytest.raises(RuntimeError):
+        H.cat([x, y])
