@@ -16,6 +16,8 @@
 // offset (engine/grid/lattice_gpu.cuh:440-488).
 #include "rmn_common.cuh"
 
+#include <mutex>
+
 namespace rmn {
 
 constexpr int kKmapBlock = 256;
@@ -254,7 +256,7 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_pairs(
   const int mirror_half = (int)overflow[1];
   const int K_full = K;
   K -= mirror_half;
-  for (int k = warp; k < K; k += kKmapBlock / 32) {
+  for (int k = warp; k < K; k += (int)(blockDim.x >> 5)) {
     const unsigned long long base = (unsigned long long)offset_ptr[k];
     unsigned long long pos = base + block_prefix[(size_t)k * n_blocks + blockIdx.x];
     const bool mirror = k < mirror_half;
@@ -449,7 +451,22 @@ extern "C" int rmn_kmap_pairs(const int32_t* d_nbr, uint32_t n_query, int K,
   const uint32_t* block_prefix = reinterpret_cast<const uint32_t*>(d_workspace);
   // the word after the totals flags a capacity overflow (kept for debugging reads)
   uint32_t* overflow = const_cast<uint32_t*>(block_prefix) + (size_t)K * nb + K;
-  k_kmap_pairs<<<nb, kKmapBlock, 0, stream>>>(d_nbr, n_query, K, d_offset_ptr, block_prefix, nb,
+  // 128 threads (four warps sharing the offsets of a 256-row block): small enough in registers to run
+  // beside a resident convolution CTA when the caller puts this launch on a second stream. An SM holds
+  // one shared-memory / L1 split at a time, so the kernel also asks for the split the convolution
+  // kernels run with (all shared memory); with the default split its blocks would wait for those CTAs
+  // to leave. It streams its data and does not miss the L1.
+  {
+    static std::once_flag once[64];
+    int dev = 0;
+    RMN_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64)
+      std::call_once(once[dev], [] {
+        cudaFuncSetAttribute(k_kmap_pairs, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             (int)cudaSharedmemCarveoutMaxShared);
+      });
+  }
+  k_kmap_pairs<<<nb, 128, 0, stream>>>(d_nbr, n_query, K, d_offset_ptr, block_prefix, nb,
                                               d_a_idx, d_q_idx, capacity, overflow);
   RMN_LAUNCH_CHECK();
   return RMN_OK;

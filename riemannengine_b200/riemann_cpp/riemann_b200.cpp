@@ -2,6 +2,7 @@
 // autograd, the C ABI of librmn_b200.so for every coordinate / convolution operation.
 #include "riemann_b200.hpp"
 
+#include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
 
@@ -122,6 +123,19 @@ at::Tensor const& KernelMap::nbr_in() {
   return nbr_in_;
 }
 
+namespace {
+// One second stream per device for the pair-list kernels: the caching allocator keeps a pool per stream, so
+// a stream picked afresh from torch's round-robin pool on every call would allocate the lists anew each time.
+c10::cuda::CUDAStream pair_list_stream(c10::DeviceIndex device) {
+  static std::mutex lock;
+  static std::map<int, c10::cuda::CUDAStream> streams;
+  std::lock_guard<std::mutex> guard(lock);
+  auto it = streams.find(static_cast<int>(device));
+  if (it == streams.end()) it = streams.emplace(static_cast<int>(device), c10::cuda::getStreamFromPool(false, device)).first;
+  return it->second;
+}
+}  // namespace
+
 std::tuple<at::Tensor, at::Tensor, at::Tensor> const& KernelMap::pairs() {
   if (have_pairs_) return pairs_;
   if (parent) {  // in <-> out of the parent's lists (engine/grid/space.cpp:104-107)
@@ -138,13 +152,37 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> const& KernelMap::pairs() {
     }
     const int64_t K = nbr_out.size(0);
     const int64_t total = host_ptr[K].item<int64_t>();
-    auto in_idx = at::empty({total}, nbr_out.options());
-    auto out_idx = at::empty({total}, nbr_out.options());
-    check(rmn_kmap_pairs(static_cast<const int32_t*>(ptr(nbr_out)), static_cast<uint32_t>(n_out),
-                         static_cast<int>(K), static_cast<const int64_t*>(ptr(offset_ptr)), ptr(workspace),
-                         static_cast<int32_t*>(ptr(in_idx)), static_cast<int32_t*>(ptr(out_idx)),
-                         static_cast<uint64_t>(total), current_stream()),
-          "rmn_kmap_pairs");
+    // The lists are written on a second stream: nothing a convolution needs depends on them, and the
+    // compaction is bound by HBM while the convolution kernels are bound by shared memory and the tensor
+    // pipe, so a convolution already queued on the caller's stream and this kernel share the SMs. The
+    // caller's stream waits for the lists before anything queued after this call.
+    auto main_stream = c10::cuda::getCurrentCUDAStream();
+    auto side_stream = pair_list_stream(main_stream.device_index());
+    at::Tensor in_idx, out_idx;
+    {
+      c10::cuda::CUDAStreamGuard on_side(side_stream);
+      in_idx = at::empty({total}, nbr_out.options());   // from the second stream's pool: memory freed on the
+      out_idx = at::empty({total}, nbr_out.options());  // caller's stream may still be in use by queued kernels
+      if (offset_ptr_ready.has_value()) {
+        offset_ptr_ready->block(side_stream);
+      } else {
+        c10::Event built(c10::DeviceType::CUDA);
+        built.record(main_stream);
+        built.block(side_stream);
+      }
+      check(rmn_kmap_pairs(static_cast<const int32_t*>(ptr(nbr_out)), static_cast<uint32_t>(n_out),
+                           static_cast<int>(K), static_cast<const int64_t*>(ptr(offset_ptr)), ptr(workspace),
+                           static_cast<int32_t*>(ptr(in_idx)), static_cast<int32_t*>(ptr(out_idx)),
+                           static_cast<uint64_t>(total), side_stream.stream()),
+            "rmn_kmap_pairs");
+      c10::Event done(c10::DeviceType::CUDA);
+      done.record(side_stream);
+      done.block(main_stream);
+    }
+    if (total > 0) {
+      c10::cuda::CUDACachingAllocator::recordStream(in_idx.storage().data_ptr(), main_stream);
+      c10::cuda::CUDACachingAllocator::recordStream(out_idx.storage().data_ptr(), main_stream);
+    }
     pairs_ = std::make_tuple(host_ptr, in_idx, out_idx);
   }
   have_pairs_ = true;
