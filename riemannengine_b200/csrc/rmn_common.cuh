@@ -39,8 +39,13 @@ struct __align__(16) TableHeader {
   int32_t mx[RMN_MAX_W];
   uint32_t bits[RMN_MAX_W];
   uint32_t shift[RMN_MAX_W];
-  uint32_t range_blocks_done;  // ticket counter of the range kernel (its last block plans the packing)
-  uint32_t pad[23];
+  uint32_t range_blocks_done;  // ticket counter of the fill + range kernel (its last block plans the packing)
+  uint32_t count_blocks_done;  // ticket counter of the first-occurrence count (its last block scans the counts)
+  // Column bounds while they are being reduced, encoded so that an all-zero header means "no row yet" and
+  // both are running maxima: mx_enc = max(v ^ 0x80000000), mn_enc = max(~(v ^ 0x80000000)).
+  uint32_t mn_enc[RMN_MAX_W];
+  uint32_t mx_enc[RMN_MAX_W];
+  uint32_t pad[6];
 };
 static_assert(sizeof(TableHeader) == 256, "header must be 256 bytes");
 

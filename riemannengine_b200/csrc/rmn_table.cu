@@ -2,12 +2,12 @@
 // stride alignment. Integer work bound by HBM/L2 bandwidth.
 //
 // Build pipeline (all on the caller's stream, no host synchronisation):
-//   header_init -> range (column min/max) -> plan (bit packing) -> memset slots
-//   -> insert (CAS on the packed key, atomicMin on the first row)
-//   -> count (rows that are the first occurrence, per 256-row block)
-//   -> scan (one block, exclusive scan of the block counts)
-//   -> finalize (unique ids, mapping, unique coordinates)
-//   -> inverse
+//   256-byte memset of the header
+//   -> fill + range (slots to the empty pattern, column min/max; the last block plans the bit packing)
+//   -> insert (one 16-byte CAS on the packed key, atomicMin on the first row)
+//   -> count (rows that are the first occurrence, per 256-row block; the last block scans the counts)
+//   -> finalize (unique ids, mapping, unique coordinates; identity inverse when nothing was a duplicate)
+//   -> inverse (only does work when there were duplicates)
 // Numbering unique rows by first occurrence reproduces the reference CPU map
 // (engine/grid/lattice_cpu.hpp:419-444) deterministically; the reference GPU
 // map lets a CAS race pick the surviving duplicate
@@ -24,36 +24,19 @@ namespace rmn {
 
 constexpr int kRowsPerBlock = 256;
 
-// Fills the slots with the empty pattern (all ones) and initialises the header.
-__global__ void __launch_bounds__(256) k_table_init(TableHeader* h, uint4* __restrict__ slots, uint32_t W,
-                                                    uint32_t n_rows, uint32_t capacity) {
+__device__ void plan_packing(TableHeader* h);
+
+// First kernel of a build, on a header that a 256-byte memset has zeroed: fills the slots with the empty
+// pattern (all ones) and reduces the column bounds of the rows in the same pass (the fill writes, the
+// reduction reads: one launch moves both at HBM speed). The last block to finish writes the header's
+// constants, decodes the bounds and plans the key packing.
+template <int W>
+__global__ void __launch_bounds__(256) k_fill_range(const int32_t* __restrict__ coords, uint32_t n,
+                                                    TableHeader* h, uint4* __restrict__ slots, uint32_t capacity) {
+  __shared__ int32_t s_mn[8][W], s_mx[8][W];
   const uint4 ones = make_uint4(~0u, ~0u, ~0u, ~0u);
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < capacity; i += gridDim.x * blockDim.x)
     slots[i] = ones;
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  h->magic = kTableMagic;
-  h->W = W;
-  h->n_rows = n_rows;
-  h->n_unique = 0;
-  h->status = RMN_OK;
-  h->capacity = capacity;
-  h->total_bits = 0;
-  h->n_dups = 0;
-  h->range_blocks_done = 0;
-  for (int c = 0; c < RMN_MAX_W; ++c) {
-    h->mn[c] = INT_MAX;
-    h->mx[c] = INT_MIN;
-    h->bits[c] = 0;
-    h->shift[c] = 0;
-  }
-}
-
-__device__ void plan_packing(TableHeader* h);
-
-template <int W>
-__global__ void __launch_bounds__(256) k_range(const int32_t* __restrict__ coords, uint32_t n,
-                                               TableHeader* h) {
-  __shared__ int32_t s_mn[8][W], s_mx[8][W];
   int32_t mn[W], mx[W];
 #pragma unroll
   for (int c = 0; c < W; ++c) { mn[c] = INT_MAX; mx[c] = INT_MIN; }
@@ -71,25 +54,33 @@ __global__ void __launch_bounds__(256) k_range(const int32_t* __restrict__ coord
     if (lane == 0) { s_mn[warp][c] = a; s_mx[warp][c] = b; }
   }
   __syncthreads();
-  // one atomic per block and column (per-warp atomics on eight addresses serialise badly)
-  if (threadIdx.x < W) {
+  // one atomic per block and column (per-warp atomics on eight addresses serialise badly); blocks that
+  // saw no row leave the zero ("no row yet") in place
+  if (threadIdx.x < W && blockIdx.x * blockDim.x < n) {
     int32_t a = s_mn[0][threadIdx.x], b = s_mx[0][threadIdx.x];
 #pragma unroll
     for (int w2 = 1; w2 < 8; ++w2) { a = min(a, s_mn[w2][threadIdx.x]); b = max(b, s_mx[w2][threadIdx.x]); }
-    atomicMin(&h->mn[threadIdx.x], a);
-    atomicMax(&h->mx[threadIdx.x], b);
+    atomicMax(&h->mn_enc[threadIdx.x], ~((uint32_t)a ^ 0x80000000u));
+    atomicMax(&h->mx_enc[threadIdx.x], (uint32_t)b ^ 0x80000000u);
   }
-  // the last block to finish plans the key packing (one launch less than a separate kernel)
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0 && atomicAdd(&h->range_blocks_done, 1u) == gridDim.x - 1) {
     __threadfence();
+    h->magic = kTableMagic;
+    h->W = W;
+    h->n_rows = n;
+    h->capacity = capacity;
+    for (int c = 0; c < RMN_MAX_W; ++c) {
+      // volatile: the bounds were written by other blocks' atomics
+      const uint32_t en = *(volatile uint32_t*)&h->mn_enc[c], ex = *(volatile uint32_t*)&h->mx_enc[c];
+      h->mn[c] = (c < W && n > 0) ? (int32_t)(~en ^ 0x80000000u) : 0;
+      h->mx[c] = (c < W && n > 0) ? (int32_t)(ex ^ 0x80000000u) : 0;
+      h->bits[c] = 0;
+      h->shift[c] = 0;
+    }
     plan_packing(h);
   }
-}
-
-__global__ void k_plan(TableHeader* h) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) plan_packing(h);
 }
 
 // One thread: bit widths and shifts of the packed key from the bounding box in the header.
@@ -101,13 +92,9 @@ __device__ void plan_packing(TableHeader* h) {
     const uint32_t c = i + 1 < h->W ? i + 1 : 0;
     uint32_t b = 0;
     if (h->n_rows > 0) {
-      // volatile: the bounds were written by other blocks' atomics
-      uint32_t span = (uint32_t) * (volatile int32_t*)&h->mx[c] - (uint32_t) * (volatile int32_t*)&h->mn[c];
+      const uint32_t span = (uint32_t)h->mx[c] - (uint32_t)h->mn[c];
       b = span == 0 ? 0 : 32 - __clz(span);
-    } else {
-      h->mn[c] = 0;
-      h->mx[c] = 0;  // empty table: every probe ends on a free slot
-    }
+    }  // empty table: bounds are zero and every probe ends on a free slot
     h->bits[c] = b;
     h->shift[c] = total > 63 ? 63 : total;
     total += b;
@@ -169,41 +156,31 @@ __global__ void __launch_bounds__(256) k_insert(const int32_t* __restrict__ coor
   if (!placed) atomicExch(&h->status, (uint32_t)RMN_ERR_PROBE_LIMIT);
 }
 
-__global__ void __launch_bounds__(kRowsPerBlock) k_count_first(const Slot* __restrict__ slots,
-                                                              const uint32_t* __restrict__ slot_of_row,
-                                                              uint32_t n, const TableHeader* h,
-                                                              uint32_t* __restrict__ block_counts) {
-  if (h->n_dups == 0) return;  // no duplicates: nothing to compact (see k_finalize)
-  const uint32_t row = blockIdx.x * kRowsPerBlock + threadIdx.x;
-  int flag = 0;
-  if (row < n && h->status == RMN_OK) flag = slots[slot_of_row[row]].first_row == row;
-  int total = __syncthreads_count(flag);
-  if (threadIdx.x == 0) block_counts[blockIdx.x] = (uint32_t)total;
-}
-
-// One block of 1024 threads: in-place exclusive scan of counts[n]; the total goes to *total_out.
+// In-place exclusive scan of counts[n] by ONE block (any multiple of 32 threads up to 1024); the total goes
+// to *total_out. Reads bypass the L1: the counts may have been written by other blocks of the same launch.
 __device__ __forceinline__ void scan_u32_block(uint32_t* __restrict__ counts, uint32_t n, uint32_t* total_out) {
   __shared__ uint32_t warp_sums[32];
-  const uint32_t per = (n + 1023u) / 1024u;
+  const uint32_t nthreads = blockDim.x, nwarps = nthreads >> 5;
+  const uint32_t per = (n + nthreads - 1u) / nthreads;
   const uint32_t begin = min(n, threadIdx.x * per), end = min(n, begin + per);
   uint32_t sum = 0;
-  for (uint32_t i = begin; i < end; ++i) sum += counts[i];
+  for (uint32_t i = begin; i < end; ++i) sum += __ldcg(counts + i);
   // block exclusive scan of `sum`
   uint32_t incl = sum;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int d = 1; d < 32; d <<= 1) {
     uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, d);
-    if (lane >= d) incl += t;
+    if (lane >= (uint32_t)d) incl += t;
   }
   if (lane == 31) warp_sums[warp] = incl;
   __syncthreads();
   if (warp == 0) {
-    uint32_t w = warp_sums[lane], wi = w;
+    uint32_t w = lane < nwarps ? warp_sums[lane] : 0u, wi = w;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
       uint32_t t = __shfl_up_sync(0xFFFFFFFFu, wi, d);
-      if (lane >= d) wi += t;
+      if (lane >= (uint32_t)d) wi += t;
     }
     warp_sums[lane] = wi - w;  // exclusive
     if (lane == 31 && total_out) *total_out = wi;
@@ -211,25 +188,41 @@ __device__ __forceinline__ void scan_u32_block(uint32_t* __restrict__ counts, ui
   __syncthreads();
   uint32_t run = warp_sums[warp] + incl - sum;
   for (uint32_t i = begin; i < end; ++i) {
-    uint32_t v = counts[i];
+    uint32_t v = __ldcg(counts + i);
     counts[i] = run;
     run += v;
   }
 }
 
-// Exclusive scan of the per-block first-occurrence counts; skipped when there are no duplicates
-// (the counts were not produced then and k_finalize takes its fast path).
-__global__ void __launch_bounds__(1024) k_scan_first_counts(uint32_t* __restrict__ counts, uint32_t n,
-                                                            TableHeader* h) {
+// Rows that are the first occurrence of their key, counted per 256-row block; the last block to finish
+// turns the counts into block offsets (exclusive scan) and writes n_unique. Returns at once when the
+// insert pass met no duplicate: nothing is compacted then (see k_finalize).
+__global__ void __launch_bounds__(kRowsPerBlock) k_count_first(const Slot* __restrict__ slots,
+                                                              const uint32_t* __restrict__ slot_of_row,
+                                                              uint32_t n, TableHeader* h,
+                                                              uint32_t* __restrict__ block_counts) {
   if (h->n_dups == 0 || h->status != RMN_OK) return;
-  scan_u32_block(counts, n, &h->n_unique);
+  __shared__ uint32_t s_last;
+  const uint32_t row = blockIdx.x * kRowsPerBlock + threadIdx.x;
+  int flag = 0;
+  if (row < n) flag = slots[slot_of_row[row]].first_row == row;
+  int total = __syncthreads_count(flag);
+  if (threadIdx.x == 0) {
+    block_counts[blockIdx.x] = (uint32_t)total;
+    __threadfence();
+    s_last = atomicAdd(&h->count_blocks_done, 1u) == gridDim.x - 1 ? 1u : 0u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  scan_u32_block(block_counts, gridDim.x, &h->n_unique);
 }
 
 template <int W>
 __global__ void __launch_bounds__(kRowsPerBlock) k_finalize(
     const int32_t* __restrict__ coords, uint32_t n, const TableHeader* h, Slot* slots,
     const uint32_t* __restrict__ slot_of_row, const uint32_t* __restrict__ block_offsets,
-    int64_t* __restrict__ mapping, int32_t* __restrict__ unique_coords) {
+    int64_t* __restrict__ mapping, int32_t* __restrict__ unique_coords, int64_t* __restrict__ inverse) {
   __shared__ uint32_t warp_counts[kRowsPerBlock / 32];
   if (h->status != RMN_OK) return;
   const uint32_t row = blockIdx.x * kRowsPerBlock + threadIdx.x;
@@ -238,6 +231,7 @@ __global__ void __launch_bounds__(kRowsPerBlock) k_finalize(
     // k_insert; only the identity mapping and the coordinate copy remain (both streaming).
     if (row < n) {
       mapping[row] = (int64_t)row;
+      if (inverse) inverse[row] = (int64_t)row;
       if (unique_coords) {
         int32_t c[W];
         load_row<W>(coords, row, c);
@@ -277,9 +271,11 @@ __global__ void __launch_bounds__(256) k_inverse(const Slot* __restrict__ slots,
                                                  const uint32_t* __restrict__ slot_of_row,
                                                  uint32_t n, const TableHeader* h,
                                                  int64_t* __restrict__ inverse) {
+  // without duplicates k_finalize has already written the identity
+  if (h->n_dups == 0 || h->status != RMN_OK) return;
   const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
-  if (row >= n || h->status != RMN_OK) return;
-  inverse[row] = h->n_dups == 0 ? (int64_t)row : (int64_t)slots[slot_of_row[row]].uid;
+  if (row >= n) return;
+  inverse[row] = (int64_t)slots[slot_of_row[row]].uid;
 }
 
 template <int W>
@@ -493,32 +489,25 @@ extern "C" int rmn_table_build(const int32_t* d_coords, uint32_t n_rows, int W, 
   auto* h = reinterpret_cast<TableHeader*>(d_table);
   auto* slots = reinterpret_cast<Slot*>(reinterpret_cast<char*>(d_table) + sizeof(TableHeader));
   const uint32_t capacity = table_capacity(n_rows);
+  RMN_CUDA_TRY(cudaMemsetAsync(h, 0, sizeof(TableHeader), stream));
   {
     const uint32_t fill_blocks = (capacity + 255u) / 256u;
-    k_table_init<<<fill_blocks < 148u * 8u ? fill_blocks : 148u * 8u, 256, 0, stream>>>(
-        h, reinterpret_cast<uint4*>(slots), (uint32_t)W, n_rows, capacity);
+    const uint32_t blocks = fill_blocks < 148u * 8u ? fill_blocks : 148u * 8u;
+    RMN_DISPATCH_W(W, k_fill_range<kW><<<blocks, 256, 0, stream>>>(d_coords, n_rows, h,
+                                                                    reinterpret_cast<uint4*>(slots), capacity));
     RMN_LAUNCH_CHECK();
   }
-  if (n_rows == 0) {
-    k_plan<<<1, 32, 0, stream>>>(h);
-    RMN_LAUNCH_CHECK();
-    return RMN_OK;
-  }
+  if (n_rows == 0) return RMN_OK;
   uint32_t* slot_of_row = reinterpret_cast<uint32_t*>(d_workspace);
   uint32_t* block_counts = slot_of_row + n_rows;
   const uint32_t nb = (n_rows + kRowsPerBlock - 1) / kRowsPerBlock;
-  const uint32_t range_blocks = nb < 148u * 8u ? nb : 148u * 8u;
-  RMN_DISPATCH_W(W, k_range<kW><<<range_blocks, 256, 0, stream>>>(d_coords, n_rows, h));
-  RMN_LAUNCH_CHECK();
   RMN_DISPATCH_W(W, k_insert<kW><<<nb, 256, 0, stream>>>(d_coords, n_rows, h, slots, slot_of_row));
   RMN_LAUNCH_CHECK();
   k_count_first<<<nb, kRowsPerBlock, 0, stream>>>(slots, slot_of_row, n_rows, h, block_counts);
   RMN_LAUNCH_CHECK();
-  k_scan_first_counts<<<1, 1024, 0, stream>>>(block_counts, nb, h);
-  RMN_LAUNCH_CHECK();
   RMN_DISPATCH_W(W, k_finalize<kW><<<nb, kRowsPerBlock, 0, stream>>>(
                         d_coords, n_rows, h, slots, slot_of_row, block_counts, d_mapping,
-                        d_unique_coords));
+                        d_unique_coords, d_inverse));
   RMN_LAUNCH_CHECK();
   if (d_inverse) {  // optional: only the quantisation modes that average or sample features read it
     k_inverse<<<nb, 256, 0, stream>>>(slots, slot_of_row, n_rows, h, d_inverse);
