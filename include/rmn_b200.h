@@ -278,6 +278,17 @@ int rmn_kmap_pairs(const int32_t *d_nbr, uint32_t n_query, int K, const int64_t 
                    uint64_t capacity, void *stream);
 
 /*
+ * rmn_kmap_pairs built to run in the shadow of a convolution: same arguments and the same lists, bit for
+ * bit, from blocks of 128 threads x 32 registers that become resident beside a convolution CTA already
+ * running on the SM (launch it on a second stream after the convolution has been queued on the first). Alone
+ * it is slower than rmn_kmap_pairs; use it only for that overlap. No counterpart in the reference, whose
+ * kernel map IS the pair lists and is always built before the convolution.
+ */
+int rmn_kmap_pairs_background(const int32_t *d_nbr, uint32_t n_query, int K, const int64_t *d_offset_ptr,
+                              const void *d_workspace, int32_t *d_a_idx, int32_t *d_q_idx, uint64_t capacity,
+                              void *stream);
+
+/*
  * Invert a neighbour table: d_nbr_t[k * n_a + a] = q where
  * d_nbr[k * n_query + q] == a, else -1. Used for the input-gradient pass and
  * for running a transposed convolution output-stationary.

@@ -243,7 +243,7 @@ __global__ void k_kmap_offset_ptr(uint32_t* __restrict__ totals, int K, int64_t*
 // Block b covers query rows [b*256, b*256+256). Warp w handles offsets
 // k = w, w+8, ...; for each it walks the 8 row groups of the block keeping a
 // running prefix, so no block-level synchronisation is needed.
-__global__ void __launch_bounds__(kKmapBlock) k_kmap_pairs(
+__device__ __forceinline__ void kmap_pairs_body(
     const int32_t* __restrict__ nbr, uint32_t n_query, int K,
     const int64_t* __restrict__ offset_ptr, const uint32_t* __restrict__ block_prefix,
     uint32_t n_blocks, int32_t* __restrict__ a_idx, int32_t* __restrict__ q_idx,
@@ -294,6 +294,25 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_pairs(
       pos += __popc(hits);
     }
   }
+}
+
+__global__ void __launch_bounds__(kKmapBlock) k_kmap_pairs(
+    const int32_t* __restrict__ nbr, uint32_t n_query, int K, const int64_t* __restrict__ offset_ptr,
+    const uint32_t* __restrict__ block_prefix, uint32_t n_blocks, int32_t* __restrict__ a_idx,
+    int32_t* __restrict__ q_idx, unsigned long long capacity, uint32_t* __restrict__ overflow) {
+  kmap_pairs_body(nbr, n_query, K, offset_ptr, block_prefix, n_blocks, a_idx, q_idx, capacity, overflow);
+}
+
+// The same compaction built to become resident BESIDE a convolution CTA: 128 threads of at most 32
+// registers. A convolution CTA (672 threads x 80 registers, allocated in groups of four warps) leaves
+// 4096 registers of an SM free, and one shared-memory / L1 split serves all CTAs of an SM, so this kernel
+// is launched with the convolution's split. It runs at a fraction of the stand-alone speed (4 KB of loads
+// in flight per SM) but inside the convolution's shadow.
+__global__ void __maxnreg__(32) k_kmap_pairs_background(
+    const int32_t* __restrict__ nbr, uint32_t n_query, int K, const int64_t* __restrict__ offset_ptr,
+    const uint32_t* __restrict__ block_prefix, uint32_t n_blocks, int32_t* __restrict__ a_idx,
+    int32_t* __restrict__ q_idx, unsigned long long capacity, uint32_t* __restrict__ overflow) {
+  kmap_pairs_body(nbr, n_query, K, offset_ptr, block_prefix, n_blocks, a_idx, q_idx, capacity, overflow);
 }
 
 __global__ void __launch_bounds__(256) k_kmap_transpose(const int32_t* __restrict__ nbr,
@@ -439,11 +458,9 @@ extern "C" int rmn_kmap_build_self(const void* d_table, const int32_t* d_coords,
   return RMN_OK;
 }
 
-extern "C" int rmn_kmap_pairs(const int32_t* d_nbr, uint32_t n_query, int K,
-                              const int64_t* d_offset_ptr, const void* d_workspace,
-                              int32_t* d_a_idx, int32_t* d_q_idx, uint64_t capacity,
-                              void* stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
+static int kmap_pairs_launch(const int32_t* d_nbr, uint32_t n_query, int K, const int64_t* d_offset_ptr,
+                             const void* d_workspace, int32_t* d_a_idx, int32_t* d_q_idx, uint64_t capacity,
+                             cudaStream_t stream, bool background) {
   if (K < 1 || !d_offset_ptr || !d_workspace) return RMN_ERR_BAD_ARG;
   if (n_query == 0 || capacity == 0) return RMN_OK;
   if (!d_nbr || !d_a_idx || !d_q_idx) return RMN_ERR_BAD_ARG;
@@ -451,25 +468,39 @@ extern "C" int rmn_kmap_pairs(const int32_t* d_nbr, uint32_t n_query, int K,
   const uint32_t* block_prefix = reinterpret_cast<const uint32_t*>(d_workspace);
   // the word after the totals flags a capacity overflow (kept for debugging reads)
   uint32_t* overflow = const_cast<uint32_t*>(block_prefix) + (size_t)K * nb + K;
-  // 128 threads (four warps sharing the offsets of a 256-row block): small enough in registers to run
-  // beside a resident convolution CTA when the caller puts this launch on a second stream. An SM holds
-  // one shared-memory / L1 split at a time, so the kernel also asks for the split the convolution
-  // kernels run with (all shared memory); with the default split its blocks would wait for those CTAs
-  // to leave. It streams its data and does not miss the L1.
-  {
+  if (!background) {
+    k_kmap_pairs<<<nb, kKmapBlock, 0, stream>>>(d_nbr, n_query, K, d_offset_ptr, block_prefix, nb, d_a_idx,
+                                                d_q_idx, capacity, overflow);
+  } else {
     static std::once_flag once[64];
     int dev = 0;
     RMN_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64)
       std::call_once(once[dev], [] {
-        cudaFuncSetAttribute(k_kmap_pairs, cudaFuncAttributePreferredSharedMemoryCarveout,
+        cudaFuncSetAttribute(k_kmap_pairs_background, cudaFuncAttributePreferredSharedMemoryCarveout,
                              (int)cudaSharedmemCarveoutMaxShared);
       });
+    k_kmap_pairs_background<<<nb, 128, 0, stream>>>(d_nbr, n_query, K, d_offset_ptr, block_prefix, nb, d_a_idx,
+                                                    d_q_idx, capacity, overflow);
   }
-  k_kmap_pairs<<<nb, 128, 0, stream>>>(d_nbr, n_query, K, d_offset_ptr, block_prefix, nb,
-                                              d_a_idx, d_q_idx, capacity, overflow);
   RMN_LAUNCH_CHECK();
   return RMN_OK;
+}
+
+extern "C" int rmn_kmap_pairs(const int32_t* d_nbr, uint32_t n_query, int K,
+                              const int64_t* d_offset_ptr, const void* d_workspace,
+                              int32_t* d_a_idx, int32_t* d_q_idx, uint64_t capacity,
+                              void* stream_) {
+  return kmap_pairs_launch(d_nbr, n_query, K, d_offset_ptr, d_workspace, d_a_idx, d_q_idx, capacity,
+                           (cudaStream_t)stream_, false);
+}
+
+extern "C" int rmn_kmap_pairs_background(const int32_t* d_nbr, uint32_t n_query, int K,
+                                         const int64_t* d_offset_ptr, const void* d_workspace,
+                                         int32_t* d_a_idx, int32_t* d_q_idx, uint64_t capacity,
+                                         void* stream_) {
+  return kmap_pairs_launch(d_nbr, n_query, K, d_offset_ptr, d_workspace, d_a_idx, d_q_idx, capacity,
+                           (cudaStream_t)stream_, true);
 }
 
 extern "C" int rmn_kmap_transpose(const int32_t* d_nbr, uint32_t n_query, int K, uint32_t n_a,

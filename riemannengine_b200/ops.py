@@ -145,17 +145,18 @@ class NeighbourTable:
         self.K = K
         self.n_table_rows = n_table_rows
 
-    def pairs(self) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-        """(offset_ptr int64 [K+1] host, a_idx int32 [P], q_idx int32 [P]); synchronises."""
+    def pairs(self, background: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """(offset_ptr int64 [K+1] host, a_idx int32 [P], q_idx int32 [P]); synchronises. ``background``
+        picks the variant built to run beside a convolution (rmn_kmap_pairs_background): same lists."""
         ptr_host = self.offset_ptr.cpu()
         total = int(ptr_host[-1])
         dev = self.nbr.device
         a = torch.empty(total, dtype=torch.int32, device=dev)
         q = torch.empty(total, dtype=torch.int32, device=dev)
         with torch.cuda.device(dev):
-            capi.check(capi.lib().rmn_kmap_pairs(_ptr(self.nbr), self.n_query, self.K, _ptr(self.offset_ptr),
-                                                 _ptr(self.workspace), _ptr(a), _ptr(q), total, _stream()),
-                       "rmn_kmap_pairs")
+            fn = capi.lib().rmn_kmap_pairs_background if background else capi.lib().rmn_kmap_pairs
+            capi.check(fn(_ptr(self.nbr), self.n_query, self.K, _ptr(self.offset_ptr), _ptr(self.workspace), _ptr(a),
+                          _ptr(q), total, _stream()), "rmn_kmap_pairs")
         return ptr_host, a, q
 
 

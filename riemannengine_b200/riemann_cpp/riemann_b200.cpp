@@ -170,11 +170,12 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> const& KernelMap::pairs() {
         built.record(main_stream);
         built.block(side_stream);
       }
-      check(rmn_kmap_pairs(static_cast<const int32_t*>(ptr(nbr_out)), static_cast<uint32_t>(n_out),
-                           static_cast<int>(K), static_cast<const int64_t*>(ptr(offset_ptr)), ptr(workspace),
-                           static_cast<int32_t*>(ptr(in_idx)), static_cast<int32_t*>(ptr(out_idx)),
-                           static_cast<uint64_t>(total), side_stream.stream()),
-            "rmn_kmap_pairs");
+      check(rmn_kmap_pairs_background(static_cast<const int32_t*>(ptr(nbr_out)), static_cast<uint32_t>(n_out),
+                                      static_cast<int>(K), static_cast<const int64_t*>(ptr(offset_ptr)),
+                                      ptr(workspace), static_cast<int32_t*>(ptr(in_idx)),
+                                      static_cast<int32_t*>(ptr(out_idx)), static_cast<uint64_t>(total),
+                                      side_stream.stream()),
+            "rmn_kmap_pairs_background");
       c10::Event done(c10::DeviceType::CUDA);
       done.record(side_stream);
       done.block(main_stream);

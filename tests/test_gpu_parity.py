@@ -291,6 +291,10 @@ def test_self_map_builder_equals_general_builder(gpu, D, ks, dil, n):
     assert torch.equal(a.offset_ptr, b.offset_ptr)
     pa, pb = a.pairs(), b.pairs()
     assert torch.equal(pa[0], pb[0])
+    # the variant built to run beside a convolution writes the same lists, bit for bit
+    for res, want in ((a, pa), (b, pb)):
+        bg = res.pairs(background=True)
+        assert all(torch.equal(x, y) for x, y in zip(bg, want))
     ptr, K = pa[0].tolist(), len(off)
     # identical lists up to and including the centre offset; above it the self map emits the exchanged
     # lists of the mirror offsets (sorted by table row instead of query row): same pair sets
