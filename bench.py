@@ -525,7 +525,7 @@ def run_product(args) -> None:
         "roofline_all": {
             "hash_insert": {"bound": "hbm", "achieved": hash_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                             "frac": hash_gbs / peaks["hbm_gbs"],
-                            "traffic": captured_traffic("table_init", "table_range", "table_insert", "table_finalize")},
+                            "traffic": captured_traffic("table_fill_range", "table_insert", "table_finalize")},
             "kernel_map": {"bound": "hbm", "achieved": kmap_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                            "frac": kmap_gbs / peaks["hbm_gbs"], "builder": "self-map (half the probes)",
                            # compulsory bytes only (query rows in, pairs out): probes served by L2 do not count
