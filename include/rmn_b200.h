@@ -101,6 +101,19 @@ int rmn_table_build(const int32_t *d_coords, uint32_t n_rows, int W, void *d_tab
                     void *stream);
 
 /*
+ * rmn_table_build in two calls on one stream, for hosts that want the number of unique rows as early as
+ * possible: after rmn_table_build_begin (header, slot fill, insert, first-occurrence counts) the header is
+ * final, so an event recorded between the two calls lets a second stream run rmn_table_info while
+ * rmn_table_build_finish (unique ids, mapping, unique coordinates, inverse) still runs on the first.
+ * Arguments as in rmn_table_build; both calls take the same table, coordinates and workspace.
+ * rmn_table_build is exactly begin followed by finish. Replaces: as rmn_table_build.
+ */
+int rmn_table_build_begin(const int32_t *d_coords, uint32_t n_rows, int W, void *d_table, size_t table_bytes,
+                          void *d_workspace, size_t workspace_bytes, void *stream);
+int rmn_table_build_finish(const int32_t *d_coords, uint32_t n_rows, int W, void *d_table, int64_t *d_mapping,
+                           int64_t *d_inverse, int32_t *d_unique_coords, void *d_workspace, void *stream);
+
+/*
  * rmn_table_build for callers that cannot allocate device memory. It has no
  * counterpart in the reference. Same inputs, outputs and results as
  * rmn_table_build, but there is no workspace argument: the build's scratch is

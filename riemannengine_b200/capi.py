@@ -27,6 +27,9 @@ SIGNATURES = {
     "rmn_table_build_workspace_bytes": (c_size_t, [c_uint32]),
     "rmn_table_build": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p,
                                 c_void_p, c_size_t, c_void_p]),
+    "rmn_table_build_begin": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_size_t, c_void_p, c_size_t, c_void_p]),
+    "rmn_table_build_finish": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p]),
     "rmn_table_build_static_max_rows": (c_uint32, []),
     "rmn_table_build_static": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p,
                                        c_void_p]),

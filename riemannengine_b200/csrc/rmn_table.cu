@@ -201,7 +201,11 @@ __global__ void __launch_bounds__(kRowsPerBlock) k_count_first(const Slot* __res
                                                               const uint32_t* __restrict__ slot_of_row,
                                                               uint32_t n, TableHeader* h,
                                                               uint32_t* __restrict__ block_counts) {
-  if (h->n_dups == 0 || h->status != RMN_OK) return;
+  if (h->status != RMN_OK) return;
+  if (h->n_dups == 0) {  // every row is its own first occurrence: publish the count, nothing to compact
+    if (blockIdx.x == 0 && threadIdx.x == 0) h->n_unique = n;
+    return;
+  }
   __shared__ uint32_t s_last;
   const uint32_t row = blockIdx.x * kRowsPerBlock + threadIdx.x;
   int flag = 0;
@@ -475,13 +479,15 @@ extern "C" size_t rmn_table_build_workspace_bytes(uint32_t n_rows) {
   return (size_t)n_rows * 4 + (nb + 1) * 4 + 256;
 }
 
-extern "C" int rmn_table_build(const int32_t* d_coords, uint32_t n_rows, int W, void* d_table,
-                               size_t table_bytes, int64_t* d_mapping, int64_t* d_inverse,
-                               int32_t* d_unique_coords, void* d_workspace,
-                               size_t workspace_bytes, void* stream_) {
+// First half of a build: header, slot fill + bounding box, insert, first-occurrence counts. When it has
+// run, the header is final (number of unique rows, status): a caller may read it back while the second
+// half is still running.
+extern "C" int rmn_table_build_begin(const int32_t* d_coords, uint32_t n_rows, int W, void* d_table,
+                                     size_t table_bytes, void* d_workspace, size_t workspace_bytes,
+                                     void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (!d_table || W < 2 || W > RMN_MAX_W || n_rows >= 0x7FFFFFFFu) return RMN_ERR_BAD_ARG;
-  if (n_rows > 0 && (!d_coords || !d_mapping || !d_workspace)) return RMN_ERR_BAD_ARG;
+  if (n_rows > 0 && (!d_coords || !d_workspace)) return RMN_ERR_BAD_ARG;
   if (((uintptr_t)d_table & 15) || !coords_aligned(d_coords, W)) return RMN_ERR_BAD_ARG;
   if (table_bytes < rmn_table_bytes(n_rows) ||
       (n_rows > 0 && workspace_bytes < rmn_table_build_workspace_bytes(n_rows)))
@@ -505,6 +511,23 @@ extern "C" int rmn_table_build(const int32_t* d_coords, uint32_t n_rows, int W, 
   RMN_LAUNCH_CHECK();
   k_count_first<<<nb, kRowsPerBlock, 0, stream>>>(slots, slot_of_row, n_rows, h, block_counts);
   RMN_LAUNCH_CHECK();
+  return RMN_OK;
+}
+
+// Second half: unique ids, mapping, unique coordinates, inverse. Same table, coordinates and workspace as
+// the first half, on the same stream.
+extern "C" int rmn_table_build_finish(const int32_t* d_coords, uint32_t n_rows, int W, void* d_table,
+                                      int64_t* d_mapping, int64_t* d_inverse, int32_t* d_unique_coords,
+                                      void* d_workspace, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (!d_table || W < 2 || W > RMN_MAX_W || n_rows >= 0x7FFFFFFFu) return RMN_ERR_BAD_ARG;
+  if (n_rows == 0) return RMN_OK;
+  if (!d_coords || !d_mapping || !d_workspace) return RMN_ERR_BAD_ARG;
+  auto* h = reinterpret_cast<TableHeader*>(d_table);
+  auto* slots = reinterpret_cast<Slot*>(reinterpret_cast<char*>(d_table) + sizeof(TableHeader));
+  uint32_t* slot_of_row = reinterpret_cast<uint32_t*>(d_workspace);
+  uint32_t* block_counts = slot_of_row + n_rows;
+  const uint32_t nb = (n_rows + kRowsPerBlock - 1) / kRowsPerBlock;
   RMN_DISPATCH_W(W, k_finalize<kW><<<nb, kRowsPerBlock, 0, stream>>>(
                         d_coords, n_rows, h, slots, slot_of_row, block_counts, d_mapping,
                         d_unique_coords, d_inverse));
@@ -514,6 +537,18 @@ extern "C" int rmn_table_build(const int32_t* d_coords, uint32_t n_rows, int W, 
     RMN_LAUNCH_CHECK();
   }
   return RMN_OK;
+}
+
+extern "C" int rmn_table_build(const int32_t* d_coords, uint32_t n_rows, int W, void* d_table,
+                               size_t table_bytes, int64_t* d_mapping, int64_t* d_inverse,
+                               int32_t* d_unique_coords, void* d_workspace,
+                               size_t workspace_bytes, void* stream_) {
+  if (n_rows > 0 && n_rows < 0x7FFFFFFFu && !d_mapping) return RMN_ERR_BAD_ARG;
+  const int rc = rmn_table_build_begin(d_coords, n_rows, W, d_table, table_bytes, d_workspace, workspace_bytes,
+                                       stream_);
+  if (rc != RMN_OK) return rc;
+  return rmn_table_build_finish(d_coords, n_rows, W, d_table, d_mapping, d_inverse, d_unique_coords, d_workspace,
+                                stream_);
 }
 
 // ---------------------------------------------------------------------------

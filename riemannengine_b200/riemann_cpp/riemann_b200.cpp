@@ -124,7 +124,7 @@ at::Tensor const& KernelMap::nbr_in() {
 }
 
 namespace {
-// One second stream per device for the pair-list kernels: the caching allocator keeps a pool per stream, so
+// One second stream per device (pair-list kernels, early header read-back): the caching allocator keeps a pool per stream, so
 // a stream picked afresh from torch's round-robin pool on every call would allocate the lists anew each time.
 c10::cuda::CUDAStream pair_list_stream(c10::DeviceIndex device) {
   static std::mutex lock;
@@ -244,12 +244,23 @@ CoordinateManager::Map CoordinateManager::build(const at::Tensor& coords, const 
   auto ws = at::empty({static_cast<int64_t>(ws_bytes)}, bytes);
   auto mapping = at::empty({n}, longs), inverse = at::empty({n}, longs);
   auto unique = at::empty({n, W}, coords.options());
-  check(rmn_table_build(static_cast<const int32_t*>(ptr(coords)), n, W, ptr(m.table), table_bytes,
-                        static_cast<int64_t*>(ptr(mapping)), static_cast<int64_t*>(ptr(inverse)),
-                        static_cast<int32_t*>(ptr(unique)), ptr(ws), ws_bytes, current_stream()),
+  // The header (number of unique rows) is final after the first half of the build: it is read back on the
+  // second stream while the second half still runs on the caller's, so the host is already preparing the
+  // next launches when the build ends.
+  auto main_stream = c10::cuda::getCurrentCUDAStream();
+  check(rmn_table_build_begin(static_cast<const int32_t*>(ptr(coords)), n, W, ptr(m.table), table_bytes, ptr(ws),
+                              ws_bytes, main_stream.stream()),
         "rmn_table_build");
+  c10::Event counted(c10::DeviceType::CUDA);
+  counted.record(main_stream);
+  check(rmn_table_build_finish(static_cast<const int32_t*>(ptr(coords)), n, W, ptr(m.table),
+                               static_cast<int64_t*>(ptr(mapping)), static_cast<int64_t*>(ptr(inverse)),
+                               static_cast<int32_t*>(ptr(unique)), ptr(ws), main_stream.stream()),
+        "rmn_table_build");
+  auto side_stream = pair_list_stream(main_stream.device_index());
+  counted.block(side_stream);
   uint32_t info[4];
-  check(rmn_table_info(ptr(m.table), info, current_stream()), "rmn_table_build");
+  check(rmn_table_info(ptr(m.table), info, side_stream.stream()), "rmn_table_build");
   m.size = info[0];
   m.coords = unique.narrow(0, 0, m.size);
   if (mapping_out) *mapping_out = mapping.narrow(0, 0, m.size);
