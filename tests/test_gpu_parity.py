@@ -339,3 +339,44 @@ def capi_status_ok():
     import ctypes
     from riemannengine_b200 import capi
     return capi.lib().rmn_device_status(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == capi.OK
+
+
+@pytest.mark.parametrize("dups", [False, True])
+def test_two_call_table_build_header_is_final_after_the_first_call(gpu, dups):
+    """rmn_table_build_begin / _finish: the unique-row count read on a second stream between the two calls
+    equals the final one, and the finished build gives rmn_table_build's mapping, inverse, unique rows and lookups."""
+    import ctypes
+    from riemannengine_b200 import capi, ops
+    lib = capi.lib()
+    c_np = _random_cloud(77, 50_000, 3, -12, 12, 3, dup_frac=0.2 if dups else 0)
+    if not dups:
+        c_np = c_np[OracleBackend().insert_and_map(c_np)[0]]
+    coords = torch.from_numpy(c_np).cuda()
+    n, w = coords.shape
+    ref = ops.table_build(coords)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    main, side = torch.cuda.current_stream(), torch.cuda.Stream()
+    tbytes, wbytes = lib.rmn_table_bytes(n), lib.rmn_table_build_workspace_bytes(n)
+    table = torch.zeros(tbytes, dtype=torch.uint8, device="cuda")
+    ws = torch.empty(wbytes, dtype=torch.uint8, device="cuda")
+    mapping = torch.full((n,), -7, dtype=torch.int64, device="cuda")
+    inverse = torch.full((n,), -7, dtype=torch.int64, device="cuda")
+    uniq = torch.full((n, w), -7, dtype=torch.int32, device="cuda")
+    sm = ctypes.c_void_p(main.cuda_stream)
+    assert lib.rmn_table_build_begin(p(coords), n, w, p(table), tbytes, p(ws), wbytes, sm) == capi.OK
+    counted = torch.cuda.Event()
+    counted.record(main)
+    assert lib.rmn_table_build_finish(p(coords), n, w, p(table), p(mapping), p(inverse), p(uniq), p(ws), sm) == capi.OK
+    side.wait_event(counted)
+    early = (ctypes.c_uint32 * 4)()
+    assert lib.rmn_table_info(p(table), early, ctypes.c_void_p(side.cuda_stream)) == capi.OK
+    late = (ctypes.c_uint32 * 4)()
+    assert lib.rmn_table_info(p(table), late, sm) == capi.OK
+    assert list(early) == list(late) and early[0] == ref.n_unique
+    nu = int(late[0])
+    assert torch.equal(mapping[:nu], ref.mapping) and torch.equal(inverse, ref.inverse)
+    assert torch.equal(uniq[:nu], ref.coords)
+    # (slot positions depend on which of two colliding keys won its CAS: compare the tables through lookups)
+    rows = torch.empty(n, dtype=torch.int32, device="cuda")
+    assert lib.rmn_table_find(p(table), p(coords), n, w, p(rows), sm) == capi.OK
+    assert torch.equal(rows.long(), ref.inverse)
