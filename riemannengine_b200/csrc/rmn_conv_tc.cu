@@ -195,11 +195,8 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
       auto load_idx = [&](int kk) -> int32_t {
         return (row_ok && kk < K) ? __ldg(nbr + (size_t)kk * n_dst + row) : -1;
       };
-      int32_t idx_w0 = load_idx(0), idx_w1 = load_idx(1), idx_w2 = load_idx(2), idx_w3 = load_idx(3);
-      for (int k = 0; k < K && !timed_out; ++k) {
-        const int32_t idx = idx_w0;
-        idx_w0 = idx_w1; idx_w1 = idx_w2; idx_w2 = idx_w3;
-        idx_w3 = load_idx(k + 4);
+      // One offset of the super-tile: fill the next ring stage(s) with the rows `idx` names and W[k].
+      auto do_offset = [&](int k, const int32_t idx) {
         const __nv_bfloat16* wk = w + (size_t)k * CIN_W * COUT_W;
 #pragma unroll 1
         for (int kb = 0; kb < NKB; ++kb, ++it) {
@@ -238,6 +235,32 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
           // (cp.async.mbarrier.arrive.noinc), so producers never wait for data: they run ahead
           // until the ring is full and every stage of shared memory can be in flight.
           cp_async_arrive_noinc(&full[s]);
+        }
+      };
+      // The four-deep window is unrolled by hand, each slot a register of its own that is reloaded right
+      // after it is read: a rotating window (w0 = w1; w1 = w2; ...) would copy registers whose loads
+      // are still in flight, and a copy waits for its source like any other use.
+      int32_t idx_w0 = load_idx(0), idx_w1 = load_idx(1), idx_w2 = load_idx(2), idx_w3 = load_idx(3);
+      for (int k = 0; k < K && !timed_out; k += 4) {
+        {
+          const int32_t idx = idx_w0;
+          idx_w0 = load_idx(k + 4);
+          do_offset(k, idx);
+        }
+        if (k + 1 < K && !timed_out) {
+          const int32_t idx = idx_w1;
+          idx_w1 = load_idx(k + 5);
+          do_offset(k + 1, idx);
+        }
+        if (k + 2 < K && !timed_out) {
+          const int32_t idx = idx_w2;
+          idx_w2 = load_idx(k + 6);
+          do_offset(k + 2, idx);
+        }
+        if (k + 3 < K && !timed_out) {
+          const int32_t idx = idx_w3;
+          idx_w3 = load_idx(k + 7);
+          do_offset(k + 3, idx);
         }
       }
     }
