@@ -6,9 +6,12 @@
 // tcgen05.mma uses the full M = 128 (TMEM lane = offset-in-group * C_in + ci)
 // while sharing the same dY tile.
 //
-// Grid = (row chunks, offset sets). A CTA keeps the accumulators of its offset
+// Grid = (row slices, offset sets). A CTA keeps the accumulators of its offset
 // set resident in TMEM (groups * C_out <= 512 columns) while it walks its row
-// chunk in blocks of 64 rows; one pipeline stage = (row block, GP offset groups):
+// slice in blocks of 64 rows. Slice c is the row blocks c, c + slices, c + 2 slices, ...: all CTAs
+// sweep the rows together, so the feature rows being gathered at any moment are the neighbours of one
+// narrow band of rows (one sample of the batch) and stay in L2; contiguous chunks would spread the
+// gathers of the CTAs over the whole feature array at once. The rest of the stage: one pipeline stage = (row block, GP offset groups):
 // GP x 64 x G gathered rows (GP x 16 KB) + the 64 dY rows, which the GP groups
 // share (copied once, and read from shared memory once per K slice: the second
 // group's MMA reuses the collector buffer). At the end the four producer
@@ -59,7 +62,7 @@ struct WgradCfg {
 template <int CIN, int COUT>
 __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
     const __nv_bfloat16* __restrict__ feats, const __nv_bfloat16* __restrict__ grad_out,
-    const int32_t* __restrict__ nbr, uint32_t n_dst, int K, uint32_t chunk_rows, int groups_per_set,
+    const int32_t* __restrict__ nbr, uint32_t n_dst, int K, int groups_per_set,
     uint32_t tmem_cols, float* __restrict__ partial) {
   using C = WgradCfg<CIN, COUT>;
   constexpr int STAGES = C::STAGES, G = C::G, GP = C::GP, kWgIdxPerThread = C::IDX_PER_THREAD;
@@ -81,9 +84,10 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
   const int group0 = blockIdx.y * groups_per_set;
   const int n_groups = min(groups_per_set, n_groups_total - group0);  // offset groups of this CTA
   const int n_sg = (n_groups + GP - 1) / GP;                          // stages per row block
-  const uint32_t j_begin = blockIdx.x * chunk_rows;
-  const uint32_t j_end = min(n_dst, j_begin + chunk_rows);
-  const uint32_t n_blocks = j_end > j_begin ? (j_end - j_begin + kRowsPerStage - 1) / kRowsPerStage : 0;
+  // row block b of this CTA covers rows [(blockIdx.x + b * gridDim.x) * 64, +64)
+  const uint32_t total_blocks = (n_dst + kRowsPerStage - 1) / kRowsPerStage;
+  const uint32_t j_end = n_dst;
+  const uint32_t n_blocks = blockIdx.x < total_blocks ? (total_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   const uint32_t n_stage = n_blocks * (uint32_t)n_sg;
 
   if (tid == 0) {
@@ -124,7 +128,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
       int32_t v = -1;
       if (lane < NIDX) {
         const int combo = lane >> 2, gp = combo / G, gg = combo % G;
-        const uint32_t j = j_begin + pf_blk * kRowsPerStage + warp * 4 + (lane & 3);
+        const uint32_t j = (blockIdx.x + pf_blk * gridDim.x) * kRowsPerStage + warp * 4 + (lane & 3);
         const int k = (group0 + pf_sg * GP + gp) * G + gg;
         if (pf_blk < n_blocks && j < j_end && k < K && pf_sg * GP + gp < n_groups) v = __ldg(nbr + (size_t)k * n_dst + j);
       }
@@ -137,7 +141,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
     int32_t idx_w0 = load_indices(), idx_w1 = load_indices(), idx_w2 = load_indices(), idx_w3 = load_indices(),
             idx_w4 = load_indices(), idx_w5 = load_indices();
     for (uint32_t blk = 0; blk < n_blocks && !timed_out; ++blk) {
-      const uint32_t j0 = j_begin + blk * kRowsPerStage;
+      const uint32_t j0 = (blockIdx.x + blk * gridDim.x) * kRowsPerStage;
 #pragma unroll 1
       for (int sg = 0; sg < n_sg; ++sg, ++it) {
         const int32_t mine = idx_w0;
@@ -288,7 +292,7 @@ __global__ void __launch_bounds__(256) k_reduce_chunks(const float* __restrict__
 }
 
 struct WgradPlan {
-  uint32_t chunks, chunk_rows;
+  uint32_t chunks;  // row slices = CTAs per offset set
   int sets, groups_per_set;
   uint32_t tmem_cols;
 };
@@ -304,10 +308,11 @@ WgradPlan plan(uint32_t n_dst, int K, int sms) {
   p.tmem_cols = pow2_at_least((uint32_t)((p.groups_per_set + C::GP - 1) / C::GP * C::GP) * COUT);
   uint32_t want = (uint32_t)(sms / p.sets);
   if (want < 1) want = 1;
-  uint32_t rows = (n_dst + want - 1) / want;
-  if (rows < 2048) rows = 2048;
-  p.chunk_rows = (rows + kRowsPerStage - 1) / kRowsPerStage * kRowsPerStage;
-  p.chunks = n_dst == 0 ? 1 : (n_dst + p.chunk_rows - 1) / p.chunk_rows;
+  // at least 32 row blocks (2048 rows) per slice: fewer, and the fp32 partials cost more than they spread
+  const uint32_t total_blocks = (n_dst + kRowsPerStage - 1) / kRowsPerStage;
+  uint32_t slices = total_blocks / 32;
+  if (slices < 1) slices = 1;
+  p.chunks = slices < want ? slices : want;
   return p;
 }
 
@@ -331,7 +336,7 @@ int launch_wgrad(const void* feats, const void* grad_out, const int32_t* nbr, ui
   }
   dim3 grid(p.chunks, p.sets);
   kern<<<grid, kWgradThreads, C::SMEM, stream>>>((const __nv_bfloat16*)feats, (const __nv_bfloat16*)grad_out, nbr,
-                                                 n_dst, K, p.chunk_rows, p.groups_per_set, p.tmem_cols,
+                                                 n_dst, K, p.groups_per_set, p.tmem_cols,
                                                  (float*)workspace);
   RMN_LAUNCH_CHECK();
   k_reduce_chunks<<<(uint32_t)((elems + 255) / 256), 256, 0, stream>>>((const float*)workspace, p.chunks, elems, dw);
