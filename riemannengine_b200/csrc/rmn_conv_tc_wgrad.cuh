@@ -11,10 +11,10 @@
 // slice in blocks of 64 rows. Slice c is the row blocks c, c + slices, c + 2 slices, ...: all CTAs
 // sweep the rows together, so the feature rows being gathered at any moment are the neighbours of one
 // narrow band of rows (one sample of the batch) and stay in L2; contiguous chunks would spread the
-// gathers of the CTAs over the whole feature array at once. The rest of the stage: one pipeline stage = (row block, GP offset groups):
+// gathers of the CTAs over the whole feature array at once. One pipeline stage = (row block, GP offset groups):
 // GP x 64 x G gathered rows (GP x 16 KB) + the 64 dY rows, which the GP groups
-// share (copied once, and read from shared memory once per K slice: the second
-// group's MMA reuses the collector buffer). At the end the four producer
+// share (copied once, and read from shared memory once per K slice: the other
+// groups' MMAs reuse the collector buffer). At the end the four producer
 // warps read the accumulators back and write an fp32 partial
 // [chunk][K][C_in][C_out]; a second kernel adds the chunks in a fixed order, so
 // the result is bit-reproducible (no atomics).
@@ -45,15 +45,20 @@ struct WgradCfg {
   static constexpr int MAX_GROUPS = 512 / COUT;           // accumulators resident in TMEM
   static constexpr uint32_t A_GROUP = kRowsPerStage * 128 * 2;   // gathered rows of one offset group
   static constexpr uint32_t B_BYTES = kRowsPerStage * COUT * 2;
-  // two offset groups per stage (sharing the dY rows) where at least three such stages fit
-  static constexpr int GP = (MAX_GROUPS >= 2 && (2 * A_GROUP + B_BYTES) * 3 <= 200 * 1024) ? 2 : 1;
+  // Offset groups per stage (they share the stage's dY rows): four where three such stages fit in shared
+  // memory and a warp's 4 * G * GP neighbour entries fit its 32 lanes, else two where three such stages
+  // fit, else one. Fewer, larger stages carry the per-stage work of a warp (index load, shuffles, barrier
+  // wait) over more copies.
+  static constexpr int GP = (MAX_GROUPS >= 4 && G <= 2 && (4 * A_GROUP + B_BYTES) * 2 <= 227 * 1024 - 256)
+                                ? 4
+                                : ((MAX_GROUPS >= 2 && (2 * A_GROUP + B_BYTES) * 3 <= 200 * 1024) ? 2 : 1);
   static constexpr uint32_t A_BYTES = GP * A_GROUP;
   static constexpr uint32_t STAGE = A_BYTES + B_BYTES;
   static constexpr int IDX_PER_THREAD = GP * kWgLinesPerGroup;
   // as many stages (up to six) as 227 KB of shared memory hold beside the barriers;
   // more than 114 KB in total also keeps one CTA (one TMEM owner) per SM
   static constexpr uint32_t STAGE_BUDGET = 227 * 1024 - 256;
-  static constexpr int STAGES = STAGE * 6 <= STAGE_BUDGET ? 6 : (STAGE * 5 <= STAGE_BUDGET ? 5 : (STAGE * 4 <= STAGE_BUDGET ? 4 : 3));
+  static constexpr int STAGES = STAGE * 6 <= STAGE_BUDGET ? 6 : (STAGE * 5 <= STAGE_BUDGET ? 5 : (STAGE * 4 <= STAGE_BUDGET ? 4 : (STAGE * 3 <= STAGE_BUDGET ? 3 : 2)));
   static_assert(STAGE * STAGES <= STAGE_BUDGET, "stages do not fit in shared memory");
   static constexpr uint32_t BAR_OFFSET = STAGES * STAGE;
   static constexpr uint32_t SMEM = BAR_OFFSET + 256;
@@ -249,15 +254,18 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
             const uint64_t a_desc = ((uint64_t)A_DESC_HI << 32) | (a_lo + (uint32_t)((jj * 16 * 128) >> 4));
             const uint64_t b_desc = ((uint64_t)B_DESC_HI << 32) | (b_lo + (uint32_t)((jj * 16 * SWB) >> 4));
             const uint32_t accumulate = (blk | (uint32_t)jj) != 0 ? 1u : 0u;
-            if constexpr (GP == 2) {
-              const uint64_t a2_desc = a_desc + (C::A_GROUP >> 4);
-              if constexpr (COUT == 64 || COUT == 128 || COUT == 256) {  // .ws shapes: dY slice read once
-                tc_mma_bf16_ws_elect<jj & 3, 0>(d0, a_desc, b_desc, IDESC, accumulate);
-                tc_mma_bf16_ws_elect<jj & 3, 2>(d0 + COUT, a2_desc, b_desc, IDESC, accumulate);
-              } else {
-                tc_mma_bf16_elect(d0, a_desc, b_desc, IDESC, accumulate);
-                tc_mma_bf16_elect(d0 + COUT, a2_desc, b_desc, IDESC, accumulate);
-              }
+            if constexpr (GP >= 2) {
+              // the GP groups of the stage multiply the same dY slice: the first MMA reads it from shared
+              // memory into collector buffer jj, the others reuse it (.ws shapes only)
+              static_for<GP>([&](auto gc) {
+                constexpr int g = decltype(gc)::value;
+                const uint64_t ag_desc = a_desc + (uint64_t)((g * C::A_GROUP) >> 4);
+                if constexpr (COUT == 64 || COUT == 128 || COUT == 256)
+                  tc_mma_bf16_ws_elect<jj & 3, g == 0 ? 0 : (g == GP - 1 ? 2 : 1)>(d0 + g * COUT, ag_desc, b_desc, IDESC,
+                                                                                  accumulate);
+                else
+                  tc_mma_bf16_elect(d0 + g * COUT, ag_desc, b_desc, IDESC, accumulate);
+              });
             } else {
               tc_mma_bf16_elect(d0, a_desc, b_desc, IDESC, accumulate);
             }
