@@ -45,11 +45,10 @@ struct WgradCfg {
   static constexpr int MAX_GROUPS = 512 / COUT;           // accumulators resident in TMEM
   static constexpr uint32_t A_GROUP = kRowsPerStage * 128 * 2;   // gathered rows of one offset group
   static constexpr uint32_t B_BYTES = kRowsPerStage * COUT * 2;
-  // Offset groups per stage (they share the stage's dY rows): four where three such stages fit in shared
-  // memory and a warp's 4 * G * GP neighbour entries fit its 32 lanes, else two where three such stages
-  // fit, else one. Fewer, larger stages carry the per-stage work of a warp (index load, shuffles, barrier
+  // Offset groups per stage (they share the stage's dY rows): four where two such stages fit in shared
+  // memory, else two where three such stages fit, else one. Fewer, larger stages carry the per-stage work of a warp (index load, shuffles, barrier
   // wait) over more copies.
-  static constexpr int GP = (MAX_GROUPS >= 4 && G <= 2 && (4 * A_GROUP + B_BYTES) * 2 <= 227 * 1024 - 256)
+  static constexpr int GP = (MAX_GROUPS >= 4 && (4 * A_GROUP + B_BYTES) * 2 <= 227 * 1024 - 256)
                                 ? 4
                                 : ((MAX_GROUPS >= 2 && (2 * A_GROUP + B_BYTES) * 3 <= 200 * 1024) ? 2 : 1);
   static constexpr uint32_t A_BYTES = GP * A_GROUP;
@@ -122,34 +121,47 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
     // A' image: one 128-byte swizzled line per (stage row, 64-channel atom of the stacked M axis);
     // eight consecutive lanes copy one line, i.e. one (CIN >= 64) or two (CIN = 32) gathered rows.
     // Neighbour indices: warp w copies rows [4w, 4w + 4) of every stage, for all G * GP offsets of the
-    // stage, i.e. 4 * G * GP <= 32 table entries: lane l < 4 * G * GP loads entry (offset l / 4, row l % 4)
-    // with ONE coalesced load per warp and stage, six stages before use (the table is streamed from DRAM) (a rotating window of
-    // named registers); the lanes of a line fetch theirs with a shuffle when the stage is issued.
+    // stage, i.e. 4 * G * GP <= 64 table entries: lane l loads entry l = (offset l / 4, row l % 4) (and entry
+    // l + 32 where there are more than 32) with one coalesced load per warp, stage and 32 entries, six stages
+    // before use (the table is streamed from DRAM; a rotating window of named registers); the lanes of a line
+    // fetch theirs with a shuffle when the stage is issued.
     uint32_t it = 0;
     constexpr int NIDX = 4 * G * GP;
     uint32_t pf_blk = 0;
     int pf_sg = 0;
-    auto load_indices = [&]() -> int32_t {
-      int32_t v = -1;
-      if (lane < NIDX) {
-        const int combo = lane >> 2, gp = combo / G, gg = combo % G;
-        const uint32_t j = (blockIdx.x + pf_blk * gridDim.x) * kRowsPerStage + warp * 4 + (lane & 3);
-        const int k = (group0 + pf_sg * GP + gp) * G + gg;
-        if (pf_blk < n_blocks && j < j_end && k < K && pf_sg * GP + gp < n_groups) v = __ldg(nbr + (size_t)k * n_dst + j);
+    // a warp's 4 * G * GP table entries of a stage: entry e = (offset e / 4, row e % 4), lane l holds
+    // entries l and (for more than 32 entries) l + 32
+    constexpr int NREG = (NIDX + 31) / 32;
+    struct Entries {
+      int32_t v[NREG];
+    };
+    auto load_indices = [&]() -> Entries {
+      Entries out;
+#pragma unroll
+      for (int r = 0; r < NREG; ++r) {
+        int32_t v = -1;
+        const int e = r * 32 + lane;
+        if (e < NIDX) {
+          const int combo = e >> 2, gp = combo / G, gg = combo % G;
+          const uint32_t j = (blockIdx.x + pf_blk * gridDim.x) * kRowsPerStage + warp * 4 + (lane & 3);
+          const int k = (group0 + pf_sg * GP + gp) * G + gg;
+          if (pf_blk < n_blocks && j < j_end && k < K && pf_sg * GP + gp < n_groups) v = __ldg(nbr + (size_t)k * n_dst + j);
+        }
+        out.v[r] = v;
       }
       if (++pf_sg == n_sg) { pf_sg = 0; ++pf_blk; }
-      return v;
+      return out;
     };
 #ifdef RMN_PROF
     long long prof_wait = 0; const long long prof_start = clock64();
 #endif
-    int32_t idx_w0 = load_indices(), idx_w1 = load_indices(), idx_w2 = load_indices(), idx_w3 = load_indices(),
+    Entries idx_w0 = load_indices(), idx_w1 = load_indices(), idx_w2 = load_indices(), idx_w3 = load_indices(),
             idx_w4 = load_indices(), idx_w5 = load_indices();
     for (uint32_t blk = 0; blk < n_blocks && !timed_out; ++blk) {
       const uint32_t j0 = (blockIdx.x + blk * gridDim.x) * kRowsPerStage;
 #pragma unroll 1
       for (int sg = 0; sg < n_sg; ++sg, ++it) {
-        const int32_t mine = idx_w0;
+        const Entries mine = idx_w0;
         idx_w0 = idx_w1; idx_w1 = idx_w2; idx_w2 = idx_w3; idx_w3 = idx_w4; idx_w4 = idx_w5;
         idx_w5 = load_indices();
         int32_t idx[kWgIdxPerThread];
@@ -157,7 +169,14 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
         for (int i = 0; i < kWgIdxPerThread; ++i) {
           const int gp = i / kWgLinesPerGroup, atom = i % kWgLinesPerGroup;
           const int gg = (atom * 8 + (lane & 7)) / (CIN / 8);
-          idx[i] = __shfl_sync(0xFFFFFFFFu, mine, (gp * G + gg) * 4 + (lane >> 3));
+          const int e = (gp * G + gg) * 4 + (lane >> 3);  // < 32 * NREG; which register is uniform per warp only
+          // when gg is, so both are read and the right one kept
+          int32_t got = __shfl_sync(0xFFFFFFFFu, mine.v[0], e & 31);
+          if constexpr (NREG > 1) {
+            const int32_t hi = __shfl_sync(0xFFFFFFFFu, mine.v[1], e & 31);
+            got = e >= 32 ? hi : got;
+          }
+          idx[i] = got;
         }
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
         {
