@@ -60,10 +60,14 @@ const char *rmn_status_string(int status);
 /* Number of CUDA kernels this library has launched in this process so far
  * (telemetry for benchmarks; no counterpart in the reference). */
 unsigned long long rmn_launch_count(void);
-/* Synchronises `stream` and returns the sticky device-side status of the
- * convolution kernels: RMN_OK, or RMN_ERR_TIMEOUT when a bounded wait inside a
- * kernel ran out (the kernel then returned early and its output is invalid).
- * No counterpart in the reference. */
+/* Synchronises `stream` and returns the device-side status of the convolution
+ * kernels: RMN_OK, or RMN_ERR_TIMEOUT when a bounded wait inside a kernel ran
+ * out (the kernel then returned early and its output is invalid). The status
+ * is ONE word per device, shared by all streams; a non-zero value is returned
+ * once and reset by the call that returns it. rmn_table_info returns the same
+ * status (and resets it) when the table itself is fine, so a host that builds
+ * a coordinate map per step checks its earlier convolutions at the read-back
+ * it makes anyway. No counterpart in the reference. */
 int rmn_device_status(void *stream);
 
 /* =======================================================================
@@ -73,7 +77,7 @@ int rmn_device_status(void *stream);
  *   and the vendored concurrent_unordered_map
  *   (vendor/concurrent_unordered_map.cuh:305-391).
  * An open-addressing table of 16-byte slots {packed key, first row, unique
- * row} at <= 50 % load, preceded by a 256-byte header.
+ * row} with 3 * n_rows + 64 slots (load <= 1/3), preceded by a 256-byte header.
  * ===================================================================== */
 
 /* Bytes of device memory a table for `n_rows` input rows needs. */
@@ -126,7 +130,9 @@ int rmn_table_build_finish(const int32_t *d_coords, uint32_t n_rows, int W, void
  *    larger inputs return RMN_ERR_TOO_LARGE and enqueue nothing.
  *  - The first call on each device looks up the device address of the scratch
  *    array (with that device current); make that first call outside any stream
- *    capture. Later calls on the same device only enqueue kernels.
+ *    capture. Later calls on the same device only enqueue kernels. The address is kept for the life of
+ *    the process: do not call cudaDeviceReset (or otherwise destroy the device's primary context) while
+ *    the library is loaded and then call this entry point again.
  *  - The call itself performs no cudaMalloc / cudaFree and calls no allocating
  *    library routine.
  *  - All calls on one GPU share the one scratch array, which keeps the
@@ -142,7 +148,8 @@ int rmn_table_build_static(const int32_t *d_coords, uint32_t n_rows, int W, void
 /*
  * Synchronising read-back: info[0] = n_unique, info[1] = device status
  * (RMN_OK / RMN_ERR_PROBE_LIMIT / RMN_ERR_RANGE), info[2] = slot count,
- * info[3] = n_rows. Returns info[1] when it is non-zero.
+ * info[3] = n_rows. Returns info[1] when it is non-zero; otherwise the pending
+ * status of earlier convolution kernels (see rmn_device_status), normally RMN_OK.
  */
 int rmn_table_info(const void *d_table, uint32_t info[4], void *stream);
 
@@ -289,6 +296,15 @@ int rmn_kmap_build_self(const void *d_table, const int32_t *d_coords, uint32_t n
 int rmn_kmap_pairs(const int32_t *d_nbr, uint32_t n_query, int K, const int64_t *d_offset_ptr,
                    const void *d_workspace, int32_t *d_a_idx, int32_t *d_q_idx,
                    uint64_t capacity, void *stream);
+
+/*
+ * Synchronising check after rmn_kmap_pairs / rmn_kmap_pairs_background on the same workspace: RMN_OK, or
+ * RMN_ERR_ALLOC when `capacity` was smaller than the number of pairs (the lists are then truncated). A
+ * caller that sizes the lists from d_offset_ptr[K] never needs it. No counterpart in the reference, whose
+ * lists are std::vectors preallocated for every (offset, row) and shrunk afterwards
+ * (engine/grid/lattice_cpu.hpp:606-673).
+ */
+int rmn_kmap_pairs_status(const void *d_workspace, uint32_t n_query, int K, void *stream);
 
 /*
  * rmn_kmap_pairs built to run in the shadow of a convolution: same arguments and the same lists, bit for

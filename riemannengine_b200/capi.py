@@ -47,6 +47,7 @@ SIGNATURES = {
                                c_void_p]),
     "rmn_kmap_pairs_background": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_uint64,
                                           c_void_p]),
+    "rmn_kmap_pairs_status": (c_int, [c_void_p, c_uint32, c_int, c_void_p]),
     "rmn_kmap_transpose": (c_int, [c_void_p, c_uint32, c_int, c_uint32, c_void_p, c_void_p]),
     "rmn_conv_forward": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_int, c_void_p, c_uint32,
                                  c_void_p, c_int, c_void_p]),

@@ -53,14 +53,6 @@ extern "C" const char* rmn_status_string(int status) {
   }
 }
 
-// RMN_B200_DISABLE_TC=1 routes bf16 through the SIMT kernels (debugging aid).
-bool use_tensor_cores() {
-  static const bool on = [] {
-    const char* e = std::getenv("RMN_B200_DISABLE_TC");
-    return !(e && e[0] == '1');
-  }();
-  return on;
-}
 
 extern "C" int rmn_device_status(void* stream_) {
   uint32_t st = 0;
@@ -80,7 +72,7 @@ extern "C" int rmn_conv_forward_fused(const void* d_feats, uint32_t n_src, int c
   cudaStream_t stream = (cudaStream_t)stream_;
   if (n_dst == 0) return RMN_OK;
   if (!conv_args_ok(n_src ? d_feats : d_out, d_weights, d_nbr, d_out, K, c_in, c_out, dtype)) return RMN_ERR_BAD_ARG;
-  if (dtype == RMN_BF16 && use_tensor_cores() && n_src > 0) {
+  if (dtype == RMN_BF16 && n_src > 0) {
     const int st = tc_conv(d_feats, n_src, d_weights, d_nbr, n_dst, K, c_in, c_out, false, d_out, d_scale, d_shift,
                            relu, stream);
     if (st != RMN_ERR_UNSUPPORTED) return st;
@@ -110,7 +102,7 @@ extern "C" int rmn_conv_backward_input(const void* d_grad_out, uint32_t n_dst, i
   }
   if (!conv_args_ok(d_grad_out, d_weights, d_nbr_t, d_grad_feats, K, c_in, c_out, dtype))
     return RMN_ERR_BAD_ARG;
-  if (dtype == RMN_BF16 && use_tensor_cores()) {
+  if (dtype == RMN_BF16) {
     const int st = tc_conv(d_grad_out, n_dst, d_weights, d_nbr_t, n_src, K, c_out, c_in, true, d_grad_feats, nullptr, nullptr, 0,
                            stream);
     if (st != RMN_ERR_UNSUPPORTED) return st;
@@ -123,7 +115,7 @@ extern "C" size_t rmn_conv_backward_weight_workspace_bytes(uint32_t n_dst, int K
                                                            int c_out, int dtype) {
   if (K < 1 || c_in < 1 || c_out < 1) return 0;
   size_t need = 0;
-  if (dtype == RMN_BF16 && use_tensor_cores() &&
+  if (dtype == RMN_BF16 &&
       tc_conv_wgrad(nullptr, nullptr, nullptr, n_dst, K, c_in, c_out, nullptr, nullptr, 0, &need, nullptr) == RMN_OK)
     return need;
   return simt_wgrad_workspace_bytes(n_dst, K, c_in, c_out);
@@ -144,7 +136,7 @@ extern "C" int rmn_conv_backward_weight(const void* d_feats, uint32_t n_src, int
     return RMN_ERR_BAD_ARG;
   if (workspace_bytes < rmn_conv_backward_weight_workspace_bytes(n_dst, K, c_in, c_out, dtype))
     return RMN_ERR_ALLOC;
-  if (dtype == RMN_BF16 && use_tensor_cores()) {
+  if (dtype == RMN_BF16) {
     size_t need = 0;
     const int st = tc_conv_wgrad(d_feats, d_grad_out, d_nbr, n_dst, K, c_in, c_out, d_grad_weights, d_workspace,
                                  workspace_bytes, &need, stream);

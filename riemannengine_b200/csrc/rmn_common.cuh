@@ -45,7 +45,12 @@ struct __align__(16) TableHeader {
   // both are running maxima: mx_enc = max(v ^ 0x80000000), mn_enc = max(~(v ^ 0x80000000)).
   uint32_t mn_enc[RMN_MAX_W];
   uint32_t mx_enc[RMN_MAX_W];
-  uint32_t pad[6];
+  // Bits of the first spatial column that are the same in every row (the rows of a map at tensor
+  // stride 2^s sit on a 2^s grid): x_or is the OR over the rows of (x - x of row 0), pos_shift its
+  // number of trailing zeros. The position inside a bucket is taken from the bits above them.
+  uint32_t x_or;
+  uint32_t pos_shift;
+  uint32_t pad[4];
 };
 static_assert(sizeof(TableHeader) == 256, "header must be 256 bytes");
 
@@ -79,20 +84,23 @@ struct Packer {
   }
 };
 
-// Slot of a key: the low three bits of the key (the low bits of the first spatial column, which
-// is packed first) select the position inside an 8-slot (128-byte) bucket; the remaining bits
-// are mixed to 32 bits and range-reduced (multiply-shift) onto the bucket index. Eight voxels
-// that are consecutive along the first spatial axis therefore share one 128-byte line, so the
-// x-1 / x / x+1 probes of a kernel map hit the line the thread has just pulled into L1.
-// Collisions step to the same position of the next bucket.
-__device__ __forceinline__ uint32_t hash_key(unsigned long long k, uint32_t capacity) {
-  const unsigned long long b = k >> 3;
+// Slot of a key: three bits of the first spatial column (packed first, so they are key bits
+// [pos_shift, pos_shift + 3)) select the position inside an 8-slot (128-byte) bucket; the bits
+// above them are mixed to 32 bits and range-reduced (multiply-shift) onto the bucket index.
+// pos_shift skips the low bits that are equal in all rows of the table (a map at tensor stride 4
+// only has x = 0 mod 4: taking the raw low three bits would leave six of the eight positions of
+// every bucket unused). Eight voxels that are consecutive along the first spatial axis (in units
+// of the map's grid) therefore share one 128-byte line, so the x-1 / x / x+1 probes of a kernel
+// map hit the line the thread has just pulled into L1. Collisions step to the same position of
+// the next bucket. A query key whose low pos_shift bits are not zero matches no stored key.
+__device__ __forceinline__ uint32_t hash_key(unsigned long long k, uint32_t capacity, uint32_t pos_shift) {
+  const unsigned long long b = k >> (3u + pos_shift);
   uint32_t h = (uint32_t)b ^ ((uint32_t)(b >> 32) * 0x9E3779B1u);
   h *= 0x85ebca6bu;
   h ^= h >> 13;
   h *= 0xc2b2ae35u;
   h ^= h >> 16;
-  return __umulhi(h, capacity >> 3) * 8u + ((uint32_t)k & 7u);
+  return __umulhi(h, capacity >> 3) * 8u + ((uint32_t)(k >> pos_shift) & 7u);
 }
 __device__ __forceinline__ uint32_t next_slot(uint32_t s, uint32_t capacity) {
   s += 8u;
@@ -104,9 +112,9 @@ __device__ __forceinline__ ulonglong2 load_slot(const Slot* s) {
 }
 
 // Lookup; returns uid or 0xFFFFFFFF. Probing is bounded by the bucket count.
-__device__ __forceinline__ uint32_t table_find(const Slot* slots, uint32_t capacity,
+__device__ __forceinline__ uint32_t table_find(const Slot* slots, uint32_t capacity, uint32_t pos_shift,
                                                unsigned long long key) {
-  uint32_t s = hash_key(key, capacity);
+  uint32_t s = hash_key(key, capacity, pos_shift);
   for (uint32_t probe = 0; probe < (capacity >> 3); ++probe) {
     ulonglong2 v = load_slot(slots + s);
     if (v.x == key) return (uint32_t)(v.y >> 32);

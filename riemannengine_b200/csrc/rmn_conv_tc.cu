@@ -35,22 +35,14 @@
 
 #include <cuda_bf16.h>
 
+#include <mutex>
+
 namespace rmn {
 
+// Sticky status word of the tensor-core kernels, one per device (not per stream): a kernel whose
+// bounded wait ran out stores RMN_ERR_TIMEOUT here and returns early. Hosts read it (and clear it)
+// through rmn_device_status, and rmn_table_info reports it at the read-back every table build makes.
 __device__ uint32_t g_tc_status = 0;
-#ifdef RMN_PROF
-__device__ unsigned long long g_prof[16];
-extern "C" int rmn_debug_prof(unsigned long long* out, int reset) {
-  if (out) cudaMemcpyFromSymbol(out, g_prof, sizeof(g_prof));
-  if (reset) { unsigned long long z[16] = {}; cudaMemcpyToSymbol(g_prof, z, sizeof(z)); }
-  return 0;
-}
-#define PROF_T0() const long long _t0 = clock64()
-#define PROF_ADD(var) var += clock64() - _t0
-#else
-#define PROF_T0()
-#define PROF_ADD(var)
-#endif
 
 namespace tc {
 
@@ -183,9 +175,6 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
     constexpr int ROWS_PER_INSTR = 32 / A_CPL;
     const uint32_t a_chunk = lane % A_CPL, a_row_sub = lane / A_CPL;
     uint32_t it = 0;
-#ifdef RMN_PROF
-    long long prof_wait = 0; const long long prof_start = clock64();
-#endif
 
     for (uint32_t st = blockIdx.x; st < n_super && !timed_out; st += gridDim.x) {
       const uint32_t row = st * (kTileM * T) + warp * 32 + lane;
@@ -201,11 +190,7 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
 #pragma unroll 1
         for (int kb = 0; kb < NKB; ++kb, ++it) {
           const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-          {
-            PROF_T0();
-            if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
-            PROF_ADD(prof_wait);
-          }
+          if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
           const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
 
           if (has_rows) {
@@ -264,9 +249,6 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
         }
       }
     }
-#ifdef RMN_PROF
-    if (lane == 0 && warp == 0) { atomicAdd(&g_prof[0], (unsigned long long)prof_wait); atomicAdd(&g_prof[1], (unsigned long long)(clock64() - prof_start)); }
-#endif
     cp_async_wait<0>();  // nothing may still be writing shared memory when the CTA exits
   } else if (warp == kFwdProducerWarps) {
     // ------------------------------ MMA issuer -----------------------------------------
@@ -276,26 +258,15 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
     constexpr uint64_t B_DESC0 = kWT ? smem_desc_sw_const(16, 8 * SWB, LT_B) : smem_desc_sw_const(B_ATOM_BYTES, 8 * SWB, LT_B);
     constexpr uint32_t A_DESC_HI = (uint32_t)(A_DESC0 >> 32), B_DESC_HI = (uint32_t)(B_DESC0 >> 32);
     uint32_t it = 0, tile_iter = 0;
-#ifdef RMN_PROF
-    long long prof_wait = 0, prof_wait_acc = 0; const long long prof_start = clock64();
-#endif
     for (uint32_t st = blockIdx.x; st < n_super && !timed_out; st += gridDim.x, ++tile_iter) {
       const uint32_t acc = tile_iter & 1u, acc_ph = (tile_iter >> 1) & 1u;
-      {
-        PROF_T0();
-        if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { timed_out = true; break; }
-        PROF_ADD(prof_wait_acc);
-      }
+      if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { timed_out = true; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * (T * CC);
       const uint32_t n_stage = (uint32_t)K * NKB;
       for (uint32_t sg = 0; sg < n_stage; ++sg, ++it) {
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-        {
-          PROF_T0();
-          if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
-          PROF_ADD(prof_wait);
-        }
+        if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
         // the copies were generic-proxy writes; the tensor core reads through the async proxy
         fence_proxy_async();
         tc_fence_after();
@@ -330,9 +301,6 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
       if (timed_out) break;
       tc_commit_elect(&tmem_full[acc]);
     }
-#ifdef RMN_PROF
-    if (lane == 0) { atomicAdd(&g_prof[2], (unsigned long long)prof_wait); atomicAdd(&g_prof[3], (unsigned long long)prof_wait_acc); atomicAdd(&g_prof[4], (unsigned long long)(clock64() - prof_start)); }
-#endif
   } else {
     // ------------------------------ epilogue -------------------------------------------
     const uint32_t quad = warp & 3;  // TMEM lanes [32*quad, 32*quad + 32)
@@ -430,13 +398,18 @@ int launch(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, i
            float* stats_partial = nullptr, uint32_t* grid_out = nullptr) {
   using C = Cfg<CR, CC>;
   auto kern = k_conv_tc<CR, CC, kWT, kStats>;
-  static bool configured[64] = {};
+  // once per device and instantiation, safe when several host threads make the first call together
+  static std::once_flag configured[64];
   int dev = 0;
   RMN_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
-    RMN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
-    configured[dev] = true;
-  }
+  cudaError_t attr_err = cudaSuccess;
+  if (dev >= 0 && dev < 64)
+    std::call_once(configured[dev], [&] {
+      attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+    });
+  else
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+  RMN_CUDA_TRY(attr_err);
   int sms = 148;
   RMN_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const uint32_t rows_per_super = kTileM * C::T;
@@ -530,9 +503,28 @@ int tc_conv_stats(const void* src, uint32_t n_src, const void* w, const int32_t*
   return RMN_ERR_UNSUPPORTED;
 }
 
+// Synchronises `stream`, returns the status word and resets it when it was set, so that one
+// time-out is reported once and later queries start clean.
 int tc_read_status(cudaStream_t stream, uint32_t* status) {
   RMN_CUDA_TRY(cudaStreamSynchronize(stream));
   RMN_CUDA_TRY(cudaMemcpyFromSymbol(status, g_tc_status, sizeof(uint32_t)));
+  if (*status != 0) {
+    const uint32_t zero = 0;
+    RMN_CUDA_TRY(cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(uint32_t)));
+  }
+  return RMN_OK;
+}
+
+// Queues a copy of the status word into page-locked host memory on `stream` (no synchronisation):
+// for hosts that already wait on that stream for something else.
+int tc_copy_status_async(uint32_t* host_dst, cudaStream_t stream) {
+  RMN_CUDA_TRY(cudaMemcpyFromSymbolAsync(host_dst, g_tc_status, sizeof(uint32_t), 0, cudaMemcpyDeviceToHost, stream));
+  return RMN_OK;
+}
+
+int tc_clear_status() {
+  const uint32_t zero = 0;
+  RMN_CUDA_TRY(cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(uint32_t)));
   return RMN_OK;
 }
 

@@ -262,13 +262,17 @@ int launch_tma(const void* src, uint32_t n_src, const void* w, const int32_t* nb
                         : make_map_bf16(&map_w, w, (uint64_t)K * CIN_W, COUT_W, KB, CC < 64 ? CC : 64);
   if (!ok_w) return RMN_ERR_UNSUPPORTED;
   auto kern = k_conv_tma<CR, CC, kWT>;
-  static bool configured[64] = {};
+  static std::once_flag configured[64];
   int dev = 0;
   RMN_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
-    RMN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
-    configured[dev] = true;
-  }
+  cudaError_t attr_err = cudaSuccess;
+  if (dev >= 0 && dev < 64)
+    std::call_once(configured[dev], [&] {
+      attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+    });
+  else
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+  RMN_CUDA_TRY(attr_err);
   int sms = 148;
   RMN_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const uint32_t rows_per_super = kTileM * C::T;

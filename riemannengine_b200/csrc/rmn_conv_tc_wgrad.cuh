@@ -152,9 +152,6 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
       if (++pf_sg == n_sg) { pf_sg = 0; ++pf_blk; }
       return out;
     };
-#ifdef RMN_PROF
-    long long prof_wait = 0; const long long prof_start = clock64();
-#endif
     Entries idx_w0 = load_indices(), idx_w1 = load_indices(), idx_w2 = load_indices(), idx_w3 = load_indices(),
             idx_w4 = load_indices(), idx_w5 = load_indices();
     for (uint32_t blk = 0; blk < n_blocks && !timed_out; ++blk) {
@@ -179,11 +176,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
           idx[i] = got;
         }
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-        {
-          PROF_T0();
-          if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
-          PROF_ADD(prof_wait);
-        }
+        if (!mbar_wait(&empty[s], ph ^ 1u)) { timed_out = true; break; }
         const uint32_t a_s = smem_base + s * C::STAGE, b_s = a_s + C::A_BYTES;
 #pragma unroll
         for (int i = 0; i < kWgIdxPerThread; ++i) {
@@ -207,9 +200,6 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
         cp_async_arrive_noinc(&full[s]);  // fires when this thread's copies have landed
       }
     }
-#ifdef RMN_PROF
-    if (tid == 0) { atomicAdd(&g_prof[8], (unsigned long long)prof_wait); atomicAdd(&g_prof[10], (unsigned long long)(clock64() - prof_start)); }
-#endif
     cp_async_wait<0>();
     // ------------------------------ epilogue (first four producer warps) ----------------
     if (warp < 4) {
@@ -247,17 +237,10 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
     constexpr uint64_t B_DESC0 = smem_desc_sw_const(B_ATOM, 8 * SWB, LT_B);
     constexpr uint32_t A_DESC_HI = (uint32_t)(A_DESC0 >> 32), B_DESC_HI = (uint32_t)(B_DESC0 >> 32);
     uint32_t it = 0;
-#ifdef RMN_PROF
-    long long prof_wait = 0; const long long prof_start = clock64();
-#endif
     for (uint32_t blk = 0; blk < n_blocks && !timed_out; ++blk) {
       for (int sg = 0; sg < n_sg; ++sg, ++it) {
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
-        {
-          PROF_T0();
-          if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
-          PROF_ADD(prof_wait);
-        }
+        if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
         fence_proxy_async();  // cp.async wrote through the generic proxy; the MMA reads through the async proxy
         tc_fence_after();
         {
@@ -293,9 +276,6 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
         }
       }
     }
-#ifdef RMN_PROF
-    if (lane == 0) { atomicAdd(&g_prof[11], (unsigned long long)prof_wait); atomicAdd(&g_prof[12], (unsigned long long)(clock64() - prof_start)); }
-#endif
     if (!timed_out) tc_commit_elect(done);
   }
 
@@ -356,11 +336,15 @@ int launch_wgrad(const void* feats, const void* grad_out, const int32_t* nbr, ui
   if (!feats) return RMN_OK;  // size query
   if (workspace_bytes < *need) return RMN_ERR_ALLOC;
   auto kern = k_conv_tc_wgrad<CIN, COUT>;
-  static bool configured[64] = {};
-  if (dev < 64 && !configured[dev]) {
-    RMN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM));
-    configured[dev] = true;
-  }
+  static std::once_flag configured[64];
+  cudaError_t attr_err = cudaSuccess;
+  if (dev >= 0 && dev < 64)
+    std::call_once(configured[dev], [&] {
+      attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+    });
+  else
+    attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
+  RMN_CUDA_TRY(attr_err);
   dim3 grid(p.chunks, p.sets);
   kern<<<grid, kWgradThreads, C::SMEM, stream>>>((const __nv_bfloat16*)feats, (const __nv_bfloat16*)grad_out, nbr,
                                                  n_dst, K, p.groups_per_set, p.tmem_cols,

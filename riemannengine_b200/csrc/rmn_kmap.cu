@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe(
   }
   __syncthreads();
 
-  const uint32_t capacity = h->capacity;
+  const uint32_t capacity = h->capacity, pos_shift = h->pos_shift;
   const uint32_t q = blockIdx.x * kKmapBlock + threadIdx.x;
   const bool active = q < n_query;
   int32_t c[W];
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe(
       for (int a = 0; a < D; ++a) in_box = in_box && (dist[a + 1] + (uint32_t)s_off[k * D + a] <= span[a + 1]);
       valid[u] = in_box;
       key[u] = (unsigned long long)(ckey + s_delta[k]);
-      slot[u] = hash_key(key[u], capacity);
+      slot[u] = hash_key(key[u], capacity, pos_shift);
       first[u] = make_ulonglong2(kEmptyKey, 0ull);
       if (in_box) first[u] = load_slot(slots + slot[u]);
     }
@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe_self(
   }
   __syncthreads();
 
-  const uint32_t capacity = h->capacity;
+  const uint32_t capacity = h->capacity, pos_shift = h->pos_shift;
   const uint32_t q = blockIdx.x * kKmapBlock + threadIdx.x;
   const bool active = q < n;
   int32_t c[W];
@@ -166,7 +166,7 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe_self(
 #pragma unroll
     for (int a = 0; a < D; ++a) in_box = in_box && (dist[a + 1] + (uint32_t)s_off[k * D + a] <= span[a + 1]);
     uint32_t uid = 0xFFFFFFFFu;
-    if (in_box) uid = table_find(slots, capacity, (unsigned long long)(ckey + s_delta[k]));
+    if (in_box) uid = table_find(slots, capacity, pos_shift, (unsigned long long)(ckey + s_delta[k]));
     if (active) {
       __stcs(nbr + (size_t)k * n + q, (int32_t)uid);
       if (uid != 0xFFFFFFFFu) nbr[(size_t)(K - 1 - k) * n + uid] = (int32_t)q;  // mirror entry
@@ -232,6 +232,7 @@ __global__ void k_kmap_offset_ptr(uint32_t* __restrict__ totals, int K, int64_t*
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   for (int k = K - mirror_half; k < K; ++k) totals[k] = totals[K - 1 - k];
   *mirror_flag = (uint32_t)mirror_half;
+  totals[K] = 0;  // "pair lists did not fit" flag of rmn_kmap_pairs (read by rmn_kmap_pairs_status)
   int64_t run = 0;
   for (int k = 0; k < K; ++k) {
     offset_ptr[k] = run;
@@ -466,7 +467,7 @@ static int kmap_pairs_launch(const int32_t* d_nbr, uint32_t n_query, int K, cons
   if (!d_nbr || !d_a_idx || !d_q_idx) return RMN_ERR_BAD_ARG;
   const uint32_t nb = kmap_blocks(n_query);
   const uint32_t* block_prefix = reinterpret_cast<const uint32_t*>(d_workspace);
-  // the word after the totals flags a capacity overflow (kept for debugging reads)
+  // the word after the totals flags a capacity overflow (zeroed by the build, read by rmn_kmap_pairs_status)
   uint32_t* overflow = const_cast<uint32_t*>(block_prefix) + (size_t)K * nb + K;
   if (!background) {
     k_kmap_pairs<<<nb, kKmapBlock, 0, stream>>>(d_nbr, n_query, K, d_offset_ptr, block_prefix, nb, d_a_idx,
@@ -485,6 +486,17 @@ static int kmap_pairs_launch(const int32_t* d_nbr, uint32_t n_query, int K, cons
   }
   RMN_LAUNCH_CHECK();
   return RMN_OK;
+}
+
+extern "C" int rmn_kmap_pairs_status(const void* d_workspace, uint32_t n_query, int K, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  if (K < 1 || !d_workspace) return RMN_ERR_BAD_ARG;
+  if (n_query == 0) return RMN_OK;
+  const uint32_t* flag = reinterpret_cast<const uint32_t*>(d_workspace) + (size_t)K * kmap_blocks(n_query) + K;
+  uint32_t v = 0;
+  RMN_CUDA_TRY(cudaMemcpyAsync(&v, flag, sizeof(v), cudaMemcpyDeviceToHost, stream));
+  RMN_CUDA_TRY(cudaStreamSynchronize(stream));
+  return v ? RMN_ERR_ALLOC : RMN_OK;
 }
 
 extern "C" int rmn_kmap_pairs(const int32_t* d_nbr, uint32_t n_query, int K,

@@ -8,7 +8,6 @@
 
 #include <cuda_bf16.h>
 
-bool use_tensor_cores();  // rmn_capi.cu
 
 namespace rmn {
 
@@ -151,7 +150,7 @@ extern "C" int rmn_conv_forward_stats(const void* d_feats, uint32_t n_src, int c
   }
   if (!d_workspace) return RMN_ERR_BAD_ARG;
   if (workspace_bytes < rmn_channel_stats_workspace_bytes(c_out)) return RMN_ERR_ALLOC;
-  if (dtype == RMN_BF16 && use_tensor_cores() && n_src > 0 && d_feats && d_weights && d_nbr && d_out && K >= 1) {
+  if (dtype == RMN_BF16 && n_src > 0 && d_feats && d_weights && d_nbr && d_out && K >= 1) {
     uint32_t n_partials = 0;
     const int st = tc_conv_stats(d_feats, n_src, d_weights, d_nbr, n_dst, K, c_in, c_out, d_out, d_scale, d_shift,
                                  relu, (float*)d_workspace, &n_partials, stream);

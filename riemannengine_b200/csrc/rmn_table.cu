@@ -22,6 +22,9 @@
 
 namespace rmn {
 
+int tc_copy_status_async(uint32_t* host_dst, cudaStream_t stream);  // rmn_conv_tc.cu
+int tc_clear_status();
+
 constexpr int kRowsPerBlock = 256;
 
 __device__ void plan_packing(TableHeader* h);
@@ -34,17 +37,23 @@ template <int W>
 __global__ void __launch_bounds__(256) k_fill_range(const int32_t* __restrict__ coords, uint32_t n,
                                                     TableHeader* h, uint4* __restrict__ slots, uint32_t capacity) {
   __shared__ int32_t s_mn[8][W], s_mx[8][W];
+  __shared__ uint32_t s_or[8];
   const uint4 ones = make_uint4(~0u, ~0u, ~0u, ~0u);
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < capacity; i += gridDim.x * blockDim.x)
     slots[i] = ones;
   int32_t mn[W], mx[W];
 #pragma unroll
   for (int c = 0; c < W; ++c) { mn[c] = INT_MAX; mx[c] = INT_MIN; }
+  // OR of (x - x of row 0) over the rows: its trailing zeros are the bits of the first spatial
+  // column that all rows share
+  const uint32_t x0 = n > 0 ? (uint32_t)__ldg(coords + 1) : 0u;
+  uint32_t x_or = 0;
   for (uint32_t r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
     int32_t v[W];
     load_row<W>(coords, r, v);
 #pragma unroll
     for (int c = 0; c < W; ++c) { mn[c] = min(mn[c], v[c]); mx[c] = max(mx[c], v[c]); }
+    x_or |= (uint32_t)v[1] - x0;
   }
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
@@ -53,6 +62,8 @@ __global__ void __launch_bounds__(256) k_fill_range(const int32_t* __restrict__ 
     const int32_t b = __reduce_max_sync(0xFFFFFFFFu, mx[c]);
     if (lane == 0) { s_mn[warp][c] = a; s_mx[warp][c] = b; }
   }
+  x_or = __reduce_or_sync(0xFFFFFFFFu, x_or);
+  if (lane == 0) s_or[warp] = x_or;
   __syncthreads();
   // one atomic per block and column (per-warp atomics on eight addresses serialise badly); blocks that
   // saw no row leave the zero ("no row yet") in place
@@ -62,6 +73,12 @@ __global__ void __launch_bounds__(256) k_fill_range(const int32_t* __restrict__ 
     for (int w2 = 1; w2 < 8; ++w2) { a = min(a, s_mn[w2][threadIdx.x]); b = max(b, s_mx[w2][threadIdx.x]); }
     atomicMax(&h->mn_enc[threadIdx.x], ~((uint32_t)a ^ 0x80000000u));
     atomicMax(&h->mx_enc[threadIdx.x], (uint32_t)b ^ 0x80000000u);
+  }
+  if (threadIdx.x == 32 && blockIdx.x * blockDim.x < n) {
+    uint32_t o = 0;
+#pragma unroll
+    for (int w2 = 0; w2 < 8; ++w2) o |= s_or[w2];
+    if (o) atomicOr(&h->x_or, o);
   }
   __threadfence();
   __syncthreads();
@@ -78,6 +95,10 @@ __global__ void __launch_bounds__(256) k_fill_range(const int32_t* __restrict__ 
       h->mx[c] = (c < W && n > 0) ? (int32_t)(ex ^ 0x80000000u) : 0;
       h->bits[c] = 0;
       h->shift[c] = 0;
+    }
+    {
+      const uint32_t o = *(volatile uint32_t*)&h->x_or;
+      h->pos_shift = o ? (uint32_t)(__ffs((int)o) - 1) : 0u;
     }
     plan_packing(h);
   }
@@ -132,7 +153,7 @@ __global__ void __launch_bounds__(256) k_insert(const int32_t* __restrict__ coor
   load_row<W>(coords, row, c);
   unsigned long long key;
   pk.pack(c, key);
-  uint32_t s = hash_key(key, capacity);
+  uint32_t s = hash_key(key, capacity, h->pos_shift);
   bool placed = false;
   // One 16-byte compare-and-swap claims a free slot (all ones) with {key, first_row = row,
   // uid = row}: without duplicates the unique numbering is the row numbering and the slot is
@@ -296,7 +317,7 @@ __global__ void __launch_bounds__(256) k_find(const TableHeader* __restrict__ h,
   load_row<W>(query, q, c);
   unsigned long long key;
   uint32_t uid = 0xFFFFFFFFu;
-  if (pk.pack(c, key)) uid = table_find(slots, capacity, key);
+  if (pk.pack(c, key)) uid = table_find(slots, capacity, h->pos_shift, key);
   rows[q] = (int32_t)uid;
 }
 
@@ -615,18 +636,29 @@ extern "C" int rmn_table_info(const void* d_table, uint32_t info[4], void* strea
   // The header is read back through a page-locked staging block owned by the calling thread: a copy into
   // pageable memory is staged by the driver and costs several microseconds more, and this read-back is the
   // one host synchronisation of a table build.
-  thread_local TableHeader* staging = nullptr;
+  // The same wait also brings back the status word of the convolution kernels (a bounded wait that ran out
+  // in a kernel queued before this read-back on a stream this one is ordered after): every table build
+  // of a host thus checks the convolutions that went before it without a synchronisation of its own.
+  struct Staging {
+    TableHeader header;
+    uint32_t conv_status;
+  };
+  thread_local Staging* staging = nullptr;
   if (!staging) {
     void* p = nullptr;
-    if (cudaHostAlloc(&p, sizeof(TableHeader), cudaHostAllocPortable) != cudaSuccess) {
+    if (cudaHostAlloc(&p, sizeof(Staging), cudaHostAllocPortable) != cudaSuccess) {
       cudaGetLastError();
       p = nullptr;
     }
-    staging = static_cast<TableHeader*>(p);
+    staging = static_cast<Staging*>(p);
   }
   TableHeader pageable;
-  TableHeader* dst = staging ? staging : &pageable;
+  TableHeader* dst = staging ? &staging->header : &pageable;
   RMN_CUDA_TRY(cudaMemcpyAsync(dst, d_table, sizeof(TableHeader), cudaMemcpyDeviceToHost, stream));
+  if (staging) {
+    staging->conv_status = 0;
+    RMN_CUDA_TRY(tc_copy_status_async(&staging->conv_status, stream) == RMN_OK ? cudaSuccess : cudaErrorUnknown);
+  }
   RMN_CUDA_TRY(cudaStreamSynchronize(stream));
   const TableHeader h = *dst;
   if (h.magic != kTableMagic) return RMN_ERR_BAD_ARG;
@@ -634,6 +666,11 @@ extern "C" int rmn_table_info(const void* d_table, uint32_t info[4], void* strea
   info[1] = h.status;
   info[2] = h.capacity;
   info[3] = h.n_rows;
+  if (h.status == RMN_OK && staging && staging->conv_status != 0) {
+    const int st = (int)staging->conv_status;
+    tc_clear_status();
+    return st;
+  }
   return (int)h.status;
 }
 

@@ -42,38 +42,49 @@ def allreduce_gradients(params: Iterable[torch.nn.Parameter], group: Optional[di
                         average: bool = False, bucket_bytes: int = 64 << 20) -> int:
     """Sum (or average) the gradients of ``params`` over the ranks with as few collectives as
     possible: gradients are packed into flat fp32 buckets of at most ``bucket_bytes``.
+
+    The bucket layout is a function of the parameter list alone, so every rank issues the same
+    collectives with the same lengths whatever happened locally: a parameter whose gradient is
+    ``None`` on this rank (a rank that was given no sample, a layer that a step did not use)
+    contributes zeros and receives the reduced value as its gradient. Parameters that do not
+    require a gradient are skipped on every rank alike.
     Returns the number of collectives issued. A no-op outside an initialised process group."""
     if not (dist.is_available() and dist.is_initialized()):
         return 0
     world = dist.get_world_size(group)
-    grads = [p.grad for p in params if p.grad is not None]
-    if world == 1 or not grads:
+    plist = [p for p in params if p.requires_grad]
+    if world == 1 or not plist:
         return 0
     calls = 0
-    bucket: List[torch.Tensor] = []
+    bucket: List[torch.nn.Parameter] = []
     size = 0
 
     def flush():
         nonlocal bucket, size, calls
         if not bucket:
             return
-        flat = torch.cat([g.reshape(-1).float() for g in bucket])
+        flat = torch.cat([(p.grad.reshape(-1).float() if p.grad is not None
+                           else torch.zeros(p.numel(), dtype=torch.float32, device=p.device)) for p in bucket])
         dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
         if average:
             flat /= world
         off = 0
-        for g in bucket:
-            n = g.numel()
-            g.copy_(flat[off:off + n].view_as(g))
+        for p in bucket:
+            n = p.numel()
+            piece = flat[off:off + n].view(p.shape)
+            if p.grad is None:
+                p.grad = piece.to(p.dtype).clone()
+            else:
+                p.grad.copy_(piece)
             off += n
         calls += 1
         bucket, size = [], 0
 
-    for g in grads:
-        nbytes = g.numel() * 4
+    for p in plist:
+        nbytes = p.numel() * 4
         if bucket and size + nbytes > bucket_bytes:
             flush()
-        bucket.append(g)
+        bucket.append(p)
         size += nbytes
     flush()
     return calls

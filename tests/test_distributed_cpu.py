@@ -44,8 +44,9 @@ def _worker(rank, world, port, out):
               torch.nn.Parameter(torch.zeros(1, 16)), torch.nn.Parameter(torch.zeros(3))]
     for i, p in enumerate(params[:3]):
         p.grad = torch.full_like(p, float(rank + 1) * (i + 1))
-    calls_one = D.allreduce_gradients(params)  # the parameter without a gradient is skipped
+    calls_one = D.allreduce_gradients(params)  # the parameter without a gradient anywhere reduces to zeros
     ok = all(torch.equal(p.grad, torch.full_like(p, 3.0 * (i + 1))) for i, p in enumerate(params[:3]))
+    ok = ok and params[3].grad is not None and torch.equal(params[3].grad, torch.zeros(3))
     for i, p in enumerate(params[:3]):
         p.grad = torch.full_like(p, float(rank + 1))
     calls_many = D.allreduce_gradients(params, average=True, bucket_bytes=4096)
@@ -65,6 +66,31 @@ def test_bucketed_allreduce_two_ranks_gloo():
             assert ok
             assert calls_one == 1          # everything fits one bucket
             assert calls_many >= 2         # small buckets -> several collectives, same result
+
+
+def _uneven_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # rank 1 was given no sample: every gradient is None there; rank 0 left one layer unused
+    params = [torch.nn.Parameter(torch.zeros(27, 4, 4)), torch.nn.Parameter(torch.zeros(5)),
+              torch.nn.Parameter(torch.zeros(2, 2), requires_grad=False)]
+    if rank == 0:
+        params[0].grad = torch.full_like(params[0], 2.0)
+    calls = D.allreduce_gradients(params, average=True)
+    ok = calls == 1 and torch.equal(params[0].grad, torch.full_like(params[0], 1.0))
+    ok = ok and torch.equal(params[1].grad, torch.zeros(5)) and params[2].grad is None
+    out[rank] = bool(ok)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_allreduce_with_missing_gradients_on_one_rank_gloo():
+    """Ranks whose gradients are None for some (or all) parameters still issue the same collective."""
+    world = 2
+    with mp.Manager() as m:
+        out = m.dict()
+        mp.spawn(_uneven_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+        assert all(out[r] for r in range(world))
 
 
 def test_allreduce_is_noop_without_process_group():

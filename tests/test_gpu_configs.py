@@ -105,3 +105,53 @@ def test_engine_lidar_unet_slice_runs_and_backpropagates():
     assert torch.isfinite(feats.grad.float()).all()
     for m in layers:
         assert m.kernel.grad is not None and torch.isfinite(m.kernel.grad.float()).all()
+
+
+# ---------------------------------------------------------------------------------------------
+# The benchmarked workload itself, at its own size, against the reference's CPU build
+# (oracle/_ref/ref_driver: engine/grid/lattice_cpu.hpp:606-673 for the pair sets,
+# engine/nn/conv.cpp:9-66 for the values).
+# ---------------------------------------------------------------------------------------------
+def _reference_as_gold(coords, feats, weights, kernel, stride):
+    from oracle import refrun
+    if not refrun.available():
+        pytest.skip("reference driver not built (make -C oracle ref)")
+    out = refrun.run(coords, feats, weights, kernel, stride, 1, timeout=1200)
+    return {"ref_" + k: v for k, v in out.items()}
+
+
+@pytest.mark.parametrize("scenes", [1, 8])
+def test_indoor_rooms_3x3x3_64_to_64_against_reference(scenes):
+    """Whole rooms of the headline batch (150 K voxels each; one room, then all eight = 1.2 M voxels):
+    coordinate map and kernel map bit-exact against the reference, fp32 path within 1e-4, and the bf16
+    tensor-core output within 1e-2 relative L2 of the reference's fp32 output."""
+    from riemannengine_b200 import synthetic
+    from tests.gpu_backend import GpuBackend
+    c = synthetic.indoor_batch(scenes, 150_000, seed=2000)
+    f = synthetic.features(2500, len(c), 64)
+    w = synthetic.conv_weights(2600, 27, 64, 64)
+    gold = _reference_as_gold(c, f, w, 3, 1)
+    assert len(gold["ref_in_coords"]) == scenes * 150_000
+    r32 = parity.run_pipeline(GpuBackend(torch.float32), c, f, w, 3, 3, 1, 1)
+    parity.check_against_reference(r32, gold, tol=1e-4, metric=rel_max)
+    fb = torch.from_numpy(f).bfloat16().float().numpy()      # the bf16 path sees rounded inputs
+    rb = parity.run_pipeline(GpuBackend(torch.bfloat16), c, fb, w, 3, 3, 1, 1)
+    assert (rb["kmap_ptr"] == gold["ref_kmap_ptr"]).all()
+    assert rel_l2(rb["out_feats"], gold["ref_out_feats"]) <= 1e-2
+    assert rel_l2(rb["grad_weights"], gold["ref_grad_weights"]) <= 3e-2   # two bf16 roundings compound
+
+
+def test_indoor_room_2x2x2_stride2_64_to_128_against_reference():
+    """The workload's second layer on one whole room: strided coordinate map (matched by coordinate: the
+    reference numbers coarse rows in hash order), kernel map, fp32 and bf16 outputs."""
+    from riemannengine_b200 import synthetic
+    from tests.gpu_backend import GpuBackend
+    c = synthetic.indoor_batch(1, 150_000, seed=2000)
+    f = synthetic.features(2500, len(c), 64)
+    w = synthetic.conv_weights(2601, 8, 64, 128)
+    gold = _reference_as_gold(c, f, w, 2, 2)
+    r32 = parity.run_pipeline(GpuBackend(torch.float32), c, f, w, 3, 2, 2, 1)
+    parity.check_against_reference(r32, gold, tol=1e-4, metric=rel_max)
+    rb = parity.run_pipeline(GpuBackend(torch.bfloat16), c, f, w, 3, 2, 2, 1)
+    perm = parity.row_permutation(rb["out_coords"], gold["ref_out_coords"])
+    assert rel_l2(rb["out_feats"], gold["ref_out_feats"][perm]) <= 1e-2

@@ -380,3 +380,49 @@ def test_two_call_table_build_header_is_final_after_the_first_call(gpu, dups):
     rows = torch.empty(n, dtype=torch.int32, device="cuda")
     assert lib.rmn_table_find(p(table), p(coords), n, w, p(rows), sm) == capi.OK
     assert torch.equal(rows.long(), ref.inverse)
+
+
+# ---------------------------------------------------------------------------------------------
+# Maps at coarse tensor strides: every coordinate is a multiple of the stride, so the low bits of
+# the first spatial column are the same in all rows; the table must still use its whole capacity.
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("ts", [4, 8, 16, 6])
+def test_insert_unique_rows_on_a_coarse_grid(gpu, ts):
+    rng = np.random.default_rng(100 + ts)
+    c = np.concatenate([rng.integers(0, 2, (60000, 1)), rng.integers(-40, 41, (60000, 3)) * ts], 1).astype(np.int32)
+    c = c[OracleBackend().insert_and_map(c)[0]]          # all rows distinct: the table's worst case
+    c[:, 1:] += 3                                         # and the grid need not pass through the origin
+    m0, i0 = OracleBackend().insert_and_map(c)
+    m1, i1 = gpu().insert_and_map(c)
+    assert (m0 == m1).all() and (i0 == i1).all()
+    # kernel map on that grid (offsets are multiples of the tensor stride)
+    O = OracleBackend()
+    off = O.region_offsets([3] * 3, [1] * 3, [ts] * 3)
+    parity.assert_kernel_maps_equal(gpu().conv_kernel_map(c, c, off), O.conv_kernel_map(c, c, off))
+    # lookups of rows off the grid miss, rows on it hit
+    from riemannengine_b200 import ops
+    from tests.gpu_backend import dev_coords
+    t = ops.table_build(dev_coords(c))
+    shifted = c.copy()
+    shifted[:, 1] += 1
+    assert (ops.table_find(t, dev_coords(shifted)).cpu().numpy() == -1).all()
+    assert (ops.table_find(t, dev_coords(c)).cpu().numpy() == np.arange(len(c))).all()
+
+
+def test_three_stride2_levels_on_a_sparse_cloud(gpu):
+    """Stride 2 -> 4 -> 8 on a cloud so sparse that almost every row stays unique at every level
+    (LiDAR-like): coordinate maps and the 3^3 kernel map of every level against the oracle."""
+    O = OracleBackend()
+    rng = np.random.default_rng(77)
+    c = np.concatenate([rng.integers(0, 2, (50000, 1)), rng.integers(-2000, 2001, (50000, 3))], 1).astype(np.int32)
+    c = c[O.insert_and_map(c)[0]]
+    ts = 1
+    for level in range(3):
+        ts *= 2
+        a0, i0 = O.stride_map(c, [ts] * 3)
+        a1, i1 = gpu().stride_map(c, [ts] * 3)
+        assert (a0 == a1).all() and (i0 == i1).all()
+        assert len(a0) > 0.9 * len(c)
+        off = O.region_offsets([3] * 3, [1] * 3, [ts] * 3)
+        parity.assert_kernel_maps_equal(gpu().conv_kernel_map(a1, a1, off), O.conv_kernel_map(a0, a0, off))
+        c = a0

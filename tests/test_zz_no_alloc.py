@@ -67,6 +67,12 @@ def test_static_table_build_matches_regular_twice_in_a_row():
         for a, b in zip(got[1:], ref[1:]):
             assert torch.equal(a, b)
         assert torch.equal(got[4].long(), got[2])  # every row finds its own unique row
+        # and directly against the CPU oracle (first-occurrence rows, row -> unique row)
+        from oracle import oracle as O
+        m0, i0 = O.insert_and_map(c)
+        assert got[0] == len(m0)
+        assert (got[1].numpy() == m0).all() and (got[2].numpy() == i0).all()
+        assert (got[3].numpy() == c[m0]).all()
 
 
 def test_static_table_build_rejects_oversized_input():
