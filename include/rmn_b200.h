@@ -370,6 +370,49 @@ int rmn_conv_backward_weight(const void *d_feats, uint32_t n_src, int c_in,
                              const int32_t *d_nbr, int K, float *d_grad_weights, int dtype,
                              void *d_workspace, size_t workspace_bytes, void *stream);
 
+/* --------------------------- convolution plans ---------------------------------------------
+ * Output rows of a sparse tensor arrive in arbitrary order, so every 128-row tile of the
+ * output-stationary kernels has some neighbour at every kernel offset and nothing can be skipped,
+ * although more than half of all (row, offset) entries of a surface scan are empty. A plan is an
+ * internal row order for ONE neighbour table - rows sorted by which sides of the kernel region they
+ * have neighbours on (a stable counting sort) - with, per 128-row tile, the set of offsets that hold
+ * any neighbour, and a copy of the table in that order. The *_planned entry points then skip
+ * (tile, offset) pairs without neighbours: no gather, no zero fill, no MMA. Public row numbering is
+ * unchanged (the kernels store row perm[p]) and the results are bit-identical to the plain entry
+ * points'. A plan costs about two passes over the table and is meant to be built once per kernel map
+ * and shared by every convolution on that map (forward; input gradient of a stride-1 self map, whose
+ * table is the same). No counterpart in the reference, whose convolution loops over per-offset pair
+ * lists in torch (engine/nn/conv.cpp:47-64).
+ */
+
+/* Bytes of a plan / of the scratch rmn_conv_plan_build needs, for a table [K, n_dst]; 0 when K exceeds the
+ * plan limit of 32 offsets (such tables are run unplanned). */
+size_t rmn_conv_plan_bytes(uint32_t n_dst, int K);
+size_t rmn_conv_plan_workspace_bytes(uint32_t n_dst, int K);
+
+/*
+ * Build the plan of neighbour table d_nbr [K, n_dst] (device). `offsets` is the HOST array [K, D] of the
+ * region (rmn_region_offsets) the table was built with; it only steers the grouping of rows, any values give
+ * correct results. d_plan: device, 256-byte aligned, rmn_conv_plan_bytes large. Returns RMN_ERR_UNSUPPORTED
+ * for K > 32 (pass NULL as the plan then).
+ */
+int rmn_conv_plan_build(const int32_t *d_nbr, uint32_t n_dst, int K, const int32_t *offsets, int D, void *d_plan,
+                        size_t plan_bytes, void *d_workspace, size_t workspace_bytes, void *stream);
+
+/* rmn_conv_forward_fused / rmn_conv_backward_input / rmn_conv_forward_stats with a plan of the table they are
+ * given (d_plan built from d_nbr, d_plan_t from d_nbr_t; NULL = no plan). The table itself is still passed: shapes
+ * and dtypes that the tensor-core kernels do not take run on it unplanned. Replaces: as the plain entry points. */
+int rmn_conv_forward_planned(const void *d_feats, uint32_t n_src, int c_in, const void *d_weights, int K,
+                             int c_out, const int32_t *d_nbr, const void *d_plan, uint32_t n_dst, void *d_out,
+                             int dtype, const float *d_scale, const float *d_shift, int relu, void *stream);
+int rmn_conv_backward_input_planned(const void *d_grad_out, uint32_t n_dst, int c_out, const void *d_weights, int K,
+                                    int c_in, const int32_t *d_nbr_t, const void *d_plan_t, uint32_t n_src,
+                                    void *d_grad_feats, int dtype, void *stream);
+int rmn_conv_forward_stats_planned(const void *d_feats, uint32_t n_src, int c_in, const void *d_weights, int K,
+                                   int c_out, const int32_t *d_nbr, const void *d_plan, uint32_t n_dst, void *d_out,
+                                   int dtype, const float *d_scale, const float *d_shift, int relu, double *d_stats,
+                                   void *d_workspace, size_t workspace_bytes, void *stream);
+
 /* ------------------- batch-normalisation pieces beside the convolution -------------------
  * The reference normalises with torch::nn::BatchNorm1d on the feature matrix after every convolution
  * (engine/nn/normalization.hpp:11-34; conv -> norm -> ReLU in engine/nn/residual.cpp:44-52). */

@@ -58,6 +58,17 @@ SIGNATURES = {
     "rmn_conv_backward_weight_workspace_bytes": (c_size_t, [c_uint32, c_int, c_int, c_int, c_int]),
     "rmn_conv_backward_weight": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_uint32, c_int, c_void_p, c_int,
                                          c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
+    "rmn_conv_plan_bytes": (c_size_t, [c_uint32, c_int]),
+    "rmn_conv_plan_workspace_bytes": (c_size_t, [c_uint32, c_int]),
+    "rmn_conv_plan_build": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_void_p, c_size_t, c_void_p,
+                                    c_size_t, c_void_p]),
+    "rmn_conv_forward_planned": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                         c_uint32, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "rmn_conv_backward_input_planned": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_int, c_void_p,
+                                                c_void_p, c_uint32, c_void_p, c_int, c_void_p]),
+    "rmn_conv_forward_stats_planned": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_int, c_void_p,
+                                               c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                               c_void_p, c_void_p, c_size_t, c_void_p]),
     "rmn_coords_expand": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_void_p, c_void_p]),
     "rmn_field_quantize": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_void_p, c_void_p]),
     "rmn_coords_discretize": (c_int, [c_void_p, c_int, c_uint64, ctypes.c_double, c_void_p, c_void_p]),

@@ -15,7 +15,7 @@ int simt_conv_backward_weight(const void* feats, int c_in, const void* grad_out,
                               void* workspace, cudaStream_t stream);
 int tc_conv(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
             int c_col, bool transposed_weights, void* out, const float* ep_scale, const float* ep_shift, int ep_relu,
-            cudaStream_t stream);
+            cudaStream_t stream, const void* plan);
 int tc_read_status(cudaStream_t stream, uint32_t* status);
 int tc_conv_wgrad(const void* feats, const void* grad_out, const int32_t* nbr, uint32_t n_dst, int K, int c_in,
                   int c_out, float* dw, void* workspace, size_t workspace_bytes, size_t* need,
@@ -69,12 +69,20 @@ static bool conv_args_ok(const void* a, const void* w, const int32_t* nbr, const
 extern "C" int rmn_conv_forward_fused(const void* d_feats, uint32_t n_src, int c_in, const void* d_weights, int K,
                                       int c_out, const int32_t* d_nbr, uint32_t n_dst, void* d_out, int dtype,
                                       const float* d_scale, const float* d_shift, int relu, void* stream_) {
+  return rmn_conv_forward_planned(d_feats, n_src, c_in, d_weights, K, c_out, d_nbr, nullptr, n_dst, d_out, dtype,
+                                  d_scale, d_shift, relu, stream_);
+}
+
+extern "C" int rmn_conv_forward_planned(const void* d_feats, uint32_t n_src, int c_in, const void* d_weights, int K,
+                                        int c_out, const int32_t* d_nbr, const void* d_plan, uint32_t n_dst,
+                                        void* d_out, int dtype, const float* d_scale, const float* d_shift, int relu,
+                                        void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (n_dst == 0) return RMN_OK;
   if (!conv_args_ok(n_src ? d_feats : d_out, d_weights, d_nbr, d_out, K, c_in, c_out, dtype)) return RMN_ERR_BAD_ARG;
   if (dtype == RMN_BF16 && n_src > 0) {
     const int st = tc_conv(d_feats, n_src, d_weights, d_nbr, n_dst, K, c_in, c_out, false, d_out, d_scale, d_shift,
-                           relu, stream);
+                           relu, stream, d_plan);
     if (st != RMN_ERR_UNSUPPORTED) return st;
   }
   // (with no source rows every neighbour entry is -1: the SIMT kernel then writes act(shift))
@@ -93,6 +101,14 @@ extern "C" int rmn_conv_backward_input(const void* d_grad_out, uint32_t n_dst, i
                                        const void* d_weights, int K, int c_in,
                                        const int32_t* d_nbr_t, uint32_t n_src, void* d_grad_feats,
                                        int dtype, void* stream_) {
+  return rmn_conv_backward_input_planned(d_grad_out, n_dst, c_out, d_weights, K, c_in, d_nbr_t, nullptr, n_src,
+                                         d_grad_feats, dtype, stream_);
+}
+
+extern "C" int rmn_conv_backward_input_planned(const void* d_grad_out, uint32_t n_dst, int c_out,
+                                               const void* d_weights, int K, int c_in, const int32_t* d_nbr_t,
+                                               const void* d_plan_t, uint32_t n_src, void* d_grad_feats, int dtype,
+                                               void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (n_src == 0) return RMN_OK;
   if (n_dst == 0) {
@@ -104,7 +120,7 @@ extern "C" int rmn_conv_backward_input(const void* d_grad_out, uint32_t n_dst, i
     return RMN_ERR_BAD_ARG;
   if (dtype == RMN_BF16) {
     const int st = tc_conv(d_grad_out, n_dst, d_weights, d_nbr_t, n_src, K, c_out, c_in, true, d_grad_feats, nullptr, nullptr, 0,
-                           stream);
+                           stream, d_plan_t);
     if (st != RMN_ERR_UNSUPPORTED) return st;
   }
   return simt_conv_backward_input(d_grad_out, c_out, d_weights, K, c_in, d_nbr_t, n_src,

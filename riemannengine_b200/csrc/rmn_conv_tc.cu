@@ -31,6 +31,7 @@
 // RMN_ERR_TIMEOUT in a device status word and leaves; all roles then meet at
 // the final barrier and the TMEM allocation is released.
 #include "rmn_common.cuh"
+#include "rmn_plan.cuh"
 #include "rmn_tc.cuh"
 
 #include <cuda_bf16.h>
@@ -98,7 +99,13 @@ __device__ __forceinline__ float warp_column_sums(float (&v)[32], int lane) {
 // kStats: the epilogue also accumulates, per output channel, the sum and the sum of squares of the
 // values it stores (the batch statistics of a following batch normalisation) and writes them to
 // stats_partial[blockIdx.x][2][CC]; a second kernel adds the per-CTA partials in a fixed order.
-template <int CR, int CC, bool kWT, bool kStats = false>
+//
+// kPlan: the rows are processed in the internal order of a convolution plan (rmn_plan.cu): `nbr` is the
+// plan's permuted table [K][n_dst] (n_dst = the padded position count), `perm` maps a position to the
+// output row it is stored to (-1: padding) and `tile_mask` holds, per 128-row tile, the offsets at which
+// any row of the tile has a neighbour. An offset at which none of the T tiles of a super-tile has a
+// neighbour takes no pipeline stage: no gather, no zero fill, no copy of W[k], no MMA.
+template <int CR, int CC, bool kWT, bool kStats = false, bool kPlan = false>
 __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_bfloat16* __restrict__ src,
                                                             const __nv_bfloat16* __restrict__ w,
                                                             const int32_t* __restrict__ nbr,
@@ -107,7 +114,9 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
                                                             uint32_t n_super,
                                                             const float* __restrict__ ep_scale,
                                                             const float* __restrict__ ep_shift, int ep_relu,
-                                                            float* __restrict__ stats_partial = nullptr) {
+                                                            float* __restrict__ stats_partial = nullptr,
+                                                            const int32_t* __restrict__ perm = nullptr,
+                                                            const uint32_t* __restrict__ tile_mask = nullptr) {
   using C = Cfg<CR, CC>;
   constexpr int STAGES = C::STAGES, KB = C::KB, NKB = C::NKB, T = C::T, SWA = C::SWA;
   constexpr int kFwdProducerWarps = C::PRODUCER_WARPS, kFwdProducers = C::PRODUCERS;
@@ -176,10 +185,30 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
     const uint32_t a_chunk = lane % A_CPL, a_row_sub = lane / A_CPL;
     uint32_t it = 0;
 
+    // kPlan: OR of the tile masks of a super-tile (the offsets at which some row has a neighbour; a plan covers
+    // at most 32 offsets), requested one super-tile ahead
+    uint32_t pf_mask = 0;
+    auto load_mask = [&](uint32_t st_next) {
+      pf_mask = 0;
+      if (st_next < n_super) {
+#pragma unroll
+        for (int t = 0; t < T; ++t) pf_mask |= __ldg(tile_mask + (size_t)st_next * T + t);
+      }
+    };
+    if constexpr (kPlan) load_mask(blockIdx.x);
     for (uint32_t st = blockIdx.x; st < n_super && !timed_out; st += gridDim.x) {
       const uint32_t row = st * (kTileM * T) + warp * 32 + lane;
       const bool row_ok = has_rows && row < n_dst;
-      // Neighbour indices are fetched four offsets ahead of their use (an L2 round trip is about
+      // kPlan: the offsets of this super-tile that still have to run; only offsets at which some row has a
+      // neighbour take a stage. Everything the per-stage path needs stays in registers: a producer's stage
+      // must not wait for a round trip through the load/store pipe (a shared-memory list of the offsets, or
+      // a spilled register, costs a quarter of a stage: the pipe's queue is full of the gathers).
+      uint32_t todo = 0;
+      if constexpr (kPlan) {
+        todo = pf_mask;
+        load_mask(st + gridDim.x);
+      }
+      // Neighbour indices are fetched four stages ahead of their use (an L2 round trip is about
       // one stage long). The window rotates through named registers: no dynamic indexing.
       auto load_idx = [&](int kk) -> int32_t {
         return (row_ok && kk < K) ? __ldg(nbr + (size_t)kk * n_dst + row) : -1;
@@ -225,27 +254,55 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
       // The four-deep window is unrolled by hand, each slot a register of its own that is reloaded right
       // after it is read: a rotating window (w0 = w1; w1 = w2; ...) would copy registers whose loads
       // are still in flight, and a copy waits for its source like any other use.
-      int32_t idx_w0 = load_idx(0), idx_w1 = load_idx(1), idx_w2 = load_idx(2), idx_w3 = load_idx(3);
-      for (int k = 0; k < K && !timed_out; k += 4) {
-        {
-          const int32_t idx = idx_w0;
-          idx_w0 = load_idx(k + 4);
-          do_offset(k, idx);
+      if constexpr (!kPlan) {
+        // The four-deep window is unrolled by hand, each slot a register of its own that is reloaded right
+        // after it is read: a rotating window (w0 = w1; w1 = w2; ...) would copy registers whose loads
+        // are still in flight, and a copy waits for its source like any other use.
+        int32_t idx_w0 = load_idx(0), idx_w1 = load_idx(1), idx_w2 = load_idx(2), idx_w3 = load_idx(3);
+        for (int k = 0; k < K && !timed_out; k += 4) {
+          {
+            const int32_t idx = idx_w0;
+            idx_w0 = load_idx(k + 4);
+            do_offset(k, idx);
+          }
+          if (k + 1 < K && !timed_out) {
+            const int32_t idx = idx_w1;
+            idx_w1 = load_idx(k + 5);
+            do_offset(k + 1, idx);
+          }
+          if (k + 2 < K && !timed_out) {
+            const int32_t idx = idx_w2;
+            idx_w2 = load_idx(k + 6);
+            do_offset(k + 2, idx);
+          }
+          if (k + 3 < K && !timed_out) {
+            const int32_t idx = idx_w3;
+            idx_w3 = load_idx(k + 7);
+            do_offset(k + 3, idx);
+          }
         }
-        if (k + 1 < K && !timed_out) {
-          const int32_t idx = idx_w1;
-          idx_w1 = load_idx(k + 5);
-          do_offset(k + 1, idx);
-        }
-        if (k + 2 < K && !timed_out) {
-          const int32_t idx = idx_w2;
-          idx_w2 = load_idx(k + 6);
-          do_offset(k + 2, idx);
-        }
-        if (k + 3 < K && !timed_out) {
-          const int32_t idx = idx_w3;
-          idx_w3 = load_idx(k + 7);
-          do_offset(k + 3, idx);
+      } else {
+        // Planned: a two-deep window over the set bits of `todo` in ascending order (two registers fewer than
+        // the plain window, which pays for the mask: the CTA is at its register limit). The offset to
+        // prefetch is the third lowest bit still set.
+        auto bit_at = [&](uint32_t m) -> int { return m ? __ffs(m) - 1 : K; };
+        int32_t idx_w0 = load_idx(bit_at(todo)), idx_w1 = load_idx(bit_at(todo & (todo - 1u)));
+        while (todo && !timed_out) {
+          {
+            const int k = __ffs(todo) - 1;
+            todo &= todo - 1u;
+            const int32_t idx = idx_w0;
+            idx_w0 = load_idx(bit_at(todo & (todo - 1u)));
+            do_offset(k, idx);
+          }
+          if (!todo || timed_out) break;
+          {
+            const int k = __ffs(todo) - 1;
+            todo &= todo - 1u;
+            const int32_t idx = idx_w1;
+            idx_w1 = load_idx(bit_at(todo & (todo - 1u)));
+            do_offset(k, idx);
+          }
         }
       }
     }
@@ -263,7 +320,20 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
       if (!mbar_wait(&tmem_empty[acc], acc_ph ^ 1u)) { timed_out = true; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * (T * CC);
-      const uint32_t n_stage = (uint32_t)K * NKB;
+      // kPlan: this warp only needs the NUMBER of stages of the super-tile (the offsets at which some row has
+      // a neighbour; which ones they are only matters to the producers). The count goes through a warp vote:
+      // a vote's result is warp-uniform by construction, so the loop below stays on the uniform datapath with
+      // its descriptors in uniform registers, like the fixed-count loop of the plain kernel. (Per-tile
+      // predicates on the MMAs were tried: derived from loaded data they are per-thread values, every MMA then
+      // moves its operands across, and the issue thread becomes the limit at 3x the plain kernel's cost.)
+      uint32_t n_stage = (uint32_t)K * NKB;
+      if constexpr (kPlan) {
+        uint32_t m = 0;
+#pragma unroll
+        for (int t = 0; t < T; ++t) m |= __ldg(tile_mask + (size_t)st * T + t);
+        const uint32_t cnt = (uint32_t)__popc(__ballot_sync(0xFFFFFFFFu, (m >> lane) & 1u));
+        n_stage = cnt * NKB;
+      }
       for (uint32_t sg = 0; sg < n_stage; ++sg, ++it) {
         const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
         if (!mbar_wait(&full[s], ph)) { timed_out = true; break; }
@@ -315,12 +385,27 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
       tc_fence_after();
 #pragma unroll
       for (int t = 0; t < T; ++t) {
-        const uint32_t row = st * (kTileM * T) + t * kTileM + quad * 32 + lane;
+        uint32_t row = st * (kTileM * T) + t * kTileM + quad * 32 + lane;
+        bool tile_any = true;  // false: no MMA wrote this tile's accumulator (no neighbour at any offset)
+        if constexpr (kPlan) {
+          const int32_t orow = __ldg(perm + row);
+          row = orow < 0 ? 0xFFFFFFFFu : (uint32_t)orow;   // padding positions store nothing
+          // the accumulators of a super-tile were written iff one of its tiles has a neighbour at some offset
+          uint32_t m = 0;
+#pragma unroll
+          for (int tt = 0; tt < T; ++tt) m |= __ldg(tile_mask + (size_t)st * T + tt);
+          tile_any = __any_sync(0xFFFFFFFFu, m != 0);  // (warp-uniform: the TMEM load below is warp-collective)
+        }
 #pragma unroll
         for (int c0 = 0; c0 < CC; c0 += 32) {
           uint32_t r[32];
-          tc_ld32(tmem_base + ((quad * 32u) << 16) + acc * (T * CC) + t * CC + c0, r);
-          tc_wait_ld();
+          if (tile_any) {
+            tc_ld32(tmem_base + ((quad * 32u) << 16) + acc * (T * CC) + t * CC + c0, r);
+            tc_wait_ld();
+          } else {
+#pragma unroll
+            for (int v = 0; v < 32; ++v) r[v] = 0u;
+          }
           if (has_ep) {
 #pragma unroll
             for (int v = 0; v < 32; ++v) {
@@ -392,12 +477,23 @@ __global__ void __launch_bounds__(Cfg<CR, CC>::THREADS, 1) k_conv_tc(const __nv_
 
 // stats_partial != nullptr selects the kStats instantiation (forward only); *grid_out receives the
 // number of CTAs, i.e. of [2][CC] partials written.
-template <int CR, int CC, bool kWT, bool kStats = false>
+// plan != nullptr: run in the internal order of that convolution plan (built for n_dst rows, K offsets).
+template <int CR, int CC, bool kWT, bool kStats = false, bool kPlan = false>
 int launch(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, void* out,
            const float* ep_scale, const float* ep_shift, int ep_relu, cudaStream_t stream,
-           float* stats_partial = nullptr, uint32_t* grid_out = nullptr) {
+           float* stats_partial = nullptr, uint32_t* grid_out = nullptr, const void* plan = nullptr) {
   using C = Cfg<CR, CC>;
-  auto kern = k_conv_tc<CR, CC, kWT, kStats>;
+  auto kern = k_conv_tc<CR, CC, kWT, kStats, kPlan>;
+  const int32_t* perm = nullptr;
+  const uint32_t* tile_mask = nullptr;
+  if constexpr (kPlan) {
+    const PlanLayout L = plan_layout(n_dst, K);
+    const char* base = static_cast<const char*>(plan);
+    perm = reinterpret_cast<const int32_t*>(base + L.perm);
+    tile_mask = reinterpret_cast<const uint32_t*>(base + L.tile_mask);
+    nbr = reinterpret_cast<const int32_t*>(base + L.nbr_p);
+    n_dst = L.n_pos;  // positions, a multiple of every super-tile size
+  }
   // once per device and instantiation, safe when several host threads make the first call together
   static std::once_flag configured[64];
   int dev = 0;
@@ -420,7 +516,7 @@ int launch(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, i
   if (grid > n_super) grid = n_super;
   kern<<<grid, C::THREADS, C::SMEM, stream>>>((const __nv_bfloat16*)src, (const __nv_bfloat16*)w, nbr, n_dst, K,
                                                (__nv_bfloat16*)out, n_super, ep_scale, ep_shift, ep_relu,
-                                               stats_partial);
+                                               stats_partial, perm, tile_mask);
   RMN_LAUNCH_CHECK();
   if (grid_out) *grid_out = grid;
   return RMN_OK;
@@ -448,7 +544,11 @@ static bool use_tma() {
 
 template <int CR, int CC, bool kWT>
 static int launch_best(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, uint32_t n_dst, int K,
-                       void* out, const float* ep_scale, const float* ep_shift, int ep_relu, cudaStream_t stream) {
+                       void* out, const float* ep_scale, const float* ep_shift, int ep_relu, cudaStream_t stream,
+                       const void* plan) {
+  if (plan)
+    return tc::launch<CR, CC, kWT, false, true>(src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream,
+                                                nullptr, nullptr, plan);
   if (use_tma() && !ep_scale && !ep_shift && !ep_relu) {
     const int st = tc::launch_tma<CR, CC, kWT>(src, n_src, w, nbr, n_dst, K, out, stream);
     if (st != RMN_ERR_UNSUPPORTED) return st;
@@ -457,14 +557,16 @@ static int launch_best(const void* src, uint32_t n_src, const void* w, const int
 }
 
 // Returns RMN_ERR_UNSUPPORTED when no tensor-core instantiation covers the shape.
+// plan: a convolution plan built for (nbr, n_dst, K), or nullptr (K above the plan limit is run unplanned).
 int tc_conv(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
             int c_col, bool transposed_weights, void* out, const float* ep_scale, const float* ep_shift, int ep_relu,
-            cudaStream_t stream) {
+            cudaStream_t stream, const void* plan) {
+  if (K > kPlanMaxK) plan = nullptr;
 #define RMN_TC_CASE(R, Cc)                                                                            \
   if (c_red == R && c_col == Cc)                                                                      \
     return transposed_weights                                                                         \
-               ? launch_best<R, Cc, true>(src, n_src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream)  \
-               : launch_best<R, Cc, false>(src, n_src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream);
+               ? launch_best<R, Cc, true>(src, n_src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream, plan)  \
+               : launch_best<R, Cc, false>(src, n_src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream, plan);
   RMN_TC_CASE(32, 32)
   RMN_TC_CASE(32, 64)
   RMN_TC_CASE(64, 32)
@@ -483,12 +585,15 @@ int tc_conv(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, 
 // sums of squares of the stored values) in stats_partial (room for 2 * SM count partials).
 int tc_conv_stats(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
                   int c_col, void* out, const float* ep_scale, const float* ep_shift, int ep_relu,
-                  float* stats_partial, uint32_t* n_partials, cudaStream_t stream) {
+                  float* stats_partial, uint32_t* n_partials, cudaStream_t stream, const void* plan) {
   (void)n_src;
+  if (K > kPlanMaxK) plan = nullptr;
 #define RMN_TC_CASE(R, Cc)            \
   if (c_red == R && c_col == Cc)      \
-    return tc::launch<R, Cc, false, true>(src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream, \
-                                          stats_partial, n_partials);
+    return plan ? tc::launch<R, Cc, false, true, true>(src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu,   \
+                                                       stream, stats_partial, n_partials, plan)                 \
+                : tc::launch<R, Cc, false, true>(src, w, nbr, n_dst, K, out, ep_scale, ep_shift, ep_relu, stream, \
+                                                 stats_partial, n_partials);
   RMN_TC_CASE(32, 32)
   RMN_TC_CASE(32, 64)
   RMN_TC_CASE(64, 32)

@@ -14,7 +14,7 @@ namespace rmn {
 // defined in rmn_conv_tc.cu
 int tc_conv_stats(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, uint32_t n_dst, int K, int c_red,
                   int c_col, void* out, const float* ep_scale, const float* ep_shift, int ep_relu,
-                  float* stats_partial, uint32_t* n_partials, cudaStream_t stream);
+                  float* stats_partial, uint32_t* n_partials, cudaStream_t stream, const void* plan);
 
 constexpr uint32_t kMaxStatPartials = 1024;
 
@@ -142,6 +142,15 @@ extern "C" int rmn_conv_forward_stats(const void* d_feats, uint32_t n_src, int c
                                       int c_out, const int32_t* d_nbr, uint32_t n_dst, void* d_out, int dtype,
                                       const float* d_scale, const float* d_shift, int relu, double* d_stats,
                                       void* d_workspace, size_t workspace_bytes, void* stream_) {
+  return rmn_conv_forward_stats_planned(d_feats, n_src, c_in, d_weights, K, c_out, d_nbr, nullptr, n_dst, d_out, dtype,
+                                        d_scale, d_shift, relu, d_stats, d_workspace, workspace_bytes, stream_);
+}
+
+extern "C" int rmn_conv_forward_stats_planned(const void* d_feats, uint32_t n_src, int c_in, const void* d_weights,
+                                              int K, int c_out, const int32_t* d_nbr, const void* d_plan,
+                                              uint32_t n_dst, void* d_out, int dtype, const float* d_scale,
+                                              const float* d_shift, int relu, double* d_stats, void* d_workspace,
+                                              size_t workspace_bytes, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   if (!d_stats || c_out < 1) return RMN_ERR_BAD_ARG;
   if (n_dst == 0) {
@@ -153,7 +162,7 @@ extern "C" int rmn_conv_forward_stats(const void* d_feats, uint32_t n_src, int c
   if (dtype == RMN_BF16 && n_src > 0 && d_feats && d_weights && d_nbr && d_out && K >= 1) {
     uint32_t n_partials = 0;
     const int st = tc_conv_stats(d_feats, n_src, d_weights, d_nbr, n_dst, K, c_in, c_out, d_out, d_scale, d_shift,
-                                 relu, (float*)d_workspace, &n_partials, stream);
+                                 relu, (float*)d_workspace, &n_partials, stream, d_plan);
     if (st == RMN_OK) {
       k_stats_reduce<<<(2 * c_out + 127) / 128, 128, 0, stream>>>((const float*)d_workspace, n_partials, c_out,
                                                                   d_stats);

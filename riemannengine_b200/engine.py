@@ -135,6 +135,40 @@ class KernelMap:
         # stride-1 self map with a point-symmetric region: nbr_in[k] == nbr_out[K-1-k], so the
         # input-gradient pass reuses nbr_out with the kernel flipped along its offset axis
         self.self_symmetric = False
+        self.region_offsets: Optional[np.ndarray] = None   # host [K, D] offsets the table was probed with
+        self._plan_out = self._plan_in = None
+        self._uses_out = self._uses_in = 0
+
+    # Convolution plans (ops.conv_plan_build), built lazily under the same rule as the C++ host layer
+    # (KernelMap::plan_out in riemann_cpp): from the second convolution pass over a table on, or at once
+    # for layers whose first pass already repays the build.
+    plan_policy = 0  # 0 automatic, 1 always, 2 never
+
+    @staticmethod
+    def _want_plan(uses: int, weight: int, rows: int) -> bool:
+        if KernelMap.plan_policy == 2 or rows < 8192:
+            return False
+        return KernelMap.plan_policy == 1 or uses >= 2 or weight >= 128 * 128
+
+    def plan_out(self, weight: int):
+        if self._parent is not None:
+            return self._parent.plan_in(weight)
+        self._uses_out += 1
+        if (self._plan_out is None and self.region_offsets is not None
+                and self._want_plan(self._uses_out, weight, self.n_out)):
+            self._plan_out = ops.conv_plan_build(self.nbr_out, self.region_offsets)
+        return self._plan_out
+
+    def plan_in(self, weight: int):
+        if self._parent is not None:
+            return self._parent.plan_out(weight)
+        if self.self_symmetric:
+            return self.plan_out(weight)
+        self._uses_in += 1
+        if (self._plan_in is None and self.region_offsets is not None
+                and self._want_plan(self._uses_in, weight, self.n_in)):
+            self._plan_in = ops.conv_plan_build(self.nbr_in, -self.region_offsets)
+        return self._plan_in
 
     @property
     def nbr_in(self) -> torch.Tensor:
@@ -372,6 +406,7 @@ class CoordinateManager:
             res = ops.kmap_build(in_map.table, out_map.coords, off, self_map=in_map is out_map)
             kmap = KernelMap(res.nbr, in_map.size, out_map.size, res)
             kmap.self_symmetric = in_map is out_map and ops.offsets_point_symmetric(off)
+            kmap.region_offsets = np.asarray(off, np.int32)
         else:
             swapped_key = (out_key.get_key(), in_key.get_key(), tuple(ks), tuple(kst), tuple(kd), region_type,
                            False, bool(is_pool), None if custom is None else custom.tobytes())
@@ -384,6 +419,7 @@ class CoordinateManager:
                 off = ops.region_offsets(region_type, ks, kd, out_map.tensor_stride, custom)
                 res = ops.kmap_build(in_map.table, out_map.coords, -off)
                 kmap = KernelMap(res.nbr, in_map.size, out_map.size, res)
+                kmap.region_offsets = -np.asarray(off, np.int32)
         self._kernel_maps[cache_key] = kmap
         return kmap
 
@@ -805,7 +841,10 @@ class _SparseConvolutionFunction(torch.autograd.Function):
         ctx.has_bias = bias is not None
         ctx.save_for_backward(features, kernel)
         # the bias add is fused into the convolution's epilogue
-        return ops.conv_forward(features, kernel, kmap.nbr_out, shift=bias)
+        bf16 = features.dtype == torch.bfloat16  # plans serve the tensor-core kernels only
+        ctx.weight = int(kernel.size(1) * kernel.size(2)) if bf16 else -1
+        plan = kmap.plan_out(ctx.weight) if bf16 else None
+        return ops.conv_forward(features, kernel, kmap.nbr_out, shift=bias, plan=plan)
 
     @staticmethod
     def backward(ctx, grad_out):
@@ -814,10 +853,11 @@ class _SparseConvolutionFunction(torch.autograd.Function):
         grad_out = grad_out.contiguous()
         g_feat = g_kernel = None
         if ctx.needs_input_grad[0]:
+            plan = kmap.plan_in(ctx.weight) if ctx.weight >= 0 else None
             if kmap.self_symmetric:
-                g_feat = ops.conv_backward_input(grad_out, kernel.flip(0), kmap.nbr_out)
+                g_feat = ops.conv_backward_input(grad_out, kernel.flip(0), kmap.nbr_out, plan=plan)
             else:
-                g_feat = ops.conv_backward_input(grad_out, kernel, kmap.nbr_in)
+                g_feat = ops.conv_backward_input(grad_out, kernel, kmap.nbr_in, plan=plan)
         if ctx.needs_input_grad[1]:
             g_kernel = ops.conv_backward_weight(features, grad_out, kmap.nbr_out).to(kernel.dtype)
         g_bias = None

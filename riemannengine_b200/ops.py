@@ -230,11 +230,33 @@ def _check_conv(feats: torch.Tensor, weights: torch.Tensor, what: str) -> None:
         raise RuntimeError(f"expected {what} and weights to have the same dtype, got {feats.dtype} and {weights.dtype}")
 
 
+def conv_plan_build(nbr: torch.Tensor, offsets: np.ndarray) -> Optional[torch.Tensor]:
+    """Convolution plan of neighbour table ``nbr`` [K, n_dst] (rmn_conv_plan_build): an internal row order in
+    which (128-row tile, offset) pairs without neighbours are skipped by the tensor-core kernels. ``offsets``
+    [K, D] is the host array of the region the table was built with. Returns the plan buffer (uint8), or
+    None when the table has no rows or more offsets than a plan covers."""
+    _require_cuda(nbr, "neighbour table")
+    K, n_dst = int(nbr.size(0)), int(nbr.size(1))
+    lib = capi.lib()
+    pbytes = lib.rmn_conv_plan_bytes(n_dst, K)
+    if n_dst == 0 or pbytes == 0:
+        return None
+    off = np.ascontiguousarray(offsets, dtype=np.int32).reshape(K, -1)
+    plan = torch.empty(pbytes, dtype=torch.uint8, device=nbr.device)
+    wbytes = lib.rmn_conv_plan_workspace_bytes(n_dst, K)
+    ws = torch.empty(wbytes, dtype=torch.uint8, device=nbr.device)
+    with torch.cuda.device(nbr.device):
+        capi.check(lib.rmn_conv_plan_build(_ptr(nbr), n_dst, K, off.ctypes.data, int(off.shape[1]), _ptr(plan), pbytes,
+                                           _ptr(ws), wbytes, _stream()), "rmn_conv_plan_build")
+    return plan
+
+
 def conv_forward(feats: torch.Tensor, weights: torch.Tensor, nbr: torch.Tensor,
                  scale: Optional[torch.Tensor] = None, shift: Optional[torch.Tensor] = None,
-                 relu: bool = False) -> torch.Tensor:
-    """out[j] = act((sum_k feats[nbr[k, j]] @ weights[k]) * scale + shift) (rmn_conv_forward_fused);
-    ``scale`` / ``shift`` are per-output-channel vectors (any float dtype, used as fp32) or None."""
+                 relu: bool = False, plan: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[j] = act((sum_k feats[nbr[k, j]] @ weights[k]) * scale + shift) (rmn_conv_forward_planned);
+    ``scale`` / ``shift`` are per-output-channel vectors (any float dtype, used as fp32) or None;
+    ``plan`` is the table's convolution plan (``conv_plan_build``) or None."""
     _check_conv(feats, weights, "features")
     feats, weights = feats.contiguous(), weights.contiguous()
     K, c_in, c_out = (int(s) for s in weights.shape)
@@ -253,24 +275,27 @@ def conv_forward(feats: torch.Tensor, weights: torch.Tensor, nbr: torch.Tensor,
 
     sc, sh = vec(scale), vec(shift)
     with torch.cuda.device(feats.device):
-        capi.check(capi.lib().rmn_conv_forward_fused(_ptr(feats), int(feats.size(0)), c_in, _ptr(weights), K, c_out,
-                                                     _ptr(nbr), n_dst, _ptr(out), _dtype_code(feats), _ptr(sc),
-                                                     _ptr(sh), int(bool(relu)), _stream()),
-                   "rmn_conv_forward_fused")
+        capi.check(capi.lib().rmn_conv_forward_planned(_ptr(feats), int(feats.size(0)), c_in, _ptr(weights), K, c_out,
+                                                       _ptr(nbr), _ptr(plan), n_dst, _ptr(out), _dtype_code(feats),
+                                                       _ptr(sc), _ptr(sh), int(bool(relu)), _stream()),
+                   "rmn_conv_forward_planned")
     return out
 
 
-def conv_backward_input(grad_out: torch.Tensor, weights: torch.Tensor, nbr_t: torch.Tensor) -> torch.Tensor:
-    """grad_feats[i] = sum_k grad_out[nbr_t[k, i]] @ weights[k]^T (rmn_conv_backward_input)."""
+def conv_backward_input(grad_out: torch.Tensor, weights: torch.Tensor, nbr_t: torch.Tensor,
+                        plan: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """grad_feats[i] = sum_k grad_out[nbr_t[k, i]] @ weights[k]^T (rmn_conv_backward_input_planned);
+    ``plan`` is the convolution plan of ``nbr_t`` or None."""
     _check_conv(grad_out, weights, "grad_out")
     grad_out, weights = grad_out.contiguous(), weights.contiguous()
     K, c_in, c_out = (int(s) for s in weights.shape)
     n_src = int(nbr_t.size(1))
     out = torch.empty((n_src, c_in), dtype=grad_out.dtype, device=grad_out.device)
     with torch.cuda.device(grad_out.device):
-        capi.check(capi.lib().rmn_conv_backward_input(_ptr(grad_out), int(grad_out.size(0)), c_out, _ptr(weights), K,
-                                                      c_in, _ptr(nbr_t), n_src, _ptr(out), _dtype_code(grad_out),
-                                                      _stream()), "rmn_conv_backward_input")
+        capi.check(capi.lib().rmn_conv_backward_input_planned(_ptr(grad_out), int(grad_out.size(0)), c_out,
+                                                              _ptr(weights), K, c_in, _ptr(nbr_t), _ptr(plan), n_src,
+                                                              _ptr(out), _dtype_code(grad_out), _stream()),
+                   "rmn_conv_backward_input_planned")
     return out
 
 
@@ -355,7 +380,7 @@ def channel_stats(x: torch.Tensor) -> torch.Tensor:
 
 def conv_forward_stats(feats: torch.Tensor, weights: torch.Tensor, nbr: torch.Tensor,
                        scale: Optional[torch.Tensor] = None, shift: Optional[torch.Tensor] = None,
-                       relu: bool = False):
+                       relu: bool = False, plan: Optional[torch.Tensor] = None):
     """conv_forward that also returns float64 [2, C_out] channel sums / sums of squares of the output it
     stores, accumulated in the tensor-core kernel's epilogue (rmn_conv_forward_stats)."""
     _check_conv(feats, weights, "features")
@@ -375,10 +400,11 @@ def conv_forward_stats(feats: torch.Tensor, weights: torch.Tensor, nbr: torch.Te
     wbytes = lib.rmn_channel_stats_workspace_bytes(c_out)
     ws = torch.empty(wbytes, dtype=torch.uint8, device=feats.device)
     with torch.cuda.device(feats.device):
-        capi.check(lib.rmn_conv_forward_stats(_ptr(feats), int(feats.size(0)), c_in, _ptr(weights), K, c_out, _ptr(nbr),
-                                              n_dst, _ptr(out), _dtype_code(feats), _ptr(sc), _ptr(sh),
-                                              int(bool(relu)), _ptr(stats), _ptr(ws), wbytes, _stream()),
-                   "rmn_conv_forward_stats")
+        capi.check(lib.rmn_conv_forward_stats_planned(_ptr(feats), int(feats.size(0)), c_in, _ptr(weights), K, c_out,
+                                                      _ptr(nbr), _ptr(plan), n_dst, _ptr(out), _dtype_code(feats),
+                                                      _ptr(sc), _ptr(sh), int(bool(relu)), _ptr(stats), _ptr(ws),
+                                                      wbytes, _stream()),
+                   "rmn_conv_forward_stats_planned")
     return out, stats
 
 

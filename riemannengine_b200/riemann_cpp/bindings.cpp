@@ -170,6 +170,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("__truediv__", [](const SparseTensor& a, const SparseTensor& b) { return a / b; })
       .def("__add__", [](const SparseTensor& a, double s) { return a + at::Scalar(s); })
       .def("__mul__", [](const SparseTensor& a, double s) { return a * at::Scalar(s); });
+  // 0 = automatic (plan a kernel map from its second convolution pass on, or at once for wide layers),
+  // 1 = always, 2 = never
+  m.def("set_convolution_plan_policy", [](int policy) { set_convolution_plan_policy(PlanPolicy::Type(policy)); },
+        py::arg("policy"));
+  m.def("convolution_plan_policy", []() { return int(convolution_plan_policy()); });
   m.def("cat", &cat, py::arg("tensors"));
   m.def("sum", &sum, py::arg("tensors"));
   m.def("mean", &mean, py::arg("tensors"));

@@ -7,6 +7,7 @@
 #include <c10/cuda/CUDAStream.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -121,6 +122,56 @@ at::Tensor const& KernelMap::nbr_in() {
           "rmn_kmap_transpose");
   }
   return nbr_in_;
+}
+
+namespace {
+std::atomic<int> g_plan_policy{PlanPolicy::AUTO};
+}
+void set_convolution_plan_policy(PlanPolicy::Type policy) { g_plan_policy.store(int(policy)); }
+PlanPolicy::Type convolution_plan_policy() { return PlanPolicy::Type(g_plan_policy.load()); }
+
+at::Tensor KernelMap::build_plan(const at::Tensor& table, bool negate_offsets) {
+  const int64_t K = table.size(0), n = table.size(1);
+  const size_t plan_bytes = rmn_conv_plan_bytes(static_cast<uint32_t>(n), static_cast<int>(K));
+  if (n == 0 || plan_bytes == 0 || region_offsets.empty()) return at::Tensor();  // (tables beyond the plan limit run unplanned)
+  c10::cuda::CUDAGuard guard(table.device());
+  std::vector<int32_t> off(region_offsets);
+  if (negate_offsets)
+    for (auto& v : off) v = -v;
+  const int D = static_cast<int>(off.size() / static_cast<size_t>(K));
+  auto bytes = table.options().dtype(at::kByte);
+  auto plan = at::empty({static_cast<int64_t>(plan_bytes)}, bytes);
+  const size_t ws_bytes = rmn_conv_plan_workspace_bytes(static_cast<uint32_t>(n), static_cast<int>(K));
+  auto ws = at::empty({static_cast<int64_t>(ws_bytes)}, bytes);
+  check(rmn_conv_plan_build(static_cast<const int32_t*>(ptr(table)), static_cast<uint32_t>(n), static_cast<int>(K),
+                            off.data(), D, ptr(plan), plan_bytes, ptr(ws), ws_bytes, current_stream()),
+        "rmn_conv_plan_build");
+  return plan;
+}
+
+namespace {
+// AUTO: plan from the second pass over a table on, or at once when one pass already repays the build (the build
+// moves about 3 x 4 K bytes per row, a skipped quarter of a pass saves about c_in * c_out / 2 bytes of gathers)
+bool want_plan(int uses, int64_t weight, int64_t rows) {
+  const int policy = g_plan_policy.load();
+  if (policy == PlanPolicy::NEVER || rows < 8192) return false;
+  return policy == PlanPolicy::ALWAYS || uses >= 2 || weight >= 128 * 128;
+}
+}  // namespace
+
+at::Tensor KernelMap::plan_out(int64_t weight) {
+  if (parent) return parent->plan_in(weight);  // a swapped view: its output table is the parent's input table
+  ++uses_out_;
+  if (!plan_out_.defined() && want_plan(uses_out_, weight, n_out)) plan_out_ = build_plan(nbr_out, false);
+  return plan_out_;
+}
+
+at::Tensor KernelMap::plan_in(int64_t weight) {
+  if (parent) return parent->plan_out(weight);
+  if (self_symmetric) return plan_out(weight);  // the input gradient of a self map runs over the same table
+  ++uses_in_;
+  if (!plan_in_.defined() && want_plan(uses_in_, weight, n_in)) plan_in_ = build_plan(nbr_in(), true);
+  return plan_in_;
 }
 
 namespace {
@@ -502,6 +553,7 @@ std::shared_ptr<KernelMap> CoordinateManager::kernel_map(const CoordinateMapKey&
                 static_cast<int64_t*>(ptr(result->offset_ptr)), ptr(result->workspace), ws_bytes, current_stream()),
           self_symmetric ? "rmn_kmap_build_self" : "rmn_kmap_build");
     result->self_symmetric = self_symmetric;
+    result->region_offsets = off;
     result->host_offset_ptr = at::empty({K + 1}, at::TensorOptions().dtype(at::kLong).pinned_memory(true));
     result->host_offset_ptr.copy_(result->offset_ptr, /*non_blocking=*/true);
     result->offset_ptr_ready.emplace(c10::DeviceType::CUDA);
@@ -857,7 +909,7 @@ namespace {
 // bias (if defined) is folded into the kernel's epilogue as a per-channel shift
 at::Tensor conv_forward(const at::Tensor& feats_in, const at::Tensor& kernel_in, const at::Tensor& nbr,
                         const at::Tensor& bias = at::Tensor(), const at::Tensor& scale_in = at::Tensor(),
-                        bool relu = false) {
+                        bool relu = false, const at::Tensor& plan = at::Tensor()) {
   TORCH_CHECK(feats_in.is_cuda() && kernel_in.is_cuda(), "features and kernel must be CUDA tensors");
   TORCH_CHECK(feats_in.scalar_type() == kernel_in.scalar_type(), "expected features and kernel to have the same dtype");
   auto feats = feats_in.contiguous(), kernel = kernel_in.contiguous();
@@ -875,24 +927,27 @@ at::Tensor conv_forward(const at::Tensor& feats_in, const at::Tensor& kernel_in,
     scale = scale_in.detach().reshape({-1}).to(at::kFloat).contiguous();
     TORCH_CHECK(scale.numel() == c_out, "scale must have one entry per output channel");
   }
-  check(rmn_conv_forward_fused(ptr(feats), static_cast<uint32_t>(feats.size(0)), c_in, ptr(kernel), K, c_out,
-                               static_cast<const int32_t*>(ptr(nbr)), static_cast<uint32_t>(nbr.size(1)), ptr(out),
-                               dtype_code(feats), scale.defined() ? static_cast<const float*>(ptr(scale)) : nullptr,
-                               static_cast<const float*>(ptr(shift)), relu ? 1 : 0, current_stream()),
-        "rmn_conv_forward_fused");
+  check(rmn_conv_forward_planned(ptr(feats), static_cast<uint32_t>(feats.size(0)), c_in, ptr(kernel), K, c_out,
+                                 static_cast<const int32_t*>(ptr(nbr)), ptr(plan), static_cast<uint32_t>(nbr.size(1)),
+                                 ptr(out), dtype_code(feats),
+                                 scale.defined() ? static_cast<const float*>(ptr(scale)) : nullptr,
+                                 static_cast<const float*>(ptr(shift)), relu ? 1 : 0, current_stream()),
+        "rmn_conv_forward_planned");
   return out;
 }
 
-at::Tensor conv_backward_input(const at::Tensor& grad_in, const at::Tensor& kernel_in, const at::Tensor& nbr_t) {
+at::Tensor conv_backward_input(const at::Tensor& grad_in, const at::Tensor& kernel_in, const at::Tensor& nbr_t,
+                               const at::Tensor& plan_t = at::Tensor()) {
   auto grad = grad_in.contiguous(), kernel = kernel_in.contiguous();
   c10::cuda::CUDAGuard guard(grad.device());
   const int K = static_cast<int>(kernel.size(0)), c_in = static_cast<int>(kernel.size(1)),
             c_out = static_cast<int>(kernel.size(2));
   auto out = at::empty({nbr_t.size(1), c_in}, grad.options());
-  check(rmn_conv_backward_input(ptr(grad), static_cast<uint32_t>(grad.size(0)), c_out, ptr(kernel), K, c_in,
-                                static_cast<const int32_t*>(ptr(nbr_t)), static_cast<uint32_t>(nbr_t.size(1)),
-                                ptr(out), dtype_code(grad), current_stream()),
-        "rmn_conv_backward_input");
+  check(rmn_conv_backward_input_planned(ptr(grad), static_cast<uint32_t>(grad.size(0)), c_out, ptr(kernel), K, c_in,
+                                        static_cast<const int32_t*>(ptr(nbr_t)), ptr(plan_t),
+                                        static_cast<uint32_t>(nbr_t.size(1)), ptr(out), dtype_code(grad),
+                                        current_stream()),
+        "rmn_conv_backward_input_planned");
   return out;
 }
 
@@ -917,14 +972,18 @@ at::Tensor conv_backward_weight(const at::Tensor& feats_in, const at::Tensor& gr
 // nbr_out for the forward pass and the weight gradient, nbr_in for the input gradient.
 class SparseConvolutionAutograd : public torch::autograd::Function<SparseConvolutionAutograd> {
 public:
+  // plan_out: plan of nbr_out for this pass; plan_in: plan of nbr_in for the input gradient (empty = none)
   static at::Tensor forward(torch::autograd::AutogradContext* ctx, at::Tensor features, at::Tensor kernel,
-                            at::Tensor nbr_out, at::Tensor nbr_in, bool flip_kernel, at::Tensor bias) {
+                            at::Tensor nbr_out, at::Tensor nbr_in, bool flip_kernel, at::Tensor bias,
+                            at::Tensor plan_out, at::Tensor plan_in) {
     ctx->save_for_backward({features, kernel});
     ctx->saved_data["has_bias"] = bias.numel() > 0;
     ctx->saved_data["nbr_out"] = nbr_out;
     ctx->saved_data["nbr_in"] = nbr_in;
+    ctx->saved_data["plan_in"] = plan_in;
     ctx->saved_data["flip_kernel"] = flip_kernel;
-    return conv_forward(features, kernel, nbr_out, bias);
+    return conv_forward(features, kernel, nbr_out, bias, at::Tensor(), false,
+                        plan_out.numel() > 0 ? plan_out : at::Tensor());
   }
   static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
                                                  torch::autograd::variable_list grad_outputs) {
@@ -933,12 +992,15 @@ public:
     auto nbr_in = ctx->saved_data["nbr_in"].toTensor();
     auto grad = grad_outputs[0].contiguous();
     at::Tensor g_feat, g_kernel;
-    if (ctx->needs_input_grad(0))
-      g_feat = conv_backward_input(grad, ctx->saved_data["flip_kernel"].toBool() ? saved[1].flip(0) : saved[1], nbr_in);
+    if (ctx->needs_input_grad(0)) {
+      auto plan_in = ctx->saved_data["plan_in"].toTensor();
+      g_feat = conv_backward_input(grad, ctx->saved_data["flip_kernel"].toBool() ? saved[1].flip(0) : saved[1], nbr_in,
+                                   plan_in.numel() > 0 ? plan_in : at::Tensor());
+    }
     if (ctx->needs_input_grad(1)) g_kernel = conv_backward_weight(saved[0], grad, nbr_out).to(saved[1].scalar_type());
     at::Tensor g_bias;
     if (ctx->saved_data["has_bias"].toBool() && ctx->needs_input_grad(4)) g_bias = grad.sum(0, /*keepdim=*/true);
-    return {g_feat, g_kernel, at::Tensor(), at::Tensor(), at::Tensor(), g_bias};
+    return {g_feat, g_kernel, at::Tensor(), at::Tensor(), at::Tensor(), g_bias, at::Tensor(), at::Tensor()};
   }
 };
 
@@ -952,7 +1014,15 @@ at::Tensor sparse_convolution(const at::Tensor& features, const at::Tensor& kern
                           : (features.requires_grad() ? kmap->nbr_in() : at::empty({0}, kmap->nbr_out.options()));
   // (autograd functions take defined tensors only: an empty tensor stands for "no bias")
   at::Tensor bias_arg = bias.defined() ? bias : at::empty({0}, kernel.options());
-  return SparseConvolutionAutograd::apply(features, kernel, kmap->nbr_out, nbr_in, kmap->self_symmetric, bias_arg);
+  const int64_t weight = kernel.size(1) * kernel.size(2);
+  auto none = at::empty({0}, kmap->nbr_out.options().dtype(at::kByte));
+  at::Tensor plan_out, plan_in;
+  if (features.scalar_type() == at::kBFloat16) {  // plans serve the tensor-core kernels only
+    plan_out = kmap->plan_out(weight);
+    if (features.requires_grad()) plan_in = kmap->plan_in(weight);
+  }
+  return SparseConvolutionAutograd::apply(features, kernel, kmap->nbr_out, nbr_in, kmap->self_symmetric, bias_arg,
+                                          plan_out.defined() ? plan_out : none, plan_in.defined() ? plan_in : none);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1009,7 +1079,9 @@ SparseTensor RiemannConvolutionBaseImpl::forward(const SparseTensor& input) {
                                   false);
   if (fold_scale_.defined() || fold_shift_.defined() || fold_relu_) {  // set by fused_conv_bn_relu for one call
     torch::NoGradGuard guard;
-    auto result = conv_forward(input.F(), kernel_, kmap->nbr_out, fold_shift_, fold_scale_, fold_relu_);
+    at::Tensor plan;
+    if (input.F().scalar_type() == at::kBFloat16) plan = kmap->plan_out(int64_t(in_channels_) * out_channels_);
+    auto result = conv_forward(input.F(), kernel_, kmap->nbr_out, fold_shift_, fold_scale_, fold_relu_, plan);
     return SparseTensor(std::move(result), output_key, std::move(manager));
   }
   auto result = sparse_convolution(input.F(), kernel_, kmap, bias_);  // the bias add is fused into the epilogue

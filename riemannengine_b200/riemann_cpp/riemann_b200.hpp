@@ -108,15 +108,32 @@ struct KernelMap {
   bool self_symmetric = false;
 
   at::Tensor const& nbr_in();
+  // Host copy of the region offsets [K, D] the table was probed with (steers the row grouping of the plans)
+  std::vector<int32_t> region_offsets;
+  // Convolution plan (rmn_conv_plan_build) of nbr_out / of nbr_in, or an undefined tensor when the policy says
+  // "not yet": a plan costs about two passes over the table, so under PlanPolicy::AUTO it is built when the
+  // map is used by its second convolution pass, or at once for channel counts whose first pass already
+  // gains more than the plan costs. `weight` is c_in * c_out of the calling layer.
+  at::Tensor plan_out(int64_t weight);
+  at::Tensor plan_in(int64_t weight);
   // (offset_ptr on the host, in rows, out rows)
   std::tuple<at::Tensor, at::Tensor, at::Tensor> const& pairs();
   std::shared_ptr<KernelMap> swapped(std::shared_ptr<KernelMap> const& self);
 
 private:
-  at::Tensor nbr_in_;
+  at::Tensor build_plan(const at::Tensor& table, bool negate_offsets);
+  at::Tensor nbr_in_, plan_out_, plan_in_;
+  int uses_out_ = 0, uses_in_ = 0;
   bool have_pairs_ = false;
   std::tuple<at::Tensor, at::Tensor, at::Tensor> pairs_;
 };
+
+// When a kernel map gets a convolution plan (see KernelMap::plan_out). No counterpart in the reference.
+namespace PlanPolicy {
+enum Type { AUTO = 0, ALWAYS = 1, NEVER = 2 };
+}
+void set_convolution_plan_policy(PlanPolicy::Type policy);
+PlanPolicy::Type convolution_plan_policy();
 
 class CoordinateManager {
 public:
