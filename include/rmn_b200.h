@@ -60,6 +60,9 @@ const char *rmn_status_string(int status);
 /* Number of CUDA kernels this library has launched in this process so far
  * (telemetry for benchmarks; no counterpart in the reference). */
 unsigned long long rmn_launch_count(void);
+/* Of those, launches of the tcgen05 convolution kernels (forward, input gradient, weight gradient): tells a
+ * host that a convolution ran on the tensor cores and not on the SIMT kernels. No counterpart in the reference. */
+unsigned long long rmn_tensor_core_launch_count(void);
 /* Synchronises `stream` and returns the device-side status of the convolution
  * kernels: RMN_OK, or RMN_ERR_TIMEOUT when a bounded wait inside a kernel ran
  * out (the kernel then returned early and its output is invalid). The status
@@ -446,6 +449,39 @@ int rmn_conv_forward_stats(const void *d_feats, uint32_t n_src, int c_in, const 
  */
 int rmn_affine_act(const void *d_x, uint32_t n_rows, int channels, const float *d_scale,
                    const float *d_shift, int relu, void *d_out, int dtype, void *stream);
+
+/* ------------------- weight-gradient all-reduce (data-parallel training) -------------------
+ * Batches shard by sample: every rank hashes, maps and convolves its own samples, and the one
+ * collective of a training step is the sum of the fp32 weight gradients over the ranks (NCCL over
+ * NVLink). No counterpart in the reference, which has no distributed code (its RiemannSyncBatchNorm
+ * is an alias of the plain layer, engine/nn/normalization.hpp:36-37). NCCL is looked up at run time
+ * (libnccl.so.2); without it these entry points return RMN_ERR_UNSUPPORTED and the rest of the
+ * library is unaffected. */
+#define RMN_COMM_ID_BYTES 128
+
+/* Rank 0: fill id_out[RMN_COMM_ID_BYTES] (ncclGetUniqueId); the host sends it to the other ranks by
+ * whatever channel it has (a torch.distributed store, MPI, a file). */
+int rmn_comm_unique_id(void *id_out);
+/* Every rank, with its CUDA device current: join the communicator (ncclCommInitRank). *comm_out is an
+ * ncclComm_t; a communicator created elsewhere with the same NCCL library may be passed to
+ * rmn_allreduce_grads instead. Collective: returns when all ranks have called it. */
+int rmn_comm_init(const void *id, int rank, int world_size, void **comm_out);
+int rmn_comm_destroy(void *comm);
+
+/* Scratch bytes of rmn_allreduce_grads for n_bufs buffers of counts[i] floats (0 for a single buffer,
+ * which is reduced in place). */
+size_t rmn_allreduce_grads_workspace_bytes(const size_t *counts, int n_bufs);
+
+/*
+ * In-place sum (average != 0: mean) over the ranks of n_bufs fp32 device buffers - the weight and bias
+ * gradients of a step, d_bufs[i] holding counts[i] floats (d_bufs and counts are HOST arrays). The buffers
+ * are packed into one flat bucket in d_workspace, reduced by ONE ncclAllReduce on `stream` and unpacked;
+ * every rank must pass the same counts in the same order (a rank without a gradient for some buffer passes
+ * zeros). With world_size == 1 it returns at once. Enqueue-only: run it on a second stream behind the
+ * weight-gradient kernel and it overlaps the input-gradient kernel of the same layer.
+ */
+int rmn_allreduce_grads(void *comm, float *const *d_bufs, const size_t *counts, int n_bufs, void *d_workspace,
+                        size_t workspace_bytes, int average, int world_size, void *stream);
 
 /* ----------------------------- local pooling --------------------------------
  * Pooling modes of rmn_pool_forward / rmn_pool_backward: the three local modes of

@@ -22,6 +22,7 @@ SIGNATURES = {
     "rmn_version": (c_int, []),
     "rmn_status_string": (c_char_p, [c_int]),
     "rmn_launch_count": (ctypes.c_ulonglong, []),
+    "rmn_tensor_core_launch_count": (ctypes.c_ulonglong, []),
     "rmn_device_status": (c_int, [c_void_p]),
     "rmn_table_bytes": (c_size_t, [c_uint32]),
     "rmn_table_build_workspace_bytes": (c_size_t, [c_uint32]),
@@ -69,6 +70,12 @@ SIGNATURES = {
     "rmn_conv_forward_stats_planned": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_int, c_void_p,
                                                c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                                c_void_p, c_void_p, c_size_t, c_void_p]),
+    "rmn_comm_unique_id": (c_int, [c_void_p]),
+    "rmn_comm_init": (c_int, [c_void_p, c_int, c_int, c_void_p]),
+    "rmn_comm_destroy": (c_int, [c_void_p]),
+    "rmn_allreduce_grads_workspace_bytes": (c_size_t, [c_void_p, c_int]),
+    "rmn_allreduce_grads": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_size_t, c_int, c_int,
+                                    c_void_p]),
     "rmn_coords_expand": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_void_p, c_void_p]),
     "rmn_field_quantize": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_void_p, c_void_p]),
     "rmn_coords_discretize": (c_int, [c_void_p, c_int, c_uint64, ctypes.c_double, c_void_p, c_void_p]),

@@ -17,6 +17,7 @@ int tc_conv(const void* src, uint32_t n_src, const void* w, const int32_t* nbr, 
             int c_col, bool transposed_weights, void* out, const float* ep_scale, const float* ep_shift, int ep_relu,
             cudaStream_t stream, const void* plan);
 int tc_read_status(cudaStream_t stream, uint32_t* status);
+unsigned long long tc_launch_count();
 int tc_conv_wgrad(const void* feats, const void* grad_out, const int32_t* nbr, uint32_t n_dst, int K, int c_in,
                   int c_out, float* dw, void* workspace, size_t workspace_bytes, size_t* need,
                   cudaStream_t stream);
@@ -35,6 +36,8 @@ using namespace rmn;
 extern "C" unsigned long long rmn_launch_count(void) {
   return g_launches.load(std::memory_order_relaxed);
 }
+
+extern "C" unsigned long long rmn_tensor_core_launch_count(void) { return tc_launch_count(); }
 
 extern "C" int rmn_version(void) { return 100; }
 

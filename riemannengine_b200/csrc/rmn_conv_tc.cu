@@ -36,9 +36,16 @@
 
 #include <cuda_bf16.h>
 
+#include <atomic>
 #include <mutex>
 
 namespace rmn {
+
+// Launches of the tcgen05 kernels of this file (forward, input gradient, weight gradient) in this process:
+// lets a host or a test tell that a convolution ran on the tensor cores rather than on the SIMT kernels.
+static std::atomic<unsigned long long> g_tc_launches{0};
+unsigned long long tc_launch_count() { return g_tc_launches.load(std::memory_order_relaxed); }
+static inline void count_tc_launch() { g_tc_launches.fetch_add(1, std::memory_order_relaxed); }
 
 // Sticky status word of the tensor-core kernels, one per device (not per stream): a kernel whose
 // bounded wait ran out stores RMN_ERR_TIMEOUT here and returns early. Hosts read it (and clear it)
@@ -518,6 +525,7 @@ int launch(const void* src, const void* w, const int32_t* nbr, uint32_t n_dst, i
                                                (__nv_bfloat16*)out, n_super, ep_scale, ep_shift, ep_relu,
                                                stats_partial, perm, tile_mask);
   RMN_LAUNCH_CHECK();
+  count_tc_launch();
   if (grid_out) *grid_out = grid;
   return RMN_OK;
 }

@@ -282,6 +282,7 @@ int launch_tma(const void* src, uint32_t n_src, const void* w, const int32_t* nb
   if (grid > n_super) grid = n_super;
   kern<<<grid, kTmaThreads, C::SMEM, stream>>>(map_src, map_w, nbr, n_src, n_dst, K, (__nv_bfloat16*)out, n_super);
   RMN_LAUNCH_CHECK();
+  count_tc_launch();
   return RMN_OK;
 }
 

@@ -67,7 +67,7 @@ template <int CIN, int COUT>
 __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
     const __nv_bfloat16* __restrict__ feats, const __nv_bfloat16* __restrict__ grad_out,
     const int32_t* __restrict__ nbr, uint32_t n_dst, int K, int groups_per_set,
-    uint32_t tmem_cols, float* __restrict__ partial) {
+    uint32_t tmem_cols, float* __restrict__ partial, uint32_t feat_stride) {
   using C = WgradCfg<CIN, COUT>;
   constexpr int STAGES = C::STAGES, G = C::G, GP = C::GP, kWgIdxPerThread = C::IDX_PER_THREAD;
   constexpr int SWB = (COUT < 64 ? COUT : 64) * 2;     // bytes per dY line
@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
           const uint32_t r = unit & (kRowsPerStage - 1), atom = unit / kRowsPerStage, c = lane & 7;
           const int cch = (atom * 8 + c) % (CIN / 8);
           cp_async16(a_s + gp * C::A_GROUP + atom * A_ATOM + r * 128 + (swz<128>(r, c) << 4),
-                     feats + (size_t)(idx[i] < 0 ? 0 : idx[i]) * CIN + cch * 8, idx[i] < 0 ? 0u : 16u);
+                     feats + (size_t)(idx[i] < 0 ? 0 : idx[i]) * feat_stride + cch * 8, idx[i] < 0 ? 0u : 16u);
         }
         // B': the 64 dY rows of this block, one swizzled line per (row, 64-column atom)
 #pragma unroll
@@ -289,13 +289,17 @@ __global__ void __launch_bounds__(kWgradThreads, 1) k_conv_tc_wgrad(
   }
 }
 
+// out[k][col0 + ci][co] = sum over the chunks of partial[chunk][k][ci][co] (ci < cin of the launch; the output
+// has cin_total input channels: a 256-channel gradient is produced as two 128-channel halves)
 __global__ void __launch_bounds__(256) k_reduce_chunks(const float* __restrict__ partial, uint32_t n_chunks,
-                                                       size_t elems, float* __restrict__ out) {
+                                                       size_t elems, float* __restrict__ out, uint32_t cin,
+                                                       uint32_t cout, uint32_t cin_total, uint32_t col0) {
   const size_t e = (size_t)blockIdx.x * 256 + threadIdx.x;
   if (e >= elems) return;
   float s = 0.f;
   for (uint32_t c = 0; c < n_chunks; ++c) s += partial[(size_t)c * elems + e];
-  out[e] = s;
+  const size_t k = e / ((size_t)cin * cout), r = e % ((size_t)cin * cout);
+  out[(k * cin_total + col0) * cout + r] = s;
 }
 
 struct WgradPlan {
@@ -323,9 +327,11 @@ WgradPlan plan(uint32_t n_dst, int K, int sms) {
   return p;
 }
 
+// feats: [*, cin_total] rows of which this launch takes the CIN channels from column col0 on
 template <int CIN, int COUT>
 int launch_wgrad(const void* feats, const void* grad_out, const int32_t* nbr, uint32_t n_dst, int K, float* dw,
-                 void* workspace, size_t workspace_bytes, size_t* need, cudaStream_t stream) {
+                 void* workspace, size_t workspace_bytes, size_t* need, cudaStream_t stream, int cin_total = CIN,
+                 int col0 = 0) {
   using C = WgradCfg<CIN, COUT>;
   int dev = 0, sms = 148;
   RMN_CUDA_TRY(cudaGetDevice(&dev));
@@ -346,11 +352,14 @@ int launch_wgrad(const void* feats, const void* grad_out, const int32_t* nbr, ui
     attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
   RMN_CUDA_TRY(attr_err);
   dim3 grid(p.chunks, p.sets);
-  kern<<<grid, kWgradThreads, C::SMEM, stream>>>((const __nv_bfloat16*)feats, (const __nv_bfloat16*)grad_out, nbr,
-                                                 n_dst, K, p.groups_per_set, p.tmem_cols,
-                                                 (float*)workspace);
+  kern<<<grid, kWgradThreads, C::SMEM, stream>>>((const __nv_bfloat16*)feats + col0, (const __nv_bfloat16*)grad_out,
+                                                 nbr, n_dst, K, p.groups_per_set, p.tmem_cols, (float*)workspace,
+                                                 (uint32_t)cin_total);
   RMN_LAUNCH_CHECK();
-  k_reduce_chunks<<<(uint32_t)((elems + 255) / 256), 256, 0, stream>>>((const float*)workspace, p.chunks, elems, dw);
+  count_tc_launch();
+  k_reduce_chunks<<<(uint32_t)((elems + 255) / 256), 256, 0, stream>>>((const float*)workspace, p.chunks, elems, dw,
+                                                                        (uint32_t)CIN, (uint32_t)COUT,
+                                                                        (uint32_t)cin_total, (uint32_t)col0);
   RMN_LAUNCH_CHECK();
   return RMN_OK;
 }
@@ -374,6 +383,18 @@ int tc_conv_wgrad(const void* feats, const void* grad_out, const int32_t* nbr, u
   RMN_WG_CASE(128, 128)
   RMN_WG_CASE(128, 256)
 #undef RMN_WG_CASE
+  // 256 input channels: the kernel stacks 128 / C_in offsets along M, so the two 128-channel halves of the
+  // feature rows are run one after the other (same workspace: the launches are ordered on the stream)
+#define RMN_WG_SPLIT(O)                                                                                          \
+  if (c_in == 256 && c_out == O) {                                                                               \
+    int st = tc::launch_wgrad<128, O>(feats, grad_out, nbr, n_dst, K, dw, workspace, workspace_bytes, need, stream, 256, 0); \
+    if (st != RMN_OK || !feats) return st;                                                                       \
+    return tc::launch_wgrad<128, O>(feats, grad_out, nbr, n_dst, K, dw, workspace, workspace_bytes, need, stream, 256, 128); \
+  }
+  RMN_WG_SPLIT(128)
+  RMN_WG_SPLIT(256)
+  RMN_WG_SPLIT(64)
+#undef RMN_WG_SPLIT
   return RMN_ERR_UNSUPPORTED;
 }
 

@@ -866,8 +866,36 @@ class _SparseConvolutionFunction(torch.autograd.Function):
         return g_feat, g_kernel, None, g_bias
 
 
+_TC_FORWARD_SHAPES = {(32, 32), (32, 64), (64, 32), (64, 64), (64, 128), (128, 64), (128, 128), (128, 256),
+                      (256, 128), (256, 256)}
+
+
+def tc_legal_shape(c_in: int, c_out: int) -> Tuple[int, int]:
+    """Smallest channel counts >= (c_in, c_out) that the tensor-core kernels take in the forward pass and,
+    with the roles exchanged, in the input-gradient pass; (c_in, c_out) itself when there is none."""
+    best, cost = (c_in, c_out), None
+    for ci in (32, 64, 128, 256):
+        for co in (32, 64, 128, 256):
+            if (ci >= c_in and co >= c_out and (ci, co) in _TC_FORWARD_SHAPES and (co, ci) in _TC_FORWARD_SHAPES
+                    and (cost is None or ci * co < cost)):
+                best, cost = (ci, co), ci * co
+    return best
+
+
 def sparse_convolution(features: torch.Tensor, kernel: torch.Tensor, kmap: KernelMap,
                        bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """bf16 channel counts without a tensor-core kernel (a 4-channel stem ...) are zero-padded to the next pair
+    that has one with differentiable torch ops around the convolution (as riemann_cpp's sparse_convolution does)."""
+    c_in, c_out = int(kernel.size(1)), int(kernel.size(2))
+    if features.dtype == torch.bfloat16 and kernel.dtype == torch.bfloat16:
+        ci, co = tc_legal_shape(c_in, c_out)
+        if (ci, co) != (c_in, c_out):
+            features = torch.nn.functional.pad(features, (0, ci - c_in))
+            kernel = torch.nn.functional.pad(kernel, (0, co - c_out, 0, ci - c_in))
+            if bias is not None and co != c_out:
+                bias = torch.nn.functional.pad(bias, (0, co - c_out))
+            out = _SparseConvolutionFunction.apply(features, kernel, kmap, bias)
+            return out[:, :c_out] if co != c_out else out
     return _SparseConvolutionFunction.apply(features, kernel, kmap, bias)
 
 

@@ -175,6 +175,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("set_convolution_plan_policy", [](int policy) { set_convolution_plan_policy(PlanPolicy::Type(policy)); },
         py::arg("policy"));
   m.def("convolution_plan_policy", []() { return int(convolution_plan_policy()); });
+  // data-parallel weight-gradient all-reduce (rmn_allreduce_grads)
+  m.def("gradient_allreduce_unique_id", []() { return py::bytes(gradient_allreduce_unique_id()); });
+  m.def("init_gradient_allreduce",
+        [](const std::string& unique_id, int rank, int world_size, bool average) {
+          init_gradient_allreduce(unique_id, rank, world_size, average);
+        },
+        py::arg("unique_id"), py::arg("rank"), py::arg("world_size"), py::arg("average") = true,
+        py::call_guard<py::gil_scoped_release>());
+  m.def("shutdown_gradient_allreduce", &shutdown_gradient_allreduce);
+  m.def("gradient_allreduce_active", &gradient_allreduce_active);
+  m.def("allreduce_gradients", &allreduce_gradients, py::arg("gradients"));
   m.def("cat", &cat, py::arg("tensors"));
   m.def("sum", &sum, py::arg("tensors"));
   m.def("mean", &mean, py::arg("tensors"));

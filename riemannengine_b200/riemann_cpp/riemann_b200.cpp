@@ -901,6 +901,59 @@ KernelGenerator::KernelParams KernelGenerator::get_kernel(const stride_type& ten
 }
 
 // ---------------------------------------------------------------------------------------------
+// Weight-gradient all-reduce over the ranks (rmn_allreduce_grads)
+// ---------------------------------------------------------------------------------------------
+namespace {
+struct GradientReducer {
+  void* comm = nullptr;
+  int rank = 0, world = 1;
+  bool average = true;
+};
+GradientReducer g_reducer;
+}  // namespace
+
+std::string gradient_allreduce_unique_id() {
+  std::string id(RMN_COMM_ID_BYTES, '\0');
+  check(rmn_comm_unique_id(id.data()), "rmn_comm_unique_id");
+  return id;
+}
+
+void init_gradient_allreduce(const std::string& unique_id, int rank, int world_size, bool average) {
+  TORCH_CHECK(unique_id.size() == RMN_COMM_ID_BYTES, "the unique id must be ", RMN_COMM_ID_BYTES, " bytes");
+  TORCH_CHECK(!g_reducer.comm, "gradient all-reduce is already initialised");
+  void* comm = nullptr;
+  check(rmn_comm_init(unique_id.data(), rank, world_size, &comm), "rmn_comm_init");
+  g_reducer = GradientReducer{comm, rank, world_size, average};
+}
+
+void shutdown_gradient_allreduce() {
+  if (g_reducer.comm) check(rmn_comm_destroy(g_reducer.comm), "rmn_comm_destroy");
+  g_reducer = GradientReducer{};
+}
+
+bool gradient_allreduce_active() { return g_reducer.comm != nullptr && g_reducer.world > 1; }
+int gradient_allreduce_world_size() { return g_reducer.world; }
+
+void allreduce_gradients(const std::vector<at::Tensor>& gradients) {
+  if (!gradient_allreduce_active() || gradients.empty()) return;
+  std::vector<float*> bufs;
+  std::vector<size_t> counts;
+  for (auto const& g : gradients) {
+    TORCH_CHECK(g.is_cuda() && g.scalar_type() == at::kFloat && g.is_contiguous(),
+                "gradients must be contiguous float32 CUDA tensors");
+    bufs.push_back(static_cast<float*>(ptr(g)));
+    counts.push_back(static_cast<size_t>(g.numel()));
+  }
+  c10::cuda::CUDAGuard guard(gradients.front().device());
+  const size_t ws_bytes = rmn_allreduce_grads_workspace_bytes(counts.data(), static_cast<int>(counts.size()));
+  at::Tensor ws;
+  if (ws_bytes) ws = at::empty({static_cast<int64_t>(ws_bytes)}, gradients.front().options().dtype(at::kByte));
+  check(rmn_allreduce_grads(g_reducer.comm, bufs.data(), counts.data(), static_cast<int>(bufs.size()), ptr(ws),
+                            ws_bytes, g_reducer.average ? 1 : 0, g_reducer.world, current_stream()),
+        "rmn_allreduce_grads");
+}
+
+// ---------------------------------------------------------------------------------------------
 // Convolution with a hand-written backward (the reference differentiates the
 // index_select / matmul / index_add_ chain through torch autograd, engine/nn/conv.cpp:47-64)
 // ---------------------------------------------------------------------------------------------
@@ -951,6 +1004,31 @@ at::Tensor conv_backward_input(const at::Tensor& grad_in, const at::Tensor& kern
   return out;
 }
 
+// (reduction channels, output channels) with a tensor-core forward / input-gradient kernel (csrc/rmn_conv_tc.cu);
+// the weight-gradient kernels cover the same pairs
+bool tc_forward_shape(int64_t c_red, int64_t c_col) {
+  static const int64_t shapes[][2] = {{32, 32}, {32, 64}, {64, 32}, {64, 64}, {64, 128}, {128, 64}, {128, 128},
+                                      {128, 256}, {256, 128}, {256, 256}};
+  for (auto const& sh : shapes)
+    if (sh[0] == c_red && sh[1] == c_col) return true;
+  return false;
+}
+// Smallest channel counts >= (c_in, c_out) that the tensor-core kernels take in the forward pass AND, with
+// the roles exchanged, in the input-gradient pass; (c_in, c_out) itself when there is none.
+std::pair<int64_t, int64_t> tc_legal_shape(int64_t c_in, int64_t c_out) {
+  static const int64_t sizes[] = {32, 64, 128, 256};
+  std::pair<int64_t, int64_t> best{c_in, c_out};
+  int64_t best_cost = -1;
+  for (auto ci : sizes)
+    for (auto co : sizes)
+      if (ci >= c_in && co >= c_out && tc_forward_shape(ci, co) && tc_forward_shape(co, ci) &&
+          (best_cost < 0 || ci * co < best_cost)) {
+        best = {ci, co};
+        best_cost = ci * co;
+      }
+  return best;
+}
+
 at::Tensor conv_backward_weight(const at::Tensor& feats_in, const at::Tensor& grad_in, const at::Tensor& nbr) {
   auto feats = feats_in.contiguous(), grad = grad_in.contiguous();
   c10::cuda::CUDAGuard guard(feats.device());
@@ -991,23 +1069,71 @@ public:
     auto nbr_out = ctx->saved_data["nbr_out"].toTensor();
     auto nbr_in = ctx->saved_data["nbr_in"].toTensor();
     auto grad = grad_outputs[0].contiguous();
-    at::Tensor g_feat, g_kernel;
+    at::Tensor g_feat, g_kernel, g_bias;
+    // (needs_input_grad counts the tensor arguments only: features 0, kernel 1, nbr_out 2, nbr_in 3, bias 4)
+    const bool want_bias = ctx->saved_data["has_bias"].toBool() && ctx->needs_input_grad(4);
+    if (gradient_allreduce_active() && (ctx->needs_input_grad(1) || want_bias)) {
+      // Data-parallel: the weight gradient comes first, its all-reduce runs on the second stream and the
+      // input gradient on this one; this stream waits for the reduced gradients before handing them on.
+      std::vector<at::Tensor> reduce;
+      if (ctx->needs_input_grad(1)) reduce.push_back(g_kernel = conv_backward_weight(saved[0], grad, nbr_out));
+      if (want_bias) reduce.push_back(g_bias = grad.sum(0, /*keepdim=*/true).to(at::kFloat).contiguous());
+      auto main_stream = c10::cuda::getCurrentCUDAStream();
+      auto side_stream = pair_list_stream(main_stream.device_index());
+      c10::Event ready(c10::DeviceType::CUDA);
+      ready.record(main_stream);
+      {
+        c10::cuda::CUDAStreamGuard on_side(side_stream);
+        ready.block(side_stream);
+        allreduce_gradients(reduce);
+      }
+      for (auto const& t : reduce) c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), side_stream);
+      if (ctx->needs_input_grad(0)) {
+        auto plan_in = ctx->saved_data["plan_in"].toTensor();
+        g_feat = conv_backward_input(grad, ctx->saved_data["flip_kernel"].toBool() ? saved[1].flip(0) : saved[1], nbr_in,
+                                     plan_in.numel() > 0 ? plan_in : at::Tensor());
+      }
+      c10::Event reduced(c10::DeviceType::CUDA);
+      reduced.record(side_stream);
+      reduced.block(main_stream);
+      if (g_kernel.defined()) g_kernel = g_kernel.to(saved[1].scalar_type());
+      if (g_bias.defined()) g_bias = g_bias.to(grad.scalar_type());
+      return {g_feat, g_kernel, at::Tensor(), at::Tensor(), at::Tensor(), g_bias, at::Tensor(), at::Tensor()};
+    }
     if (ctx->needs_input_grad(0)) {
       auto plan_in = ctx->saved_data["plan_in"].toTensor();
       g_feat = conv_backward_input(grad, ctx->saved_data["flip_kernel"].toBool() ? saved[1].flip(0) : saved[1], nbr_in,
                                    plan_in.numel() > 0 ? plan_in : at::Tensor());
     }
     if (ctx->needs_input_grad(1)) g_kernel = conv_backward_weight(saved[0], grad, nbr_out).to(saved[1].scalar_type());
-    at::Tensor g_bias;
-    if (ctx->saved_data["has_bias"].toBool() && ctx->needs_input_grad(4)) g_bias = grad.sum(0, /*keepdim=*/true);
+    if (want_bias) g_bias = grad.sum(0, /*keepdim=*/true);
     return {g_feat, g_kernel, at::Tensor(), at::Tensor(), at::Tensor(), g_bias, at::Tensor(), at::Tensor()};
   }
 };
 
 }  // namespace
 
-at::Tensor sparse_convolution(const at::Tensor& features, const at::Tensor& kernel,
-                              const std::shared_ptr<KernelMap>& kmap, const at::Tensor& bias) {
+at::Tensor sparse_convolution(const at::Tensor& features_in, const at::Tensor& kernel_in,
+                              const std::shared_ptr<KernelMap>& kmap, const at::Tensor& bias_in) {
+  // bf16 channel counts without a tensor-core kernel (a 4-channel stem, 48 or 96 channels ...) are zero-padded
+  // to the next pair that has one, with differentiable torch ops around the convolution: padded input channels
+  // multiply zero weights, padded output channels are cut off again, and autograd slices the gradients back.
+  at::Tensor features = features_in, kernel = kernel_in, bias = bias_in;
+  const int64_t c_in = kernel.size(1), c_out = kernel.size(2);
+  int64_t pad_out = 0;
+  if (features.scalar_type() == at::kBFloat16 && kernel.scalar_type() == at::kBFloat16) {
+    auto legal = tc_legal_shape(c_in, c_out);
+    if (legal.first != c_in || legal.second != c_out) {
+      pad_out = legal.second - c_out;
+      features = at::constant_pad_nd(features, {0, legal.first - c_in});
+      kernel = at::constant_pad_nd(kernel, {0, pad_out, 0, legal.first - c_in});
+      if (bias.defined() && bias.numel() > 0 && pad_out) bias = at::constant_pad_nd(bias, {0, pad_out});
+    }
+  }
+  if (pad_out) {
+    auto padded = sparse_convolution(features, kernel, kmap, bias);
+    return padded.narrow(1, 0, c_out);
+  }
   // the inverse table is cached in the kernel map; it is only needed when the features want a gradient
   at::Tensor nbr_in = kmap->self_symmetric
                           ? kmap->nbr_out

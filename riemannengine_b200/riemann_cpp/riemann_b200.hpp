@@ -135,6 +135,22 @@ enum Type { AUTO = 0, ALWAYS = 1, NEVER = 2 };
 void set_convolution_plan_policy(PlanPolicy::Type policy);
 PlanPolicy::Type convolution_plan_policy();
 
+// Data-parallel training: batches shard by sample over the ranks (one process per GPU) and the only
+// collective is the sum of the weight gradients, done by rmn_allreduce_grads (NCCL over NVLink). The
+// reference has no distributed code. Usage: rank 0 calls gradient_allreduce_unique_id() and sends the
+// 128 bytes to the other ranks (for instance through the torch.distributed store); every rank then calls
+// init_gradient_allreduce with its CUDA device current. From then on the backward pass of every
+// convolution layer reduces its weight (and bias) gradient as soon as the weight-gradient kernel has
+// finished, on a second stream, while the input-gradient kernel of the same layer runs: the gradients
+// autograd hands on are already the sum (average = false) or the mean over the ranks.
+std::string gradient_allreduce_unique_id();
+void init_gradient_allreduce(const std::string& unique_id, int rank, int world_size, bool average = true);
+void shutdown_gradient_allreduce();
+bool gradient_allreduce_active();
+int gradient_allreduce_world_size();
+// In-place reduction of fp32 CUDA tensors as ONE flat bucket on the current stream (what the layers call).
+void allreduce_gradients(const std::vector<at::Tensor>& gradients);
+
 class CoordinateManager {
 public:
   CoordinateManager(int D, CoordinateMapBackend::Type map_type = CoordinateMapBackend::CUDA,

@@ -177,3 +177,47 @@ def test_cpp_tensor_field_matches_reference_fixture(C, name):
     assert np.array_equal(fq.cpu().numpy(), g["ref_sq_feats"])
     assert np.array_equal(unique.cpu().numpy(), g["ref_sq_unique_index"])
     assert np.array_equal(inverse.cpu().numpy(), g["ref_sq_inverse"])
+
+
+@pytest.mark.parametrize("host", ["cpp", "python"])
+@pytest.mark.parametrize("c_in,c_out", [(4, 32), (16, 16), (48, 96), (256, 128), (256, 256), (32, 128)])
+def test_bf16_channel_counts_without_a_kernel_run_padded_on_the_tensor_cores(C, host, c_in, c_out):
+    """A 4-channel stem, 16 -> 16, 48 -> 96 ...: the host layers zero-pad the channels to a shape the tcgen05
+    kernels take (and split a 256-channel weight gradient into two halves); values and gradients against the
+    fp64 oracle on the same bf16-rounded inputs, and the tensor-core launch counter must move (forward, input
+    gradient and weight gradient = at least 3 launches, none on the SIMT kernels)."""
+    from riemannengine_b200 import capi, engine as E, synthetic
+    O = OracleBackend(f64=True)
+    pts = synthetic.indoor_scene(91, 12000)
+    c = np.concatenate([np.zeros((len(pts), 1), np.int32), pts], 1)
+    f = synthetic.features(92, len(c), c_in)
+    w = synthetic.conv_weights(93, 27, c_in, c_out)
+    fb = torch.from_numpy(f).bfloat16()
+    wb = torch.from_numpy(w).bfloat16()
+    feats = fb.cuda().requires_grad_(True)
+    if host == "cpp":
+        x = C.SparseTensor(feats, torch.from_numpy(c).cuda())
+        conv = C.RiemannConvolution(c_in, c_out, kernel_size=3, dimension=3)
+        conv.to("cuda")
+        conv.to(torch.bfloat16)
+    else:
+        x = E.SparseTensor(feats, torch.from_numpy(c).cuda())
+        conv = E.RiemannConvolution(c_in, c_out, kernel_size=3, dimension=3).cuda().bfloat16()
+    with torch.no_grad():
+        conv.kernel.copy_(wb.cuda())
+    lib = capi.lib()
+    tc0, all0 = lib.rmn_tensor_core_launch_count(), lib.rmn_launch_count()
+    y = conv(x)
+    g = torch.from_numpy(synthetic.features(94, len(c), c_out)).bfloat16()
+    y.F.backward(g.cuda())
+    torch.cuda.synchronize()
+    assert lib.rmn_tensor_core_launch_count() - tc0 >= 3
+    off = O.region_offsets([3] * 3, [1] * 3, [1] * 3)
+    k0 = O.conv_kernel_map(c, c, off)
+    y0 = O.conv_forward(fb.float().numpy(), wb.float().numpy(), k0, len(c), len(c))
+    gi0, gw0 = O.conv_backward(fb.float().numpy(), g.float().numpy(), wb.float().numpy(), k0, len(c), len(c))
+    assert tuple(y.F.shape) == (len(c), c_out)
+    assert parity.rel_l2(y.F.detach().float().cpu().numpy(), y0) <= 1e-2
+    assert parity.rel_l2(feats.grad.float().cpu().numpy(), gi0) <= 1e-2
+    assert parity.rel_l2(conv.kernel.grad.float().cpu().numpy(), gw0) <= 1e-2
+    assert tuple(conv.kernel.grad.shape) == (27, c_in, c_out)
