@@ -236,6 +236,145 @@ def run_reference(args) -> None:
 
 
 # ------------------------------------------------------------------------------------------
+# training step of the headline workload and the other configurations (extra keys of the line)
+# ------------------------------------------------------------------------------------------
+def run_extras(args, C, dev, rank, world, coords, feats, weights_np, res, xf, conv) -> dict:
+    """``train``: forward + backward (dX, dW) + weight-gradient all-reduce of the headline layer through the
+    C++ host layer; ``configs``: the other benchmark configurations (riemannengine_b200/workloads.py). Times
+    are the slowest rank's, voxels the sum over the ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from riemannengine_b200 import ops, workloads as W
+
+    steps = max(3, min(args.steps, 10))
+    warmup = 2
+
+    def over_ranks(ms: float, voxels: float):
+        t = torch.tensor([ms, voxels], dtype=torch.float64, device=dev)
+        if world > 1:
+            mx, sm = t.clone(), t.clone()
+            dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+            dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+            return float(mx[0]), float(sm[1])
+        return ms, voxels
+
+    if world > 1:  # the layers reduce their weight gradients over this communicator in their backward pass
+        box = [C.gradient_allreduce_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        with stdout_to_stderr():
+            C.init_gradient_allreduce(box[0], rank, world, True)
+
+    out = {}
+    # ---- train: the headline layer, forward + backward + all-reduce ----------------------------------
+    tconv = C.RiemannConvolution(C_IN, C_OUT, kernel_size=KSIZE, dimension=3)
+    tconv.to(f"cuda:{dev.index}")
+    tconv.to(torch.bfloat16)
+    with torch.no_grad():
+        tconv.kernel.copy_(torch.from_numpy(weights_np).to(dev))
+    tfeats = feats.detach().clone().requires_grad_(True)
+    grad_out = torch.randn(int(coords.size(0)), C_OUT, device=dev).bfloat16()  # stands in for the rest of a network
+
+    def train_step():
+        tconv.zero_grad()
+        tfeats.grad = None
+        y = tconv(C.SparseTensor(tfeats, coords))
+        y.F.backward(grad_out)
+
+    ms = W.time_steps(train_step, steps, warmup)
+    ms_all, vox_all = over_ranks(ms, float(coords.size(0)))
+    # the phases alone, on the cached map (device events, no host synchronisation in between)
+    gy = grad_out
+    wk = conv.kernel.detach()
+    plan = ops.conv_plan_build(res.nbr, ops.region_offsets(0, [KSIZE] * 3, [1] * 3, [1] * 3))
+    dw = ops.conv_backward_weight(xf, gy, res.nbr)
+    fns = [lambda: ops.conv_forward(xf, wk, res.nbr, plan=plan),
+           lambda: ops.conv_backward_input(gy, wk.flip(0), res.nbr, plan=plan),
+           lambda: ops.conv_backward_weight(xf, gy, res.nbr),
+           lambda: C.allreduce_gradients([dw])]
+    marks = [[torch.cuda.Event(enable_timing=True) for _ in range(len(fns) + 1)] for _ in range(8)]
+    for rep in marks:
+        rep[0].record()
+        for i, fn in enumerate(fns):
+            fn()
+            rep[i + 1].record()
+    torch.cuda.synchronize()
+    med = [statistics.median(rep[i].elapsed_time(rep[i + 1]) for rep in marks[2:]) for i in range(len(fns))]
+    out["train"] = {
+        "workload": "headline batch, 3^3 64->64 bf16: hash insert + kernel map + forward + backward (dX, dW) + "
+                    "weight-gradient all-reduce, fresh manager every step, C++ host layer",
+        "ms_per_step": ms_all, "mvoxels_per_s": vox_all / (ms_all / 1e3) / 1e6, "steps": steps,
+        "phases_ms": {"forward_planned": med[0], "input_gradient_planned": med[1], "weight_gradient": med[2],
+                      "allreduce_alone": med[3] if world > 1 else 0.0},
+        "allreduce_bytes": int(dw.numel() * 4) if world > 1 else 0,
+        "allreduce": ("one ncclAllReduce per layer on a second stream behind the weight-gradient kernel, "
+                      "overlapping the input-gradient kernel") if world > 1 else "single rank: none",
+    }
+    del tfeats, grad_out, dw, plan
+
+    # ---- the other configurations ---------------------------------------------------------------------
+    configs = {}
+    runs = [("config1_sphere_shell_fp32", lambda: W.run_sphere_shell(C, dev, steps, warmup), "weak"),
+            ("config3_lidar_chain_train", lambda: W.run_lidar_chain(C, dev, rank, steps, warmup), "weak"),
+            ("config4_spatiotemporal_81_offsets", lambda: W.run_spatiotemporal(C, dev, rank, steps, warmup), "weak"),
+            ("config5_unet_train", lambda: W.run_unet(C, dev, rank, world, max(3, steps // 2), 1), "strong")]
+    for name, fn, scaling in runs:
+        r = fn()
+        torch.cuda.empty_cache()
+        r["ms_per_step"], vox = over_ranks(r["ms_per_step"], float(r["voxels_per_step"]))
+        r["voxels_per_step"] = vox
+        r["mvoxels_per_s"] = vox / (r["ms_per_step"] / 1e3) / 1e6
+        r["scaling"] = scaling
+        r["n_gpus"] = world
+        configs[name] = r
+    if rank == 0 and world == 1:
+        for name, base in cpu_baselines_of_configs().items():
+            configs[name]["cpu_baseline"] = base
+    out["configs"] = configs
+    if world > 1:
+        C.shutdown_gradient_allreduce()
+    return out
+
+
+def cpu_baselines_of_configs() -> dict:
+    """The reference's CPU path (oracle/_ref/ref_driver) on a bounded sample of each of the other
+    configurations, on the host cores of this box (rank 0, one GPU only): a reported baseline."""
+    from oracle import refrun
+    from riemannengine_b200 import synthetic, workloads as W
+    if not refrun.available():
+        return {}
+    out = {}
+
+    def entry(r, voxels, sample, fwd_bwd):
+        ms = float(r["times_ms"][3]) + float(r["times_ms"][0]) if fwd_bwd else float(r["times_ms"][0] + r["times_ms"][1])
+        return {"value": voxels / (ms / 1e3) / 1e6, "unit": UNIT, "cores": int(r["info"][1]), "kind": "reference",
+                "ms": ms, "sample": sample}
+
+    c, f, w = W.sphere_shell_inputs()
+    r = refrun.run(c, f, w, 3, 1, 1, reps=3, warmup=1, timing_only=True)
+    out["config1_sphere_shell_fp32"] = entry(r, len(c), "the whole configuration (101 930 voxels): SparseTensor "
+                                             "construction + first forward, median of 3", False)
+    c = W.lidar_batch(1, 3000)
+    r = refrun.run(c, synthetic.features(1, len(c), 4), synthetic.conv_weights(2, 27, 4, 32), 3, 1, 1, reps=1,
+                   timing_only=True)
+    out["config3_lidar_chain_train"] = entry(r, len(c), "one sweep, first layer only (3^3 4->32, fp32): SparseTensor "
+                                             "construction + forward + backward, one run", True)
+    c = W.spatiotemporal_batch(1, 2, 4000)
+    r = refrun.run(c, synthetic.features(3, len(c), 32), synthetic.conv_weights(4, 81, 32, 32), 3, 1, 1, reps=1,
+                   timing_only=True)
+    out["config4_spatiotemporal_81_offsets"] = entry(r, len(c), "one clip, two frames (300 K voxels), 3^4 32->32 fp32: "
+                                                     "SparseTensor construction + first forward, one run", False)
+    pts = synthetic.indoor_scene(5000, 150_000)
+    c = np.concatenate([np.zeros((len(pts), 1), np.int32), pts], 1)
+    r = refrun.run(c, synthetic.features(5, len(c), 32), synthetic.conv_weights(6, 27, 32, 32), 3, 1, 1, reps=1,
+                   timing_only=True)
+    out["config5_unet_train"] = entry(r, len(c), "one room, ONE 3^3 32->32 layer of the network (fp32): SparseTensor "
+                                      "construction + forward + backward, one run (the network has 26 such passes at "
+                                      "stride 1 alone)", True)
+    return out
+
+
+# ------------------------------------------------------------------------------------------
 # product arm
 # ------------------------------------------------------------------------------------------
 def run_product(args) -> None:
@@ -469,6 +608,29 @@ def run_product(args) -> None:
         barrier()
         e2e_ms = g0.elapsed_time(g1)
 
+        # ---- convolution plan: build time and the planned (cached-map) forward ---------------------
+        plan_marks = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(reps + 2)]
+        plan = ops.conv_plan_build(res.nbr, offsets)
+        for rep in plan_marks:
+            rep[0].record()
+            ops.conv_plan_build(res.nbr, offsets)
+            rep[1].record()
+            ops.conv_forward(xf, conv.kernel, res.nbr, plan=plan)
+            rep[2].record()
+        torch.cuda.synchronize()
+        t_plan = statistics.median(rep[0].elapsed_time(rep[1]) for rep in plan_marks[2:])
+        t_fwd_planned = statistics.median(rep[1].elapsed_time(rep[2]) for rep in plan_marks[2:])
+        assert torch.equal(ops.conv_forward(xf, conv.kernel, res.nbr, plan=plan), ops.conv_forward(xf, conv.kernel, res.nbr))
+        # fraction of (512-row super-tile, offset) stages the planned kernel skips
+        n_pos = (n_unique + 511) // 512 * 512
+        tile_masks = plan[256 + ((n_pos * 4 + 255) & ~255):][:n_pos // 128 * 4].view(torch.int32).view(-1, 4)
+        st_mask = tile_masks[:, 0] | tile_masks[:, 1] | tile_masks[:, 2] | tile_masks[:, 3]
+        stages_run = int(sum(int(((st_mask >> k) & 1).sum()) for k in range(K_VOL)))
+        stage_fraction = stages_run / float(st_mask.numel() * K_VOL)
+
+    extras = run_extras(args, cpp_host, dev, rank, world, coords, feats, weights_np, res, xf, conv) \
+        if cpp_host is not None and not args.no_extras else {}
+
     # ---- max over ranks ------------------------------------------------------------------------
     stats = torch.tensor([elapsed_ms, e2e_ms, float(n_vox), e2e_serial_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -492,7 +654,9 @@ def run_product(args) -> None:
     bytes_hash = n_vox * (4 * W + 32)
     bytes_kmap = n_unique * 4 * W + n_unique * K_VOL * 32 + 8 * total_pairs
     phases = {"hash_insert_ms": t_hash, "kmap_probe_ms": t_kmap, "kmap_probe_general_ms": t_kmap_general,
-              "kmap_pairs_ms": t_pairs, "conv_fwd_ms": t_fwd}
+              "kmap_pairs_ms": t_pairs, "conv_fwd_ms": t_fwd, "conv_plan_build_ms": t_plan,
+              "conv_fwd_planned_ms": t_fwd_planned}
+    planned_tflops = flops / (t_fwd_planned / 1e3) / 1e12
     fwd_tflops = flops / (t_fwd / 1e3) / 1e12
     kmap_gbs = bytes_kmap / ((t_kmap + t_pairs) / 1e3) / 1e9
     hash_gbs = bytes_hash / (t_hash / 1e3) / 1e9
@@ -539,7 +703,17 @@ def run_product(args) -> None:
                                     "frac": (bytes_hash + bytes_kmap) / ((t_hash + t_kmap + t_pairs) / 1e3) / 1e9
                                     / peaks["hbm_gbs"]},
             "conv_forward": {"bound": "tensor", "achieved": fwd_tflops, "peak": peaks["bf16_tflops"],
-                             "unit": "TFLOP/s", "frac": fwd_tflops / peaks["bf16_tflops"]},
+                             "unit": "TFLOP/s", "frac": fwd_tflops / peaks["bf16_tflops"],
+                             "note": "first use of a kernel map (what the timed step runs): no plan"},
+            # the same layer on a map that has a convolution plan (second and later layers on a map, the
+            # input-gradient pass): offsets at which no row of a 512-row super-tile has a neighbour are skipped
+            "conv_forward_planned": {"bound": "tensor", "achieved": planned_tflops, "peak": peaks["bf16_tflops"],
+                                     "unit": "TFLOP/s", "frac": planned_tflops / peaks["bf16_tflops"],
+                                     "stages_run_fraction": stage_fraction,
+                                     # MMAs issued (zero rows included) against the measured peak
+                                     "executed_frac": (2.0 * stages_run * 512 * C_IN * C_OUT)
+                                     / (t_fwd_planned / 1e3) / 1e12 / peaks["bf16_tflops"],
+                                     "plan_build_ms": t_plan},
         },
         "cpu_baseline": {"value": cpu_value, "unit": UNIT, "cores": info["cores"], "kind": info["kind"],
                          "sample": f"all {CPU_SAMPLE_SCENES} scenes of one rank's batch ({cpu_vox} voxels), fp32, "
@@ -553,6 +727,7 @@ def run_product(args) -> None:
                 "d2h_bytes_per_step": int(h_out.numel() * 2)},
         "gpu_launches": int(launches),
         "clocks": clocks,
+        **extras,
         "strided_layer": {"layer": "2x2x2 stride-2 conv 64->128 on the same batch (hash insert + strided map + "
                                    "kernel map + forward, fresh manager)", "ms_per_step": down_ms,
                           "mvoxels_per_s": n_vox / (down_ms / 1e3) / 1e6, "output_voxels_per_gpu": int(n_down),
@@ -643,6 +818,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the training step and the other configurations (headline line only)")
     ap.add_argument("--host", default="auto", choices=["auto", "cpp", "py"],
                     help="host layer driving the step: the C++/LibTorch riemann_cpp module or the Python mirror")
     args = ap.parse_args()

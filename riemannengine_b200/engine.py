@@ -140,22 +140,22 @@ class KernelMap:
         self._uses_out = self._uses_in = 0
 
     # Convolution plans (ops.conv_plan_build), built lazily under the same rule as the C++ host layer
-    # (KernelMap::plan_out in riemann_cpp): from the second convolution pass over a table on, or at once
-    # for layers whose first pass already repays the build.
+    # (KernelMap::plan_out in riemann_cpp): by the pass that brings the work done on the table (sum of
+    # c_in * c_out over the passes) to four 64 x 64 layers' worth, where the plan repays its build.
     plan_policy = 0  # 0 automatic, 1 always, 2 never
 
     @staticmethod
-    def _want_plan(uses: int, weight: int, rows: int) -> bool:
+    def _want_plan(weight_sum: int, rows: int) -> bool:
         if KernelMap.plan_policy == 2 or rows < 8192:
             return False
-        return KernelMap.plan_policy == 1 or uses >= 2 or weight >= 128 * 128
+        return KernelMap.plan_policy == 1 or weight_sum >= 4 * 64 * 64
 
     def plan_out(self, weight: int):
         if self._parent is not None:
             return self._parent.plan_in(weight)
-        self._uses_out += 1
+        self._uses_out += weight
         if (self._plan_out is None and self.region_offsets is not None
-                and self._want_plan(self._uses_out, weight, self.n_out)):
+                and self._want_plan(self._uses_out, self.n_out)):
             self._plan_out = ops.conv_plan_build(self.nbr_out, self.region_offsets)
         return self._plan_out
 
@@ -164,9 +164,9 @@ class KernelMap:
             return self._parent.plan_out(weight)
         if self.self_symmetric:
             return self.plan_out(weight)
-        self._uses_in += 1
+        self._uses_in += weight
         if (self._plan_in is None and self.region_offsets is not None
-                and self._want_plan(self._uses_in, weight, self.n_in)):
+                and self._want_plan(self._uses_in, self.n_in)):
             self._plan_in = ops.conv_plan_build(self.nbr_in, -self.region_offsets)
         return self._plan_in
 

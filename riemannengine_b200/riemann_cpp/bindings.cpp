@@ -3,6 +3,7 @@
 // python/src/nn_bindings.cpp:91-117), so that the C++ classes can be driven from pytest.
 #include <torch/extension.h>
 
+#include "networks.hpp"
 #include "riemann_b200.hpp"
 
 namespace py = pybind11;
@@ -254,6 +255,34 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("in_channels"), py::arg("out_channels"), py::arg("kernel_size") = 3, py::arg("stride") = 1,
            py::arg("dilation") = 1, py::arg("bias") = false, py::arg("convolution_mode") = ConvolutionMode::DEFAULT,
            py::arg("dimension") = 3);
+
+  // the example encoder/decoder of networks.hpp (the network the benchmark trains)
+  {
+    using Net = networks::MinkUNetImpl;
+    py::class_<Net, std::shared_ptr<Net>> cls(m, "MinkUNet");
+    cls.def(py::init([](int in_channels, int out_channels, int width, int dimension) {
+              return std::make_shared<Net>(in_channels, out_channels, width, dimension);
+            }),
+            py::arg("in_channels"), py::arg("out_channels"), py::arg("width") = 32, py::arg("dimension") = 3);
+    cls.def("forward", [](Net& self, const SparseTensor& input) { return self.forward(input); }, py::arg("input"),
+            py::call_guard<py::gil_scoped_release>());
+    cls.def("__call__", [](Net& self, const SparseTensor& input) { return self.forward(input); }, py::arg("input"),
+            py::call_guard<py::gil_scoped_release>());
+    cls.def("parameters", [](Net& self) { return self.parameters(); });
+    cls.def("named_parameters", [](Net& self) {
+      py::dict out;
+      for (auto& p : self.named_parameters()) out[py::str(p.key())] = p.value();
+      return out;
+    });
+    cls.def("to", [](Net& self, py::object dtype_or_device) {
+      if (THPDtype_Check(dtype_or_device.ptr()))
+        self.to(reinterpret_cast<THPDtype*>(dtype_or_device.ptr())->scalar_type);
+      else
+        self.to(torch::Device(py::cast<std::string>(py::str(dtype_or_device))));
+    });
+    cls.def("zero_grad", [](Net& self) { self.zero_grad(); });
+    cls.def("train", [](Net& self, bool on) { self.train(on); }, py::arg("on") = true);
+  }
 
   // inference fold of a batch norm given by its tensors (what torch.nn.BatchNorm1d holds in eval mode)
   m.def(

@@ -150,27 +150,30 @@ at::Tensor KernelMap::build_plan(const at::Tensor& table, bool negate_offsets) {
 }
 
 namespace {
-// AUTO: plan from the second pass over a table on, or at once when one pass already repays the build (the build
-// moves about 3 x 4 K bytes per row, a skipped quarter of a pass saves about c_in * c_out / 2 bytes of gathers)
-bool want_plan(int uses, int64_t weight, int64_t rows) {
+// AUTO: a plan costs about two passes over the table (0.12 ms for 1.2 M rows x 27 offsets) and saves 10-18 % of
+// every tensor-core pass over it, which for a 64 -> 64 layer is a quarter of the build. The passes over a table
+// are therefore weighed by c_in * c_out and the plan is built by the pass that brings the sum to four 64 x 64
+// layers' worth: at once for a 128 -> 128 layer, at the fourth pass of a 64 -> 64 network, never for a map that
+// one or two narrow layers use.
+bool want_plan(int64_t weight_sum, int64_t rows) {
   const int policy = g_plan_policy.load();
   if (policy == PlanPolicy::NEVER || rows < 8192) return false;
-  return policy == PlanPolicy::ALWAYS || uses >= 2 || weight >= 128 * 128;
+  return policy == PlanPolicy::ALWAYS || weight_sum >= 4 * 64 * 64;
 }
 }  // namespace
 
 at::Tensor KernelMap::plan_out(int64_t weight) {
   if (parent) return parent->plan_in(weight);  // a swapped view: its output table is the parent's input table
-  ++uses_out_;
-  if (!plan_out_.defined() && want_plan(uses_out_, weight, n_out)) plan_out_ = build_plan(nbr_out, false);
+  weight_out_ += weight;
+  if (!plan_out_.defined() && want_plan(weight_out_, n_out)) plan_out_ = build_plan(nbr_out, false);
   return plan_out_;
 }
 
 at::Tensor KernelMap::plan_in(int64_t weight) {
   if (parent) return parent->plan_out(weight);
   if (self_symmetric) return plan_out(weight);  // the input gradient of a self map runs over the same table
-  ++uses_in_;
-  if (!plan_in_.defined() && want_plan(uses_in_, weight, n_in)) plan_in_ = build_plan(nbr_in(), true);
+  weight_in_ += weight;
+  if (!plan_in_.defined() && want_plan(weight_in_, n_in)) plan_in_ = build_plan(nbr_in(), true);
   return plan_in_;
 }
 

@@ -111,9 +111,9 @@ struct KernelMap {
   // Host copy of the region offsets [K, D] the table was probed with (steers the row grouping of the plans)
   std::vector<int32_t> region_offsets;
   // Convolution plan (rmn_conv_plan_build) of nbr_out / of nbr_in, or an undefined tensor when the policy says
-  // "not yet": a plan costs about two passes over the table, so under PlanPolicy::AUTO it is built when the
-  // map is used by its second convolution pass, or at once for channel counts whose first pass already
-  // gains more than the plan costs. `weight` is c_in * c_out of the calling layer.
+  // "not yet": a plan costs about two passes over the table, so under PlanPolicy::AUTO it is built by the pass
+  // that brings the work done on the table (sum of c_in * c_out of the passes) to the point where the plan
+  // repays itself. `weight` is c_in * c_out of the calling layer.
   at::Tensor plan_out(int64_t weight);
   at::Tensor plan_in(int64_t weight);
   // (offset_ptr on the host, in rows, out rows)
@@ -123,7 +123,7 @@ struct KernelMap {
 private:
   at::Tensor build_plan(const at::Tensor& table, bool negate_offsets);
   at::Tensor nbr_in_, plan_out_, plan_in_;
-  int uses_out_ = 0, uses_in_ = 0;
+  int64_t weight_out_ = 0, weight_in_ = 0;  // sum of c_in * c_out over the passes made on each table
   bool have_pairs_ = false;
   std::tuple<at::Tensor, at::Tensor, at::Tensor> pairs_;
 };
