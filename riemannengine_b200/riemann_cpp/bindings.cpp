@@ -117,6 +117,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            },
            py::arg("in_key"), py::arg("kernel_size"), py::arg("kernel_dilation"), py::arg("out_tensor_stride"),
            py::arg("region_type") = RegionType::HYPER_CUBE, py::arg("offsets") = py::none())
+      .def("origin", &CoordinateManager::origin)
       .def("kernel_map_pairs",
            [](CoordinateManager& self, const CoordinateMapKey& in_key, const CoordinateMapKey& out_key,
               stride_type kernel_size, stride_type kernel_stride, stride_type kernel_dilation,

@@ -418,6 +418,24 @@ CoordinateMapKey CoordinateManager::stride(const CoordinateMapKey& in_key, const
   return CoordinateMapKey(in_key.get_coordinate_size(), out_key);
 }
 
+std::pair<CoordinateMapKey, bool> CoordinateManager::origin() {
+  if (maps_.empty()) throw std::runtime_error("No coordinate map found");
+  const size_t D = maps_.begin()->second.tensor_stride.size();
+  coordinate_map_key_type origin_key(stride_type(D, 0), "");
+  const bool created = !maps_.count(origin_key);
+  if (created) {
+    // seed: the smallest map (every map holds every batch index that has any voxel at its stride)
+    const Map* seed = nullptr;
+    for (auto const& kv : maps_)
+      if (!seed || kv.second.size < seed->size) seed = &kv.second;
+    c10::cuda::CUDAGuard guard(seed->coords.device());
+    auto zeroed = at::zeros_like(seed->coords);
+    zeroed.select(1, 0).copy_(seed->coords.select(1, 0));
+    maps_[origin_key] = build(zeroed, origin_key.first, nullptr, nullptr);  // dedup on the batch column
+  }
+  return {CoordinateMapKey(static_cast<size_type>(D + 1), origin_key), created};
+}
+
 std::vector<at::Tensor> CoordinateManager::union_map(const std::vector<CoordinateMapKey>& in_keys,
                                                      CoordinateMapKey& out_key) {
   if (in_keys.empty()) throw std::runtime_error("union_map needs at least one map");

@@ -162,6 +162,11 @@ public:
 
   CoordinateMapKey stride(const CoordinateMapKey& in_key, const stride_type& kernel_stride,
                           std::string string_id = "");
+  // The origin map (engine/grid/space.hpp:817-906 `origin`, space_impl.hpp:383-421, lattice_cpu.hpp:539-558): one
+  // row per batch index present in the manager's maps, spatial columns zero, tensor stride all zeros, key
+  // (zeros, ""). Returns the key and whether the map was created by this call. Rows are numbered by first
+  // occurrence of the batch index in the seed map (the reference numbers them in hash-iteration order).
+  std::pair<CoordinateMapKey, bool> origin();
   // Union of maps of one tensor stride (engine/grid/space.hpp:862-863, space_impl.hpp:896-914): sets out_key to the
   // merged map and returns one int64 [2, N_i] tensor per input map (row in that map, row in the merged map).
   std::vector<at::Tensor> union_map(const std::vector<CoordinateMapKey>& in_keys, CoordinateMapKey& out_key);
