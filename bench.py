@@ -810,10 +810,41 @@ def run_train(args) -> None:
         dist.destroy_process_group()
 
 
+def run_kernels(args) -> None:
+    """One pass over the kernels of the headline workload (for profilers: `ncu -k regex:<kernel> ...
+    python bench.py --mode kernels`): table build, both kernel-map builders, pair lists, plan build, forward
+    (plain and planned), input gradient, weight gradient - `--steps` times each after one warm-up, no timing."""
+    import torch
+
+    from riemannengine_b200 import capi, ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    coords_np, feats_np, weights_np = make_batch(0)
+    coords = torch.from_numpy(coords_np).to(dev)
+    feats = torch.from_numpy(feats_np).to(dev).bfloat16()
+    w = torch.from_numpy(weights_np).to(dev).bfloat16()
+    offsets = ops.region_offsets(capi.HYPER_CUBE, [KSIZE] * 3, [1] * 3, [1] * 3)
+    gy = torch.randn(len(coords_np), C_OUT, device=dev).bfloat16()
+    for _ in range(1 + max(args.steps, 1)):
+        table = ops.table_build(coords)
+        res = ops.kmap_build(table, table.coords, offsets, self_map=True)
+        ops.kmap_build(table, table.coords, offsets)
+        res.pairs()
+        plan = ops.conv_plan_build(res.nbr, offsets)
+        ops.conv_forward(feats, w, res.nbr)
+        ops.conv_forward(feats, w, res.nbr, plan=plan)
+        ops.conv_backward_input(gy, w.flip(0), res.nbr, plan=plan)
+        ops.conv_backward_weight(feats, gy, res.nbr)
+    torch.cuda.synchronize()
+    print(json.dumps({"mode": "kernels", "voxels": len(coords_np), "passes": 1 + max(args.steps, 1)}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--mode", default="fwd", choices=["fwd", "train"],
-                    help="fwd: the headline forward metric; train: forward + backward + gradient all-reduce")
+    ap.add_argument("--mode", default="fwd", choices=["fwd", "train", "kernels"],
+                    help="fwd: the headline forward metric; train: forward + backward + gradient all-reduce "
+                         "(Python host layer); kernels: one untimed pass over every kernel, for profilers")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
@@ -827,6 +858,8 @@ def main() -> None:
         run_reference(args)
     elif args.mode == "train":
         run_train(args)
+    elif args.mode == "kernels":
+        run_kernels(args)
     else:
         run_product(args)
 
