@@ -169,6 +169,38 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi"}
 
 
+def bind_to_gpu_numa_node(local_rank: int) -> dict:
+    """Pin this process to the CPUs of the NUMA node its GPU hangs off (read from sysfs; read-only queries),
+    BEFORE any page-locked buffer is allocated, so that first touch places the staging buffers of the
+    end-to-end path on the GPU's own node. Returns what was found for the bench line."""
+    info = {"numa_node": None, "cpus_bound": None}
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        idx = int(visible.split(",")[local_rank]) if visible and visible.split(",")[local_rank].isdigit() else local_rank
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(idx)).busId
+        bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+        if len(bus.split(":")[0]) == 8:      # NVML prints an 8-digit domain, sysfs a 4-digit one
+            bus = bus[4:]
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        info["numa_node"] = node
+        if node >= 0:
+            with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+                cpus = set()
+                for part in f.read().strip().split(","):
+                    lo, _, hi = part.partition("-")
+                    cpus.update(range(int(lo), int(hi or lo) + 1))
+            allowed = cpus & os.sched_getaffinity(0)
+            if allowed:
+                os.sched_setaffinity(0, allowed)
+                info["cpus_bound"] = len(allowed)
+    except Exception as exc:  # no NVML / sysfs entry: run unbound
+        info["error"] = str(exc)[:80]
+    return info
+
+
 def make_batch(rank: int):
     from riemannengine_b200 import synthetic
     coords = synthetic.indoor_batch(N_SCENES, N_VOXELS, seed=2000 + 100 * rank)
@@ -388,6 +420,7 @@ def run_product(args) -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    numa = bind_to_gpu_numa_node(local_rank)
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
@@ -599,6 +632,20 @@ def run_product(args) -> None:
             s_main.wait_stream(s_out)
             s_main.wait_stream(s_in)
 
+        # raw copy rates of this rank's page-locked buffers, all ranks copying at the same time
+        barrier()
+        c0, c1, c2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        c0.record()
+        for _ in range(3):
+            d_feats[0].copy_(h_feats, non_blocking=True)
+        c1.record()
+        for _ in range(3):
+            h_outs[0].copy_(d_feats[0][:n_unique], non_blocking=True)
+        c2.record()
+        barrier()
+        h2d_gbs = 3 * h_feats.numel() * 2 / (c0.elapsed_time(c1) / 1e3) / 1e9
+        d2h_gbs = 3 * h_outs[0].numel() * 2 / (c1.elapsed_time(c2) / 1e3) / 1e9
+
         run_pipelined(3)
         barrier()
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -630,6 +677,15 @@ def run_product(args) -> None:
 
     extras = run_extras(args, cpp_host, dev, rank, world, coords, feats, weights_np, res, xf, conv) \
         if cpp_host is not None and not args.no_extras else {}
+
+    # ---- per-rank host-link figures (gathered to rank 0) ------------------------------------------
+    link = torch.tensor([h2d_gbs, d2h_gbs, float(numa["numa_node"] if numa["numa_node"] is not None else -2)],
+                        dtype=torch.float64, device=dev)
+    links = [torch.zeros_like(link) for _ in range(world)] if world > 1 else [link]
+    if world > 1:
+        dist.all_gather(links, link)
+    per_rank_link = [{"rank": r, "h2d_gbs": round(float(t[0]), 1), "d2h_gbs": round(float(t[1]), 1),
+                      "gpu_numa_node": int(t[2])} for r, t in enumerate(links)]
 
     # ---- max over ranks ------------------------------------------------------------------------
     stats = torch.tensor([elapsed_ms, e2e_ms, float(n_vox), e2e_serial_ms], dtype=torch.float64, device=dev)
@@ -709,6 +765,7 @@ def run_product(args) -> None:
             # input-gradient pass): offsets at which no row of a 512-row super-tile has a neighbour are skipped
             "conv_forward_planned": {"bound": "tensor", "achieved": planned_tflops, "peak": peaks["bf16_tflops"],
                                      "unit": "TFLOP/s", "frac": planned_tflops / peaks["bf16_tflops"],
+                                     "traffic": captured_traffic("conv_forward_planned"),
                                      "stages_run_fraction": stage_fraction,
                                      # MMAs issued (zero rows included) against the measured peak
                                      "executed_frac": (2.0 * stages_run * 512 * C_IN * C_OUT)
@@ -724,7 +781,10 @@ def run_product(args) -> None:
                 "serial_value": total_vox * args.steps / (e2e_serial_ms / 1e3) / 1e6,
                 "serial_ms_per_step": e2e_serial_ms / args.steps,
                 "h2d_bytes_per_step": int(h_coords.numel() * 4 + h_feats.numel() * 2),
-                "d2h_bytes_per_step": int(h_out.numel() * 2)},
+                "d2h_bytes_per_step": int(h_out.numel() * 2),
+                # each rank is pinned to the CPUs of its GPU's NUMA node before it allocates its page-locked
+                # buffers; raw copy rates with all ranks copying at once
+                "host_link_per_rank": per_rank_link, "numa_binding": numa},
         "gpu_launches": int(launches),
         "clocks": clocks,
         **extras,

@@ -1070,6 +1070,10 @@ class RiemannConvolutionBase(torch.nn.Module):
         manager = input.coordinate_manager
         if not self.is_transpose and any(s != 1 for s in params.kernel_stride):
             out_key = manager.stride(input.coordinate_map_key, params.kernel_stride)
+        if self.is_transpose and self.kernel_generator.expand_coordinates():
+            # generative layer: the output coordinates are generated (as riemann_cpp's layer does)
+            out_key = manager.stride_region(input.coordinate_map_key, params.kernel_size, params.kernel_dilation,
+                                            out_stride, params.region_type, params.region_offsets)
         kmap = manager.kernel_map(input.coordinate_map_key, out_key, params.kernel_size, params.kernel_stride,
                                   params.kernel_dilation, params.region_type, params.region_offsets,
                                   self.is_transpose, False)
@@ -1115,9 +1119,8 @@ class RiemannConvolutionTranspose(_ConvWrapper):
 
 
 class RiemannGenerativeConvolutionTranspose(_ConvWrapper):
-    """engine/nn/conv.hpp:74-88. As in the reference the layer never expands coordinates
-    (conv.cpp:104-138 does not call stride_region), so it behaves like the plain transposed
-    convolution."""
+    """engine/nn/conv.hpp:74-88 with the coordinate expansion the flag stands for: the output coordinates are
+    generated by ``stride_region`` (the reference's own forward, conv.cpp:104-138, never reaches it)."""
     _transpose = True
     _expand_default = True
 

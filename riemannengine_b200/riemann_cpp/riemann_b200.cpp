@@ -1221,6 +1221,14 @@ SparseTensor RiemannConvolutionBaseImpl::forward(const SparseTensor& input) {
   auto manager = input.coordinate_manager();
   if (!is_transpose_ && params.kernel_stride != stride_type(dimension_, 1))
     output_key = manager->stride(input.coordinate_map_key(), params.kernel_stride);
+  // Generative transposed convolution: the output coordinates are generated, every input voxel spawning its
+  // whole kernel region on the output stride (stride_region: engine/grid/space_impl.hpp:362-380,
+  // engine/grid/lattice_cpu.hpp:499-534), instead of being looked up among the maps that exist. (The
+  // reference's layer carries the flag but its forward never reaches stride_region, engine/nn/conv.cpp:104-138,
+  // 173-189; its pooling-transpose layer does, and this follows that path.)
+  if (is_transpose_ && kernel_generator_.expand_coordinates())
+    output_key = manager->stride_region(input.coordinate_map_key(), params.kernel_size, params.kernel_dilation,
+                                        output_stride, params.region_type, params.region_offsets);
   auto kmap = manager->kernel_map(input.coordinate_map_key(), output_key, params.kernel_size, params.kernel_stride,
                                   params.kernel_dilation, params.region_type, params.region_offsets, is_transpose_,
                                   false);

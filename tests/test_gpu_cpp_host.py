@@ -263,3 +263,40 @@ def test_cpp_example_unet_runs_and_is_reproducible(C):
         outs.append((y.F.detach().clone(), grads))
     assert torch.equal(outs[0][0], outs[1][0])
     assert all(torch.allclose(outs[0][1][k], outs[1][1][k], rtol=1e-2, atol=1e-4) for k in outs[0][1])
+
+
+@pytest.mark.parametrize("kernel,stride", [(2, 2), (3, 2), (3, 1)])
+def test_cpp_generative_transposed_convolution_expands_coordinates(C, kernel, stride):
+    """RiemannGenerativeConvolutionTranspose generates its output coordinates (every coarse voxel spawns its
+    kernel region on the finer stride) and convolves onto them. Bar: the oracle's composition of the same two
+    steps - region expansion + first-occurrence dedup, which the pooling-transpose fixtures of the reference pin
+    (tests/golden/unpool_*.npz), and the transposed kernel map + convolution - values and gradients in fp32."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(40 + kernel + stride)
+    raw = np.concatenate([rng.integers(0, 2, (600, 1)), rng.integers(-6, 7, (600, 3)) * stride], 1).astype(np.int32)
+    coarse = raw[O.insert_and_map(raw)[0]]
+    feats = rng.standard_normal((len(coarse), 5)).astype(np.float32)
+    # a tensor on the coarse stride: insert the aligned coordinates under that tensor stride
+    m = C.CoordinateManager(3)
+    key, _ = m.insert_and_map(torch.from_numpy(coarse).cuda(), [stride] * 3, "")
+    f = torch.from_numpy(feats).cuda().requires_grad_(True)
+    x = C.SparseTensor(f, key, m)
+    layer = C.RiemannGenerativeConvolutionTranspose(5, 4, kernel_size=kernel, stride=stride, dimension=3)
+    layer.to("cuda")
+    y = layer(x)
+    assert y.tensor_stride == [1, 1, 1]
+    (y.F * y.F).sum().mul(0.5).backward()
+    # oracle: out = in + off on the output stride (1), deduplicated in first-occurrence order over (row, offset)
+    off = O.region_offsets(O.HYPER_CUBE, [kernel] * 3, [1] * 3, [1] * 3)
+    expanded = (coarse[:, None, :].astype(np.int64)
+                + np.concatenate([np.zeros((len(off), 1), np.int64), off.astype(np.int64)], 1)[None]).reshape(-1, 4)
+    expanded = expanded.astype(np.int32)
+    generated = expanded[O.insert_and_map(expanded)[0]]
+    assert (y.C.cpu().numpy() == generated).all()
+    kmap = O.conv_kernel_map(coarse, generated, off, transposed=True)
+    w = layer.kernel.detach().cpu().numpy()
+    want = O.conv_forward(feats, w, *kmap, len(generated), f64=True)
+    assert rel_max(y.F.detach().cpu().numpy(), want) <= 1e-4
+    gi, gw = O.conv_backward(feats, want.astype(np.float32), w, *kmap, f64=True)
+    assert rel_max(f.grad.cpu().numpy(), gi) <= 1e-4
+    assert rel_max(layer.kernel.grad.cpu().numpy(), gw) <= 1e-4
