@@ -450,6 +450,42 @@ int rmn_conv_forward_stats(const void *d_feats, uint32_t n_src, int c_in, const 
 int rmn_affine_act(const void *d_x, uint32_t n_rows, int channels, const float *d_scale,
                    const float *d_shift, int relu, void *d_out, int dtype, void *stream);
 
+/* ------------------- training-mode batch normalisation as streaming passes -------------------
+ * Replaces: torch::nn::BatchNorm1d on the feature matrix (engine/nn/normalization.hpp:11-34) in training mode,
+ * forward and backward. Forward: rmn_channel_dot_stats(x, x) -> rmn_bn_forward_coeffs -> rmn_affine_act(x, scale,
+ * shift). Backward: rmn_channel_dot_stats(dy, x) -> rmn_bn_backward_coeffs -> rmn_affine2(dy, x). */
+
+/* Scratch bytes of rmn_channel_dot_stats. */
+size_t rmn_channel_dot_stats_workspace_bytes(int channels);
+/*
+ * d_stats[0][c] = sum_r a[r][c], d_stats[1][c] = sum_r a[r][c] * b[r][c] (double [2, channels]); a == b gives the
+ * sum and the sum of squares. Rows are read 16 bytes per lane at memory speed, partial sums are combined in a
+ * fixed order. RMN_ERR_UNSUPPORTED unless channels * element size / 16 is a power of two <= 32 (bf16: 8 ... 256
+ * channels, fp32: 4 ... 128) and both pointers are 16-byte aligned: use rmn_channel_stats then.
+ */
+int rmn_channel_dot_stats(const void *d_a, const void *d_b, uint32_t n_rows, int channels, int dtype,
+                          double *d_stats, void *d_workspace, size_t workspace_bytes, void *stream);
+/*
+ * One tiny kernel: from d_stats (sum, sum of squares over `count` rows) the batch mean and 1 / sqrt(var + eps)
+ * (fp32 [channels] each, kept for the backward pass), the affine y = x * scale + shift that normalises and applies
+ * gamma / beta (NULL: 1 / 0), and the update of the running statistics in place (NULL: none; momentum and the
+ * unbiased variance as torch.nn.BatchNorm1d). gamma, beta and the running statistics are `param_dtype` arrays.
+ */
+int rmn_bn_forward_coeffs(const double *d_stats, double count, const void *d_gamma, const void *d_beta,
+                          void *d_running_mean, void *d_running_var, int param_dtype, float momentum, float eps,
+                          int channels, float *d_scale, float *d_shift, float *d_mean, float *d_inv, void *stream);
+/*
+ * One tiny kernel: from d_dots = rmn_channel_dot_stats(dy, x) the gradients of gamma and beta (fp32) and the
+ * coefficients of dx = c_dy * dy + c_x * x + c_0 (the batch-norm input gradient, to be applied by rmn_affine2).
+ */
+int rmn_bn_backward_coeffs(const double *d_dots, const float *d_mean, const float *d_inv, const void *d_gamma,
+                           int param_dtype, double count, int channels, float *d_c_dy, float *d_c_x, float *d_c_0,
+                           float *d_dgamma, float *d_dbeta, void *stream);
+/* out[r][c] = c_a[c] * a[r][c] + c_b[c] * b[r][c] + c_0[c]; channels * element size a multiple of 16 bytes, pointers
+ * 16-byte aligned (else RMN_ERR_UNSUPPORTED). */
+int rmn_affine2(const void *d_a, const void *d_b, uint32_t n_rows, int channels, const float *d_c_a,
+                const float *d_c_b, const float *d_c_0, void *d_out, int dtype, void *stream);
+
 /* ------------------- weight-gradient all-reduce (data-parallel training) -------------------
  * Batches shard by sample: every rank hashes, maps and convolves its own samples, and the one
  * collective of a training step is the sum of the fp32 weight gradients over the ranks (NCCL over

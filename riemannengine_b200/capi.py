@@ -70,6 +70,16 @@ SIGNATURES = {
     "rmn_conv_forward_stats_planned": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_int, c_int, c_void_p,
                                                c_void_p, c_uint32, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                                c_void_p, c_void_p, c_size_t, c_void_p]),
+    "rmn_channel_dot_stats_workspace_bytes": (c_size_t, [c_int]),
+    "rmn_channel_dot_stats": (c_int, [c_void_p, c_void_p, c_uint32, c_int, c_int, c_void_p, c_void_p, c_size_t,
+                                      c_void_p]),
+    "rmn_bn_forward_coeffs": (c_int, [c_void_p, ctypes.c_double, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                      ctypes.c_float, ctypes.c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p]),
+    "rmn_bn_backward_coeffs": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, ctypes.c_double, c_int,
+                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "rmn_affine2": (c_int, [c_void_p, c_void_p, c_uint32, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                            c_void_p]),
     "rmn_comm_unique_id": (c_int, [c_void_p]),
     "rmn_comm_init": (c_int, [c_void_p, c_int, c_int, c_void_p]),
     "rmn_comm_destroy": (c_int, [c_void_p]),

@@ -257,6 +257,29 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("dilation") = 1, py::arg("bias") = false, py::arg("convolution_mode") = ConvolutionMode::DEFAULT,
            py::arg("dimension") = 3);
 
+  // engine/nn/normalization.hpp:11-34
+  {
+    using BN = RiemannBatchNormImpl;
+    py::class_<BN, std::shared_ptr<BN>> cls(m, "RiemannBatchNorm");
+    cls.def(py::init([](int64_t num_features, double eps, double momentum) {
+              return std::make_shared<BN>(num_features, eps, momentum);
+            }),
+            py::arg("num_features"), py::arg("eps") = 1e-5, py::arg("momentum") = 0.1);
+    cls.def("forward", [](BN& self, const SparseTensor& input) { return self.forward(input); }, py::arg("input"));
+    cls.def("__call__", [](BN& self, const SparseTensor& input) { return self.forward(input); }, py::arg("input"));
+    cls.def_property_readonly("weight", [](BN& self) { return self.normalization()->weight; });
+    cls.def_property_readonly("bias", [](BN& self) { return self.normalization()->bias; });
+    cls.def_property_readonly("running_mean", [](BN& self) { return self.normalization()->running_mean; });
+    cls.def_property_readonly("running_var", [](BN& self) { return self.normalization()->running_var; });
+    cls.def("train", [](BN& self, bool on) { self.train(on); }, py::arg("on") = true);
+    cls.def("to", [](BN& self, py::object dtype_or_device) {
+      if (THPDtype_Check(dtype_or_device.ptr()))
+        self.to(reinterpret_cast<THPDtype*>(dtype_or_device.ptr())->scalar_type);
+      else
+        self.to(torch::Device(py::cast<std::string>(py::str(dtype_or_device))));
+    });
+  }
+
   // the example encoder/decoder of networks.hpp (the network the benchmark trains)
   {
     using Net = networks::MinkUNetImpl;

@@ -122,3 +122,46 @@ def test_fused_training_bf16_close_to_fp32():
     err = float((y16.float() - y32).norm() / y32.norm())
     assert err <= 1e-2, err
     assert float((bn16.running_mean - bn.running_mean).abs().max()) < 1e-2
+
+
+@pytest.mark.parametrize("dtype,channels,rows", [(torch.float32, 32, 20000), (torch.bfloat16, 32, 50000),
+                                                 (torch.bfloat16, 64, 7001), (torch.bfloat16, 256, 3000),
+                                                 (torch.float32, 8, 999), (torch.bfloat16, 24, 5000)])
+def test_cpp_batch_norm_training_matches_torch(dtype, channels, rows):
+    """RiemannBatchNorm of the C++ host layer in training mode (streaming kernels: rmn_channel_dot_stats,
+    rmn_bn_forward_coeffs, rmn_affine_act; backward rmn_bn_backward_coeffs, rmn_affine2) against
+    torch.nn.BatchNorm1d, which is what the reference runs (engine/nn/normalization.hpp:11-34): output, input
+    gradient, parameter gradients and running statistics. 24 bf16 channels have no streaming kernel and take
+    torch's path."""
+    from riemannengine_b200 import cpp
+    C = cpp.load()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = (torch.randn(rows, channels, device="cuda", generator=g) * 2 + 0.5).to(dtype)
+    gy = torch.randn(rows, channels, device="cuda", generator=g).to(dtype)
+    coords = torch.cat([torch.zeros(rows, 1, dtype=torch.int32), torch.arange(rows, dtype=torch.int32).view(-1, 1),
+                        torch.zeros(rows, 2, dtype=torch.int32)], 1).cuda()
+    ref = torch.nn.BatchNorm1d(channels).cuda()
+    with torch.no_grad():
+        ref.weight.uniform_(0.5, 1.5)
+        ref.bias.uniform_(-0.5, 0.5)
+    bn = C.RiemannBatchNorm(channels)
+    bn.to("cuda")
+    with torch.no_grad():
+        bn.weight.copy_(ref.weight)
+        bn.bias.copy_(ref.bias)
+    bn.to(dtype)
+    bn.train(True)
+    xr = x.float().clone().requires_grad_(True)       # torch reference in fp32 on the same (rounded) inputs
+    yr = ref(xr)
+    yr.backward(gy.float())
+    xs = x.clone().requires_grad_(True)
+    m = C.CoordinateManager(3)
+    key, _ = m.insert_and_map(coords, [1, 1, 1], "")
+    y = bn(C.SparseTensor(xs, key, m))
+    y.F.backward(gy)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    rel = lambda a, b: float((a.float() - b.float()).norm() / b.float().norm())  # noqa: E731
+    assert rel(y.F, yr) <= tol
+    assert rel(xs.grad, xr.grad) <= tol
+    assert rel(bn.weight.grad, ref.weight.grad) <= tol and rel(bn.bias.grad, ref.bias.grad) <= tol
+    assert rel(bn.running_mean, ref.running_mean) <= tol and rel(bn.running_var, ref.running_var) <= tol
