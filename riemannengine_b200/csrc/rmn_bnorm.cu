@@ -100,14 +100,18 @@ __global__ void __launch_bounds__(256) k_channel_dot_partial(const T* __restrict
   }
 }
 
-// stats[2][C] (double) = sum over the partials, in partial order
-__global__ void k_dot_reduce(const float* __restrict__ partial, uint32_t n_partials, int C,
-                             double* __restrict__ stats) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+// stats[2][C] (double) = sum over the partials: one warp per output, lanes stride over the partials and are
+// combined by a fixed butterfly (deterministic; a serial loop of ~600 dependent loads per output cost more than
+// the statistics pass itself)
+__global__ void __launch_bounds__(256) k_dot_reduce(const float* __restrict__ partial, uint32_t n_partials, int C,
+                                                    double* __restrict__ stats) {
+  const int i = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (i >= 2 * C) return;
   double t = 0.0;
-  for (uint32_t p = 0; p < n_partials; ++p) t += (double)partial[(size_t)p * 2 * C + i];
-  stats[i] = t;
+  for (uint32_t p = lane; p < n_partials; p += 32) t += (double)partial[(size_t)p * 2 * C + i];
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, d);
+  if (lane == 0) stats[i] = t;
 }
 
 __device__ __forceinline__ float ld_param(const void* p, int i, int dtype) {
@@ -229,7 +233,7 @@ extern "C" int rmn_channel_dot_stats(const void* d_a, const void* d_b, uint32_t 
                                                                         (const __nv_bfloat16*)d_b, n_rows, channels,
                                                                         partial);
   RMN_LAUNCH_CHECK();
-  k_dot_reduce<<<(2 * channels + 127) / 128, 128, 0, stream>>>(partial, blocks, channels, d_stats);
+  k_dot_reduce<<<(2 * channels + 7) / 8, 256, 0, stream>>>(partial, blocks, channels, d_stats);
   RMN_LAUNCH_CHECK();
   return RMN_OK;
 }
