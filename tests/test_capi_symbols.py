@@ -40,6 +40,19 @@ def test_host_only_entry_points():
     assert lib.rmn_table_bytes(0) == 256 + 16 * 64
     assert lib.rmn_table_bytes(1000) == 256 + 16 * 3072  # 3n + 64 slots rounded up to a multiple of 32
     assert lib.rmn_table_bytes(1 << 20) == 256 + 16 * ((3 << 20) + 64)
+    # convolution plan sizes: header + perm + tile masks + permuted table, positions padded to 512 rows
+    assert lib.rmn_conv_plan_bytes(1000, 27) == 256 + 4 * 1024 + 256 + 27 * 1024 * 4
+    assert lib.rmn_conv_plan_bytes(1000, 33) == 0 and lib.rmn_conv_plan_workspace_bytes(1000, 27) > 1000 * 5
+    # gradient all-reduce: a single rank (or nothing to reduce) returns at once, without NCCL or a GPU
+    import ctypes
+    counts = (ctypes.c_size_t * 2)(10, 20)
+    assert lib.rmn_allreduce_grads_workspace_bytes(counts, 2) == 30 * 4
+    assert lib.rmn_allreduce_grads_workspace_bytes(counts, 1) == 0
+    bufs = (ctypes.c_void_p * 2)(None, None)
+    assert lib.rmn_allreduce_grads(None, bufs, counts, 2, None, 0, 1, 1, None) == capi.OK
+    assert lib.rmn_allreduce_grads(None, bufs, counts, 0, None, 0, 1, 4, None) == capi.OK
+    assert lib.rmn_allreduce_grads(None, bufs, counts, 2, None, 0, 1, 4, None) == capi.ERR_BAD_ARG   # no communicator
+    assert lib.rmn_channel_dot_stats_workspace_bytes(64) == 148 * 4 * 2 * 64 * 4
 
 
 def test_region_offsets_match_oracle():
