@@ -155,3 +155,20 @@ def test_indoor_room_2x2x2_stride2_64_to_128_against_reference():
     rb = parity.run_pipeline(GpuBackend(torch.bfloat16), c, f, w, 3, 2, 2, 1)
     perm = parity.row_permutation(rb["out_coords"], gold["ref_out_coords"])
     assert rel_l2(rb["out_feats"], gold["ref_out_feats"][perm]) <= 1e-2
+
+
+def test_spatiotemporal_clip_81_offsets_against_reference():
+    """One sample of the 4-D configuration at its own size: one clip, two frames (300 K voxels, coordinates
+    (b, x, y, z, t)), 3^4 = 81 offsets, 32 -> 32. Coordinate map and kernel map bit-exact against the reference's
+    CPU build, fp32 path within 1e-4, bf16 tensor-core output within 1e-2 relative L2."""
+    from riemannengine_b200 import synthetic, workloads
+    from tests.gpu_backend import GpuBackend
+    c = workloads.spatiotemporal_batch(1, 2, 4000)
+    assert c.shape == (300_000, 5)
+    f = synthetic.features(4500, len(c), 32)
+    w = synthetic.conv_weights(4601, 81, 32, 32)
+    gold = _reference_as_gold(c, f, w, 3, 1)
+    r32 = parity.run_pipeline(GpuBackend(torch.float32), c, f, w, 4, 3, 1, 1)
+    parity.check_against_reference(r32, gold, tol=1e-4, metric=rel_max)
+    rb = parity.run_pipeline(GpuBackend(torch.bfloat16), c, f, w, 4, 3, 1, 1)
+    assert rel_l2(rb["out_feats"], gold["ref_out_feats"]) <= 1e-2

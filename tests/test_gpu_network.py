@@ -110,3 +110,85 @@ def test_encoder_decoder_matches_cpu_reference_arithmetic():
     for bn, g, b in zip(bns, G, B):
         assert rel(bn.weight.grad, g.grad) <= 1e-4 and rel(bn.bias.grad, b.grad) <= 1e-4
     assert rel(head.bias.grad, head_bias.grad) <= 1e-4
+
+
+def test_cpp_host_network_on_a_whole_room_matches_cpu_reference_arithmetic():
+    """The same encoder/decoder at the size of one benchmark sample (a whole 150 K-voxel room) through the C++
+    host layer as a user of the reference writes it - separate convolution, RiemannBatchNorm (training mode:
+    the streaming batch-norm kernels) and RiemannReLU modules, riemann::cat for the skip - against the
+    reference's arithmetic on the CPU in fp64. fp32, bar 1e-4 on the output and on every gradient."""
+    from riemannengine_b200 import cpp, synthetic
+    C = cpp.load()
+    pts = synthetic.indoor_scene(5000, 150_000)
+    coords = np.concatenate([np.zeros((len(pts), 1), np.int32), pts], 1)
+    n = len(coords)
+    feats = synthetic.features(5001, n, C_IN)
+
+    def conv(ci, co, k, s, transpose=False, bias=False):
+        cls = C.RiemannConvolutionTranspose if transpose else C.RiemannConvolution
+        layer = cls(ci, co, kernel_size=k, stride=s, bias=bias, dimension=3)
+        layer.to("cuda")
+        return layer
+
+    torch.manual_seed(6)
+    convs = [conv(C_IN, C1, 3, 1), conv(C1, C1, 3, 1), conv(C1, C2, 2, 2), conv(C2, C2, 3, 1),
+             conv(C2, C1, 2, 2, transpose=True), conv(2 * C1, C_OUT, 3, 1, bias=True)]
+    bns = []
+    for c in (C1, C1, C2, C2, C1):
+        bn = C.RiemannBatchNorm(c)
+        bn.to("cuda")
+        bn.train(True)
+        with torch.no_grad():
+            bn.weight.uniform_(0.5, 1.5)
+            bn.bias.uniform_(-0.3, 0.3)
+        bns.append(bn)
+    relu = C.RiemannReLU()
+    f = torch.from_numpy(feats).cuda().requires_grad_(True)
+    x = C.SparseTensor(f, torch.from_numpy(coords).cuda())
+    s0 = relu(bns[0](convs[0](x)))
+    s1 = relu(bns[1](convs[1](s0)))
+    d1 = relu(bns[2](convs[2](s1)))
+    d2 = relu(bns[3](convs[3](d1)))
+    u1 = relu(bns[4](convs[4](d2)))
+    out = convs[5](C.cat([u1, s1]))
+    loss = (out.F * out.F).mean()
+    loss.backward()
+
+    O = OracleBackend()
+    k_fine = O.conv_kernel_map(coords, coords, O.region_offsets([3] * 3, [1] * 3, [1] * 3))
+    c_coarse, _ = O.stride_map(coords, [2, 2, 2])
+    assert (d1.C.cpu().numpy() == c_coarse).all()
+    k_down = O.conv_kernel_map(coords, c_coarse, O.region_offsets([2] * 3, [1] * 3, [1] * 3))
+    k_coarse = O.conv_kernel_map(c_coarse, c_coarse, O.region_offsets([3] * 3, [1] * 3, [2] * 3))
+    k_up = O.conv_kernel_map(c_coarse, coords, O.region_offsets([2] * 3, [1] * 3, [1] * 3), transposed=True)
+
+    def leaf(t):
+        return t.detach().double().cpu().requires_grad_(True)
+
+    W = [leaf(c.kernel) for c in convs]
+    G = [leaf(b.weight) for b in bns]
+    B = [leaf(b.bias) for b in bns]
+    head_bias = leaf(convs[5].bias)
+    fr = torch.from_numpy(feats).double().requires_grad_(True)
+    nc = len(c_coarse)
+    r0 = _bn_relu(_cpu_conv(fr, W[0], k_fine, n), G[0], B[0])
+    r1 = _bn_relu(_cpu_conv(r0, W[1], k_fine, n), G[1], B[1])
+    q1 = _bn_relu(_cpu_conv(r1, W[2], k_down, nc), G[2], B[2])
+    q2 = _bn_relu(_cpu_conv(q1, W[3], k_coarse, nc), G[3], B[3])
+    v1 = _bn_relu(_cpu_conv(q2, W[4], k_up, n), G[4], B[4])
+    ref = _cpu_conv(torch.cat([v1, r1], 1), W[5], k_fine, n) + head_bias
+    ref_loss = (ref * ref).mean()
+    ref_loss.backward()
+
+    def rel(a, b):
+        a, b = a.detach().double().cpu(), b.detach().double()
+        return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+    assert rel(out.F, ref) <= 1e-4
+    assert abs(float(loss) - float(ref_loss)) / float(ref_loss) <= 1e-4
+    assert rel(f.grad, fr.grad) <= 1e-4
+    for layer, w in zip(convs, W):
+        assert rel(layer.kernel.grad, w.grad) <= 1e-4
+    for bn, g, b in zip(bns, G, B):
+        assert rel(bn.weight.grad, g.grad) <= 1e-4 and rel(bn.bias.grad, b.grad) <= 1e-4
+    assert rel(convs[5].bias.grad, head_bias.grad) <= 1e-4
