@@ -157,6 +157,17 @@ int rmn_table_build_static(const int32_t *d_coords, uint32_t n_rows, int W, void
 int rmn_table_info(const void *d_table, uint32_t info[4], void *stream);
 
 /*
+ * Queue a read-back of `bytes` (a multiple of 4, at most 1 MiB) from device memory into PAGE-LOCKED host
+ * memory on `stream`, carried out by a kernel that stores into the host block instead of by a copy engine:
+ * a device-to-host cudaMemcpyAsync queues behind every copy already running on that engine on any stream
+ * (a step's few bytes of bookkeeping behind the previous step's result on its way to the host), SM stores
+ * do not. The host reads the block after synchronising the stream or an event recorded behind the call.
+ * rmn_table_info reads the header this way. A block that is not mapped into the device falls back to
+ * cudaMemcpyAsync. No counterpart in the reference (its maps live on the host).
+ */
+int rmn_readback_small(const void *d_src, void *h_dst_pinned, size_t bytes, void *stream);
+
+/*
  * Look rows up: d_rows[i] = unique row of d_query[i] or -1.
  * Replaces: CoordinateMapCPU::find (engine/grid/lattice_cpu.hpp:449-470),
  *   remap_inverse_map (engine/grid/lattice_gpu.cu:58-71).

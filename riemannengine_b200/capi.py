@@ -35,6 +35,7 @@ SIGNATURES = {
     "rmn_table_build_static": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p,
                                        c_void_p]),
     "rmn_table_info": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "rmn_readback_small": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "rmn_table_find": (c_int, [c_void_p, c_void_p, c_uint32, c_int, c_void_p, c_void_p]),
     "rmn_coords_stride": (c_int, [c_void_p, c_uint32, c_int, c_void_p, c_void_p, c_void_p]),
     "rmn_region_volume": (c_int, [c_int, c_int, c_void_p, c_int]),

@@ -635,6 +635,29 @@ int tc_copy_status_async(uint32_t* host_dst, cudaStream_t stream) {
   return RMN_OK;
 }
 
+// Device address of the status word on the current device (looked up once per device), for kernels of other
+// translation units that read it; NULL when the lookup fails.
+const uint32_t* tc_status_device_address() {
+  constexpr int kMaxDevices = 64;
+  static std::atomic<const uint32_t*> address[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  const uint32_t* p = address[dev].load(std::memory_order_acquire);
+  if (!p) {
+    void* q = nullptr;
+    if (cudaGetSymbolAddress(&q, g_tc_status) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    p = static_cast<const uint32_t*>(q);
+    address[dev].store(p, std::memory_order_release);
+  }
+  return p;
+}
+
 int tc_clear_status() {
   const uint32_t zero = 0;
   RMN_CUDA_TRY(cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(uint32_t)));

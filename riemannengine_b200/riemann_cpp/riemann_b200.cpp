@@ -576,7 +576,11 @@ std::shared_ptr<KernelMap> CoordinateManager::kernel_map(const CoordinateMapKey&
     result->self_symmetric = self_symmetric;
     result->region_offsets = off;
     result->host_offset_ptr = at::empty({K + 1}, at::TensorOptions().dtype(at::kLong).pinned_memory(true));
-    result->host_offset_ptr.copy_(result->offset_ptr, /*non_blocking=*/true);
+    // stored by a kernel, not a copy engine: behind a large device-to-host copy of the caller's (the previous
+    // step's result) an engine copy of these few bytes would wait for all of it
+    check(rmn_readback_small(ptr(result->offset_ptr), result->host_offset_ptr.data_ptr(),
+                             static_cast<size_t>(K + 1) * sizeof(int64_t), current_stream()),
+          "rmn_readback_small");
     result->offset_ptr_ready.emplace(c10::DeviceType::CUDA);
     result->offset_ptr_ready->record(c10::cuda::getCurrentCUDAStream());
   }

@@ -53,6 +53,12 @@ def test_host_only_entry_points():
     assert lib.rmn_allreduce_grads(None, bufs, counts, 0, None, 0, 1, 4, None) == capi.OK
     assert lib.rmn_allreduce_grads(None, bufs, counts, 2, None, 0, 1, 4, None) == capi.ERR_BAD_ARG   # no communicator
     assert lib.rmn_channel_dot_stats_workspace_bytes(64) == 148 * 4 * 2 * 64 * 4
+    # small read-back: argument checks come before any CUDA call
+    word = ctypes.c_uint32(0)
+    assert lib.rmn_readback_small(None, None, 0, None) == capi.OK
+    assert lib.rmn_readback_small(None, ctypes.byref(word), 4, None) == capi.ERR_BAD_ARG
+    assert lib.rmn_readback_small(ctypes.byref(word), ctypes.byref(word), 6, None) == capi.ERR_BAD_ARG
+    assert lib.rmn_readback_small(ctypes.byref(word), ctypes.byref(word), (1 << 20) + 4, None) == capi.ERR_BAD_ARG
 
 
 def test_region_offsets_match_oracle():

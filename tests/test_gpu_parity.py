@@ -382,6 +382,35 @@ def test_two_call_table_build_header_is_final_after_the_first_call(gpu, dups):
     assert torch.equal(rows.long(), ref.inverse)
 
 
+def test_small_readback_without_the_copy_engine():
+    """rmn_readback_small delivers device words into page-locked host memory (stored by a kernel) and into
+    pageable memory (copy fallback), also while a large device-to-host copy is queued on another stream."""
+    import ctypes
+    from riemannengine_b200 import capi
+    lib = capi.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for n_words in (1, 28, 1000, 70_000):
+        src = torch.arange(n_words, dtype=torch.int32, device="cuda") * 3 + 1
+        pinned = torch.zeros(n_words, dtype=torch.int32).pin_memory()
+        pageable = np.zeros(n_words, dtype=np.int32)
+        big_d = torch.zeros(64 << 20, dtype=torch.uint8, device="cuda")
+        big_h = torch.empty(64 << 20, dtype=torch.uint8).pin_memory()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            big_h.copy_(big_d, non_blocking=True)
+        assert lib.rmn_readback_small(ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(pinned.data_ptr()),
+                                      n_words * 4, stream) == capi.OK
+        assert lib.rmn_readback_small(ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(pageable.ctypes.data),
+                                      n_words * 4, stream) == capi.OK
+        torch.cuda.synchronize()
+        assert torch.equal(pinned, src.cpu())
+        assert (pageable == src.cpu().numpy()).all()
+    src = torch.zeros(4, dtype=torch.int32, device="cuda")
+    dst = torch.zeros(4, dtype=torch.int32).pin_memory()
+    assert lib.rmn_readback_small(ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(dst.data_ptr()), 6, stream) == capi.ERR_BAD_ARG
+    assert lib.rmn_readback_small(ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(dst.data_ptr()), 0, stream) == capi.OK
+
+
 # ---------------------------------------------------------------------------------------------
 # Maps at coarse tensor strides: every coordinate is a multiple of the stride, so the low bits of
 # the first spatial column are the same in all rows; the table must still use its whole capacity.
