@@ -103,8 +103,12 @@ __global__ void __launch_bounds__(256) k_plan_masks(const int32_t* __restrict__ 
 
 // One warp per (chunk, class): exclusive scan of its 32 per-block counts in place, totals[chunk][class] = rows
 // of the class in the chunk. (Blocks past the end of the table were never written: n_blocks bounds the reads.)
+// The first thread also writes the plan's header (handed over as a kernel argument: a host-to-device copy of
+// it would wait behind whatever large upload - the next batch of an input pipeline - is on the copy engine).
 __global__ void __launch_bounds__(256) k_plan_scan(uint32_t* __restrict__ hist, uint32_t n_blocks, int n_bins,
-                                                   uint32_t n_chunks, uint32_t* __restrict__ totals) {
+                                                   uint32_t n_chunks, uint32_t* __restrict__ totals,
+                                                   const PlanHeader hdr, PlanHeader* __restrict__ hdr_out) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) *hdr_out = hdr;
   const uint32_t pair = blockIdx.x * 8 + (threadIdx.x >> 5);  // chunk * n_bins + class
   const int lane = threadIdx.x & 31;
   if (pair >= n_chunks * (uint32_t)n_bins) return;
@@ -300,21 +304,21 @@ extern "C" int rmn_conv_plan_build(const int32_t* d_nbr, uint32_t n_dst, int K, 
   uint32_t* totals = hist + (size_t)chunks * 256 * kPlanBlocksPerChunk;
 
   char* plan = static_cast<char*>(d_plan);
-  PlanHeader hdr;
+  PlanHeader hdr = {};
   hdr.magic = kPlanMagic;
   hdr.n_dst = n_dst;
   hdr.K = (uint32_t)K;
   hdr.n_pos = L.n_pos;
   hdr.n_tiles = L.n_tiles;
   hdr.words = (uint32_t)words;
-  RMN_CUDA_TRY(cudaMemcpyAsync(plan, &hdr, sizeof(hdr), cudaMemcpyHostToDevice, stream));
   RMN_CUDA_TRY(cudaMemsetAsync(plan + L.tile_mask, 0, (size_t)L.n_tiles * words * 4, stream));
   if ((n_dst & 3u) == 0 && ((uintptr_t)d_nbr & 15) == 0)
     k_plan_masks<true><<<nb, 256, 0, stream>>>(d_nbr, n_dst, K, gb, rowmask, cls, hist, n_bins);
   else
     k_plan_masks<false><<<nb, 256, 0, stream>>>(d_nbr, n_dst, K, gb, rowmask, cls, hist, n_bins);
   RMN_LAUNCH_CHECK();
-  k_plan_scan<<<(chunks * (uint32_t)n_bins + 7) / 8, 256, 0, stream>>>(hist, nb, n_bins, chunks, totals);
+  k_plan_scan<<<(chunks * (uint32_t)n_bins + 7) / 8, 256, 0, stream>>>(hist, nb, n_bins, chunks, totals, hdr,
+                                                                       reinterpret_cast<PlanHeader*>(plan));
   RMN_LAUNCH_CHECK();
   k_plan_scatter<<<nb, kPlanBlock, 0, stream>>>(d_nbr, n_dst, K, rowmask, cls, hist, totals, nb, n_bins, L.n_pos,
                                                 reinterpret_cast<int32_t*>(plan + L.perm),
