@@ -80,7 +80,8 @@ int rmn_device_status(void *stream);
  *   and the vendored concurrent_unordered_map
  *   (vendor/concurrent_unordered_map.cuh:305-391).
  * An open-addressing table of 16-byte slots {packed key, first row, unique
- * row} with 3 * n_rows + 64 slots (load <= 1/3), preceded by a 256-byte header.
+ * row} with 4 * n_rows + 64 slots (load <= 1/4; 3 * n_rows + 64 once that would exceed
+ * 120 MiB: ask rmn_table_bytes), preceded by a 256-byte header.
  * ===================================================================== */
 
 /* Bytes of device memory a table for `n_rows` input rows needs. */

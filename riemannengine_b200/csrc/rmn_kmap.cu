@@ -96,8 +96,9 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe(
         ulonglong2 v = first[u];
         uint32_t s = slot[u];
         for (uint32_t probe = 0; probe < (capacity >> 3); ++probe) {
-          if (v.x == key[u]) { uid = (uint32_t)(v.y >> 32); break; }
-          if (v.x == kEmptyKey) break;
+          const uint32_t found = (uint32_t)(v.y >> 32);
+          if (v.x == key[u]) { uid = found & ~kPassedBit; break; }
+          if (v.x == kEmptyKey || !(found & kPassedBit)) break;  // free, or no key was displaced past this slot
           s = next_slot(s, capacity);
           v = load_slot(slots + s);
         }

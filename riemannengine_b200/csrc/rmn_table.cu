@@ -174,6 +174,8 @@ __global__ void __launch_bounds__(256) k_insert(const int32_t* __restrict__ coor
       placed = true;
       break;
     }
+    // another key lives here and this one walks on: leave word for the lookups (kPassedBit)
+    if (!((uint32_t)(cur_rows >> 32) & kPassedBit)) atomicOr(&slots[s].uid, kPassedBit);
     s = next_slot(s, capacity);
   }
   if (!placed) atomicExch(&h->status, (uint32_t)RMN_ERR_PROBE_LIMIT);
@@ -283,7 +285,7 @@ __global__ void __launch_bounds__(kRowsPerBlock) k_finalize(
   for (int w = 0; w < warp; ++w) base += warp_counts[w];
   if (flag) {
     const uint32_t uid = base + __popc(ballot & ((1u << lane) - 1u));
-    slots[s].uid = uid;
+    slots[s].uid = uid | (slots[s].uid & kPassedBit);
     mapping[uid] = (int64_t)row;
     if (unique_coords) {
       int32_t c[W];
@@ -302,7 +304,7 @@ __global__ void __launch_bounds__(256) k_inverse(const Slot* __restrict__ slots,
   if (h->n_dups == 0 || h->status != RMN_OK) return;
   const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= n) return;
-  inverse[row] = (int64_t)slots[slot_of_row[row]].uid;
+  inverse[row] = (int64_t)(slots[slot_of_row[row]].uid & ~kPassedBit);
 }
 
 template <int W>

@@ -38,8 +38,10 @@ def test_host_only_entry_points():
     assert lib.rmn_version() >= 100
     assert lib.rmn_status_string(capi.ERR_PROBE_LIMIT).decode().startswith("hash probe limit")
     assert lib.rmn_table_bytes(0) == 256 + 16 * 64
-    assert lib.rmn_table_bytes(1000) == 256 + 16 * 3072  # 3n + 64 slots rounded up to a multiple of 32
-    assert lib.rmn_table_bytes(1 << 20) == 256 + 16 * ((3 << 20) + 64)
+    assert lib.rmn_table_bytes(1000) == 256 + 16 * 4064  # 4n + 64 slots (a multiple of 32)
+    assert lib.rmn_table_bytes(1001) == 256 + 16 * 4096  # ... rounded up
+    assert lib.rmn_table_bytes(1 << 20) == 256 + 16 * ((4 << 20) + 64)
+    assert lib.rmn_table_bytes(1 << 22) == 256 + 16 * ((3 << 22) + 64)  # past 120 MiB: 3n + 64
     # convolution plan sizes: header + perm + tile masks + permuted table, positions padded to 512 rows
     assert lib.rmn_conv_plan_bytes(1000, 27) == 256 + 4 * 1024 + 256 + 27 * 1024 * 4
     assert lib.rmn_conv_plan_bytes(1000, 33) == 0 and lib.rmn_conv_plan_workspace_bytes(1000, 27) > 1000 * 5
