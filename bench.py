@@ -338,6 +338,8 @@ def run_extras(args, C, dev, rank, world, coords, feats, weights_np, res, xf, co
         "ms_per_step": ms_all, "mvoxels_per_s": vox_all / (ms_all / 1e3) / 1e6, "steps": steps,
         "phases_ms": {"forward_planned": med[0], "input_gradient_planned": med[1], "weight_gradient": med[2],
                       "allreduce_alone": med[3] if world > 1 else 0.0},
+        "phases_note": "each phase timed alone on a cached map with a convolution plan; the step builds a fresh map, "
+                       "for which the plan policy (two passes of one 64->64 layer) builds no plan",
         "allreduce_bytes": int(dw.numel() * 4) if world > 1 else 0,
         "allreduce": ("one ncclAllReduce per layer on a second stream behind the weight-gradient kernel, "
                       "overlapping the input-gradient kernel") if world > 1 else "single rank: none",
