@@ -358,6 +358,14 @@ def run_extras(args, C, dev, rank, world, coords, feats, weights_np, res, xf, co
         r["ms_per_step"], vox = over_ranks(r["ms_per_step"], float(r["voxels_per_step"]))
         r["voxels_per_step"] = vox
         r["mvoxels_per_s"] = vox / (r["ms_per_step"] / 1e3) / 1e6
+        if "algorithmic_flops_per_step" in r:   # all ranks' flops over the slowest rank's time
+            _, flops = over_ranks(0.0, float(r["algorithmic_flops_per_step"]))
+            r["algorithmic_flops_per_step"] = flops
+            r["algorithmic_tflops"] = flops / (r["ms_per_step"] / 1e3) / 1e12
+            if r.get("dtype") == "bf16":          # the whole step (maps, norms, host gaps included) against the GEMM peak
+                peak = load_peaks()
+                r["frac_of_tensor_peak"] = r["algorithmic_tflops"] / (peak["bf16_tflops"] * world)
+                r["peak_source"] = peak["source"]
         r["scaling"] = scaling
         r["n_gpus"] = world
         configs[name] = r

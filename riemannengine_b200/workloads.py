@@ -31,6 +31,34 @@ def time_steps(step: Callable[[], None], steps: int, warmup: int) -> float:
     return e0.elapsed_time(e1) / steps
 
 
+class _Pyramid:
+    """Pair counts of the kernel maps a network builds on ``coords``: stride-1 maps (3^D region) per level and
+    the 2^D stride-2 maps between the levels. Built once, outside any timed region, through the same C ABI; used
+    only to state the algorithmic flops (2 * pairs * c_in * c_out per convolution pass) of a configuration."""
+
+    def __init__(self, coords: torch.Tensor, levels: int):
+        from . import capi, ops
+        d = int(coords.size(1)) - 1
+        self.rows: List[int] = []
+        self.self_pairs: List[int] = []
+        self.down_pairs: List[int] = []
+        table = ops.table_build(coords)
+        for level in range(levels):
+            ts = [2 ** level] * d
+            self.rows.append(int(table.n_unique))
+            off3 = ops.region_offsets(capi.HYPER_CUBE, [3] * d, [1] * d, ts)
+            self.self_pairs.append(int(ops.kmap_build(table, table.coords, off3, self_map=True).offset_ptr[-1]))
+            if level + 1 < levels:
+                nxt = ops.table_build(ops.coords_stride(table.coords, [2 ** (level + 1)] * d))
+                off2 = ops.region_offsets(capi.HYPER_CUBE, [2] * d, [1] * d, ts)
+                self.down_pairs.append(int(ops.kmap_build(table, nxt.coords, off2).offset_ptr[-1]))
+                table = nxt
+
+
+def _rate(flops: float, ms: float) -> Dict:
+    return {"algorithmic_flops_per_step": flops, "algorithmic_tflops": flops / (ms / 1e3) / 1e12}
+
+
 def _conv(C, c_in, c_out, kernel_size, stride, dimension, dev, dtype, transpose=False, seed=0):
     cls = C.RiemannConvolutionTranspose if transpose else C.RiemannConvolution
     layer = cls(c_in, c_out, kernel_size=kernel_size, stride=stride, dimension=dimension)
@@ -63,9 +91,11 @@ def run_sphere_shell(C, dev, steps: int, warmup: int) -> Dict:
         with torch.no_grad():
             conv(C.SparseTensor(feats, coords))
 
+    ms = time_steps(step, steps, warmup)
+    pairs = _Pyramid(coords, 1).self_pairs[0]
     return {"workload": "sphere shell r=64 (101 930 voxels), 3^3 stride-1 32->32 fp32: hash insert + kernel map + "
                         "forward on a fresh manager", "dtype": "f32", "voxels_per_step": len(coords_np),
-            "ms_per_step": time_steps(step, steps, warmup)}
+            "ms_per_step": ms, "pairs": pairs, **_rate(2.0 * pairs * 32 * 32, ms)}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -96,11 +126,17 @@ def run_lidar_chain(C, dev, rank: int, steps: int, warmup: int, sweeps_per_gpu: 
             x = layer(x)
         (x.F.float() ** 2).mean().backward()   # the layers all-reduce their weight gradients in backward
 
-    return {"workload": f"LiDAR-like sweeps ({sweeps_per_gpu} per GPU, ~90 K voxels each, voxel 0.1 m), bf16, 4 input "
+    ms = time_steps(step, steps, warmup)
+    pyr = _Pyramid(coords, 2)
+    p0, p1, pd = pyr.self_pairs[0], pyr.self_pairs[1], pyr.down_pairs[0]
+    fwd = 2.0 * (p0 * (4 * 32 + 32 * 64) + pd * 64 * 64 + p1 * 64 * 128 + pd * 128 * 64)
+    flops = 3.0 * fwd - 2.0 * p0 * 4 * 32   # forward + input gradient + weight gradient; the input needs no gradient
+    return {"flops_note": "2 * pairs * c_in * c_out per convolution pass", **_rate(flops, ms),
+            "workload": f"LiDAR-like sweeps ({sweeps_per_gpu} per GPU, ~90 K voxels each, voxel 0.1 m), bf16, 4 input "
                         "channels: 3^3 4->32, 3^3 32->64, 2^3 s2 64->64, 3^3 64->128, transposed 2^3 s2 128->64; "
                         "loss mean(out^2); hash insert + kernel maps + forward + backward + weight-gradient "
                         "all-reduce on a fresh manager", "dtype": "bf16", "voxels_per_step": len(coords_np),
-            "ms_per_step": time_steps(step, steps, warmup)}
+            "ms_per_step": ms}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -130,10 +166,12 @@ def run_spatiotemporal(C, dev, rank: int, steps: int, warmup: int, batch: int = 
         with torch.no_grad():
             conv(C.SparseTensor(feats, coords))
 
+    ms = time_steps(step, steps, warmup)
+    pairs = _Pyramid(coords, 1).self_pairs[0]
     return {"workload": f"4-D clips: batch {batch} x {frames} frames of a 150 K-voxel room moving 0-2 voxels per frame, "
                         "coordinates (b, x, y, z, t); 3^4 = 81 offsets, 32->32 bf16: hash insert + kernel map + "
                         "forward on a fresh manager", "dtype": "bf16", "voxels_per_step": len(coords_np),
-            "ms_per_step": time_steps(step, steps, warmup)}
+            "ms_per_step": ms, "pairs": pairs, **_rate(2.0 * pairs * 32 * 32, ms)}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -165,9 +203,27 @@ def run_unet(C, dev, rank: int, world: int, steps: int, warmup: int, total_scene
             for p, g in zip([p for p in norm_params if p.grad is not None], grads):
                 p.grad.copy_(g)
 
-    return {"workload": f"MinkUNet-style encoder/decoder (stem 32; stages 32/64/128/256 of two BasicBlocks; 2^3 s2 "
+    ms = time_steps(step, steps, warmup)
+    # algorithmic flops of the network of riemann_cpp/networks.hpp (width 32): per level s (c = 32 * 2^s) four
+    # 3^3 c->c convolutions in the encoder; a 2^3 stride-2 c/2->c convolution into the level; in the decoder a
+    # transposed 2^3 c->c/2 convolution out of it, a 3^3 c->c/2 fuse and two 3^3 c/2->c/2 convolutions one level up
+    pyr = _Pyramid(coords, 4)
+    width, fwd = 32, 0.0
+    fwd += 2.0 * pyr.self_pairs[0] * 4 * width                              # stem
+    for s_ in range(4):
+        c = width * 2 ** s_
+        fwd += 2.0 * pyr.self_pairs[s_] * 4 * c * c                         # two BasicBlocks
+        if s_ > 0:
+            half = c // 2
+            fwd += 2.0 * pyr.down_pairs[s_ - 1] * (half * c + c * half)     # down into the level, up out of it
+            fwd += 2.0 * pyr.self_pairs[s_ - 1] * (c * half + 2 * half * half)  # fuse + BasicBlock one level up
+    fwd += 2.0 * pyr.rows[0] * width * 20                                   # 1x1 head
+    flops = 3.0 * fwd - 2.0 * pyr.self_pairs[0] * 4 * width                 # the input features need no gradient
+    return {"flops_note": "2 * pairs * c_in * c_out per convolution pass (forward, input gradient, weight gradient)",
+            **_rate(flops, ms),
+            "workload": f"MinkUNet-style encoder/decoder (stem 32; stages 32/64/128/256 of two BasicBlocks; 2^3 s2 "
                         f"downs, transposed ups with skip concatenation; batch norm + ReLU), bf16, 4 input channels, "
                         f"{total_scenes} rooms of 150 K voxels over {world} GPU(s) (fixed total batch): hash insert + "
                         "kernel maps + forward + backward (+ gradient all-reduce) on a fresh manager",
             "dtype": "bf16", "voxels_per_step": len(coords_np), "scenes_this_rank": len(mine),
-            "ms_per_step": time_steps(step, steps, warmup)}
+            "ms_per_step": ms}
