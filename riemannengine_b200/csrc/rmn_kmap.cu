@@ -70,43 +70,60 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe(
   // Offsets are handled kUnroll at a time: the first-probe loads of a batch are issued before any
   // is examined, so a thread keeps several table reads in flight. With the region's first axis
   // varying fastest, a batch of three is the x-1 / x / x+1 triple that shares one table line.
+  // Only the HOME slot is read here. One lookup in eight has to walk on (a foreign key with the
+  // passed-over bit), but in almost every warp some lane does, so walking inside this loop made
+  // every warp pay a second and third dependent table read per offset; those lookups are noted in
+  // a bit mask instead (64 offsets per chunk) and finished, thread by thread, after the chunk.
   constexpr int kUnroll = 3;
-  for (int k0 = 0; k0 < K; k0 += kUnroll) {
-    unsigned long long key[kUnroll];
-    uint32_t slot[kUnroll];
-    ulonglong2 first[kUnroll];
-    bool valid[kUnroll];
+  for (int chunk0 = 0; chunk0 < K; chunk0 += 64) {
+    const int chunk_end = min(K, chunk0 + 64);
+    unsigned long long pending = 0ull;
+    for (int k0 = chunk0; k0 < chunk_end; k0 += kUnroll) {
+      unsigned long long key[kUnroll];
+      ulonglong2 first[kUnroll];
+      bool valid[kUnroll];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int k = min(k0 + u, K - 1);
-      bool in_box = batch_ok && (k0 + u < K);
+      for (int u = 0; u < kUnroll; ++u) {
+        const int k = min(k0 + u, chunk_end - 1);
+        bool in_box = batch_ok && (k0 + u < chunk_end);
 #pragma unroll
-      for (int a = 0; a < D; ++a) in_box = in_box && (dist[a + 1] + (uint32_t)s_off[k * D + a] <= span[a + 1]);
-      valid[u] = in_box;
-      key[u] = (unsigned long long)(ckey + s_delta[k]);
-      slot[u] = hash_key(key[u], capacity, pos_shift);
-      first[u] = make_ulonglong2(kEmptyKey, 0ull);
-      if (in_box) first[u] = load_slot(slots + slot[u]);
-    }
+        for (int a = 0; a < D; ++a) in_box = in_box && (dist[a + 1] + (uint32_t)s_off[k * D + a] <= span[a + 1]);
+        valid[u] = in_box;
+        key[u] = (unsigned long long)(ckey + s_delta[k]);
+        first[u] = make_ulonglong2(kEmptyKey, 0ull);
+        if (in_box) first[u] = load_slot(slots + hash_key(key[u], capacity, pos_shift));
+      }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int k = k0 + u;
-      uint32_t uid = 0xFFFFFFFFu;
-      if (valid[u]) {
-        ulonglong2 v = first[u];
-        uint32_t s = slot[u];
-        for (uint32_t probe = 0; probe < (capacity >> 3); ++probe) {
-          const uint32_t found = (uint32_t)(v.y >> 32);
-          if (v.x == key[u]) { uid = found & ~kPassedBit; break; }
-          if (v.x == kEmptyKey || !(found & kPassedBit)) break;  // free, or no key was displaced past this slot
-          s = next_slot(s, capacity);
-          v = load_slot(slots + s);
+      for (int u = 0; u < kUnroll; ++u) {
+        const int k = k0 + u;
+        if (k < chunk_end) {  // uniform across the block
+          const uint32_t found = (uint32_t)(first[u].y >> 32);
+          uint32_t uid = 0xFFFFFFFFu;
+          if (valid[u]) {
+            if (first[u].x == key[u]) uid = found & ~kPassedBit;
+            else if (first[u].x != kEmptyKey && (found & kPassedBit)) pending |= 1ull << (k - chunk0);
+          }
+          if (active) __stcs(nbr + (size_t)k * n_query + q, (int32_t)uid);
+          const uint32_t hits = __ballot_sync(0xFFFFFFFFu, uid != 0xFFFFFFFFu);
+          if (lane == 0) atomicAdd(&s_cnt[k], (uint32_t)__popc(hits));
         }
       }
-      if (k < K) {  // uniform across the block
-        if (active) __stcs(nbr + (size_t)k * n_query + q, (int32_t)uid);
-        const uint32_t hits = __ballot_sync(0xFFFFFFFFu, uid != 0xFFFFFFFFu);
-        if (lane == 0) atomicAdd(&s_cnt[k], (uint32_t)__popc(hits));
+    }
+    while (pending) {  // the lookups that walk on: from the slot behind the home slot
+      const int k = chunk0 + __ffsll((long long)pending) - 1;
+      pending &= pending - 1ull;
+      const unsigned long long key = (unsigned long long)(ckey + s_delta[k]);
+      uint32_t s = next_slot(hash_key(key, capacity, pos_shift), capacity);
+      for (uint32_t probe = 1; probe < (capacity >> 3); ++probe) {
+        const ulonglong2 v = load_slot(slots + s);
+        const uint32_t found = (uint32_t)(v.y >> 32);
+        if (v.x == key) {
+          __stcs(nbr + (size_t)k * n_query + q, (int32_t)(found & ~kPassedBit));
+          atomicAdd(&s_cnt[k], 1u);
+          break;
+        }
+        if (v.x == kEmptyKey || !(found & kPassedBit)) break;
+        s = next_slot(s, capacity);
       }
     }
   }
@@ -162,6 +179,8 @@ __global__ void __launch_bounds__(kKmapBlock) k_kmap_probe_self(
   }
   const int lane = threadIdx.x & 31;
   if (active) __stcs(nbr + (size_t)half * n + q, (int32_t)q);  // centre offset: identity
+  // (Deferring the few lookups that walk past their home slot to a second loop, as the general builder does,
+  // made this kernel slower: 0.153 against 0.144 ms.)
   for (int k = 0; k < half; ++k) {
     bool in_box = active;
 #pragma unroll
