@@ -757,8 +757,8 @@ def run_product(args) -> None:
             "kernel_map": {"bound": "hbm", "achieved": kmap_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                            "frac": kmap_gbs / peaks["hbm_gbs"], "builder": "self-map (half the probes)",
                            # the same time against the bytes of the probes this builder actually issues
-                           # (K/2 probes per row, the mirror entries come from 4-byte stores): the survey's
-                           # formula above charges all K probes
+                           # (K/2 probes per row, the mirror entries come from 4-byte stores): the
+                           # algorithmic figure above charges all K probes of 32 bytes each
                            "achieved_on_probes_issued": (n_unique * 4 * W + n_unique * (K_VOL // 2) * 32 + 8 * total_pairs)
                            / ((t_kmap + t_pairs) / 1e3) / 1e9,
                            "frac_on_probes_issued": (n_unique * 4 * W + n_unique * (K_VOL // 2) * 32 + 8 * total_pairs)
